@@ -1,0 +1,394 @@
+#!/usr/bin/env python3
+"""Benchmark of the KV-cache hot path: quantized-KV decode attention at 128K context.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload decode128k|batch64|splitctx] [--mode planar4] [--ctx 131072]
+
+A step is one decode token of one sequence through all 16 full-attention layers: per layer
+one fused append (IMROPE + quantize + store of the new K/V rows) and one split-K decode
+attention over the whole cache.  The default workload is the configuration the headline
+metric is quoted on: planar4 cache, 24 q / 4 kv heads, head_dim 256, context 131072, batch 1,
+seeded N(0,1) K/V with 1 % of the channels scaled x20.  Every step reads 16 x 138 MB of cache,
+far more than the 126 MB L2, so no separate L2 flush is needed.
+
+With N > 1 (torchrun, one rank per GPU) every rank decodes its own independent sequence of
+the same shape: sequences shard across GPUs with no collective on the data path (weak
+scaling); torch.distributed is used only for the barrier and the max over ranks.
+
+Prints one JSON line.  `value` is device-resident throughput (CUDA events on the library's
+stream, max over ranks), `e2e` the same step through the host-buffer entry point
+(bk_attn_step_host: pinned staging, H2D of q/k/v and D2H of the output inside the timed
+region), `roofline` the decode kernel's algorithmic bytes / its measured launch time against
+the measured HBM copy bandwidth, `cpu_baseline` the CPU oracle on a bounded sample.
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+NH, NKV, HD, N_LAYERS = 24, 4, 256, 16
+FALLBACK_HBM_GBS = 6650.0
+
+
+def row_bytes(mode):
+    if mode.kind == "f32":
+        return 1024, 1024
+    if mode.kind == "f16":
+        return 512, 512
+    k = 32 * mode.bits + 4
+    return k, (k if mode.v_quant else 1024)
+
+
+def attn_bytes(mode, n_pos):
+    """Algorithmic bytes of one decode-attention launch: every cache byte once, q in, out out."""
+    rk, rv = row_bytes(mode)
+    return n_pos * NKV * (rk + rv) + 2 * NH * HD * 4
+
+
+def append_bytes(mode, n_tok=1):
+    rk, rv = row_bytes(mode)
+    return n_tok * (2 * NKV * HD * 4 + NKV * (rk + rv))
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def synth_chunk(rng, n, channels):
+    """N(0,1) K/V rows, the seeded outlier channels scaled x20."""
+    k = rng.standard_normal((n, NKV, HD), dtype=np.float32)
+    v = rng.standard_normal((n, NKV, HD), dtype=np.float32)
+    k[:, :, channels] *= np.float32(20.0)
+    v[:, :, channels] *= np.float32(20.0)
+    return k, v
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.rows, self.proc = device, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, val in zip(names, r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    """Returns (rank, world, local_rank, torch.distributed or None)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world <= 1:
+        return 0, 1, 0, None
+    import torch
+    import torch.distributed as dist
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return dist.get_rank(), world, local, dist
+
+
+def max_over_ranks(dist, local, value):
+    if dist is None:
+        return value
+    import torch
+    t = torch.tensor([value], dtype=torch.float64, device=f"cuda:{local}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(dist):
+    if dist is not None:
+        dist.barrier()
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm: the reference's own CPU path (the C restatement; the Rust crate cannot be
+# built here) on the host cores
+# ---------------------------------------------------------------------------------------------
+
+def cpu_fill(oracle, mode_tuple, chunks, n_pos):
+    ref = oracle.cache(*mode_tuple)
+    p = 0
+    for k, v in chunks:
+        for i in range(k.shape[0]):
+            if p >= n_pos:
+                return ref
+            ref.append(0, k[i], v[i], p)
+            p += 1
+    return ref
+
+
+def cpu_layer_step(ref, q, k, v, pos, threads):
+    t0 = time.perf_counter()
+    ref.step(0, q, k, v, pos, threads=threads)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, mode, chunks_fn):
+    from oracle_lib import MODE_F16, MODE_F32, MODE_PLANAR, load_oracle
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle = load_oracle()
+    kind = {"f32": MODE_F32, "f16": MODE_F16, "planar": MODE_PLANAR}[mode.kind]
+    threads = oracle.lib.or_max_threads()
+    n0 = args.ctx - (args.steps + args.warmup)
+    chunks, extra = chunks_fn()
+    ref = cpu_fill(oracle, (kind, mode.bits, mode.v_quant), chunks, n0)
+    rng = np.random.default_rng(1234)
+    times = []
+    for s in range(args.warmup + args.steps):
+        q = rng.standard_normal((NH, HD), dtype=np.float32)
+        k, v = extra[0][s % extra[0].shape[0]], extra[1][s % extra[1].shape[0]]
+        t = cpu_layer_step(ref, q, k, v, n0 + s, threads)
+        if s >= args.warmup:
+            times.append(t)
+    t_layer = float(np.mean(times))
+    tok_s = 1.0 / (t_layer * N_LAYERS)
+    sample = (f"1 of {N_LAYERS} layers per step at the full context ({args.ctx} positions), append + attention, "
+              f"time x{N_LAYERS}")
+    line = {
+        "impl": "reference", "metric": "quantized-KV decode attention tokens/s at 128K ctx", "value": tok_s,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": t_layer * N_LAYERS * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, mode),
+        "effective_gbs": attn_bytes(mode, args.ctx) / t_layer / 1e9,
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": min(threads, NH), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, mode):
+    return {"workload": f"decode128k: 1 sequence/GPU, {N_LAYERS} full-attention layers, context {args.ctx}, "
+                        f"{args.mode} KV cache, {NH} q / {NKV} kv heads, head_dim {HD}",
+            "kv_mode": args.mode, "context": args.ctx, "layers": N_LAYERS, "batch_per_gpu": 1,
+            "l2": "each step streams %.2f GB of cache, larger than the 126 MB L2 (no flush needed)"
+                  % (N_LAYERS * attn_bytes(mode, args.ctx) / 1e9)}
+
+
+# ---------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="planar4")
+    ap.add_argument("--ctx", type=int, default=131072)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--chunk", type=int, default=8192)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    bk = importlib.import_module("ternary-bonsai-inference_b200")
+    mode = bk.parse_mode(args.mode)
+    total_steps = args.steps + args.warmup
+    n0 = args.ctx - total_steps           # the context reaches args.ctx at the last step
+    assert n0 > 0
+
+    def make_chunks(seed=0):
+        """Prefill rows for one layer (shared by all layers) + the rows appended by the steps."""
+        rng = np.random.default_rng(seed)
+        channels = rng.choice(HD, size=3, replace=False)
+        chunks, left = [], n0
+        while left > 0:
+            n = min(args.chunk, left)
+            chunks.append(synth_chunk(rng, n, channels))
+            left -= n
+        return chunks, synth_chunk(rng, total_steps, channels)
+
+    if args.impl == "reference":
+        run_reference(args, mode, make_chunks)
+        return
+
+    rank, world, local, dist = dist_setup(args.gpus)
+    ctx = bk.Context(local)
+    cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=args.ctx)
+    chunks, (k_new, v_new) = make_chunks(seed=rank)
+
+    # ---- prefill through the append kernel (not timed) ----------------------------------
+    dk, dv = ctx.alloc(args.chunk * NKV * HD * 4), ctx.alloc(args.chunk * NKV * HD * 4)
+    for k, v in chunks:
+        dk.upload(k, sync=False)
+        dv.upload(v, sync=True)
+        for il in range(N_LAYERS):
+            cache.append_device(il, dk.ptr, dv.ptr, n_tokens=k.shape[0])
+        ctx.synchronize()
+    dk.free(); dv.free()
+    assert cache.n_pos(0) == n0
+
+    # ---- step inputs, resident in HBM -------------------------------------------------------
+    rng = np.random.default_rng(1234 + rank)
+    q_all = rng.standard_normal((total_steps, N_LAYERS, NH, HD), dtype=np.float32)
+    d_q = ctx.to_device(q_all)
+    d_k = ctx.to_device(k_new)
+    d_v = ctx.to_device(v_new)
+    d_out = ctx.alloc(N_LAYERS * NH * HD * 4)
+    q_stride, kv_stride = NH * HD * 4, NKV * HD * 4
+
+    def device_step(s, events=None):
+        for il in range(N_LAYERS):
+            cache.append_device(il, d_k.offset(s * kv_stride), d_v.offset(s * kv_stride), n_tokens=1)
+            if events is not None:
+                events[il][0].record()
+            cache.decode_device(il, d_q.offset((s * N_LAYERS + il) * q_stride), d_out.offset(il * q_stride))
+            if events is not None:
+                events[il][1].record()
+
+    for s in range(args.warmup):
+        device_step(s)
+    ctx.synchronize()
+    barrier(dist)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = ctx.event(), ctx.event()
+    launches0 = ctx.launch_count
+    ev0.record()
+    for s in range(args.warmup, total_steps):
+        device_step(s)
+    ev1.record()
+    ctx.synchronize()
+    barrier(dist)
+    launches = ctx.launch_count - launches0
+    ms_total = max_over_ranks(dist, local, ev0.elapsed_ms(ev1))
+    ms_step = ms_total / args.steps
+    final_ctx = cache.n_pos(0)
+
+    # ---- roofline of the dominant kernel: per-launch events, steps replayed on the full cache ----
+    for il in range(N_LAYERS):
+        cache.set_n_pos(il, 0, final_ctx - args.steps)
+    evs = [[(ctx.event(), ctx.event()) for _ in range(N_LAYERS)] for _ in range(args.steps)]
+    for i, s in enumerate(range(args.warmup, total_steps)):
+        device_step(s, evs[i])
+    ctx.synchronize()
+    dec_ms = [a.elapsed_ms(b) for step in evs for (a, b) in step]
+    dec_ms_avg = float(np.mean(dec_ms))
+    clocks = sampler.stop() if rank == 0 else None
+    peak, peak_kind = measured_peak()
+    alg = attn_bytes(mode, args.ctx - args.steps // 2)
+    achieved = alg / (dec_ms_avg * 1e-3) / 1e9
+
+    # ---- e2e: the same steps through the host-buffer entry point ---------------------------------
+    for il in range(N_LAYERS):
+        cache.set_n_pos(il, 0, final_ctx - args.steps)
+    hq = ctx.pinned((N_LAYERS, NH * HD), np.float32)
+    hk = ctx.pinned((NKV * HD,), np.float32)
+    hv = ctx.pinned((NKV * HD,), np.float32)
+    hout = ctx.pinned((N_LAYERS, NH * HD), np.float32)
+    lib = ctx.lib
+    barrier(dist)
+    t0 = time.perf_counter()
+    for s in range(args.warmup, total_steps):
+        hq.array[:] = q_all[s].reshape(N_LAYERS, -1)
+        hk.array[:] = k_new[s].ravel()
+        hv.array[:] = v_new[s].ravel()
+        pos = cache.n_pos(0)
+        for il in range(N_LAYERS):
+            ctx.check(lib.bk_attn_step_host(cache.h, il, 0, pos, hq.ptr + il * q_stride, hk.ptr, hv.ptr,
+                                            hout.ptr + il * q_stride))
+    e2e_s = max_over_ranks(dist, local, time.perf_counter() - t0)
+    barrier(dist)
+    e2e_tok_s = world * args.steps / e2e_s
+    checksum = float(np.abs(hout.array).sum())
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- CPU baseline (rank 0, N = 1 only): the oracle on one layer at the full context ----------
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        from oracle_lib import MODE_F16, MODE_F32, MODE_PLANAR, load_oracle
+        oracle = load_oracle()
+        kind = {"f32": MODE_F32, "f16": MODE_F16, "planar": MODE_PLANAR}[mode.kind]
+        threads = oracle.lib.or_max_threads()
+        ref = cpu_fill(oracle, (kind, mode.bits, mode.v_quant), chunks, n0)
+        ts = [cpu_layer_step(ref, q_all[s, 0], k_new[s], v_new[s], n0 + s, threads) for s in range(3)]
+        t_layer = float(np.mean(ts[1:]))
+        cpu = {"value": 1.0 / (t_layer * N_LAYERS), "unit": "tokens/s", "cores": min(threads, NH), "kind": "port",
+               "sample": f"1 of {N_LAYERS} layers at context {n0} (append + attention, 2 timed steps after 1 warm-up), "
+                         f"time x{N_LAYERS}; q-heads spread over {min(threads, NH)} host threads",
+               "ms_per_layer": t_layer * 1e3}
+
+    tok_s = world * 1e3 / ms_step
+    step_bytes = N_LAYERS * (attn_bytes(mode, args.ctx - args.steps // 2) + append_bytes(mode))
+    line = {
+        "metric": "quantized-KV decode attention tokens/s at 128K ctx",
+        "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload_config(args, mode),
+        "effective_gbs": world * step_bytes / (ms_step * 1e-3) / 1e9,
+        "gpu_launches": launches,
+        "e2e": {"value": e2e_tok_s, "unit": "tokens/s",
+                "h2d_bytes_per_step": N_LAYERS * (NH + 2 * NKV) * HD * 4, "d2h_bytes_per_step": N_LAYERS * NH * HD * 4,
+                "api": "bk_attn_step_host per layer (host q/k/v in, host out; blocks per layer like the reference)",
+                "out_checksum": checksum},
+        "roofline": {"bound": "hbm", "kernel": "decode_kernel (split-K GQA decode attention)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "algorithmic_bytes_per_launch": alg, "avg_launch_ms": dec_ms_avg,
+                     "frac_of_8TBs_nominal": achieved / 8000.0},
+        "cpu_baseline": cpu, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,175 @@
+// Internal declarations shared by the translation units of libbonsai_kv.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "bonsai_kv.h"
+
+namespace bk {
+
+constexpr int kHd = 256;               // head_dim every kernel is specialised for
+constexpr int kMaxBits = 8;
+constexpr int kBookStride = 256;       // floats reserved per codebook in device memory
+constexpr int kMaxSeqsPerLaunch = 64;  // sequences one decode launch can carry in its parameters
+constexpr int kMaxItems = 4096;        // split-K work items one decode launch may create
+constexpr int kMaxRep = 8;             // q heads per kv head the scratch is sized for
+constexpr int kPartStride = kHd + 2;   // floats per partial result: acc[hd], m, l
+constexpr int kDescSlots = 8;          // launches of bk_append_batch that may be in flight
+constexpr int kDescCap = 4096;         // tokens one bk_append_batch call may carry
+
+// Host set-up math (bk_host_tables.cpp).  The reference computes the same three tables on
+// the CPU and uploads them: src/gdev.rs:360-368 (Givens + codebook), src/rope.rs:23-57.
+void host_codebook(int hd, int bits, float *out);
+void host_givens(int hd, float *out);
+// cos/sin of the IMROPE angle of pair j at position p: out[(p - pos0) * (n_rot/2) + j] = (cos, sin).
+void host_rope_rows(int64_t pos0, int64_t n_pos, int n_rot, float freq_base, float2 *out);
+// Which of the four position ids (t, h, w, e -> 0..3) pair j takes: src/rope.rs:37-49.
+int host_rope_band(int j, const int32_t sections[4]);
+
+struct RopeTable {
+    int n_rot = 0;
+    float freq_base = 0.f;
+    int n_pos = 0;
+    float2 *d = nullptr;  // [n_pos][n_rot/2]
+    int device = 0;
+    ~RopeTable();
+};
+
+enum RowKind : int { ROW_F32 = 0, ROW_F16 = 1, ROW_PLANAR = 2 };
+
+}  // namespace bk
+
+struct bk_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::string err;
+    uint64_t launches = 0;
+    float *d_givens = nullptr;     // 128 (cos, sin) pairs
+    float *d_codebooks = nullptr;  // 8 books, book of width b at (b-1)*kBookStride
+    float h_givens[bk::kHd];
+    float h_codebooks[bk::kMaxBits * bk::kBookStride];
+    // staging for the *_host entry points (grown on demand)
+    void *h_stage = nullptr;
+    size_t h_stage_bytes = 0;
+    void *d_stage = nullptr;
+    size_t d_stage_bytes = 0;
+    // split-K scratch of the decode kernel: partial results and arrival counters
+    float *d_partials = nullptr;
+    unsigned *d_counters = nullptr;
+    int n_sms = 148;
+    std::vector<std::shared_ptr<bk::RopeTable>> ropes;
+    // token descriptors of bk_append_batch: a ring of pinned/device slots, one event per slot
+    // so that a slot is rewritten only after the launch that read it has finished
+    int4 *h_desc = nullptr, *d_desc = nullptr;
+    cudaEvent_t desc_ev[bk::kDescSlots] = {};
+    unsigned desc_next = 0;
+};
+
+struct bk_cache {
+    bk_ctx *ctx = nullptr;
+    bk_cache_config cfg{};
+    int k_kind = 0, v_kind = 0;         // bk::RowKind
+    size_t k_row_bytes = 0, v_row_bytes = 0;  // bytes of one (pos, kv head) row, norms excluded
+    uint8_t *d_k = nullptr, *d_v = nullptr;   // [layer][seq][n_ctx][n_kv][row_bytes]
+    float *d_kn = nullptr, *d_vn = nullptr;   // [layer][seq][n_ctx][n_kv], planar sides only
+    std::vector<int32_t> n_pos;               // [layer][seq]
+    std::shared_ptr<bk::RopeTable> rope;
+    size_t device_bytes = 0;
+
+    size_t slab(int layer, int seq) const { return (size_t)layer * cfg.n_seqs + seq; }
+    uint8_t *k_rows(int layer, int seq) const {
+        return d_k + slab(layer, seq) * cfg.n_ctx * cfg.n_kv * k_row_bytes;
+    }
+    uint8_t *v_rows(int layer, int seq) const {
+        return d_v + slab(layer, seq) * cfg.n_ctx * cfg.n_kv * v_row_bytes;
+    }
+    float *k_norms(int layer, int seq) const {
+        return d_kn ? d_kn + slab(layer, seq) * cfg.n_ctx * cfg.n_kv : nullptr;
+    }
+    float *v_norms(int layer, int seq) const {
+        return d_vn ? d_vn + slab(layer, seq) * cfg.n_ctx * cfg.n_kv : nullptr;
+    }
+};
+
+struct bk_event {
+    cudaEvent_t ev = nullptr;
+    int device = 0;
+};
+
+namespace bk {
+
+bk_status fail(bk_ctx *ctx, bk_status st, const std::string &msg);
+bk_status cuda_fail(bk_ctx *ctx, cudaError_t e, const char *what);
+#define BK_CUDA(ctx, call)                                              \
+    do {                                                                \
+        cudaError_t e__ = (call);                                       \
+        if (e__ != cudaSuccess) return bk::cuda_fail((ctx), e__, #call); \
+    } while (0)
+
+bk_status ensure_stage(bk_ctx *ctx, size_t bytes);
+
+// ---- kernel launchers (bk_append.cu, bk_decode.cu, bk_kvq.cu) --------------
+
+struct AppendArgs {
+    const float *k, *v;        // [n_tokens][n_kv][hd]
+    uint8_t *k_rows, *v_rows;  // slab base of (layer, seq) when desc == nullptr, else of layer
+    float *k_norms, *v_norms;
+    const float2 *rope;        // [rope_n_pos][n_rot/2]
+    const float *givens;
+    const float *book;         // codebook of this width (null unless planar)
+    const int4 *desc;          // per token (seq, row, rope_pos, 0); nullptr = contiguous single sequence
+    size_t seq_stride_rows;    // rows (pos*n_kv units) between sequences of one layer
+    int n_tokens, n_kv, n_rot, bits;
+    int row0, pos0;            // first cache row and rope position when desc == nullptr
+    int k_kind, v_kind;
+    size_t k_row_bytes, v_row_bytes;
+};
+bk_status launch_append(bk_ctx *ctx, const AppendArgs &a);
+
+struct DecodeMeta {
+    int n_seqs;
+    int chunk_len;   // positions per split-K work item
+    int n_items;
+    int seq_id[kMaxSeqsPerLaunch];
+    int n_pos[kMaxSeqsPerLaunch];
+    int q_pos[kMaxSeqsPerLaunch];
+    int item_start[kMaxSeqsPerLaunch + 1];
+};
+struct DecodeArgs {
+    const uint8_t *k_rows, *v_rows;  // layer base: [seq][n_ctx][n_kv][row_bytes]
+    const float *k_norms, *v_norms;  // layer base
+    size_t seq_stride_rows;          // n_ctx * n_kv
+    const float *q;                  // [n_seqs][n_head][hd]
+    float *out;                      // [n_seqs][n_head][hd] or [n_seqs][n_head][hd+2] when partial
+    int partial;
+    const float2 *rope;
+    int n_rot;
+    const float *givens, *book;
+    int bits, n_head, n_kv, k_kind, v_kind;
+    size_t k_row_bytes, v_row_bytes;
+    float *partials;
+    unsigned *counters;
+    int no_rope;  // 1: q is used as given (one-shot f32 attention)
+};
+bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
+bk_status launch_lse_merge(bk_ctx *ctx, int n_parts, int n_rows, int hd, const float *parts, float *out);
+
+bk_status launch_quantize(bk_ctx *ctx, int bits, int n_vec, const float *x, uint8_t *packed, float *norms);
+bk_status launch_dequantize(bk_ctx *ctx, int bits, int n_vec, const uint8_t *packed, const float *norms,
+                            float *out);
+bk_status launch_rotate(bk_ctx *ctx, int n_vec, int inverse, const float *x, float *out);
+bk_status launch_dot_rotated(bk_ctx *ctx, int bits, int n_vec, const float *q_rot, const uint8_t *packed,
+                             const float *norms, float *out);
+// heads: [n_heads][hd] in place; rows4: [4][n_dims/2] (cos, sin) rows of the ids t, h, w, e;
+// band: [n_dims/2] which of the four rows pair j uses.
+bk_status launch_rope(bk_ctx *ctx, int n_heads, int hd, float *heads, const float2 *rows4, int n_dims,
+                      const int *band);
+bk_status launch_f32_to_half(bk_ctx *ctx, size_t n, const float *in, uint16_t *out);
+bk_status launch_half_to_f32(bk_ctx *ctx, size_t n, const uint16_t *in, float *out);
+
+}  // namespace bk

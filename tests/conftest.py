@@ -25,3 +25,15 @@ def golden():
     import numpy as np
     path = os.path.join(ROOT, "tests", "golden", "kvpath_golden.npz")
     return dict(np.load(path))
+
+
+@pytest.fixture(scope="session")
+def bk():
+    """The package (its directory name has a '-', hence importlib)."""
+    import importlib
+    return importlib.import_module("ternary-bonsai-inference_b200")
+
+
+@pytest.fixture(scope="session")
+def gpu_ctx(bk):
+    return bk.Context(0)

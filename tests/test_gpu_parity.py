@@ -1,0 +1,447 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bars: stored bytes (packed indices, norm bits, f16 bits, f32 bits) are bit-exact; attention
+outputs are within max-abs 1e-3 and max-abs / max|reference| 1e-3 (the reference's own `rel`
+measure, src/bin/bonsai-golden.rs:150-166) of the oracle's f32 path.
+"""
+import numpy as np
+import pytest
+
+from oracle_lib import MODE_F16, MODE_F32, MODE_PLANAR
+
+pytestmark = pytest.mark.gpu
+
+HD, NKV, NH = 256, 4, 24
+ABS_TOL = 1e-3
+REL_TOL = 1e-3
+
+MODES = [("f32", MODE_F32, 0, False), ("f16", MODE_F16, 0, False), ("planar4", MODE_PLANAR, 4, True),
+         ("planar3", MODE_PLANAR, 3, True), ("planar4k", MODE_PLANAR, 4, False), ("planar8", MODE_PLANAR, 8, True),
+         ("planar1", MODE_PLANAR, 1, True), ("planar2", MODE_PLANAR, 2, True), ("planar5", MODE_PLANAR, 5, True),
+         ("planar6k", MODE_PLANAR, 6, False), ("planar7", MODE_PLANAR, 7, True)]
+
+
+def bits_of(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def assert_close(got, want, what=""):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    max_abs = np.max(np.abs(got - want))
+    scale = max(np.max(np.abs(want)), 1e-30)
+    assert max_abs <= ABS_TOL and max_abs / scale <= REL_TOL, f"{what}: max_abs {max_abs:.3e}, rel {max_abs / scale:.3e}"
+
+
+def synth_kv(rng, n, outliers=True):
+    """N(0,1) rows with 1 % of the 256 channels (3 of them, seeded) scaled x20."""
+    k = rng.standard_normal((n, NKV, HD)).astype(np.float32)
+    v = rng.standard_normal((n, NKV, HD)).astype(np.float32)
+    if outliers:
+        ch = rng.choice(HD, size=3, replace=False)
+        k[:, :, ch] *= np.float32(20.0)
+        v[:, :, ch] *= np.float32(20.0)
+    return k, v
+
+
+def compare_dumps(gpu_dump, ref_dump):
+    assert sorted(gpu_dump) == sorted(ref_dump)
+    for key, ref in ref_dump.items():
+        got = gpu_dump[key]
+        assert got.shape == ref.shape, key
+        if ref.dtype == np.float32:
+            assert np.array_equal(bits_of(got), bits_of(ref)), f"{key}: f32 bits differ"
+        else:
+            assert np.array_equal(got, ref), f"{key}: bytes differ"
+
+
+# ---------------------------------------------------------------------------
+# kvquant.rs entry points
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("bits", range(1, 9))
+def test_quantize_bytes_and_norm_bits(bk, gpu_ctx, oracle, golden, bits):
+    pq = bk.PlanarQuant(HD, bits, gpu_ctx)
+    opq = oracle.pq(HD, bits)
+    rng = np.random.default_rng(100 + bits)
+    x = np.concatenate([golden["quant_in"].view(np.float32),
+                        oracle.rand_floats(11, 64 * HD).reshape(64, HD),
+                        synth_kv(rng, 40)[0].reshape(-1, HD)])
+    packed, norms = pq.quantize(x)
+    for r in range(x.shape[0]):
+        p_ref, n_ref = opq.quantize(x[r])
+        assert np.array_equal(packed[r], p_ref), (bits, r)
+        assert bits_of(norms[r]) == bits_of(n_ref), (bits, r)
+    g = golden["quant_in"].shape[0]
+    assert np.array_equal(packed[:g], golden[f"quant_bytes_b{bits}"])
+    assert np.array_equal(bits_of(norms[:g]), golden[f"quant_norm_b{bits}"])
+
+
+@pytest.mark.parametrize("bits", [1, 3, 4, 7, 8])
+def test_dequantize_rotate_dot_rotated_exact(bk, gpu_ctx, oracle, bits):
+    pq, opq = bk.PlanarQuant(HD, bits, gpu_ctx), oracle.pq(HD, bits)
+    x = oracle.rand_floats(23 + bits, 8 * HD).reshape(8, HD)
+    q = oracle.rand_floats(57 + bits, 8 * HD).reshape(8, HD)
+    packed, norms = pq.quantize(x)
+    deq, rot, inv = pq.dequantize(packed, norms), pq.rotate(q), pq.rotate_inv(q)
+    dots = pq.dot_rotated(rot, packed, norms)
+    for r in range(8):
+        assert np.array_equal(bits_of(deq[r]), bits_of(opq.dequantize(packed[r], norms[r])))
+        assert np.array_equal(bits_of(rot[r]), bits_of(opq.rotate(q[r])))
+        assert np.array_equal(bits_of(inv[r]), bits_of(opq.rotate_inv(q[r])))
+        assert bits_of(dots[r]) == bits_of(opq.dot_rotated(rot[r], packed[r], norms[r]))
+
+
+def test_reference_unit_tests_through_the_abi(bk, gpu_ctx, oracle):
+    """src/kvquant.rs:631-667, 723-738 run against the GPU entry points."""
+    p = bk.PlanarQuant(HD, 4, gpu_ctx)
+    x = oracle.rand_floats(7, HD)
+    assert np.max(np.abs(p.rotate_inv(p.rotate(x)) - x)) < 1e-5            # givens_is_orthogonal
+    xs = oracle.rand_floats(11, 64 * HD).reshape(64, HD)                   # quantize_roundtrip_error_is_small
+    packed, norms = p.quantize(xs)
+    y = p.dequantize(packed, norms)
+    rel = np.sqrt(((xs - y) ** 2).sum(1)) / np.maximum(np.sqrt((xs * xs).sum(1)), 1e-9)
+    assert rel.max() < 0.12
+    s = oracle.rand_floats(23, 2 * HD)                                      # dot_rotated_matches_dequantized_dot
+    k, q = s[:HD], s[HD:]
+    pk, nk = p.quantize(k)
+    a = p.dot_rotated(p.rotate(q), pk, nk)
+    assert abs(a - float(np.dot(q.astype(np.float64), p.dequantize(pk, nk).astype(np.float64)))) < 1e-4
+
+
+def test_rope_bits(bk, gpu_ctx, oracle, golden):
+    head = golden["rope_in"].view(np.float32).reshape(2, HD)
+    for pos, want in zip(golden["rope_pos"], golden["rope_out"]):
+        got = bk.rope_imrope(head, *[int(p) for p in pos], ctx=gpu_ctx)
+        assert np.array_equal(bits_of(got.ravel()), want), pos
+    # the reference's check_rope recipe (src/bin/bonsai-vk.rs:237-269): 24 heads, pos 37
+    heads = oracle.rand_floats(0x7777, NH * HD).reshape(NH, HD)
+    got = bk.rope_imrope(heads, 37, 37, 37, 37, ctx=gpu_ctx)
+    for h in range(NH):
+        assert np.array_equal(bits_of(got[h]), bits_of(oracle.rope(heads[h], 37, 37, 37, 37)))
+    # other geometry: n_dims 8, sections [2,1,1,0], base 1e4 (the reference's mini config)
+    small = oracle.rand_floats(0x99, 3 * 16).reshape(3, 16)
+    got = bk.rope_imrope(small, 3, 5, 7, 2, n_dims=8, sections=(2, 1, 1, 0), freq_base=1e4, ctx=gpu_ctx)
+    for h in range(3):
+        want = oracle.rope(small[h], 3, 5, 7, 2, n_dims=8, sections=np.array([2, 1, 1, 0], np.int32), freq_base=1e4)
+        assert np.array_equal(bits_of(got[h]), bits_of(want))
+
+
+def test_f16_conversions(bk, gpu_ctx, oracle, golden):
+    vin = golden["f16_in"].view(np.float32)
+    assert np.array_equal(bk.f32_to_half(vin, gpu_ctx), golden["f16_out"])
+    back = bk.half_to_f32(golden["half_in"], gpu_ctx)
+    assert np.array_equal(bits_of(back), golden["half_out"])
+    # every f16 bit pattern widens like the reference (NaNs: only NaN-ness is compared)
+    allh = np.arange(65536, dtype=np.uint16)
+    got = bk.half_to_f32(allh, gpu_ctx)
+    ref = np.array([oracle.lib.or_half_to_f32(int(h)) for h in allh], np.float32)
+    nan = np.isnan(ref)
+    assert np.array_equal(np.isnan(got), nan) and np.array_equal(bits_of(got[~nan]), bits_of(ref[~nan]))
+    # the reference's subnormal rule (shift, then round) on a dense sweep below 2^-14
+    rng = np.random.default_rng(5)
+    tiny = (rng.standard_normal(20000) * 2.0 ** rng.integers(-30, -12, 20000)).astype(np.float32)
+    ref = np.array([oracle.lib.or_f32_to_half(float(v)) for v in tiny], np.uint16)
+    assert np.array_equal(bk.f32_to_half(tiny, gpu_ctx), ref)
+
+
+# ---------------------------------------------------------------------------
+# append: stored bytes are bit-exact
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("tag,mode,bits,vq", MODES)
+def test_append_bytes_bit_exact(bk, gpu_ctx, oracle, tag, mode, bits, vq):
+    n = 70
+    rng = np.random.default_rng(7)
+    k, v = synth_kv(rng, n)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=2, n_seqs=1, n_ctx=128)
+    ref = oracle.cache(mode, bits, vq)
+    for p in range(n):
+        ref.append(0, k[p], v[p], p)
+    # tokens 0..9 one call each, then a bulk call of 60 (both routes must give the same rows)
+    for p in range(10):
+        cache.append(1, k[p], v[p])
+    cache.append(1, k[10:], v[10:])
+    assert cache.n_pos(1) == n and cache.n_pos(0) == 0
+    compare_dumps(cache.dump_kv(1), ref.dump(0))
+    cache.close()
+
+
+def test_append_golden_rows(bk, gpu_ctx, oracle, golden):
+    """Rows stored by three decode steps equal the independent restatement's fixture."""
+    for tag in ("f32", "f16", "planar4", "planar3", "planar4k"):
+        cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=16)
+        want = golden[f"attn_{tag}_out"]
+        for pos in range(want.shape[0]):
+            q = oracle.rand_floats(0xA000 + 3 * pos, NH * HD)
+            k = oracle.rand_floats(0xA000 + 3 * pos + 1, NKV * HD)
+            v = oracle.rand_floats(0xA000 + 3 * pos + 2, NKV * HD)
+            out = bk.full_attention_step(cache, 0, q, k, v, pos)
+            assert_close(out.ravel(), want[pos].view(np.float32), f"{tag} step {pos}")
+        d = cache.dump_kv(0)
+        n = want.shape[0]
+        gk, gv = golden[f"attn_{tag}_k"], golden[f"attn_{tag}_v"]
+        if tag.startswith("planar"):
+            assert np.array_equal(d["kq"].reshape(n * NKV, -1), gk)
+            assert np.array_equal(bits_of(d["kn"].ravel()), golden[f"attn_{tag}_kn"])
+            if tag.endswith("k"):
+                assert np.array_equal(bits_of(d["v"].reshape(n * NKV, -1)), bits_of(gv))
+            else:
+                assert np.array_equal(d["vq"].reshape(n * NKV, -1), gv)
+                assert np.array_equal(bits_of(d["vn"].ravel()), golden[f"attn_{tag}_vn"])
+        elif tag == "f16":
+            assert np.array_equal(d["k16"].reshape(n * NKV, -1), gk) and np.array_equal(d["v16"].reshape(n * NKV, -1), gv)
+        else:
+            assert np.array_equal(bits_of(d["k"].reshape(n * NKV, -1)), bits_of(gk))
+        cache.close()
+
+
+def test_append_special_vectors(bk, gpu_ctx, oracle):
+    """Zero vectors, tiny norms (inv = 0 branch), huge norms, f16 overflow and subnormals."""
+    k = np.zeros((6, NKV, HD), np.float32)
+    v = np.zeros((6, NKV, HD), np.float32)
+    r = oracle.rand_floats(0x42, 6 * NKV * HD).reshape(6, NKV, HD)
+    k[1], v[1] = r[1] * np.float32(1e-14), r[1] * np.float32(1e-20)
+    k[2], v[2] = r[2] * np.float32(1e18), r[2] * np.float32(7e4)
+    k[3], v[3] = r[3] * np.float32(3e-6), r[3] * np.float32(6e-8)
+    k[4], v[4] = r[4], -r[4]
+    k[5, :, 0], v[5, :, 255] = 1.0, -1.0
+    for tag, mode, bits, vq in MODES[:5]:
+        cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=8)
+        ref = oracle.cache(mode, bits, vq)
+        for p in range(6):
+            ref.append(0, k[p], v[p], p)
+        cache.append(0, k, v)
+        compare_dumps(cache.dump_kv(0), ref.dump(0))
+        cache.close()
+
+
+def test_append_at_far_positions(bk, gpu_ctx, oracle):
+    """Rope positions up to the 262144-token training context; rows land at the next index."""
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode("planar4"), n_layers=1, n_ctx=8, rope_positions=262144)
+    ref = oracle.cache(MODE_PLANAR, 4, True)
+    rng = np.random.default_rng(3)
+    k, v = synth_kv(rng, 4)
+    for i, pos in enumerate([0, 4096, 131071, 262143]):
+        ref.append(0, k[i], v[i], pos)
+        cache.append(0, k[i], v[i], pos=pos)
+    compare_dumps(cache.dump_kv(0), ref.dump(0))
+    cache.close()
+
+
+def test_append_batch_many_sequences(bk, gpu_ctx, oracle):
+    """One token for each of several sequences per launch, ragged lengths."""
+    n_seqs = 5
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode("planar3"), n_layers=2, n_seqs=n_seqs, n_ctx=16)
+    refs = [oracle.cache(MODE_PLANAR, 3, True) for _ in range(n_seqs)]
+    rng = np.random.default_rng(11)
+    lens = [3, 0, 7, 1, 5]
+    for s, n in enumerate(lens):  # ragged prefill
+        if n:
+            k, v = synth_kv(rng, n)
+            cache.append(1, k, v, seq=s)
+            for p in range(n):
+                refs[s].append(0, k[p], v[p], p)
+    for _ in range(3):  # three batched steps over a subset, in a scrambled order
+        ids = [4, 0, 2, 1]
+        k, v = synth_kv(rng, len(ids))
+        dk, dv = gpu_ctx.to_device(k), gpu_ctx.to_device(v)
+        cache.append_batch_device(1, dk.ptr, dv.ptr, len(ids), seq_ids=ids)
+        gpu_ctx.synchronize()
+        for i, s in enumerate(ids):
+            refs[s].append(0, k[i], v[i], refs[s].n_pos(0))
+    for s in range(n_seqs):
+        assert cache.n_pos(1, s) == refs[s].n_pos(0)
+        if refs[s].n_pos(0):
+            compare_dumps(cache.dump_kv(1, seq=s), refs[s].dump(0))
+    cache.close()
+
+
+def test_context_exhaustion_is_an_error(bk, gpu_ctx):
+    """src/gdev.rs:907-912: a position beyond n_ctx fails instead of wrapping."""
+    cache = bk.AttnCache(gpu_ctx, bk.F32, n_layers=1, n_ctx=4)
+    z = np.zeros((4, NKV, HD), np.float32)
+    cache.append(0, z, z)
+    with pytest.raises(bk.BonsaiKvError) as e:
+        cache.append(0, z[0], z[0])
+    assert e.value.status == bk._abi.BK_ERR_RANGE and "BONSAI_CTX" in str(e.value)
+    with pytest.raises(bk.BonsaiKvError):
+        cache.step(0, np.zeros(NH * HD, np.float32), z[0], z[0], 4)
+    cache.reset()
+    assert cache.n_pos(0) == 0
+    with pytest.raises(bk.BonsaiKvError) as e:  # the step must target the next row
+        cache.step(0, np.zeros(NH * HD, np.float32), z[0], z[0], 2)
+    assert e.value.status == bk._abi.BK_ERR_INVALID
+    cache.close()
+
+
+def test_unsupported_geometry_is_refused(bk, gpu_ctx):
+    with pytest.raises(bk.BonsaiKvError) as e:
+        bk.AttnCache(gpu_ctx, bk.F32, n_layers=1, n_ctx=4, hd=128)
+    assert e.value.status == bk._abi.BK_ERR_UNSUPPORTED
+    with pytest.raises(bk.BonsaiKvError):
+        bk.AttnCache(gpu_ctx, bk.KvMode("planar", 9, True), n_layers=1, n_ctx=4)
+
+
+def test_snapshot_roundtrip(bk, gpu_ctx):
+    """dump_kv -> upload_kv into a fresh cache gives identical rows and identical attention."""
+    rng = np.random.default_rng(21)
+    k, v = synth_kv(rng, 50)
+    q = rng.standard_normal((NH, HD)).astype(np.float32)
+    a = bk.AttnCache(gpu_ctx, bk.parse_mode("planar4"), n_layers=1, n_ctx=64)
+    a.append(0, k, v)
+    rows = a.dump_kv(0)
+    b = bk.AttnCache(gpu_ctx, bk.parse_mode("planar4"), n_layers=1, n_ctx=64)
+    b.upload_kv(0, rows)
+    b.set_n_pos(0, 0, 50)
+    compare_dumps(b.dump_kv(0), rows)
+    assert np.array_equal(a.attend(0, q), b.attend(0, q))
+    a.close()
+    b.close()
+
+
+# ---------------------------------------------------------------------------
+# decode attention
+# ---------------------------------------------------------------------------
+
+def run_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, n_pos_list, seed=0, outliers=True, n_ctx=None):
+    """Prefill several sequences, attend once per sequence on both paths, compare."""
+    rng = np.random.default_rng(seed)
+    n_seqs = len(n_pos_list)
+    n_ctx = n_ctx or max(max(n_pos_list), 1)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_seqs=n_seqs, n_ctx=n_ctx)
+    q = rng.standard_normal((n_seqs, NH, HD)).astype(np.float32)
+    want = np.zeros((n_seqs, NH, HD), np.float32)
+    for s, n in enumerate(n_pos_list):
+        if n == 0:
+            continue
+        k, v = synth_kv(rng, n, outliers)
+        cache.append(0, k, v, seq=s)
+        ref = oracle.cache(mode, bits, vq)
+        for p in range(n):
+            ref.append(0, k[p], v[p], p)
+        want[s] = ref.attend(0, q[s], n - 1, n, threads=8)
+    got = cache.attend(0, q, n_seqs=n_seqs)
+    cache.close()
+    return got, want
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq", MODES)
+def test_decode_matches_oracle(bk, gpu_ctx, oracle, tag, mode, bits, vq):
+    got, want = run_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, [600], seed=1)
+    assert_close(got, want, tag)
+
+
+@pytest.mark.parametrize("n_pos", [1, 2, 7, 8, 9, 37, 63, 64, 65, 127, 129, 1000])
+def test_decode_ragged_lengths(bk, gpu_ctx, oracle, n_pos):
+    for tag, mode, bits, vq in MODES[:3]:
+        got, want = run_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, [n_pos], seed=n_pos)
+        assert_close(got, want, f"{tag} n_pos={n_pos}")
+
+
+def test_decode_long_context_split_k(bk, gpu_ctx, oracle):
+    """Enough positions for many chunks per kv head (the partials + last-arriver combine)."""
+    for tag, mode, bits, vq in [MODES[2], MODES[1]]:
+        got, want = run_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, [20000], seed=9)
+        assert_close(got, want, tag)
+
+
+def test_decode_batch_of_ragged_sequences(bk, gpu_ctx, oracle):
+    lens = [300, 0, 1, 4097, 64, 129, 2050]
+    for tag, mode, bits, vq in [MODES[2], MODES[0]]:
+        got, want = run_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, lens, seed=4)
+        assert np.all(got[1] == 0.0)
+        assert_close(got, want, tag)
+
+
+def test_decode_more_sequences_than_one_launch_carries(bk, gpu_ctx, oracle):
+    lens = [5 + (i * 7) % 40 for i in range(70)]
+    got, want = run_both(bk, gpu_ctx, oracle, "planar4", MODE_PLANAR, 4, True, lens, seed=8)
+    assert_close(got, want)
+
+
+def test_decode_peaked_softmax(bk, gpu_ctx, oracle):
+    """One position dominates (score gap ~ 90): the running-max rescale path."""
+    rng = np.random.default_rng(2)
+    n = 300
+    k, v = synth_kv(rng, n, outliers=False)
+    q = rng.standard_normal((NH, HD)).astype(np.float32)
+    for tag, mode, bits, vq in MODES[:3]:
+        cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=n)
+        ref = oracle.cache(mode, bits, vq)
+        kk = k.copy()
+        kk[200] *= np.float32(6.0)
+        # rope at position 0 for q too, so that q.k[200] really is large for every head group
+        for kvh in range(NKV):
+            kk[200, kvh] = q[kvh * 6] * np.float32(6.0)
+        for p in range(n):
+            ref.append(0, kk[p], v[p], 0)
+        for p in range(n):
+            cache.append(0, kk[p], v[p], pos=0)
+        got = cache.attend(0, q, q_pos=[0])[0]
+        want = ref.attend(0, q, 0, n)
+        assert_close(got, want, tag)
+        cache.close()
+
+
+def test_attn_step_sequence(bk, gpu_ctx, oracle):
+    """64 successive decode steps (append + attend) as one sequence, f16 cache."""
+    rng = np.random.default_rng(12)
+    n0, steps = 500, 64
+    k, v = synth_kv(rng, n0 + steps)
+    q = rng.standard_normal((steps, NH, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.F16, n_layers=1, n_ctx=n0 + steps)
+    ref = oracle.cache(MODE_F16)
+    cache.append(0, k[:n0], v[:n0])
+    for p in range(n0):
+        ref.append(0, k[p], v[p], p)
+    for t in range(steps):
+        got = bk.full_attention_step(cache, 0, q[t], k[n0 + t], v[n0 + t], n0 + t)
+        want = ref.step(0, q[t], k[n0 + t], v[n0 + t], n0 + t, threads=8)
+        assert_close(got, want, f"step {t}")
+    compare_dumps(cache.dump_kv(0), ref.dump(0))
+    cache.close()
+
+
+def test_check_attn_recipe(bk, gpu_ctx, oracle):
+    """src/bin/bonsai-vk.rs:315-372 through the one-shot entry point: 24/4/256, n_pos 37, 1e-4."""
+    q = oracle.rand_floats(0x1010, NH * HD)
+    kc = oracle.rand_floats(0x2020, 37 * NKV * HD)
+    vc = oracle.rand_floats(0x3030, 37 * NKV * HD)
+    got = bk.attn_step(gpu_ctx, q, kc, vc, 37, NH, NKV, HD)
+    k3, v3, q2 = kc.reshape(37, NKV, HD).astype(np.float64), vc.reshape(37, NKV, HD).astype(np.float64), q.reshape(NH, HD)
+    for h in range(NH):
+        s = (k3[:, h // 6, :] @ q2[h].astype(np.float64)) / 16.0
+        p = np.exp(s - s.max())
+        want = (p / p.sum()) @ v3[:, h // 6, :]
+        assert np.max(np.abs(got[h] - want)) < 1e-4
+    with pytest.raises(bk.BonsaiKvError):  # size validation like the reference
+        bk.attn_step(gpu_ctx, q[:-1], kc, vc, 37, NH, NKV, HD)
+
+
+def test_partials_merge_equals_whole(bk, gpu_ctx, oracle):
+    """Context split: attend over two halves held by two caches, merge with bk_lse_merge."""
+    rng = np.random.default_rng(31)
+    n = 1500
+    cut = 700
+    k, v = synth_kv(rng, n)
+    q = rng.standard_normal((NH, HD)).astype(np.float32)
+    mode = bk.parse_mode("planar4")
+    whole = bk.AttnCache(gpu_ctx, mode, n_layers=1, n_ctx=n)
+    whole.append(0, k, v)
+    want = whole.attend(0, q, q_pos=[n - 1])[0]
+    lo = bk.AttnCache(gpu_ctx, mode, n_layers=1, n_ctx=cut, rope_positions=n)
+    hi = bk.AttnCache(gpu_ctx, mode, n_layers=1, n_ctx=n - cut, rope_positions=n)
+    lo.append(0, k[:cut], v[:cut], pos=0)
+    hi.append(0, k[cut:], v[cut:], pos=cut)
+    parts = np.stack([lo.attend(0, q, q_pos=[n - 1], partial=True)[0], hi.attend(0, q, q_pos=[n - 1], partial=True)[0]])
+    dparts = gpu_ctx.to_device(parts)
+    dout = gpu_ctx.alloc(NH * HD * 4)
+    gpu_ctx.check(gpu_ctx.lib.bk_lse_merge(gpu_ctx.h, 2, NH, HD, dparts.ptr, dout.ptr))
+    got = dout.download((NH, HD), np.float32)
+    assert np.max(np.abs(got - want)) < 2e-5
+    ref = oracle.cache(MODE_PLANAR, 4, True)
+    for p in range(n):
+        ref.append(0, k[p], v[p], p)
+    assert_close(got, ref.attend(0, q, n - 1, n, threads=8))
+    for c in (whole, lo, hi):
+        c.close()
