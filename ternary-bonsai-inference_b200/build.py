@@ -27,9 +27,10 @@ SOURCES = {
     "bk_append.cu": ["--fmad=false"],
     "bk_kvq.cu": ["--fmad=false"],
     "bk_decode.cu": [],
+    "bk_decode_mma.cu": [],
     "bk_host_tables.cpp": [],
 }
-HEADERS = ["bk_internal.h", "bk_device.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]
+HEADERS = ["bk_internal.h", "bk_device.cuh", "bk_decode_common.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]
 
 
 def nvcc():

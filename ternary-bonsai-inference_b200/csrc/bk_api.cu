@@ -10,9 +10,33 @@
 #include <new>
 #include <string>
 
+#include <cuda_fp16.h>
+
 #include "bk_internal.h"
 
 namespace bk {
+
+// Scale alpha in [1, 2) that minimises the worst relative error of f16(alpha * c) / alpha over a
+// codebook: the centroids are only 2^bits distinct values, so a good alpha makes all of them
+// round almost exactly and the tensor-core path loses nothing to the f16 table.
+static float best_lut_alpha(const float *book, int n) {
+    float best_a = 1.0f, best_e = 1e30f;
+    for (int i = 0; i < 4096; i++) {
+        const float al = 1.0f + (float)i / 4096.0f;
+        float worst = 0.f;
+        for (int k = 0; k < n; k++) {
+            const float c = book[k];
+            if (c == 0.f) continue;
+            const float r = __half2float(__float2half_rn(c * al)) / al;
+            worst = std::max(worst, fabsf(r - c) / fabsf(c));
+        }
+        if (worst < best_e) {
+            best_e = worst;
+            best_a = al;
+        }
+    }
+    return best_a;
+}
 
 static thread_local std::string g_err;  // failures that have no context to hang on
 
@@ -156,7 +180,15 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
         return bail(e, "cudaStreamCreate");
     host_givens(kHd, ctx->h_givens);
     memset(ctx->h_codebooks, 0, sizeof(ctx->h_codebooks));
-    for (int b = 1; b <= kMaxBits; b++) host_codebook(kHd, b, ctx->h_codebooks + (b - 1) * kBookStride);
+    for (int b = 1; b <= kMaxBits; b++) {
+        host_codebook(kHd, b, ctx->h_codebooks + (b - 1) * kBookStride);
+        ctx->lut_alpha[b] = best_lut_alpha(ctx->h_codebooks + (b - 1) * kBookStride, 1 << b);
+    }
+    {
+        const char *e1 = getenv("BONSAI_KV_GENERIC"), *e2 = getenv("BONSAI_KV_QSPLIT");
+        ctx->force_generic = e1 && e1[0] == '1';
+        ctx->qsplit = e2 && e2[0] == '1';
+    }
     if ((e = cudaMalloc(&ctx->d_givens, sizeof(ctx->h_givens))) != cudaSuccess) return bail(e, "cudaMalloc givens");
     if ((e = cudaMalloc(&ctx->d_codebooks, sizeof(ctx->h_codebooks))) != cudaSuccess)
         return bail(e, "cudaMalloc codebooks");
@@ -598,10 +630,14 @@ static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const i
                                              ctx->stream));
         }
         if (total == 0) continue;
-        // chunk length: about 4 CTAs per SM over the whole launch, at least 64 positions each
-        const int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * 4 / n_kv);
+        // chunk length.  Generic kernel: about 4 CTAs per SM over the whole launch, at least 64
+        // positions each.  Tensor-core kernel: one CTA per SM, chunks in units of 128 positions
+        // (8 warps x 16-position tiles).
+        const bool use_mma = !ctx->force_generic && decode_mma_supported(a);
+        const int64_t gran = use_mma ? 128 : 64;
+        const int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * (use_mma ? 1 : 4) / n_kv);
         int64_t L = (total + target_items - 1) / target_items;
-        L = std::max<int64_t>(64, (L + 63) / 64 * 64);
+        L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
         for (;;) {
             int64_t items = 0;
             for (int i = 0; i < nb; i++) items += (int64_t)n_kv * ((m.n_pos[i] + L - 1) / L);
@@ -618,7 +654,8 @@ static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const i
         m.n_items = items;
         a.q = q_dev + (size_t)base * n_head * kHd;
         a.out = out_dev + (size_t)base * out_stride;
-        if ((st = launch_decode(ctx, a, m)) != BK_OK) return st;
+        st = use_mma ? launch_decode_mma(ctx, a, m, ctx->lut_alpha[a.bits], ctx->qsplit) : launch_decode(ctx, a, m);
+        if (st != BK_OK) return st;
     }
     return BK_OK;
 }

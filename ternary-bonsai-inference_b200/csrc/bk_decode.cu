@@ -15,8 +15,7 @@
 // Algorithmic traffic per (position, kv head): K row + V row (+ 2 norms); q and out once.
 #include <math_constants.h>
 
-#include "bk_device.cuh"
-#include "bk_internal.h"
+#include "bk_decode_common.cuh"
 
 namespace bk {
 
@@ -235,85 +234,9 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a, DecodeMe
         __syncthreads();
     }
 
-    // ---- merge the chunks of this (sequence, kv head) ------------------------
+    // ---- merge the chunks of this (sequence, kv head), rotate back, write ------
     const int first_item = meta.item_start[s] + kv * n_chunks;
-    if (n_chunks > 1) {
-        float *part = a.partials + ((size_t)item * NREP) * kPartStride;
-        for (int i = tid; i < NREP * kHd; i += kThreads) {
-            const int r = i / kHd, d = i - r * kHd;
-            part[(size_t)r * kPartStride + d] = s_q[r][d];
-        }
-        if (tid < NREP) {
-            part[(size_t)tid * kPartStride + kHd] = s_M[tid];
-            part[(size_t)tid * kPartStride + kHd + 1] = s_L[tid];
-        }
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const unsigned ticket = atomicAdd(&a.counters[s * a.n_kv + kv], 1u);
-            s_last = (ticket == (unsigned)(n_chunks - 1));
-        }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-        if (tid < NREP) {
-            float M = -CUDART_INF_F;
-            for (int c = 0; c < n_chunks; c++)
-                M = fmaxf(M, __ldcg(a.partials + ((size_t)(first_item + c) * NREP + tid) * kPartStride + kHd));
-            float Lsum = 0.f;
-            for (int c = 0; c < n_chunks; c++) {
-                const float *pc = a.partials + ((size_t)(first_item + c) * NREP + tid) * kPartStride;
-                const float mc = __ldcg(pc + kHd);
-                if (mc > -CUDART_INF_F) Lsum += __ldcg(pc + kHd + 1) * exp2f(mc - M);
-            }
-            s_M[tid] = M;
-            s_L[tid] = Lsum;
-        }
-        __syncthreads();
-        for (int r = 0; r < NREP; r++) {
-            float sum = 0.f;
-            const float M = s_M[r];
-            for (int c = 0; c < n_chunks; c++) {
-                const float *pc = a.partials + ((size_t)(first_item + c) * NREP + r) * kPartStride;
-                const float mc = __ldcg(pc + kHd);
-                const float f = (mc > -CUDART_INF_F) ? exp2f(mc - M) : 0.f;
-                sum = fmaf(__ldcg(pc + tid), f, sum);
-            }
-            s_q[r][tid] = sum;
-        }
-        if (tid == 0) a.counters[s * a.n_kv + kv] = 0;  // ready for the next launch
-        __syncthreads();
-    }
-
-    // ---- finish: planar V is still in rotated space (src/forward.rs:349) ------
-    if (VK == ROW_PLANAR) {
-        for (int i = tid; i < NREP * (kHd / 2); i += kThreads) {
-            const int r = i / (kHd / 2), pr = i - r * (kHd / 2);
-            float o0, o1;
-            givens_inv(s_q[r][2 * pr], s_q[r][2 * pr + 1], a.givens[2 * pr], a.givens[2 * pr + 1], o0, o1);
-            s_q[r][2 * pr] = o0;
-            s_q[r][2 * pr + 1] = o1;
-        }
-        __syncthreads();
-    }
-    if (a.partial) {
-        float *out = a.out + ((size_t)s * a.n_head + (size_t)kv * NREP) * kPartStride;
-        for (int i = tid; i < NREP * kHd; i += kThreads) {
-            const int r = i / kHd, d = i - r * kHd;
-            out[(size_t)r * kPartStride + d] = s_q[r][d];
-        }
-        if (tid < NREP) {
-            out[(size_t)tid * kPartStride + kHd] = s_M[tid] * 0.6931471805599453f;  // log2 -> ln
-            out[(size_t)tid * kPartStride + kHd + 1] = s_L[tid];
-        }
-    } else {
-        float *out = a.out + ((size_t)s * a.n_head + (size_t)kv * NREP) * kHd;
-        for (int i = tid; i < NREP * kHd; i += kThreads) {
-            const int r = i / kHd;
-            const float Ls = s_L[r];
-            out[i] = Ls > 0.f ? (&s_q[0][0])[i] / Ls : 0.f;
-        }
-    }
+    finish_item<NREP>(a, s, kv, item, n_chunks, first_item, &s_q[0][0], s_M, s_L, &s_last, VK == ROW_PLANAR);
 }
 
 // out[row][d] = sum_g acc_g[d] e^{m_g - M} / sum_g l_g e^{m_g - M}

@@ -53,6 +53,9 @@ struct bk_ctx {
     float *d_codebooks = nullptr;  // 8 books, book of width b at (b-1)*kBookStride
     float h_givens[bk::kHd];
     float h_codebooks[bk::kMaxBits * bk::kBookStride];
+    float lut_alpha[bk::kMaxBits + 1] = {};  // per width: scale applied to centroids before f16 rounding
+    bool force_generic = false;            // BONSAI_KV_GENERIC=1: never take the tensor-core path
+    bool qsplit = false;                   // BONSAI_KV_QSPLIT=1: q as f16 hi + lo in the tensor-core path
     // staging for the *_host entry points (grown on demand)
     void *h_stage = nullptr;
     size_t h_stage_bytes = 0;
@@ -157,6 +160,9 @@ struct DecodeArgs {
     int no_rope;  // 1: q is used as given (one-shot f32 attention)
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
+// Tensor-core path for 4-bit planar K and V (bk_decode_mma.cu).  Chunks must be multiples of 128.
+bool decode_mma_supported(const DecodeArgs &a);
+bk_status launch_decode_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
 bk_status launch_lse_merge(bk_ctx *ctx, int n_parts, int n_rows, int hd, const float *parts, float *out);
 
 bk_status launch_quantize(bk_ctx *ctx, int bits, int n_vec, const float *x, uint8_t *packed, float *norms);
