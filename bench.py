@@ -36,7 +36,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-NH, NKV, HD, N_LAYERS = 24, 4, 256, 16
+NH, NKV, HD = 24, 4, 256
+N_LAYERS = 16  # --layers overrides it for small profiling runs
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -219,6 +220,155 @@ def workload_config(args, mode):
 
 
 # ---------------------------------------------------------------------------------------------
+# secondary workloads (the other sharded configurations; same JSON shape, no CPU arm)
+# ---------------------------------------------------------------------------------------------
+
+def run_other_workload(args):
+    bk = importlib.import_module("ternary-bonsai-inference_b200")
+    par = importlib.import_module("ternary-bonsai-inference_b200.parallel")
+    mode = bk.parse_mode(args.mode)
+    args.warmup = max(args.warmup, 3)
+    rank, world, local, dist = dist_setup(args.gpus)
+    ctx = bk.Context(local)
+    total_steps = args.steps + args.warmup
+    rng = np.random.default_rng(99)          # same plan and data on every rank
+    channels = rng.choice(HD, size=3, replace=False)
+    line = {"metric": "quantized-KV decode attention tokens/s", "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic"}
+
+    if args.workload == "batch64":
+        n_seqs = 64
+        lens = rng.integers(2048, 16385, n_seqs)
+        mine = par.shard_sequences(lens, world)[rank]
+        n_local = len(mine)
+        n_ctx = int(lens.max()) + total_steps
+        cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=max(n_local, 1), n_ctx=n_ctx)
+        k, v = synth_chunk(rng, 16384, channels)
+        dk, dv = ctx.to_device(k), ctx.to_device(v)
+        for j, i in enumerate(mine):
+            for il in range(N_LAYERS):
+                cache.append_device(il, dk.ptr, dv.ptr, n_tokens=int(lens[i]), seq=j)
+        ctx.synchronize()
+        d_q = ctx.to_device(rng.standard_normal((N_LAYERS, max(n_local, 1), NH, HD), dtype=np.float32))
+        d_out = ctx.alloc(max(n_local, 1) * NH * HD * 4)
+
+        def step(_s):
+            for il in range(N_LAYERS):
+                if n_local:
+                    cache.append_batch_device(il, dk.ptr, dv.ptr, n_local)
+                    cache.decode_device(il, d_q.offset(il * n_local * NH * HD * 4), d_out.ptr, n_seqs=n_local)
+        step_bytes = N_LAYERS * sum(attn_bytes(mode, int(lens[i])) + append_bytes(mode) for i in range(n_seqs))
+        tokens_per_step, scaling = n_seqs, "strong"
+        cfg = {"workload": f"batch64: {n_seqs} sequences, contexts U[2048,16384] (seeded, mean {lens.mean():.0f}), "
+                           f"{N_LAYERS} layers, {args.mode}; sequences sharded greedily over {world} GPU(s), no collective",
+               "l2": "%.2f GB of cache per step, larger than L2" % (step_bytes / 1e9)}
+    elif args.workload == "splitctx":
+        import torch
+        n_total = 262144
+        chunks = par.split_context(n_total - total_steps, world)
+        b, e = chunks[rank]
+        owner = par.tail_owner(chunks)
+        cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=(e - b) + total_steps, rope_positions=n_total)
+        k, v = synth_chunk(rng, 8192, channels)
+        dk, dv = ctx.to_device(k), ctx.to_device(v)
+        for il in range(N_LAYERS):
+            p = b
+            while p < e:
+                n = min(8192, e - p)
+                cache.append_device(il, dk.ptr, dv.ptr, n_tokens=n, pos=p)
+                p += n
+        ctx.synchronize()
+        d_q = ctx.to_device(rng.standard_normal((N_LAYERS, NH, HD), dtype=np.float32))
+        dev = torch.device("cuda", local)
+        part = torch.zeros((NH, HD + 2), dtype=torch.float32, device=dev)
+        out = torch.zeros((NH, HD), dtype=torch.float32, device=dev)
+        gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
+        pos_now = [n_total - total_steps]
+
+        def step(_s):
+            for il in range(N_LAYERS):
+                if rank == owner:
+                    cache.append_device(il, dk.ptr, dv.ptr, n_tokens=1, pos=pos_now[0])
+                if world == 1:
+                    cache.decode_device(il, d_q.offset(il * NH * HD * 4), out.data_ptr(), q_pos=[pos_now[0]])
+                else:
+                    cache.decode_device(il, d_q.offset(il * NH * HD * 4), part.data_ptr(), q_pos=[pos_now[0]], partial=True)
+                    ctx.synchronize()                       # library stream -> NCCL (torch stream)
+                    dist.all_gather_into_tensor(gathered.view(-1), part.view(-1))
+                    torch.cuda.current_stream().synchronize()
+                    ctx.check(ctx.lib.bk_lse_merge(ctx.h, world, NH, HD, gathered.data_ptr(), out.data_ptr()))
+            pos_now[0] += 1
+        step_bytes = N_LAYERS * (attn_bytes(mode, n_total) + append_bytes(mode))
+        tokens_per_step, scaling = 1, "strong"
+        cfg = {"workload": f"splitctx: 1 sequence, context {n_total}, {N_LAYERS} layers, {args.mode}; contiguous context "
+                           f"chunks over {world} GPU(s), per layer one all-gather of (acc, m, l) partials (NCCL) + LSE merge",
+               "l2": "%.2f GB of cache per step over all GPUs" % (step_bytes / 1e9)}
+    else:  # appendsweep
+        cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=4096 * 2)
+        k, v = synth_chunk(rng, 4096, channels)
+        dk, dv = ctx.to_device(k), ctx.to_device(v)
+        table = []
+        n = 1
+        while n <= 4096:
+            reps = max(4, min(64, 8192 // n))
+            ts = []
+            for r in range(reps + 2):
+                cache.reset()
+                e0, e1 = ctx.event(), ctx.event()
+                e0.record()
+                for il in range(N_LAYERS):
+                    cache.append_device(il, dk.ptr, dv.ptr, n_tokens=n, pos=0)
+                e1.record()
+                ctx.synchronize()
+                if r >= 2:
+                    ts.append(e0.elapsed_ms(e1))
+            t = float(np.median(ts)) * 1e-3
+            table.append({"tokens_per_call": n, "tokens_per_s": n / t, "gb_per_s": N_LAYERS * append_bytes(mode, n) / t / 1e9,
+                          "us_per_call_all_layers": t * 1e6})
+            n *= 2
+        if rank == 0:
+            line.update({"metric": "KV append throughput (fused rope+quantize+store)", "value": table[-1]["tokens_per_s"],
+                         "ms_per_step": table[-1]["us_per_call_all_layers"] / 1e3, "scaling": "weak",
+                         "config": {"workload": f"appendsweep: 1..4096 tokens per call, {N_LAYERS} layers, {args.mode}"},
+                         "sweep": table})
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    for s_ in range(args.warmup):
+        step(s_)
+    ctx.synchronize()
+    barrier(dist)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = ctx.launch_count
+    ev0, ev1 = ctx.event(), ctx.event()
+    ev0.record()
+    for s_ in range(args.steps):
+        step(s_)
+    ev1.record()
+    ctx.synchronize()
+    barrier(dist)
+    ms_step = max_over_ranks(dist, local, ev0.elapsed_ms(ev1)) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        gbs = step_bytes / (ms_step * 1e-3) / 1e9
+        line.update({"value": tokens_per_step * 1e3 / ms_step, "ms_per_step": ms_step, "scaling": scaling, "config": cfg,
+                     "effective_gbs": gbs, "gpu_launches": ctx.launch_count - launches0,
+                     "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s",
+                                  "frac": gbs / world / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                                  "note": "whole step (append + decode of every layer) per GPU, not one kernel"},
+                     "clocks": clocks})
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
 
 def main():
     ap = argparse.ArgumentParser()
@@ -230,7 +380,16 @@ def main():
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunk", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=16, help="full-attention layers (16 = qwen35; fewer only to keep a profiler capture small)")
+    ap.add_argument("--workload", default="decode128k", choices=["decode128k", "batch64", "splitctx", "appendsweep"],
+                    help="decode128k: the headline (default).  batch64: 64 sequences, contexts U[2048,16384], sharded "
+                         "over the ranks.  splitctx: one 262144-token sequence, context chunks per rank, LSE merge.  "
+                         "appendsweep: append throughput for 1..4096 tokens per call")
     args = ap.parse_args()
+    global N_LAYERS
+    N_LAYERS = args.layers
+    if args.workload != "decode128k" and args.impl == "ours":
+        return run_other_workload(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     bk = importlib.import_module("ternary-bonsai-inference_b200")

@@ -187,7 +187,9 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
     {
         const char *e1 = getenv("BONSAI_KV_GENERIC"), *e2 = getenv("BONSAI_KV_QSPLIT");
         ctx->force_generic = e1 && e1[0] == '1';
-        ctx->qsplit = e2 && e2[0] == '1';
+        ctx->qsplit = !(e2 && e2[0] == '0');  // on unless BONSAI_KV_QSPLIT=0
+        const char *e3 = getenv("BONSAI_KV_DBG");
+        ctx->dbg = e3 ? atoi(e3) : 0;
     }
     if ((e = cudaMalloc(&ctx->d_givens, sizeof(ctx->h_givens))) != cudaSuccess) return bail(e, "cudaMalloc givens");
     if ((e = cudaMalloc(&ctx->d_codebooks, sizeof(ctx->h_codebooks))) != cudaSuccess)
@@ -197,7 +199,7 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
     if ((e = cudaMemcpy(ctx->d_codebooks, ctx->h_codebooks, sizeof(ctx->h_codebooks), cudaMemcpyHostToDevice)) !=
         cudaSuccess)
         return bail(e, "upload codebooks");
-    const size_t part_bytes = (size_t)kMaxItems * kMaxRep * kPartStride * sizeof(float);
+    const size_t part_bytes = (size_t)kMaxItems * kMaxRep * kScratchStride * sizeof(float);
     if ((e = cudaMalloc(&ctx->d_partials, part_bytes)) != cudaSuccess) return bail(e, "cudaMalloc partials");
     const size_t cnt_bytes = (size_t)kMaxSeqsPerLaunch * 64 * sizeof(unsigned);
     if ((e = cudaMalloc(&ctx->d_counters, cnt_bytes)) != cudaSuccess) return bail(e, "cudaMalloc counters");
@@ -606,56 +608,73 @@ static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const i
     a.partials = ctx->d_partials;
     a.counters = ctx->d_counters;
     a.no_rope = 0;
+    a.dbg = ctx->dbg;
 
-    for (int base = 0; base < n_seqs; base += kMaxSeqsPerLaunch) {
-        const int nb = std::min(kMaxSeqsPerLaunch, n_seqs - base);
-        DecodeMeta m{};
-        m.n_seqs = nb;
-        int64_t total = 0;
-        for (int i = 0; i < nb; i++) {
-            const int s = seq_ids ? seq_ids[base + i] : base + i;
-            if (s < 0 || s >= c->cfg.n_seqs) return fail(ctx, BK_ERR_INVALID, std::string(who) + ": bad sequence id");
-            const int cached = c->n_pos[c->slab(layer, s)];
-            const int np = n_pos ? n_pos[base + i] : cached;
-            if (np < 0 || np > c->cfg.n_ctx) return fail(ctx, BK_ERR_RANGE, std::string(who) + ": n_pos beyond n_ctx");
-            const int qp = q_pos ? q_pos[base + i] : std::max(np - 1, 0);
-            if (qp < 0 || qp >= c->rope->n_pos)
-                return fail(ctx, BK_ERR_RANGE, std::string(who) + ": q position beyond the rope table");
-            m.seq_id[i] = s;
-            m.n_pos[i] = np;
-            m.q_pos[i] = qp;
-            total += np;
-            if (np == 0)  // nothing to attend to: zeros (and l = 0 for partials)
-                BK_CUDA(ctx, cudaMemsetAsync(out_dev + (size_t)(base + i) * out_stride, 0, out_stride * sizeof(float),
-                                             ctx->stream));
+    a.q = q_dev;
+    a.out = out_dev;
+
+    // Validate everything first, then sort the sequences into two classes: long ones go to the
+    // tensor-core kernel (4-bit planar caches), short ones to the generic f32 kernel.  Below
+    // kMmaMinPos positions a sequence cannot fill the machine anyway, and the f16 lookup table of
+    // the tensor-core path (relative error ~1e-4 per centroid) is only averaged out over many
+    // positions, so short contexts keep the exact f32 arithmetic.
+    const bool mma_ok = !ctx->force_generic && decode_mma_supported(a);
+    struct Entry { int slot, seq, np, qp; };
+    std::vector<Entry> cls[2];
+    for (int i = 0; i < n_seqs; i++) {
+        const int s = seq_ids ? seq_ids[i] : i;
+        if (s < 0 || s >= c->cfg.n_seqs) return fail(ctx, BK_ERR_INVALID, std::string(who) + ": bad sequence id");
+        const int np = n_pos ? n_pos[i] : c->n_pos[c->slab(layer, s)];
+        if (np < 0 || np > c->cfg.n_ctx) return fail(ctx, BK_ERR_RANGE, std::string(who) + ": n_pos beyond n_ctx");
+        const int qp = q_pos ? q_pos[i] : std::max(np - 1, 0);
+        if (qp < 0 || qp >= c->rope->n_pos)
+            return fail(ctx, BK_ERR_RANGE, std::string(who) + ": q position beyond the rope table");
+        if (np == 0) {  // nothing to attend to: zeros (and l = 0 for partials)
+            BK_CUDA(ctx, cudaMemsetAsync(out_dev + (size_t)i * out_stride, 0, out_stride * sizeof(float), ctx->stream));
+            continue;
         }
-        if (total == 0) continue;
-        // chunk length.  Generic kernel: about 4 CTAs per SM over the whole launch, at least 64
-        // positions each.  Tensor-core kernel: one CTA per SM, chunks in units of 128 positions
-        // (8 warps x 16-position tiles).
-        const bool use_mma = !ctx->force_generic && decode_mma_supported(a);
-        const int64_t gran = use_mma ? 128 : 64;
-        const int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * (use_mma ? 1 : 4) / n_kv);
-        int64_t L = (total + target_items - 1) / target_items;
-        L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
-        for (;;) {
-            int64_t items = 0;
-            for (int i = 0; i < nb; i++) items += (int64_t)n_kv * ((m.n_pos[i] + L - 1) / L);
-            if (items <= kMaxItems) break;
-            L *= 2;
+        cls[(mma_ok && np >= kMmaMinPos) ? 1 : 0].push_back({i, s, np, qp});
+    }
+    for (int k = 0; k < 2; k++) {
+        const bool use_mma = k == 1;
+        const std::vector<Entry> &list = cls[k];
+        for (size_t base = 0; base < list.size(); base += kMaxSeqsPerLaunch) {
+            const int nb = (int)std::min<size_t>(kMaxSeqsPerLaunch, list.size() - base);
+            DecodeMeta m{};
+            m.n_seqs = nb;
+            int64_t total = 0;
+            for (int i = 0; i < nb; i++) {
+                const Entry &e = list[base + i];
+                m.slot[i] = e.slot;
+                m.seq_id[i] = e.seq;
+                m.n_pos[i] = e.np;
+                m.q_pos[i] = e.qp;
+                total += e.np;
+            }
+            // chunk length.  Generic kernel: about 4 CTAs per SM over the whole launch, at least
+            // 64 positions each.  Tensor-core kernel: one CTA per SM, chunks in units of 128
+            // positions (8 warps x 16-position tiles).
+            const int64_t gran = use_mma ? 128 : 64;
+            const int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * (use_mma ? 1 : 4) / n_kv);
+            int64_t L = (total + target_items - 1) / target_items;
+            L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
+            for (;;) {
+                int64_t items = 0;
+                for (int i = 0; i < nb; i++) items += (int64_t)n_kv * ((m.n_pos[i] + L - 1) / L);
+                if (items <= kMaxItems) break;
+                L *= 2;
+            }
+            m.chunk_len = (int)L;
+            int items = 0;
+            for (int i = 0; i < nb; i++) {
+                m.item_start[i] = items;
+                items += n_kv * (int)((m.n_pos[i] + L - 1) / L);
+            }
+            m.item_start[nb] = items;
+            m.n_items = items;
+            st = use_mma ? launch_decode_mma(ctx, a, m, ctx->lut_alpha[a.bits], ctx->qsplit) : launch_decode(ctx, a, m);
+            if (st != BK_OK) return st;
         }
-        m.chunk_len = (int)L;
-        int items = 0;
-        for (int i = 0; i < nb; i++) {
-            m.item_start[i] = items;
-            items += n_kv * (int)((m.n_pos[i] + L - 1) / L);
-        }
-        m.item_start[nb] = items;
-        m.n_items = items;
-        a.q = q_dev + (size_t)base * n_head * kHd;
-        a.out = out_dev + (size_t)base * out_stride;
-        st = use_mma ? launch_decode_mma(ctx, a, m, ctx->lut_alpha[a.bits], ctx->qsplit) : launch_decode(ctx, a, m);
-        if (st != BK_OK) return st;
     }
     return BK_OK;
 }

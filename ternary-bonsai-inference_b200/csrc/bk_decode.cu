@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a, DecodeMe
 
     // ---- q: rope, optional Givens rotation, fold scale*log2(e) --------------
     {
-        const float *q = a.q + ((size_t)s * a.n_head + (size_t)kv * NREP) * kHd;
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * kHd;
         for (int i = tid; i < NREP * kHd; i += kThreads) (&s_q[0][0])[i] = q[i];
         if (BITS > 0)
             for (int i = tid; i < (1 << BITS); i += kThreads) s_book[i] = a.book[i];
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a, DecodeMe
 
     // ---- merge the chunks of this (sequence, kv head), rotate back, write ------
     const int first_item = meta.item_start[s] + kv * n_chunks;
-    finish_item<NREP>(a, s, kv, item, n_chunks, first_item, &s_q[0][0], s_M, s_L, &s_last, VK == ROW_PLANAR);
+    finish_item<NREP>(a, meta.slot[s], s, kv, item, n_chunks, first_item, &s_q[0][0], s_M, s_L, &s_last, VK == ROW_PLANAR);
 }
 
 // out[row][d] = sum_g acc_g[d] e^{m_g - M} / sum_g l_g e^{m_g - M}

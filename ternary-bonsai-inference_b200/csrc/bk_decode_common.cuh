@@ -10,6 +10,7 @@
 //     held by other caches / GPUs itself.
 #pragma once
 
+#include <cuda/atomic>
 #include <math_constants.h>
 
 #include "bk_device.cuh"
@@ -17,67 +18,135 @@
 
 namespace bk {
 
+constexpr int kFactorCap = 256;  // chunks whose rescale factors are cached in shared memory
+
 template <int NREP>
-__device__ __forceinline__ void finish_item(const DecodeArgs &a, int s, int kv, int item, int n_chunks,
+__device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s, int kv, int item, int n_chunks,
                                             int first_item, float *s_acc /* [NREP][kHd] */, float *s_M, float *s_L,
                                             int *s_last, bool v_planar) {
-    const int tid = threadIdx.x, nt = blockDim.x;
+    __shared__ float s_f[kFactorCap * NREP];
+    const int tid = threadIdx.x, nt = blockDim.x;  // nt == 256 in every caller
+    const int warp = tid >> 5, lane = tid & 31;
     if (n_chunks > 1) {
-        float *part = a.partials + ((size_t)item * NREP) * kPartStride;
+        float *part = a.partials + ((size_t)item * NREP) * kScratchStride;
         for (int i = tid; i < NREP * kHd; i += nt) {
             const int r = i / kHd, d = i - r * kHd;
-            part[(size_t)r * kPartStride + d] = s_acc[i];
+            part[(size_t)r * kScratchStride + d] = s_acc[i];
         }
         if (tid < NREP) {
-            part[(size_t)tid * kPartStride + kHd] = s_M[tid];
-            part[(size_t)tid * kPartStride + kHd + 1] = s_L[tid];
+            part[(size_t)tid * kScratchStride + kHd] = s_M[tid];
+            part[(size_t)tid * kScratchStride + kHd + 1] = s_L[tid];
         }
-        __threadfence();
+        // Publish: the barrier orders every thread's stores before thread 0's release, which
+        // makes them visible to whoever later acquires the counter (cumulativity), so no thread
+        // needs a full __threadfence().
         __syncthreads();
         if (tid == 0) {
-            const unsigned ticket = atomicAdd(&a.counters[s * a.n_kv + kv], 1u);
+            cuda::atomic_ref<unsigned, cuda::thread_scope_device> cnt(a.counters[s * a.n_kv + kv]);
+            const unsigned ticket = cnt.fetch_add(1u, cuda::memory_order_acq_rel);
             *s_last = (ticket == (unsigned)(n_chunks - 1));
         }
         __syncthreads();
-        if (!*s_last) return;
-        __threadfence();
-        const float *base = a.partials + (size_t)first_item * NREP * kPartStride;
-        if (tid < NREP) {
-            float M = -CUDART_INF_F;
-            for (int c = 0; c < n_chunks; c++)
-                M = fmaxf(M, __ldcg(base + ((size_t)c * NREP + tid) * kPartStride + kHd));
-            float Lsum = 0.f;
-            for (int c = 0; c < n_chunks; c++) {
-                const float *pc = base + ((size_t)c * NREP + tid) * kPartStride;
-                const float mc = __ldcg(pc + kHd);
-                if (mc > -CUDART_INF_F) Lsum += __ldcg(pc + kHd + 1) * exp2f(mc - M);
+        if (!*s_last || (a.dbg & 16)) { if (tid == 0 && *s_last) a.counters[s * a.n_kv + kv] = 0; return; }
+        const float *base = a.partials + (size_t)first_item * NREP * kScratchStride;
+        // 64 threads span one 256-float row with float4 loads; the four 64-thread groups take
+        // every fourth chunk.  The (head, chunk) pairs of a thread form one flat list walked 24
+        // independent 16-byte loads at a time.  The first batch is issued before the m/l sweep
+        // below so that both travel in the same L2 round trip.
+        const int rg = tid >> 6, x = tid & 63;
+        const int per_rg = (n_chunks - rg + 3) / 4;  // chunks rg, rg+4, ...
+        const int n_pairs = per_rg * NREP;
+        constexpr int kBatch = (NREP == 6) ? 30 : 32;  // a multiple of NREP: slot u is always head u % NREP
+        float4 v[kBatch];
+        auto load_batch = [&](int i0) {
+#pragma unroll
+            for (int u = 0; u < kBatch; u++) {
+                const int i = i0 + u, r = u % NREP;
+                const int c = rg + 4 * (i / NREP);
+                if (i < n_pairs)
+                    v[u] = __ldcg(reinterpret_cast<const float4 *>(base + ((size_t)c * NREP + r) * kScratchStride) + x);
+                else
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            s_M[tid] = M;
-            s_L[tid] = Lsum;
+        };
+        load_batch(0);
+        // one warp per head: global max, the chunks' rescale factors and the merged l, from one
+        // sweep over the (m, l) pairs
+        if (warp < NREP) {
+            const int r = warp;
+            constexpr int kPer = kFactorCap / 32;  // (m, l) pairs a lane keeps in registers
+            float2 ml[kPer];
+            float M = -CUDART_INF_F;
+#pragma unroll
+            for (int u = 0; u < kPer; u++) {
+                const int c = lane + 32 * u;
+                ml[u] = make_float2(-CUDART_INF_F, 0.f);
+                if (c < n_chunks)
+                    ml[u] = __ldcg(reinterpret_cast<const float2 *>(base + ((size_t)c * NREP + r) * kScratchStride + kHd));
+                M = fmaxf(M, ml[u].x);
+            }
+            for (int c = kFactorCap + lane; c < n_chunks; c += 32)  // beyond the cached range (rare)
+                M = fmaxf(M, __ldcg(base + ((size_t)c * NREP + r) * kScratchStride + kHd));
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+            float Lsum = 0.f;
+#pragma unroll
+            for (int u = 0; u < kPer; u++) {
+                const int c = lane + 32 * u;
+                const float f = ml[u].x > -CUDART_INF_F ? exp2f(ml[u].x - M) : 0.f;
+                Lsum = fmaf(ml[u].y, f, Lsum);
+                if (c < n_chunks) s_f[c * NREP + r] = f;
+            }
+            for (int c = kFactorCap + lane; c < n_chunks; c += 32) {
+                const float2 x2 = __ldcg(reinterpret_cast<const float2 *>(base + ((size_t)c * NREP + r) * kScratchStride + kHd));
+                Lsum = fmaf(x2.y, x2.x > -CUDART_INF_F ? exp2f(x2.x - M) : 0.f, Lsum);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, off);
+            if (lane == 0) {
+                s_M[r] = M;
+                s_L[r] = Lsum;
+            }
         }
         __syncthreads();
-        for (int i = tid; i < NREP * kHd; i += nt) {
-            const int r = i / kHd, d = i - r * kHd;
-            const float M = s_M[r];
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-            int c = 0;
-            for (; c + 4 <= n_chunks; c += 4) {  // four independent loads in flight per thread
-                const float *p0 = base + ((size_t)c * NREP + r) * kPartStride;
-                const float *p1 = p0 + (size_t)NREP * kPartStride, *p2 = p1 + (size_t)NREP * kPartStride,
-                            *p3 = p2 + (size_t)NREP * kPartStride;
-                const float v0 = __ldcg(p0 + d), v1 = __ldcg(p1 + d), v2 = __ldcg(p2 + d), v3 = __ldcg(p3 + d);
-                const float m0 = __ldcg(p0 + kHd), m1 = __ldcg(p1 + kHd), m2 = __ldcg(p2 + kHd), m3 = __ldcg(p3 + kHd);
-                sum0 = fmaf(v0, m0 > -CUDART_INF_F ? exp2f(m0 - M) : 0.f, sum0);
-                sum1 = fmaf(v1, m1 > -CUDART_INF_F ? exp2f(m1 - M) : 0.f, sum1);
-                sum2 = fmaf(v2, m2 > -CUDART_INF_F ? exp2f(m2 - M) : 0.f, sum2);
-                sum3 = fmaf(v3, m3 > -CUDART_INF_F ? exp2f(m3 - M) : 0.f, sum3);
+        float4 sum[NREP];
+#pragma unroll
+        for (int r = 0; r < NREP; r++) sum[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i0 = 0; i0 < n_pairs; i0 += kBatch) {
+            if (i0 > 0) load_batch(i0);
+#pragma unroll
+            for (int u = 0; u < kBatch; u++) {
+                const int i = i0 + u, r = u % NREP;
+                const int c = rg + 4 * (i / NREP);
+                float f = 0.f;
+                if (i < n_pairs) {
+                    if (c < kFactorCap) f = s_f[c * NREP + r];
+                    else {
+                        const float mc = __ldcg(base + ((size_t)c * NREP + r) * kScratchStride + kHd);
+                        f = mc > -CUDART_INF_F ? exp2f(mc - s_M[r]) : 0.f;
+                    }
+                }
+                sum[r].x = fmaf(v[u].x, f, sum[r].x);
+                sum[r].y = fmaf(v[u].y, f, sum[r].y);
+                sum[r].z = fmaf(v[u].z, f, sum[r].z);
+                sum[r].w = fmaf(v[u].w, f, sum[r].w);
             }
-            for (; c < n_chunks; c++) {
-                const float *pc = base + ((size_t)c * NREP + r) * kPartStride;
-                const float mc = __ldcg(pc + kHd);
-                sum0 = fmaf(__ldcg(pc + d), mc > -CUDART_INF_F ? exp2f(mc - M) : 0.f, sum0);
+        }
+        // fixed order over the four groups keeps the result deterministic
+        for (int gsel = 0; gsel < 4; gsel++) {
+            if (rg == gsel) {
+#pragma unroll
+                for (int r = 0; r < NREP; r++) {
+                    float4 *dst = reinterpret_cast<float4 *>(s_acc + r * kHd) + x;
+                    if (gsel == 0) *dst = sum[r];
+                    else {
+                        float4 o = *dst;
+                        o.x += sum[r].x; o.y += sum[r].y; o.z += sum[r].z; o.w += sum[r].w;
+                        *dst = o;
+                    }
+                }
             }
-            s_acc[i] = (sum0 + sum1) + (sum2 + sum3);
+            __syncthreads();
         }
         if (tid == 0) a.counters[s * a.n_kv + kv] = 0;  // ready for the next launch
         __syncthreads();
@@ -95,7 +164,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int s, int kv, 
         __syncthreads();
     }
     if (a.partial) {
-        float *out = a.out + ((size_t)s * a.n_head + (size_t)kv * NREP) * kPartStride;
+        float *out = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP) * kPartStride;
         for (int i = tid; i < NREP * kHd; i += nt) {
             const int r = i / kHd, d = i - r * kHd;
             out[(size_t)r * kPartStride + d] = s_acc[i];
@@ -105,7 +174,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int s, int kv, 
             out[(size_t)tid * kPartStride + kHd + 1] = s_L[tid];
         }
     } else {
-        float *out = a.out + ((size_t)s * a.n_head + (size_t)kv * NREP) * kHd;
+        float *out = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP) * kHd;
         for (int i = tid; i < NREP * kHd; i += nt) {
             const float Ls = s_L[i / kHd];
             out[i] = Ls > 0.f ? s_acc[i] / Ls : 0.f;

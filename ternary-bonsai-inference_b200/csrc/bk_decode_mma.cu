@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
     // ---- q: rope, Givens rotation, scale, split into f16 hi/lo (scratch: the table's region) --
     {
         float *sq = reinterpret_cast<float *>(lut_ptr);  // [NREP][256]
-        const float *q = a.q + ((size_t)s * a.n_head + (size_t)kv * NREP) * kHd;
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * kHd;
         for (int i = tid; i < NREP * kHd; i += kMT) sq[i] = q[i];
         __syncthreads();
         if (!a.no_rope) {
@@ -218,9 +218,14 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
     for (int j = 0; j < 16; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     float M0 = -CUDART_INF_F, M1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
+    const int dbg = a.dbg;
     auto compute_tile = [&](int tile, const TileRegs &r) {
         // ---- scores^T = Kc . Q^T ------------------------------------------------------------
-        float sc[4] = {0.f, 0.f, 0.f, 0.f};
+        // four independent accumulator chains (the 16 or 32 MMAs of a tile would otherwise be one
+        // dependent chain), summed at the end
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        float sc2[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!(dbg & 2))
 #pragma unroll
         for (int c = 0; c < 2; c++) {
             const uint32_t xg[4] = {r.k[c].x, r.k[c].y, r.k[c].z, r.k[c].w};
@@ -231,17 +236,20 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
                 {
                     const uint32_t a0 = lut<0>(xg[w], lane_base), a1 = lut<0>(xh[w], lane_base);
                     const uint32_t a2 = lut<1>(xg[w], lane_base), a3 = lut<1>(xh[w], lane_base);
-                    mma16816(sc, a0, a1, a2, a3, qh[ks][0], qh[ks][1]);
-                    if (QSPLIT) mma16816(sc, a0, a1, a2, a3, ql[QSPLIT ? ks : 0][0], ql[QSPLIT ? ks : 0][1]);
+                    mma16816(c ? sb : sa, a0, a1, a2, a3, qh[ks][0], qh[ks][1]);
+                    if (QSPLIT) mma16816(c ? sd : sc2, a0, a1, a2, a3, ql[QSPLIT ? ks : 0][0], ql[QSPLIT ? ks : 0][1]);
                 }
                 {
                     const uint32_t a0 = lut<2>(xg[w], lane_base), a1 = lut<2>(xh[w], lane_base);
                     const uint32_t a2 = lut<3>(xg[w], lane_base), a3 = lut<3>(xh[w], lane_base);
-                    mma16816(sc, a0, a1, a2, a3, qh[ks + 1][0], qh[ks + 1][1]);
-                    if (QSPLIT) mma16816(sc, a0, a1, a2, a3, ql[QSPLIT ? ks + 1 : 0][0], ql[QSPLIT ? ks + 1 : 0][1]);
+                    mma16816(c ? sd : sc2, a0, a1, a2, a3, qh[ks + 1][0], qh[ks + 1][1]);
+                    if (QSPLIT) mma16816(c ? sb : sa, a0, a1, a2, a3, ql[QSPLIT ? ks + 1 : 0][0], ql[QSPLIT ? ks + 1 : 0][1]);
                 }
             }
         }
+        float sc[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) sc[i] = (sa[i] + sb[i]) + (sc2[i] + sd[i]);
         // ---- online softmax in the exp2 domain; reference point = max of s + log2||v|| -------
         const int pb = p0 + tile * kTile;
         const bool ok0 = pb + g < p1, ok1 = pb + g + 8 < p1;
@@ -283,6 +291,7 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
         const uint32_t x1[4] = {r.v[1].x, r.v[1].y, r.v[1].z, r.v[1].w};
         const uint32_t x2[4] = {r.v[2].x, r.v[2].y, r.v[2].z, r.v[2].w};
         const uint32_t x3[4] = {r.v[3].x, r.v[3].y, r.v[3].z, r.v[3].w};
+        if (!(dbg & 4))
 #pragma unroll
         for (int w = 0; w < 4; w++) {
             const uint32_t m = 0x0f0f0f0fu;
@@ -309,6 +318,7 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
         }
     }
 
+    if (dbg & 1) { if (M0 == 123.f) a.out[0] = l0 + acc[0][0] + acc[5][1]; return; }
     // ---- merge the warps ---------------------------------------------------------------------
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -369,8 +379,9 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
     for (int r = 0; r < NREP; r++) s_acc[r * kHd + tid] = sums[r];
     __syncthreads();
 
+    if (dbg & 8) return;
     const int first_item = meta.item_start[s] + kv * n_chunks;
-    finish_item<NREP>(a, s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, true);
+    finish_item<NREP>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, true);
 }
 
 template <int NREP, bool QSPLIT>

@@ -18,7 +18,9 @@ constexpr int kBookStride = 256;       // floats reserved per codebook in device
 constexpr int kMaxSeqsPerLaunch = 64;  // sequences one decode launch can carry in its parameters
 constexpr int kMaxItems = 4096;        // split-K work items one decode launch may create
 constexpr int kMaxRep = 8;             // q heads per kv head the scratch is sized for
-constexpr int kPartStride = kHd + 2;   // floats per partial result: acc[hd], m, l
+constexpr int kPartStride = kHd + 2;   // floats per partial result handed to callers: acc[hd], m, l
+constexpr int kScratchStride = kHd + 4; // floats per partial in the split-K scratch (16-byte aligned rows)
+constexpr int kMmaMinPos = 2048;       // shorter sequences take the generic f32 decode kernel
 constexpr int kDescSlots = 8;          // launches of bk_append_batch that may be in flight
 constexpr int kDescCap = 4096;         // tokens one bk_append_batch call may carry
 
@@ -55,7 +57,8 @@ struct bk_ctx {
     float h_codebooks[bk::kMaxBits * bk::kBookStride];
     float lut_alpha[bk::kMaxBits + 1] = {};  // per width: scale applied to centroids before f16 rounding
     bool force_generic = false;            // BONSAI_KV_GENERIC=1: never take the tensor-core path
-    bool qsplit = false;                   // BONSAI_KV_QSPLIT=1: q as f16 hi + lo in the tensor-core path
+    int dbg = 0;
+    bool qsplit = true;                    // q as f16 hi + lo in the tensor-core path (BONSAI_KV_QSPLIT=0: hi only)
     // staging for the *_host entry points (grown on demand)
     void *h_stage = nullptr;
     size_t h_stage_bytes = 0;
@@ -138,6 +141,7 @@ struct DecodeMeta {
     int n_seqs;
     int chunk_len;   // positions per split-K work item
     int n_items;
+    int slot[kMaxSeqsPerLaunch];     // row of this sequence in the caller's q / out arrays
     int seq_id[kMaxSeqsPerLaunch];
     int n_pos[kMaxSeqsPerLaunch];
     int q_pos[kMaxSeqsPerLaunch];
@@ -158,6 +162,7 @@ struct DecodeArgs {
     float *partials;
     unsigned *counters;
     int no_rope;  // 1: q is used as given (one-shot f32 attention)
+    int dbg;
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
 // Tensor-core path for 4-bit planar K and V (bk_decode_mma.cu).  Chunks must be multiples of 128.

@@ -1,0 +1,74 @@
+"""Sharding of the KV path over the GPUs of one node (one process per GPU).
+
+The reference is single-device, so nothing here has a counterpart in it.  Two ways to
+shard, both natural for this path:
+
+* independent sequences: each rank owns whole sequences (all layers); no collective touches
+  the data path.  `shard_sequences` balances bytes (context lengths) greedily.
+* one long sequence: contiguous context chunks per rank.  Every rank attends over its chunk
+  with the same (replicated) q and produces, per q head, the triple (acc[hd], m, l); one
+  all-gather of those 24 x 258 floats per layer and a log-sum-exp merge give the output.
+  New tokens are appended on the rank that owns the tail chunk.
+
+torch.distributed is only the transport (NCCL on GPUs, gloo in the CPU tests).
+"""
+import numpy as np
+
+
+def shard_sequences(lengths, world):
+    """Greedy longest-first assignment of sequences to ranks; returns a list of index lists.
+    Ties keep the lower rank, so every rank computes the same plan."""
+    order = sorted(range(len(lengths)), key=lambda i: (-int(lengths[i]), i))
+    loads = [0] * world
+    plan = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda k: (loads[k], k))
+        plan[r].append(i)
+        loads[r] += int(lengths[i])
+    for p in plan:
+        p.sort()
+    return plan
+
+
+def split_context(n_pos, world, granularity=128):
+    """Contiguous chunks [begin, end) per rank, sizes multiples of `granularity` except the last
+    non-empty one; trailing ranks may be empty when n_pos is small."""
+    per = -(-n_pos // world)
+    per = -(-per // granularity) * granularity
+    out = []
+    for r in range(world):
+        b = min(r * per, n_pos)
+        out.append((b, min(b + per, n_pos)))
+    return out
+
+
+def tail_owner(chunks):
+    """Rank that owns the last position (where new tokens are appended)."""
+    owner = 0
+    for r, (b, e) in enumerate(chunks):
+        if e > b:
+            owner = r
+    return owner
+
+
+def merge_partials_host(parts):
+    """Log-sum-exp merge of partial results on the host (numpy): parts [n_parts, rows, hd+2] with
+    (acc, m, l) per row.  The GPU path uses bk_lse_merge; this is for tests of the exchange."""
+    parts = np.asarray(parts, dtype=np.float64)
+    acc, m, l = parts[..., :-2], parts[..., -2], parts[..., -1]
+    valid = l > 0
+    M = np.max(np.where(valid, m, -np.inf), axis=0)
+    w = np.where(valid, np.exp(np.where(valid, m - M, 0.0)), 0.0)
+    L = (l * w).sum(0)
+    out = (acc * w[..., None]).sum(0)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        return np.where(L[..., None] > 0, out / L[..., None], 0.0).astype(np.float32)
+
+
+def all_gather_partials(dist, part, world):
+    """All-gather of one rank's [rows, hd+2] partial tensor -> [world, rows, hd+2] (torch)."""
+    import torch
+    out = torch.empty((world,) + tuple(part.shape), dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(out.view(-1), part.contiguous().view(-1)) if part.is_cuda else \
+        dist.all_gather(list(out.unbind(0)), part.contiguous())
+    return out

@@ -447,16 +447,16 @@ def test_partials_merge_equals_whole(bk, gpu_ctx, oracle):
         c.close()
 
 
-@pytest.mark.parametrize("env", [{"BONSAI_KV_GENERIC": "1"}, {"BONSAI_KV_QSPLIT": "1"}, {}])
+@pytest.mark.parametrize("env", [{"BONSAI_KV_GENERIC": "1"}, {}])
 def test_planar4_kernel_variants(bk, oracle, monkeypatch, env):
-    """The 4-bit cache has three decode kernels behind the same entry point: the tensor-core
-    path (default), the same with q split into f16 hi + lo, and the generic f32 path
+    """The 4-bit cache has two decode kernels behind the same entry point: the tensor-core
+    path (default for 2048 positions and more) and the generic f32 path
     (BONSAI_KV_GENERIC=1, read when the context is created).  All must meet the bar, on
     lengths that hit ragged tiles, single chunks and many chunks."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     ctx = bk.Context(0)
-    for lens in ([1], [15], [16], [17], [127, 128, 129], [5000], [40000, 3]):
+    for lens in ([1], [17], [127, 128, 129], [2047], [2048], [2049], [2063, 2064, 2065], [5000], [40000, 3, 2500]):
         got, want = run_both(bk, ctx, oracle, "planar4", MODE_PLANAR, 4, True, lens, seed=sum(lens))
         assert_close(got, want, f"{env} {lens}")
     ctx.close()
@@ -466,7 +466,7 @@ def test_planar4_tensor_core_path_other_group_sizes(bk, gpu_ctx, oracle):
     """GQA groups of 1, 2 and 4 q heads per kv head through the tensor-core path, 8 through the
     generic one."""
     rng = np.random.default_rng(77)
-    n = 700
+    n = 2500
     for n_head, n_kv in ((4, 4), (8, 4), (8, 2), (16, 2)):
         k = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
         v = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
