@@ -74,10 +74,11 @@ bk_status ensure_stage(bk_ctx *ctx, size_t bytes) {
     return BK_OK;
 }
 
-static bk_status bind(bk_ctx *ctx) {
+bk_status bind_device(bk_ctx *ctx) {
     BK_CUDA(ctx, cudaSetDevice(ctx->device));
     return BK_OK;
 }
+static bk_status bind(bk_ctx *ctx) { return bind_device(ctx); }
 
 // A rope table for (n_rot, freq_base) that covers n_pos positions, shared between caches.
 static bk_status get_rope(bk_ctx *ctx, int n_rot, float freq_base, int n_pos, std::shared_ptr<RopeTable> *out) {
@@ -574,6 +575,102 @@ bk_status bk_append_batch(bk_cache *c, int32_t layer, int32_t n_seqs, const int3
 
 /* ---- decode ---------------------------------------------------------------- */
 
+}  // extern "C"
+
+namespace bk {
+
+void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out) {
+    bk_ctx *ctx = c->ctx;
+    DecodeArgs a{};
+    a.k_rows = c->k_rows(layer, 0);
+    a.v_rows = c->v_rows(layer, 0);
+    a.k_norms = c->k_norms(layer, 0);
+    a.v_norms = c->v_norms(layer, 0);
+    a.seq_stride_rows = (size_t)c->cfg.n_ctx * c->cfg.n_kv;
+    a.partial = partial;
+    a.rope = c->rope->d;
+    a.n_rot = c->cfg.n_rot;
+    a.givens = ctx->d_givens;
+    a.bits = c->cfg.mode.kind == BK_MODE_PLANAR ? c->cfg.mode.bits : 0;
+    a.book = a.bits ? ctx->d_codebooks + (a.bits - 1) * kBookStride : nullptr;
+    a.n_head = c->cfg.n_head;
+    a.n_kv = c->cfg.n_kv;
+    a.k_kind = c->k_kind;
+    a.v_kind = c->v_kind;
+    a.k_row_bytes = c->k_row_bytes;
+    a.v_row_bytes = c->v_row_bytes;
+    a.partials = ctx->d_partials;
+    a.counters = ctx->d_counters;
+    a.no_rope = 0;
+    a.dbg = ctx->dbg;
+    *out = a;
+}
+
+bk_status check_decode_entry(const bk_cache *c, int layer, int slot, const int32_t *seq_ids, const int32_t *n_pos,
+                             const int32_t *q_pos, const char *who, DecodeEntry *e) {
+    bk_ctx *ctx = c->ctx;
+    const int s = seq_ids ? seq_ids[slot] : slot;
+    if (s < 0 || s >= c->cfg.n_seqs) return fail(ctx, BK_ERR_INVALID, std::string(who) + ": bad sequence id");
+    const int np = n_pos ? n_pos[slot] : c->n_pos[c->slab(layer, s)];
+    if (np < 0 || np > c->cfg.n_ctx) return fail(ctx, BK_ERR_RANGE, std::string(who) + ": n_pos beyond n_ctx");
+    const int qp = q_pos ? q_pos[slot] : std::max(np - 1, 0);
+    if (qp < 0 || qp >= c->rope->n_pos)
+        return fail(ctx, BK_ERR_RANGE, std::string(who) + ": q position beyond the rope table");
+    *e = DecodeEntry{slot, s, np, qp};
+    return BK_OK;
+}
+
+// One launch for up to kMaxSeqsPerLaunch sequences of one class.  Chunk length: generic kernel
+// about 4 CTAs per SM over the whole launch, at least 64 positions each; tensor-core kernel one
+// CTA per SM, chunks in units of 128 positions (8 warps x 16-position tiles); never more than
+// max_items work items (the capacity of the split-K scratch behind a.partials).
+bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntry *list, int nb, bool use_mma,
+                              int max_items) {
+    const int n_kv = a.n_kv;
+    if ((int64_t)nb * n_kv > max_items)
+        return fail(ctx, BK_ERR_INVALID, "decode: more (sequence, kv head) pairs than the split-K scratch holds");
+    DecodeMeta m{};
+    m.n_seqs = nb;
+    int64_t total = 0;
+    for (int i = 0; i < nb; i++) {
+        m.slot[i] = list[i].slot;
+        m.seq_id[i] = list[i].seq;
+        m.n_pos[i] = list[i].np;
+        m.q_pos[i] = list[i].qp;
+        total += list[i].np;
+    }
+    const int64_t gran = use_mma ? 128 : 64;
+    int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * (use_mma ? 1 : 4) / n_kv);
+    target_items = std::min<int64_t>(target_items, std::max<int64_t>(1, max_items / n_kv));
+    int64_t L = (total + target_items - 1) / target_items;
+    L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
+    for (;;) {
+        int64_t items = 0;
+        for (int i = 0; i < nb; i++) items += (int64_t)n_kv * ((m.n_pos[i] + L - 1) / L);
+        if (items <= max_items) break;
+        L *= 2;
+    }
+    m.chunk_len = (int)L;
+    int items = 0;
+    for (int i = 0; i < nb; i++) {
+        m.item_start[i] = items;
+        items += n_kv * (int)((m.n_pos[i] + L - 1) / L);
+    }
+    m.item_start[nb] = items;
+    m.n_items = items;
+    return use_mma ? launch_decode_mma(ctx, a, m, ctx->lut_alpha[a.bits], ctx->qsplit) : launch_decode(ctx, a, m);
+}
+
+bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos) {
+    // Long sequences of 4-bit planar caches go to the tensor-core kernel, short ones to the
+    // generic f32 kernel.  Below kMmaMinPos positions a sequence cannot fill the machine anyway,
+    // and the f16 lookup table of the tensor-core path (relative error ~1e-4 per centroid) is
+    // only averaged out over many positions, so short contexts keep the exact f32 arithmetic.
+    return !ctx->force_generic && decode_mma_supported(a) && n_pos >= kMmaMinPos;
+}
+
+}  // namespace bk
+
 static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const int32_t *seq_ids, const int32_t *n_pos,
                              const int32_t *q_pos, const float *q_dev, float *out_dev, int partial, const char *who) {
     if (!c || layer < 0 || layer >= c->cfg.n_layers)
@@ -584,100 +681,32 @@ static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const i
     if (!q_dev || !out_dev) return fail(ctx, BK_ERR_INVALID, std::string(who) + ": null q/out");
     bk_status st = bind(ctx);
     if (st != BK_OK) return st;
-    const int n_kv = c->cfg.n_kv, n_head = c->cfg.n_head;
-    const size_t out_stride = (size_t)n_head * (partial ? kPartStride : kHd);
-
-    DecodeArgs a{};
-    a.k_rows = c->k_rows(layer, 0);
-    a.v_rows = c->v_rows(layer, 0);
-    a.k_norms = c->k_norms(layer, 0);
-    a.v_norms = c->v_norms(layer, 0);
-    a.seq_stride_rows = (size_t)c->cfg.n_ctx * n_kv;
-    a.partial = partial;
-    a.rope = c->rope->d;
-    a.n_rot = c->cfg.n_rot;
-    a.givens = ctx->d_givens;
-    a.bits = c->cfg.mode.kind == BK_MODE_PLANAR ? c->cfg.mode.bits : 0;
-    a.book = a.bits ? ctx->d_codebooks + (a.bits - 1) * kBookStride : nullptr;
-    a.n_head = n_head;
-    a.n_kv = n_kv;
-    a.k_kind = c->k_kind;
-    a.v_kind = c->v_kind;
-    a.k_row_bytes = c->k_row_bytes;
-    a.v_row_bytes = c->v_row_bytes;
-    a.partials = ctx->d_partials;
-    a.counters = ctx->d_counters;
-    a.no_rope = 0;
-    a.dbg = ctx->dbg;
-
+    const size_t out_stride = (size_t)c->cfg.n_head * (partial ? kPartStride : kHd);
+    DecodeArgs a;
+    fill_decode_args(c, layer, partial, &a);
     a.q = q_dev;
     a.out = out_dev;
 
-    // Validate everything first, then sort the sequences into two classes: long ones go to the
-    // tensor-core kernel (4-bit planar caches), short ones to the generic f32 kernel.  Below
-    // kMmaMinPos positions a sequence cannot fill the machine anyway, and the f16 lookup table of
-    // the tensor-core path (relative error ~1e-4 per centroid) is only averaged out over many
-    // positions, so short contexts keep the exact f32 arithmetic.
-    const bool mma_ok = !ctx->force_generic && decode_mma_supported(a);
-    struct Entry { int slot, seq, np, qp; };
-    std::vector<Entry> cls[2];
+    // Validate everything first, then sort the sequences into the two kernel classes.
+    std::vector<DecodeEntry> cls[2];
     for (int i = 0; i < n_seqs; i++) {
-        const int s = seq_ids ? seq_ids[i] : i;
-        if (s < 0 || s >= c->cfg.n_seqs) return fail(ctx, BK_ERR_INVALID, std::string(who) + ": bad sequence id");
-        const int np = n_pos ? n_pos[i] : c->n_pos[c->slab(layer, s)];
-        if (np < 0 || np > c->cfg.n_ctx) return fail(ctx, BK_ERR_RANGE, std::string(who) + ": n_pos beyond n_ctx");
-        const int qp = q_pos ? q_pos[i] : std::max(np - 1, 0);
-        if (qp < 0 || qp >= c->rope->n_pos)
-            return fail(ctx, BK_ERR_RANGE, std::string(who) + ": q position beyond the rope table");
-        if (np == 0) {  // nothing to attend to: zeros (and l = 0 for partials)
+        DecodeEntry e;
+        if ((st = check_decode_entry(c, layer, i, seq_ids, n_pos, q_pos, who, &e)) != BK_OK) return st;
+        if (e.np == 0) {  // nothing to attend to: zeros (and l = 0 for partials)
             BK_CUDA(ctx, cudaMemsetAsync(out_dev + (size_t)i * out_stride, 0, out_stride * sizeof(float), ctx->stream));
             continue;
         }
-        cls[(mma_ok && np >= kMmaMinPos) ? 1 : 0].push_back({i, s, np, qp});
+        cls[decode_entry_uses_mma(ctx, a, e.np) ? 1 : 0].push_back(e);
     }
-    for (int k = 0; k < 2; k++) {
-        const bool use_mma = k == 1;
-        const std::vector<Entry> &list = cls[k];
-        for (size_t base = 0; base < list.size(); base += kMaxSeqsPerLaunch) {
-            const int nb = (int)std::min<size_t>(kMaxSeqsPerLaunch, list.size() - base);
-            DecodeMeta m{};
-            m.n_seqs = nb;
-            int64_t total = 0;
-            for (int i = 0; i < nb; i++) {
-                const Entry &e = list[base + i];
-                m.slot[i] = e.slot;
-                m.seq_id[i] = e.seq;
-                m.n_pos[i] = e.np;
-                m.q_pos[i] = e.qp;
-                total += e.np;
-            }
-            // chunk length.  Generic kernel: about 4 CTAs per SM over the whole launch, at least
-            // 64 positions each.  Tensor-core kernel: one CTA per SM, chunks in units of 128
-            // positions (8 warps x 16-position tiles).
-            const int64_t gran = use_mma ? 128 : 64;
-            const int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * (use_mma ? 1 : 4) / n_kv);
-            int64_t L = (total + target_items - 1) / target_items;
-            L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
-            for (;;) {
-                int64_t items = 0;
-                for (int i = 0; i < nb; i++) items += (int64_t)n_kv * ((m.n_pos[i] + L - 1) / L);
-                if (items <= kMaxItems) break;
-                L *= 2;
-            }
-            m.chunk_len = (int)L;
-            int items = 0;
-            for (int i = 0; i < nb; i++) {
-                m.item_start[i] = items;
-                items += n_kv * (int)((m.n_pos[i] + L - 1) / L);
-            }
-            m.item_start[nb] = items;
-            m.n_items = items;
-            st = use_mma ? launch_decode_mma(ctx, a, m, ctx->lut_alpha[a.bits], ctx->qsplit) : launch_decode(ctx, a, m);
-            if (st != BK_OK) return st;
+    for (int k = 0; k < 2; k++)
+        for (size_t base = 0; base < cls[k].size(); base += kMaxSeqsPerLaunch) {
+            const int nb = (int)std::min<size_t>(kMaxSeqsPerLaunch, cls[k].size() - base);
+            if ((st = launch_decode_group(ctx, a, cls[k].data() + base, nb, k == 1, kMaxItems)) != BK_OK) return st;
         }
-    }
     return BK_OK;
 }
+
+extern "C" {
 
 bk_status bk_decode_attn(bk_cache *c, int32_t layer, int32_t n_seqs, const int32_t *seq_ids, const int32_t *n_pos,
                          const int32_t *q_pos, const float *q_dev, float *out_dev) {

@@ -165,6 +165,18 @@ struct DecodeArgs {
     int dbg;
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
+
+// Host-side planning shared by the decode entry points (bk_api.cu).
+struct DecodeEntry {
+    int slot, seq, np, qp;  // row in the caller's q/out arrays, sequence id, positions to scan, q position
+};
+void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out);
+bk_status check_decode_entry(const bk_cache *c, int layer, int slot, const int32_t *seq_ids, const int32_t *n_pos,
+                             const int32_t *q_pos, const char *who, DecodeEntry *e);
+bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntry *list, int nb, bool use_mma,
+                              int max_items);
+bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos);
+bk_status bind_device(bk_ctx *ctx);
 // Tensor-core path for 4-bit planar K and V (bk_decode_mma.cu).  Chunks must be multiples of 128.
 bool decode_mma_supported(const DecodeArgs &a);
 bk_status launch_decode_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
