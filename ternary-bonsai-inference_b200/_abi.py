@@ -57,6 +57,7 @@ SIGNATURES = {
     "bk_append_batch": (C.c_int, [_vp, _i32, _i32, _pi32, _pi32, _vp, _vp]),
     "bk_decode_attn": (C.c_int, [_vp, _i32, _i32, _pi32, _pi32, _pi32, _vp, _vp]),
     "bk_decode_attn_partial": (C.c_int, [_vp, _i32, _i32, _pi32, _pi32, _pi32, _vp, _vp]),
+    "bk_decode_attn_noalloc": (C.c_int, [_vp, _i32, _i32, _pi32, _pi32, _pi32, _vp, _vp]),
     "bk_lse_merge": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp]),
     "bk_attn_step": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bk_attn_step_host": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),

@@ -28,6 +28,7 @@ SOURCES = {
     "bk_kvq.cu": ["--fmad=false"],
     "bk_decode.cu": [],
     "bk_decode_mma.cu": [],
+    "bk_noalloc.cu": [],
     "bk_host_tables.cpp": [],
 }
 HEADERS = ["bk_internal.h", "bk_device.cuh", "bk_decode_common.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]
