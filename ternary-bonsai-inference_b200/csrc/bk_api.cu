@@ -189,8 +189,6 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
         const char *e1 = getenv("BONSAI_KV_GENERIC"), *e2 = getenv("BONSAI_KV_QSPLIT");
         ctx->force_generic = e1 && e1[0] == '1';
         ctx->qsplit = !(e2 && e2[0] == '0');  // on unless BONSAI_KV_QSPLIT=0
-        const char *e3 = getenv("BONSAI_KV_DBG");
-        ctx->dbg = e3 ? atoi(e3) : 0;
     }
     if ((e = cudaMalloc(&ctx->d_givens, sizeof(ctx->h_givens))) != cudaSuccess) return bail(e, "cudaMalloc givens");
     if ((e = cudaMalloc(&ctx->d_codebooks, sizeof(ctx->h_codebooks))) != cudaSuccess)
@@ -205,6 +203,8 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
     const size_t cnt_bytes = (size_t)kMaxSeqsPerLaunch * 64 * sizeof(unsigned);
     if ((e = cudaMalloc(&ctx->d_counters, cnt_bytes)) != cudaSuccess) return bail(e, "cudaMalloc counters");
     if ((e = cudaMemset(ctx->d_counters, 0, cnt_bytes)) != cudaSuccess) return bail(e, "clear counters");
+    if ((e = cudaMalloc(&ctx->d_err, sizeof(int))) != cudaSuccess) return bail(e, "cudaMalloc error flag");
+    if ((e = cudaMemset(ctx->d_err, 0, sizeof(int))) != cudaSuccess) return bail(e, "clear error flag");
     *out = ctx;
     return BK_OK;
 }
@@ -218,6 +218,7 @@ void bk_ctx_destroy(bk_ctx *ctx) {
     if (ctx->d_codebooks) cudaFree(ctx->d_codebooks);
     if (ctx->d_partials) cudaFree(ctx->d_partials);
     if (ctx->d_counters) cudaFree(ctx->d_counters);
+    if (ctx->d_err) cudaFree(ctx->d_err);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->d_stage) cudaFree(ctx->d_stage);
     if (ctx->h_desc) cudaFreeHost(ctx->h_desc);
@@ -233,6 +234,12 @@ const char *bk_last_error(const bk_ctx *ctx) { return ctx ? ctx->err.c_str() : g
 bk_status bk_synchronize(bk_ctx *ctx) {
     if (!ctx) return fail(nullptr, BK_ERR_INVALID, "bk_synchronize: ctx is null");
     BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    int flag = 0;
+    BK_CUDA(ctx, cudaMemcpy(&flag, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag) {
+        cudaMemset(ctx->d_err, 0, sizeof(int));
+        return fail(ctx, BK_ERR_CUDA, "a decode kernel gave up waiting for its shared-memory copies; results are invalid");
+    }
     return BK_OK;
 }
 
@@ -363,13 +370,23 @@ bk_status bk_cache_create(bk_ctx *ctx, const bk_cache_config *cfg, bk_cache **ou
     };
     if ((st = alloc((void **)&c->d_k, rows * c->k_row_bytes)) != BK_OK ||
         (st = alloc((void **)&c->d_v, rows * c->v_row_bytes)) != BK_OK ||
-        (k_kind == ROW_PLANAR && (st = alloc((void **)&c->d_kn, rows * 4)) != BK_OK) ||
-        (v_kind == ROW_PLANAR && (st = alloc((void **)&c->d_vn, rows * 4)) != BK_OK) ||
+        // norms carry one tile (16 positions) of slack: the tensor-core decode copies whole tiles
+        (k_kind == ROW_PLANAR && (st = alloc((void **)&c->d_kn, (rows + 16 * cfg->n_kv) * 4)) != BK_OK) ||
+        (v_kind == ROW_PLANAR && (st = alloc((void **)&c->d_vn, (rows + 16 * cfg->n_kv) * 4)) != BK_OK) ||
         (st = get_rope(ctx, cfg->n_rot, cfg->freq_base, rope_n, &c->rope)) != BK_OK) {
         bk_cache_destroy(c);
         return st;
     }
     c->n_pos.assign((size_t)cfg->n_layers * cfg->n_seqs, 0);
+    if (k_kind == ROW_PLANAR && v_kind == ROW_PLANAR && bits == 4) {
+        st = make_p4_tensor_maps(ctx, c->d_k, c->d_v, cfg->n_kv, (size_t)cfg->n_layers * cfg->n_seqs * cfg->n_ctx,
+                                 c->tmap_k, c->tmap_v);
+        if (st != BK_OK) {
+            bk_cache_destroy(c);
+            return st;
+        }
+        c->has_tmaps = true;
+    }
     *out = c;
     return BK_OK;
 }
@@ -602,7 +619,10 @@ void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out
     a.partials = ctx->d_partials;
     a.counters = ctx->d_counters;
     a.no_rope = 0;
-    a.dbg = ctx->dbg;
+    a.h_tmap_k = c->has_tmaps ? c->tmap_k : nullptr;
+    a.h_tmap_v = c->has_tmaps ? c->tmap_v : nullptr;
+    a.layer_pos0 = layer * c->cfg.n_seqs * c->cfg.n_ctx;
+    a.n_ctx = c->cfg.n_ctx;
     *out = a;
 }
 

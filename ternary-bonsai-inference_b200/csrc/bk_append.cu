@@ -128,6 +128,16 @@ bk_status launch_append(bk_ctx *ctx, const AppendArgs &a) {
     const int threads = 32 * 2 * a.n_kv;
     if (threads > 512) return fail(ctx, BK_ERR_UNSUPPORTED, "append: n_kv > 8");
     const size_t smem = (size_t)(2 * a.n_kv * kVecPad + 256) * sizeof(float);
+    // Decode launches use nearly all of the SM's shared memory; asking for the same carve-out here
+    // keeps the SM from being reconfigured between the append and the decode of every layer.
+    static bool carveout_set[64] = {};
+    if (ctx->device >= 0 && ctx->device < 64 && !carveout_set[ctx->device]) {
+        dispatch_bits(a.bits > 0 ? a.bits : 4, [&]<int B>() {
+            cudaFuncSetAttribute(append_kernel<B>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        });
+        cudaFuncSetAttribute(append_kernel<0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carveout_set[ctx->device] = true;
+    }
     const bool planar = a.k_kind == ROW_PLANAR || a.v_kind == ROW_PLANAR;
     if (!planar) {
         append_kernel<0><<<a.n_tokens, threads, smem, ctx->stream>>>(a);

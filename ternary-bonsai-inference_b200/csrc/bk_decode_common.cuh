@@ -47,7 +47,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
             *s_last = (ticket == (unsigned)(n_chunks - 1));
         }
         __syncthreads();
-        if (!*s_last || (a.dbg & 16)) { if (tid == 0 && *s_last) a.counters[s * a.n_kv + kv] = 0; return; }
+        if (!*s_last) return;
         const float *base = a.partials + (size_t)first_item * NREP * kScratchStride;
         // 64 threads span one 256-float row with float4 loads; the four 64-thread groups take
         // every fourth chunk.  The (head, chunk) pairs of a thread form one flat list walked 24

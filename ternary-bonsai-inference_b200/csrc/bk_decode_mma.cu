@@ -3,8 +3,15 @@
 // A 4-bit row carries 11.6 multiply-adds per byte once six q heads share it, more than the
 // FP32 pipes of an SM can retire at HBM speed, and a non-uniform Lloyd-Max codebook needs a
 // table lookup per index.  So this kernel
-//   * reads packed rows straight into registers with 128-bit loads, two 16-position tiles
-//     ahead (no shared-memory staging: the shared-memory pipe is kept for the lookups);
+//   * streams packed rows through a per-warp ring of shared-memory stages filled by the TMA
+//     engine: one tiled cp.async.bulk.tensor copy of 16 rows x 128 bytes for K and one for V per
+//     tile (a 3-D tensor map over [position][kv head][128 B] picks the rows of one kv head out
+//     of the interleaved cache) plus two small plain bulk copies for the norms of the same 16
+//     positions, completion on an mbarrier with a bounded wait.  HBM latency
+//     on this part needs more than 100 KB in flight per SM, which registers cannot hold.  The
+//     tiles land with the 128-byte swizzle (16-byte chunk ^= row & 7), and the kernel reads
+//     K as (row g, chunks 2t, 2t+1) and V as (rows 2t.., chunk g), which makes every 128-bit
+//     fragment read conflict-free;
 //   * dequantizes with one shared-memory lookup per packed BYTE: a 256-entry table of
 //     half2(c[lo nibble], c[hi nibble]), replicated per lane (entry e, lane l at byte offset
 //     e*256 + l*4 of a 64 KiB-aligned region) so that no lookup ever bank-conflicts and the
@@ -24,6 +31,7 @@
 // Output error against the f32 CPU path stays in the 1e-4 range.
 //
 // Work split, partials and the last-arriver combine are shared with the generic kernel.
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "bk_decode_common.cuh"
@@ -40,6 +48,11 @@ constexpr uint32_t kOtherBytes = 10240; // q fragments + merge bookkeeping
 constexpr int kHeadStride = 276;        // floats per head in the warp-merge area (bank-conflict free)
 constexpr float kWScale = 16384.0f;     // 2^14: V weights are stored as f16 in (0, 2^14]
 constexpr int kRowBytes = 128;          // 256 coordinates x 4 bit
+constexpr int kTileBytes = kTile * kRowBytes;   // 2048: one K or V tile, dense rows, 128B-swizzled
+constexpr int kNormBytes = 512;                 // norms of 16 positions x up to 8 kv heads (all heads travel)
+constexpr int kStageBytes = 2 * kTileBytes + 2 * kNormBytes;  // K tile, V tile, K norms, V norms; 1 KiB aligned
+constexpr int kMaxStages = 6;
+constexpr int kWaitPolls = 1 << 22;     // mbarrier polls before a wait gives up and flags an error
 
 struct Other {                          // lives outside the lookup table
     __half q_hi[8][kHd];
@@ -47,6 +60,7 @@ struct Other {                          // lives outside the lookup table
     float m_w[kMW][8], l_w[kMW][8];
     float M[8], L[8];
     int last;
+    unsigned long long bar[kMW][kMaxStages];  // one mbarrier per warp and stage
 };
 static_assert(sizeof(Other) <= kOtherBytes, "Other does not fit");
 
@@ -82,25 +96,76 @@ __device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
     return v;
 }
 
-struct TileRegs {
-    uint4 k[4];   // K: rows g / g+8, 16-byte chunks t / t+4
-    uint4 v[4];   // V: positions 2t, 2t+1, 2t+8, 2t+9, 16-byte chunk g
-    float kn[2], vn[2];
-};
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Plain 1-D bulk copy (the norms of a tile), same completion mechanism.
+__device__ __forceinline__ void tma_bulk(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// One tile (16 positions x 128 bytes of one kv head) global -> shared through the TMA engine;
+// completion is counted on `bar`.  Coordinates: byte in row (0), kv head, global position.
+__device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap *map, int kv, int pos, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(kv), "r"(pos), "r"(bar)
+        : "memory");
+}
 
 template <int NREP, bool QSPLIT>
-__global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+__global__ void __launch_bounds__(kMT, 1)
+decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t smem_bytes, int *err_flag,
+                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
 
-    // ---- shared-memory layout: the table must start on a 64 KiB boundary of the shared window
+    // ---- shared-memory layout.  The table must start on a 64 KiB boundary of the shared window
+    // (its index is spliced into byte 1 of the address).  What lies before and after it holds the
+    // bookkeeping block and the per-warp stage ring; the number of stages is whatever fits.
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t lut_addr = (base + (kLutBytes - 1)) & ~(kLutBytes - 1);
-    const uint32_t other_addr = (lut_addr - base >= kOtherBytes) ? base : lut_addr + kLutBytes;
+    uint32_t a_lo = (base + 1023u) & ~1023u, a_hi = lut_addr;           // region before the table
+    uint32_t b_lo = lut_addr + kLutBytes, b_hi = base + smem_bytes;    // region after it
+    uint32_t other_addr;
+    if (a_hi > a_lo && a_hi - a_lo >= kOtherBytes) { other_addr = a_lo; a_lo += kOtherBytes; }
+    else { other_addr = b_lo; b_lo += kOtherBytes; }
+    const uint32_t n_a = (a_hi > a_lo ? a_hi - a_lo : 0u) / kStageBytes, n_b = (b_hi > b_lo ? b_hi - b_lo : 0u) / kStageBytes;
+    const int n_stages = min((int)((n_a + n_b) / kMW), kMaxStages);
+    if (n_stages < 1) {  // the table's alignment left no room for the ring: report, do not run
+        if (tid == 0) atomicExch(err_flag, 2);
+        return;
+    }
+    auto stage_addr = [&](int st) -> uint32_t {
+        const uint32_t n = (uint32_t)(warp * n_stages + st);
+        return n < n_a ? a_lo + n * kStageBytes : b_lo + (n - n_a) * kStageBytes;
+    };
     uint8_t *lut_ptr = smem_raw + (lut_addr - base);
     Other &o = *reinterpret_cast<Other *>(smem_raw + (other_addr - base));
     const uint32_t lane_base = lut_addr | (uint32_t)(lane << 2);
+    const uint32_t bar0 = other_addr + (uint32_t)offsetof(Other, bar) + (uint32_t)(warp * kMaxStages) * 8u;
+    if (lane < kMaxStages) mbar_init(bar0 + lane * 8u, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    __syncthreads();
 
     // ---- which item ------------------------------------------------------------------------
     const int item = blockIdx.x;
@@ -114,35 +179,36 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
     const int p0 = chunk * L, p1 = min(p0 + L, n_pos);
     const int n_tiles = (p1 - p0 + kTile - 1) / kTile;
     const size_t seq_rows = (size_t)meta.seq_id[s] * a.seq_stride_rows;
-    const uint8_t *k_base = a.k_rows + (seq_rows + kv) * kRowBytes;
-    const uint8_t *v_base = a.v_rows + (seq_rows + kv) * kRowBytes;
-    const float *kn_base = a.k_norms + seq_rows + kv;
-    const float *vn_base = a.v_norms + seq_rows + kv;
-    const size_t row_stride = (size_t)a.n_kv * kRowBytes;
 
-    auto load_tile = [&](int tile, TileRegs &r) {
-        const int pb = p0 + tile * kTile, last = p1 - 1;
-        const int pg = min(pb + g, last), pg8 = min(pb + g + 8, last);
-        const uint8_t *kr0 = k_base + (size_t)pg * row_stride, *kr1 = k_base + (size_t)pg8 * row_stride;
-        r.k[0] = ldg128(kr0 + t * 16);
-        r.k[1] = ldg128(kr0 + (t + 4) * 16);
-        r.k[2] = ldg128(kr1 + t * 16);
-        r.k[3] = ldg128(kr1 + (t + 4) * 16);
-        const int pv0 = min(pb + 2 * t, last), pv1 = min(pb + 2 * t + 1, last);
-        const int pv2 = min(pb + 2 * t + 8, last), pv3 = min(pb + 2 * t + 9, last);
-        r.v[0] = ldg128(v_base + (size_t)pv0 * row_stride + g * 16);
-        r.v[1] = ldg128(v_base + (size_t)pv1 * row_stride + g * 16);
-        r.v[2] = ldg128(v_base + (size_t)pv2 * row_stride + g * 16);
-        r.v[3] = ldg128(v_base + (size_t)pv3 * row_stride + g * 16);
-        r.kn[0] = __ldg(kn_base + (size_t)pg * a.n_kv);
-        r.kn[1] = __ldg(kn_base + (size_t)pg8 * a.n_kv);
-        r.vn[0] = __ldg(vn_base + (size_t)pg * a.n_kv);
-        r.vn[1] = __ldg(vn_base + (size_t)pg8 * a.n_kv);
+    // One lane arms the stage's mbarrier for 4 KiB and issues the two tile copies.  Rows past the
+    // end of the chunk are whatever follows in the cache (or zeros past its end); their weights
+    // are forced to zero below.
+    const int gpos0 = a.layer_pos0 + meta.seq_id[s] * a.n_ctx + p0;  // position index in the tensor map
+    auto issue_tile = [&](int tile, int st) {
+        if (lane == 0) {
+            const uint32_t bar = bar0 + (uint32_t)st * 8u, dst = stage_addr(st);
+            const uint32_t nb = (uint32_t)(kTile * 4 * a.n_kv);  // norms of 16 positions, every kv head
+            mbar_expect_tx(bar, 2 * kTileBytes + 2 * nb);
+            tma_tile(dst, &tm_k, kv, gpos0 + tile * kTile, bar);
+            tma_tile(dst + kTileBytes, &tm_v, kv, gpos0 + tile * kTile, bar);
+            const size_t nrow = seq_rows + (size_t)(p0 + tile * kTile) * a.n_kv;
+            tma_bulk(dst + 2 * kTileBytes, a.k_norms + nrow, nb, bar);
+            tma_bulk(dst + 2 * kTileBytes + kNormBytes, a.v_norms + nrow, nb, bar);
+        }
     };
-
-    TileRegs buf0, buf1;
-    if (warp < n_tiles) load_tile(warp, buf0);
-    if (warp + kMW < n_tiles) load_tile(warp + kMW, buf1);
+    auto wait_tile = [&](int st, uint32_t parity) {
+        const uint32_t bar = bar0 + (uint32_t)st * 8u;
+        int polls = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            if (++polls > kWaitPolls) {  // never expected; leave a mark and go on rather than hang
+                if (lane == 0) atomicExch(err_flag, 1);
+                break;
+            }
+        }
+    };
+    // fill the ring before anything else so that the copies fly during the set-up below
+    for (int st = 0; st < n_stages; st++)
+        if (warp + st * kMW < n_tiles) issue_tile(warp + st * kMW, st);
 
     // ---- q: rope, Givens rotation, scale, split into f16 hi/lo (scratch: the table's region) --
     {
@@ -191,12 +257,12 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
         __syncthreads();
     }
 
-    // ---- q fragments: k-step ks = c*8 + w*2 + bp covers coordinates (t+4c)*32 + w*8 + bp*4 + 0..3
+    // ---- q fragments: k-step ks = c*8 + w*2 + bp covers coordinates (2t+c)*32 + w*8 + bp*4 + 0..3
     uint32_t qh[16][2];
 #pragma unroll
     for (int ks = 0; ks < 16; ks++) {
         const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
-        const int d0 = (t + 4 * c) * 32 + w * 8 + bp * 4;
+        const int d0 = (2 * t + c) * 32 + w * 8 + bp * 4;
         const uint2 v = *reinterpret_cast<const uint2 *>(&o.q_hi[g][d0]);
         qh[ks][0] = v.x;
         qh[ks][1] = v.y;
@@ -206,7 +272,7 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
 #pragma unroll
         for (int ks = 0; ks < 16; ks++) {
             const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
-            const int d0 = (t + 4 * c) * 32 + w * 8 + bp * 4;
+            const int d0 = (2 * t + c) * 32 + w * 8 + bp * 4;
             const uint2 v = *reinterpret_cast<const uint2 *>(&o.q_lo[g][d0]);
             ql[QSPLIT ? ks : 0][0] = v.x;
             ql[QSPLIT ? ks : 0][1] = v.y;
@@ -218,18 +284,30 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
     for (int j = 0; j < 16; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     float M0 = -CUDART_INF_F, M1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
-    const int dbg = a.dbg;
-    auto compute_tile = [&](int tile, const TileRegs &r) {
+    auto compute_tile = [&](int tile, uint32_t st_addr) {
+        // norms of positions g and g + 8 for this kv head (rows past the chunk are masked below)
+        float kn[2], vn[2];
+        {
+            const uint32_t na = st_addr + 2 * kTileBytes + (uint32_t)((g * a.n_kv + kv) * 4), step = (uint32_t)(8 * a.n_kv * 4);
+            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(kn[0]) : "r"(na));
+            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(kn[1]) : "r"(na + step));
+            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(vn[0]) : "r"(na + kNormBytes));
+            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(vn[1]) : "r"(na + kNormBytes + step));
+        }
+        // swizzled reads: the 16-byte chunk index is XORed with (row & 7); rows g and g + 8 share it
+        const uint32_t k_row = st_addr + g * kRowBytes;
+        const uint32_t v_tile = st_addr + kTileBytes;
         // ---- scores^T = Kc . Q^T ------------------------------------------------------------
         // four independent accumulator chains (the 16 or 32 MMAs of a tile would otherwise be one
         // dependent chain), summed at the end
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
         float sc2[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
-        if (!(dbg & 2))
 #pragma unroll
         for (int c = 0; c < 2; c++) {
-            const uint32_t xg[4] = {r.k[c].x, r.k[c].y, r.k[c].z, r.k[c].w};
-            const uint32_t xh[4] = {r.k[2 + c].x, r.k[2 + c].y, r.k[2 + c].z, r.k[2 + c].w};
+            const uint32_t koff = (uint32_t)(((2 * t + c) ^ g) << 4);                 // chunks 2t, 2t+1
+            const uint4 rk_g = lds128(k_row + koff), rk_h = lds128(k_row + 8 * kRowBytes + koff);
+            const uint32_t xg[4] = {rk_g.x, rk_g.y, rk_g.z, rk_g.w};
+            const uint32_t xh[4] = {rk_h.x, rk_h.y, rk_h.z, rk_h.w};
 #pragma unroll
             for (int w = 0; w < 4; w++) {
                 const int ks = c * 8 + w * 2;
@@ -253,8 +331,8 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
         // ---- online softmax in the exp2 domain; reference point = max of s + log2||v|| -------
         const int pb = p0 + tile * kTile;
         const bool ok0 = pb + g < p1, ok1 = pb + g + 8 < p1;
-        const float s00 = sc[0] * r.kn[0], s01 = sc[1] * r.kn[0], s10 = sc[2] * r.kn[1], s11 = sc[3] * r.kn[1];
-        const float lv0 = log2f(fmaxf(r.vn[0], 1e-37f)), lv1 = log2f(fmaxf(r.vn[1], 1e-37f));
+        const float s00 = sc[0] * kn[0], s01 = sc[1] * kn[0], s10 = sc[2] * kn[1], s11 = sc[3] * kn[1];
+        const float lv0 = log2f(fmaxf(vn[0], 1e-37f)), lv1 = log2f(fmaxf(vn[1], 1e-37f));
         const float t00 = ok0 ? s00 + lv0 : -CUDART_INF_F, t01 = ok0 ? s01 + lv0 : -CUDART_INF_F;
         const float t10 = ok1 ? s10 + lv1 : -CUDART_INF_F, t11 = ok1 ? s11 + lv1 : -CUDART_INF_F;
         float mx0 = fmaxf(t00, t10), mx1 = fmaxf(t01, t11);
@@ -287,11 +365,14 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
         const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
         const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
         // ---- out^T += Vc^T . W : MMA j covers coordinates 32g + 2j (rows g) and 32g + 2j + 1 (rows g+8)
-        const uint32_t x0[4] = {r.v[0].x, r.v[0].y, r.v[0].z, r.v[0].w};
-        const uint32_t x1[4] = {r.v[1].x, r.v[1].y, r.v[1].z, r.v[1].w};
-        const uint32_t x2[4] = {r.v[2].x, r.v[2].y, r.v[2].z, r.v[2].w};
-        const uint32_t x3[4] = {r.v[3].x, r.v[3].y, r.v[3].z, r.v[3].w};
-        if (!(dbg & 4))
+        const uint32_t r0 = 2 * t, r1 = 2 * t + 1;  // rows 2t, 2t+1 (and +8: same swizzle), chunk g
+        const uint32_t vo0 = r0 * kRowBytes + (((uint32_t)g ^ (r0 & 7)) << 4), vo1 = r1 * kRowBytes + (((uint32_t)g ^ (r1 & 7)) << 4);
+        const uint4 rv0 = lds128(v_tile + vo0), rv1 = lds128(v_tile + vo1);
+        const uint4 rv2 = lds128(v_tile + 8 * kRowBytes + vo0), rv3 = lds128(v_tile + 8 * kRowBytes + vo1);
+        const uint32_t x0[4] = {rv0.x, rv0.y, rv0.z, rv0.w};
+        const uint32_t x1[4] = {rv1.x, rv1.y, rv1.z, rv1.w};
+        const uint32_t x2[4] = {rv2.x, rv2.y, rv2.z, rv2.w};
+        const uint32_t x3[4] = {rv3.x, rv3.y, rv3.z, rv3.w};
 #pragma unroll
         for (int w = 0; w < 4; w++) {
             const uint32_t m = 0x0f0f0f0fu;
@@ -308,17 +389,19 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
         }
     };
 
-    // ---- scan: two tiles in flight per warp ----------------------------------------------------
-    for (int tile = warp; tile < n_tiles; tile += 2 * kMW) {
-        compute_tile(tile, buf0);
-        if (tile + 2 * kMW < n_tiles) load_tile(tile + 2 * kMW, buf0);
-        if (tile + kMW < n_tiles) {
-            compute_tile(tile + kMW, buf1);
-            if (tile + 3 * kMW < n_tiles) load_tile(tile + 3 * kMW, buf1);
+    // ---- scan: the warp's tiles are warp, warp + 8, ...; tile i lives in stage i % n_stages ------
+    {
+        int st = 0;
+        uint32_t parity = 0;
+        for (int tile = warp; tile < n_tiles; tile += kMW) {
+            wait_tile(st, parity);
+            compute_tile(tile, stage_addr(st));
+            __syncwarp();  // every lane has read the stage: lane 0 may refill it
+            if (tile + n_stages * kMW < n_tiles) issue_tile(tile + n_stages * kMW, st);
+            if (++st == n_stages) { st = 0; parity ^= 1u; }
         }
     }
 
-    if (dbg & 1) { if (M0 == 123.f) a.out[0] = l0 + acc[0][0] + acc[5][1]; return; }
     // ---- merge the warps ---------------------------------------------------------------------
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -379,22 +462,33 @@ __global__ void __launch_bounds__(kMT, 1) decode_p4_mma_kernel(DecodeArgs a, Dec
     for (int r = 0; r < NREP; r++) s_acc[r * kHd + tid] = sums[r];
     __syncthreads();
 
-    if (dbg & 8) return;
     const int first_item = meta.item_start[s] + kv * n_chunks;
     finish_item<NREP>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, true);
 }
 
 template <int NREP, bool QSPLIT>
 bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha) {
-    const size_t smem = 2 * (size_t)kLutBytes + kOtherBytes;
-    static bool configured[64] = {};  // per template instance and device
-    if (ctx->device >= 64 || !configured[ctx->device]) {
-        cudaError_t e = cudaFuncSetAttribute(decode_p4_mma_kernel<NREP, QSPLIT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(decode_p4_mma_kernel)");
-        if (ctx->device < 64) configured[ctx->device] = true;
+    // Dynamic shared memory: everything the SM allows beyond the kernel's static part.  The kernel
+    // lays out table, bookkeeping and as many ring stages as fit (at least 2 are needed).
+    static size_t smem_for[64] = {};
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (mma): device index above 63");
+    if (smem_for[dev] == 0) {
+        cudaFuncAttributes fa;
+        BK_CUDA(ctx, cudaFuncGetAttributes(&fa, decode_p4_mma_kernel<NREP, QSPLIT>));
+        int optin = 0;
+        BK_CUDA(ctx, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        const size_t dyn = (size_t)optin - fa.sharedSizeBytes;
+        const size_t need = (size_t)kLutBytes + kOtherBytes + 2 * (size_t)kMW * kStageBytes;
+        if (dyn < need) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (mma): not enough shared memory per block on this device");
+        BK_CUDA(ctx, cudaFuncSetAttribute(decode_p4_mma_kernel<NREP, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        smem_for[dev] = dyn;
     }
-    decode_p4_mma_kernel<NREP, QSPLIT><<<m.n_items, kMT, smem, ctx->stream>>>(a, m, alpha);
+    const size_t smem = smem_for[dev];
+    if (!a.h_tmap_k || !a.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "decode (mma): the cache has no tensor maps");
+    decode_p4_mma_kernel<NREP, QSPLIT><<<m.n_items, kMT, smem, ctx->stream>>>(
+        a, m, alpha, (uint32_t)smem, ctx->d_err, *static_cast<const CUtensorMap *>(a.h_tmap_k),
+        *static_cast<const CUtensorMap *>(a.h_tmap_v));
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     return BK_OK;
@@ -402,9 +496,44 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
 
 }  // namespace
 
+// Tensor maps over the K and V rows of a 4-bit planar cache: dims (128 bytes, n_kv, positions of all
+// layers and sequences), box (128, 1, 16), 128-byte swizzle.  Built once per cache.
+bk_status make_p4_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, int n_kv, size_t total_pos,
+                              void *out_k, void *out_v) {
+    static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        BK_CUDA(ctx, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
+        if (!fn || qr != cudaDriverEntryPointSuccess)
+            return fail(ctx, BK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available in this driver");
+        encode = (EncodeFn)fn;
+    }
+    if (total_pos >= (size_t)1 << 31) return fail(ctx, BK_ERR_UNSUPPORTED, "cache has more than 2^31 positions");
+    const cuuint64_t dims[3] = {(cuuint64_t)kRowBytes, (cuuint64_t)n_kv, (cuuint64_t)total_pos};
+    const cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, (cuuint64_t)kRowBytes * n_kv};
+    const cuuint32_t box[3] = {(cuuint32_t)kRowBytes, 1, (cuuint32_t)kTile};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const void *ptrs[2] = {k_rows, v_rows};
+    void *outs[2] = {out_k, out_v};
+    for (int i = 0; i < 2; i++) {
+        const CUresult r = encode(static_cast<CUtensorMap *>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                                  const_cast<void *>(ptrs[i]), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(ctx, BK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    }
+    return BK_OK;
+}
+
 bool decode_mma_supported(const DecodeArgs &a) {
     const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
-    return a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && a.bits == 4 &&
+    // (the norms of a tile travel as a 16-byte aligned bulk copy: n_ctx * n_kv must be a multiple of 4)
+    return a.h_tmap_k && a.h_tmap_v && (a.seq_stride_rows % 4 == 0) && a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && a.bits == 4 &&
            (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 

@@ -57,7 +57,6 @@ struct bk_ctx {
     float h_codebooks[bk::kMaxBits * bk::kBookStride];
     float lut_alpha[bk::kMaxBits + 1] = {};  // per width: scale applied to centroids before f16 rounding
     bool force_generic = false;            // BONSAI_KV_GENERIC=1: never take the tensor-core path
-    int dbg = 0;
     bool qsplit = true;                    // q as f16 hi + lo in the tensor-core path (BONSAI_KV_QSPLIT=0: hi only)
     // staging for the *_host entry points (grown on demand)
     void *h_stage = nullptr;
@@ -67,6 +66,7 @@ struct bk_ctx {
     // split-K scratch of the decode kernel: partial results and arrival counters
     float *d_partials = nullptr;
     unsigned *d_counters = nullptr;
+    int *d_err = nullptr;          // set by a kernel whose bounded wait ran out; read by bk_synchronize
     int n_sms = 148;
     std::vector<std::shared_ptr<bk::RopeTable>> ropes;
     // token descriptors of bk_append_batch: a ring of pinned/device slots, one event per slot
@@ -86,6 +86,8 @@ struct bk_cache {
     std::vector<int32_t> n_pos;               // [layer][seq]
     std::shared_ptr<bk::RopeTable> rope;
     size_t device_bytes = 0;
+    alignas(64) unsigned char tmap_k[128], tmap_v[128];  // CUtensorMap objects (4-bit planar K+V caches)
+    bool has_tmaps = false;
 
     size_t slab(int layer, int seq) const { return (size_t)layer * cfg.n_seqs + seq; }
     uint8_t *k_rows(int layer, int seq) const {
@@ -162,7 +164,10 @@ struct DecodeArgs {
     float *partials;
     unsigned *counters;
     int no_rope;  // 1: q is used as given (one-shot f32 attention)
-    int dbg;
+    // tensor-core path only: host copies of the cache's tensor maps, and where (layer, sequence)
+    // sits in them: position index = layer_pos0 + seq * n_ctx + pos
+    const void *h_tmap_k, *h_tmap_v;
+    int layer_pos0, n_ctx;
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
 
@@ -179,6 +184,8 @@ bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos);
 bk_status bind_device(bk_ctx *ctx);
 // Tensor-core path for 4-bit planar K and V (bk_decode_mma.cu).  Chunks must be multiples of 128.
 bool decode_mma_supported(const DecodeArgs &a);
+bk_status make_p4_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, int n_kv, size_t total_pos,
+                              void *out_k, void *out_v);
 bk_status launch_decode_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
 bk_status launch_lse_merge(bk_ctx *ctx, int n_parts, int n_rows, int hd, const float *parts, float *out);
 
