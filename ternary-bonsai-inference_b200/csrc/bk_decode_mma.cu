@@ -44,7 +44,7 @@ constexpr int kMW = 8;                  // warps per CTA
 constexpr int kMT = kMW * 32;
 constexpr int kTile = 16;               // positions per warp tile (the MMA's M)
 constexpr uint32_t kLutBytes = 65536;   // 256 entries x 256 B (128 B used: one word per lane)
-constexpr uint32_t kOtherBytes = 14336; // q halves and fragments + merge bookkeeping + mbarriers (multiple of 1 KiB)
+constexpr uint32_t kOtherBytes = 10240; // q fragments + merge bookkeeping
 constexpr int kHeadStride = 276;        // floats per head in the warp-merge area (bank-conflict free)
 constexpr float kWScale = 16384.0f;     // 2^14: V weights are stored as f16 in (0, 2^14]
 constexpr int kRowBytes = 128;          // 256 coordinates x 4 bit
@@ -58,7 +58,6 @@ struct Other {                          // lives outside the lookup table
     __half q_hi[8][kHd];
     __half q_lo[8][kHd];
     float m_w[kMW][8], l_w[kMW][8];
-    uint2 q_lo_frag[16][32];             // q_lo as B fragments: [k-step][lane]
     float M[8], L[8];
     int last;
     unsigned long long bar[kMW][kMaxStages];  // one mbarrier per warp and stage
@@ -85,7 +84,7 @@ template <int K>
 __device__ __forceinline__ uint32_t lut(uint32_t x, uint32_t lane_base) {
     uint32_t addr, v;
     asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(addr) : "r"(x), "r"(lane_base), "n"(0x7604 | (K << 4)));
-    asm("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
     return v;
 }
 
@@ -268,29 +267,24 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         qh[ks][0] = v.x;
         qh[ks][1] = v.y;
     }
-    if (QSPLIT) {  // the low halves stay in shared memory: one conflict-free 8-byte read per k-step
+    uint32_t ql[QSPLIT ? 16 : 1][2];
+    if (QSPLIT) {
 #pragma unroll
         for (int ks = 0; ks < 16; ks++) {
             const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
             const int d0 = (2 * t + c) * 32 + w * 8 + bp * 4;
-            o.q_lo_frag[ks][lane] = *reinterpret_cast<const uint2 *>(&o.q_lo[g][d0]);
+            const uint2 v = *reinterpret_cast<const uint2 *>(&o.q_lo[g][d0]);
+            ql[QSPLIT ? ks : 0][0] = v.x;
+            ql[QSPLIT ? ks : 0][1] = v.y;
         }
-        __syncwarp();
     }
-    const uint32_t ql_addr = other_addr + (uint32_t)offsetof(Other, q_lo_frag) + (uint32_t)lane * 8u;
-    auto ql_frag = [&](int ks, uint32_t &x, uint32_t &y) {
-        asm("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(x), "=r"(y) : "r"(ql_addr + (uint32_t)ks * 256u));
-    };
 
     float acc[16][4];
 #pragma unroll
     for (int j = 0; j < 16; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     float M0 = -CUDART_INF_F, M1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
-    // K phase of a tile: scores, online softmax, weights as B fragments (b0, b1).  When the running
-    // maximum moves it also brings l and the accumulators to the new reference, so it must come
-    // after the V phase of the previous tile in program order.
-    auto k_phase = [&](int tile, uint32_t st_addr, uint32_t &b0, uint32_t &b1) {
+    auto compute_tile = [&](int tile, uint32_t st_addr) {
         // norms of positions g and g + 8 for this kv head (rows past the chunk are masked below)
         float kn[2], vn[2];
         {
@@ -302,6 +296,8 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         }
         // swizzled reads: the 16-byte chunk index is XORed with (row & 7); rows g and g + 8 share it
         const uint32_t k_row = st_addr + g * kRowBytes;
+        const uint32_t v_tile = st_addr + kTileBytes;
+        // ---- scores^T = Kc . Q^T ------------------------------------------------------------
         // four independent accumulator chains (the 16 or 32 MMAs of a tile would otherwise be one
         // dependent chain), summed at the end
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
@@ -319,21 +315,13 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                     const uint32_t a0 = lut<0>(xg[w], lane_base), a1 = lut<0>(xh[w], lane_base);
                     const uint32_t a2 = lut<1>(xg[w], lane_base), a3 = lut<1>(xh[w], lane_base);
                     mma16816(c ? sb : sa, a0, a1, a2, a3, qh[ks][0], qh[ks][1]);
-                    if (QSPLIT) {
-                        uint32_t lx, ly;
-                        ql_frag(ks, lx, ly);
-                        mma16816(c ? sd : sc2, a0, a1, a2, a3, lx, ly);
-                    }
+                    if (QSPLIT) mma16816(c ? sd : sc2, a0, a1, a2, a3, ql[QSPLIT ? ks : 0][0], ql[QSPLIT ? ks : 0][1]);
                 }
                 {
                     const uint32_t a0 = lut<2>(xg[w], lane_base), a1 = lut<2>(xh[w], lane_base);
                     const uint32_t a2 = lut<3>(xg[w], lane_base), a3 = lut<3>(xh[w], lane_base);
                     mma16816(c ? sd : sc2, a0, a1, a2, a3, qh[ks + 1][0], qh[ks + 1][1]);
-                    if (QSPLIT) {
-                        uint32_t lx, ly;
-                        ql_frag(ks + 1, lx, ly);
-                        mma16816(c ? sb : sa, a0, a1, a2, a3, lx, ly);
-                    }
+                    if (QSPLIT) mma16816(c ? sb : sa, a0, a1, a2, a3, ql[QSPLIT ? ks + 1 : 0][0], ql[QSPLIT ? ks + 1 : 0][1]);
                 }
             }
         }
@@ -374,12 +362,9 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         l0 += (ok0 ? exp2f(s00 - M0) : 0.f) + (ok1 ? exp2f(s10 - M0) : 0.f);
         l1 += (ok0 ? exp2f(s01 - M1) : 0.f) + (ok1 ? exp2f(s11 - M1) : 0.f);
         const __half2 pl = __floats2half2_rn(w00, w01), ph = __floats2half2_rn(w10, w11);
-        b0 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
-        b1 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
-    };
-    // V phase: out^T += Vc^T . W; MMA j covers coordinates 32g + 2j (rows g) and 32g + 2j + 1 (rows g+8)
-    auto v_phase = [&](uint32_t st_addr, uint32_t b0, uint32_t b1) {
-        const uint32_t v_tile = st_addr + kTileBytes;
+        const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
+        const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
+        // ---- out^T += Vc^T . W : MMA j covers coordinates 32g + 2j (rows g) and 32g + 2j + 1 (rows g+8)
         const uint32_t r0 = 2 * t, r1 = 2 * t + 1;  // rows 2t, 2t+1 (and +8: same swizzle), chunk g
         const uint32_t vo0 = r0 * kRowBytes + (((uint32_t)g ^ (r0 & 7)) << 4), vo1 = r1 * kRowBytes + (((uint32_t)g ^ (r1 & 7)) << 4);
         const uint4 rv0 = lds128(v_tile + vo0), rv1 = lds128(v_tile + vo1);
@@ -404,28 +389,16 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         }
     };
 
-    // ---- scan: the warp's tiles are warp, warp + 8, ...; tile i lives in stage i % n_stages.
-    // Software-pipelined by one tile: an iteration runs the V phase of tile i together with the K
-    // phase of tile i + 1, two independent instruction streams that hide each other's latencies
-    // (the K phase ends in a serial stretch of shuffles, exponentials and a transpose).
-    if (warp < n_tiles) {
+    // ---- scan: the warp's tiles are warp, warp + 8, ...; tile i lives in stage i % n_stages ------
+    {
         int st = 0;
-        uint32_t parity = 0, b0, b1;
-        wait_tile(0, 0);
-        k_phase(warp, stage_addr(0), b0, b1);
+        uint32_t parity = 0;
         for (int tile = warp; tile < n_tiles; tile += kMW) {
-            const uint32_t sa_cur = stage_addr(st);
-            const int st_cur = st;
+            wait_tile(st, parity);
+            compute_tile(tile, stage_addr(st));
+            __syncwarp();  // every lane has read the stage: lane 0 may refill it
+            if (tile + n_stages * kMW < n_tiles) issue_tile(tile + n_stages * kMW, st);
             if (++st == n_stages) { st = 0; parity ^= 1u; }
-            const bool more = tile + kMW < n_tiles;
-            uint32_t nb0 = 0, nb1 = 0;
-            if (more) wait_tile(st, parity);
-            v_phase(sa_cur, b0, b1);
-            if (more) k_phase(tile + kMW, stage_addr(st), nb0, nb1);
-            __syncwarp();  // every lane has read stage st_cur (its K tile an iteration ago): refill it
-            if (tile + n_stages * kMW < n_tiles) issue_tile(tile + n_stages * kMW, st_cur);
-            b0 = nb0;
-            b1 = nb1;
         }
     }
 
