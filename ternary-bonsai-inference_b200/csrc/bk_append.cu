@@ -87,6 +87,11 @@ __global__ void __launch_bounds__(512) append_kernel(AppendArgs a) {
     if (BITS > 0) {
         for (int i = threadIdx.x; i < (1 << BITS); i += blockDim.x) sbook[i] = a.book[i];
     }
+    // k and v may come from the previous kernel in the stream: with programmatic dependent launch
+    // only the codebook copy above runs ahead of it.  Nothing after this kernel depends on more
+    // than its completion, so dependents may be scheduled right away.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
     const float *src = (is_v ? a.v : a.k) + ((size_t)tok * n_kv + kv) * kHd;
     const float4 *src4 = reinterpret_cast<const float4 *>(src);
@@ -139,15 +144,25 @@ bk_status launch_append(bk_ctx *ctx, const AppendArgs &a) {
         carveout_set[ctx->device] = true;
     }
     const bool planar = a.k_kind == ROW_PLANAR || a.v_kind == ROW_PLANAR;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)a.n_tokens);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see griddepcontrol.* in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err = cudaSuccess;
     if (!planar) {
-        append_kernel<0><<<a.n_tokens, threads, smem, ctx->stream>>>(a);
+        err = cudaLaunchKernelEx(&cfg, append_kernel<0>, a);
     } else {
-        const bool ok = dispatch_bits(a.bits, [&]<int B>() {
-            append_kernel<B><<<a.n_tokens, threads, smem, ctx->stream>>>(a);
-        });
+        const bool ok = dispatch_bits(a.bits, [&]<int B>() { err = cudaLaunchKernelEx(&cfg, append_kernel<B>, a); });
         if (!ok) return fail(ctx, BK_ERR_INVALID, "append: bits must be 1..8");
     }
     ctx->launches++;
+    BK_CUDA(ctx, err);
     BK_CUDA(ctx, cudaGetLastError());
     return BK_OK;
 }

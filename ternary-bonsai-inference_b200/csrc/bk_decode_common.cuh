@@ -23,13 +23,17 @@ constexpr int kFactorCap = 256;  // chunks whose rescale factors are cached in s
 template <int NREP>
 __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s, int kv, int item, int n_chunks,
                                             int first_item, float *s_acc /* [NREP][kHd] */, float *s_M, float *s_L,
-                                            int *s_last, bool v_planar) {
+                                            int *s_last, bool v_planar,
+                                            const float *givens = nullptr /* shared-memory copy, if the caller has one */) {
     __shared__ float s_f[kFactorCap * NREP];
-    const int tid = threadIdx.x, nt = blockDim.x;  // nt == 256 in every caller
+    // the first 256 threads work; a larger CTA's remaining threads only take part in the barriers
+    const int tid = threadIdx.x, nt = 256;
+    const bool act = threadIdx.x < 256;
+    const int tid0 = act ? tid : (1 << 30);  // loop start that keeps idle threads out of strided loops
     const int warp = tid >> 5, lane = tid & 31;
     if (n_chunks > 1) {
         float *part = a.partials + ((size_t)item * NREP) * kScratchStride;
-        for (int i = tid; i < NREP * kHd; i += nt) {
+        for (int i = tid0; i < NREP * kHd; i += nt) {
             const int r = i / kHd, d = i - r * kHd;
             part[(size_t)r * kScratchStride + d] = s_acc[i];
         }
@@ -55,7 +59,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
         // below so that both travel in the same L2 round trip.
         const int rg = tid >> 6, x = tid & 63;
         const int per_rg = (n_chunks - rg + 3) / 4;  // chunks rg, rg+4, ...
-        const int n_pairs = per_rg * NREP;
+        const int n_pairs = act ? per_rg * NREP : 0;
         constexpr int kBatch = (NREP == 6) ? 30 : 32;  // a multiple of NREP: slot u is always head u % NREP
         float4 v[kBatch];
         auto load_batch = [&](int i0) {
@@ -153,10 +157,11 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
     }
 
     if (v_planar) {
-        for (int i = tid; i < NREP * (kHd / 2); i += nt) {
+        for (int i = tid0; i < NREP * (kHd / 2); i += nt) {
             const int r = i / (kHd / 2), pr = i - r * (kHd / 2);
             float o0, o1;
-            givens_inv(s_acc[r * kHd + 2 * pr], s_acc[r * kHd + 2 * pr + 1], a.givens[2 * pr], a.givens[2 * pr + 1],
+            const float *gv = givens ? givens : a.givens;
+            givens_inv(s_acc[r * kHd + 2 * pr], s_acc[r * kHd + 2 * pr + 1], gv[2 * pr], gv[2 * pr + 1],
                        o0, o1);
             s_acc[r * kHd + 2 * pr] = o0;
             s_acc[r * kHd + 2 * pr + 1] = o1;
@@ -165,7 +170,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
     }
     if (a.partial) {
         float *out = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP) * kPartStride;
-        for (int i = tid; i < NREP * kHd; i += nt) {
+        for (int i = tid0; i < NREP * kHd; i += nt) {
             const int r = i / kHd, d = i - r * kHd;
             out[(size_t)r * kPartStride + d] = s_acc[i];
         }
@@ -175,7 +180,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
         }
     } else {
         float *out = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP) * kHd;
-        for (int i = tid; i < NREP * kHd; i += nt) {
+        for (int i = tid0; i < NREP * kHd; i += nt) {
             const float Ls = s_L[i / kHd];
             out[i] = Ls > 0.f ? s_acc[i] / Ls : 0.f;
         }

@@ -40,11 +40,11 @@ namespace bk {
 
 namespace {
 
-constexpr int kMW = 8;                  // warps per CTA
+constexpr int kMW = 12;                 // warps per CTA
 constexpr int kMT = kMW * 32;
 constexpr int kTile = 16;               // positions per warp tile (the MMA's M)
 constexpr uint32_t kLutBytes = 65536;   // 256 entries x 256 B (128 B used: one word per lane)
-constexpr uint32_t kOtherBytes = 10240; // q fragments + merge bookkeeping
+constexpr uint32_t kOtherBytes = 28672; // q halves and fragments + merge bookkeeping (multiple of 1 KiB)
 constexpr int kHeadStride = 276;        // floats per head in the warp-merge area (bank-conflict free)
 constexpr float kWScale = 16384.0f;     // 2^14: V weights are stored as f16 in (0, 2^14]
 constexpr int kRowBytes = 128;          // 256 coordinates x 4 bit
@@ -57,7 +57,11 @@ constexpr int kWaitPolls = 1 << 22;     // mbarrier polls before a wait gives up
 struct Other {                          // lives outside the lookup table
     __half q_hi[8][kHd];
     __half q_lo[8][kHd];
+    uint2 q_hi_frag[16][32], q_lo_frag[16][32];  // q as B fragments: [k-step][lane], 8-byte conflict-free reads
     float m_w[kMW][8], l_w[kMW][8];
+    float sq[8 * kHd];                   // q of the group while it is roped and rotated
+    float givens[kHd];                   // (cos, sin) pairs, fetched once (the epilogue needs them again)
+    float2 rope_row[kHd / 2];            // (cos, sin) of the q position
     float M[8], L[8];
     int last;
     unsigned long long bar[kMW][kMaxStages];  // one mbarrier per warp and stage
@@ -206,23 +210,42 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             }
         }
     };
-    // fill the ring before anything else so that the copies fly during the set-up below
-    for (int st = 0; st < n_stages; st++)
-        if (warp + st * kMW < n_tiles) issue_tile(warp + st * kMW, st);
-
-    // ---- q: rope, Givens rotation, scale, split into f16 hi/lo (scratch: the table's region) --
+    // ---- set-up that touches only constant tables comes first: with programmatic dependent launch
+    // it overlaps the tail of the previous kernel in the stream.  Everything a previous kernel may
+    // have written (q, the newest cache row, the split-K scratch) is read after the wait below.
     {
-        float *sq = reinterpret_cast<float *>(lut_ptr);  // [NREP][256]
-        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * kHd;
-        for (int i = tid; i < NREP * kHd; i += kMT) sq[i] = q[i];
-        __syncthreads();
+        for (int i = tid; i < kHd; i += kMT) o.givens[i] = a.givens[i];
         if (!a.no_rope) {
             const int half = a.n_rot >> 1;
             const float2 *cs = a.rope + (size_t)meta.q_pos[s] * half;
+            for (int i = tid; i < half; i += kMT) o.rope_row[i] = cs[i];
+        }
+        const float c_lo = a.book[lane & 15] * lut_alpha;  // lanes 0..15 hold the 16 scaled centroids
+        // the lookup table: entry e -> half2(alpha*c[e & 15], alpha*c[e >> 4]), one copy per lane
+        for (int e = warp; e < 256; e += kMW) {
+            const float lo = __shfl_sync(0xffffffffu, c_lo, e & 15), hi = __shfl_sync(0xffffffffu, c_lo, e >> 4);
+            const __half2 h = __floats2half2_rn(lo, hi);
+            *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + lane * 4) = h;
+        }
+    }
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // fill the ring now so that the copies fly during the rest of the set-up
+    for (int st = 0; st < n_stages; st++)
+        if (warp + st * kMW < n_tiles) issue_tile(warp + st * kMW, st);
+
+    // ---- q: rope, Givens rotation, scale, split into f16 hi/lo (scratch: the first stage-free
+    // bytes of the bookkeeping block, since the table's region is already live) ---------------
+    {
+        float *sq = o.sq;  // [NREP][256]
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * kHd;
+        for (int i = tid; i < NREP * kHd; i += kMT) sq[i] = q[i];
+        __syncthreads();  // also: givens / rope row / table are complete
+        if (!a.no_rope) {
+            const int half = a.n_rot >> 1;
             for (int i = tid; i < NREP * half; i += kMT) {
                 const int r = i / half, j = i - r * half;
                 float x0 = sq[r * kHd + j], x1 = sq[r * kHd + j + half];
-                rope_pair(x0, x1, cs[j]);
+                rope_pair(x0, x1, o.rope_row[j]);
                 sq[r * kHd + j] = x0;
                 sq[r * kHd + j + half] = x1;
             }
@@ -234,7 +257,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             const int r = i / (kHd / 2), pr = i - r * (kHd / 2);
             float o0 = 0.f, o1 = 0.f;
             if (r < NREP) {
-                givens_fwd(sq[r * kHd + 2 * pr], sq[r * kHd + 2 * pr + 1], a.givens[2 * pr], a.givens[2 * pr + 1], o0, o1);
+                givens_fwd(sq[r * kHd + 2 * pr], sq[r * kHd + 2 * pr + 1], o.givens[2 * pr], o.givens[2 * pr + 1], o0, o1);
                 o0 *= qscale;
                 o1 *= qscale;
             }
@@ -246,38 +269,23 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         }
         __syncthreads();
     }
-    // ---- the lookup table: entry e -> half2(alpha*c[e & 15], alpha*c[e >> 4]), one copy per lane
-    {
-        const float c_lo = a.book[lane & 15] * lut_alpha;  // lanes 0..15 hold the 16 scaled centroids
-        for (int e = warp; e < 256; e += kMW) {
-            const float lo = __shfl_sync(0xffffffffu, c_lo, e & 15), hi = __shfl_sync(0xffffffffu, c_lo, e >> 4);
-            const __half2 h = __floats2half2_rn(lo, hi);
-            *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + lane * 4) = h;
-        }
-        __syncthreads();
-    }
 
     // ---- q fragments: k-step ks = c*8 + w*2 + bp covers coordinates (2t+c)*32 + w*8 + bp*4 + 0..3
-    uint32_t qh[16][2];
-#pragma unroll
-    for (int ks = 0; ks < 16; ks++) {
-        const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
-        const int d0 = (2 * t + c) * 32 + w * 8 + bp * 4;
-        const uint2 v = *reinterpret_cast<const uint2 *>(&o.q_hi[g][d0]);
-        qh[ks][0] = v.x;
-        qh[ks][1] = v.y;
-    }
-    uint32_t ql[QSPLIT ? 16 : 1][2];
-    if (QSPLIT) {
+    if (warp == 0) {  // one warp lays the fragments out (every warp has the same (g, t) view)
 #pragma unroll
         for (int ks = 0; ks < 16; ks++) {
             const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
             const int d0 = (2 * t + c) * 32 + w * 8 + bp * 4;
-            const uint2 v = *reinterpret_cast<const uint2 *>(&o.q_lo[g][d0]);
-            ql[QSPLIT ? ks : 0][0] = v.x;
-            ql[QSPLIT ? ks : 0][1] = v.y;
+            o.q_hi_frag[ks][lane] = *reinterpret_cast<const uint2 *>(&o.q_hi[g][d0]);
+            o.q_lo_frag[ks][lane] = *reinterpret_cast<const uint2 *>(&o.q_lo[g][d0]);
         }
     }
+    __syncthreads();
+    const uint32_t qh_addr = other_addr + (uint32_t)offsetof(Other, q_hi_frag) + (uint32_t)lane * 8u;
+    const uint32_t ql_addr = other_addr + (uint32_t)offsetof(Other, q_lo_frag) + (uint32_t)lane * 8u;
+    auto q_frag = [&](uint32_t addr0, int ks, uint32_t &x, uint32_t &y) {
+        asm("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(x), "=r"(y) : "r"(addr0 + (uint32_t)ks * 256u));
+    };
 
     float acc[16][4];
 #pragma unroll
@@ -314,14 +322,24 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                 {
                     const uint32_t a0 = lut<0>(xg[w], lane_base), a1 = lut<0>(xh[w], lane_base);
                     const uint32_t a2 = lut<1>(xg[w], lane_base), a3 = lut<1>(xh[w], lane_base);
-                    mma16816(c ? sb : sa, a0, a1, a2, a3, qh[ks][0], qh[ks][1]);
-                    if (QSPLIT) mma16816(c ? sd : sc2, a0, a1, a2, a3, ql[QSPLIT ? ks : 0][0], ql[QSPLIT ? ks : 0][1]);
+                    uint32_t qx, qy;
+                    q_frag(qh_addr, ks, qx, qy);
+                    mma16816(c ? sb : sa, a0, a1, a2, a3, qx, qy);
+                    if (QSPLIT) {
+                        q_frag(ql_addr, ks, qx, qy);
+                        mma16816(c ? sd : sc2, a0, a1, a2, a3, qx, qy);
+                    }
                 }
                 {
                     const uint32_t a0 = lut<2>(xg[w], lane_base), a1 = lut<2>(xh[w], lane_base);
                     const uint32_t a2 = lut<3>(xg[w], lane_base), a3 = lut<3>(xh[w], lane_base);
-                    mma16816(c ? sd : sc2, a0, a1, a2, a3, qh[ks + 1][0], qh[ks + 1][1]);
-                    if (QSPLIT) mma16816(c ? sb : sa, a0, a1, a2, a3, ql[QSPLIT ? ks + 1 : 0][0], ql[QSPLIT ? ks + 1 : 0][1]);
+                    uint32_t qx, qy;
+                    q_frag(qh_addr, ks + 1, qx, qy);
+                    mma16816(c ? sd : sc2, a0, a1, a2, a3, qx, qy);
+                    if (QSPLIT) {
+                        q_frag(ql_addr, ks + 1, qx, qy);
+                        mma16816(c ? sb : sa, a0, a1, a2, a3, qx, qy);
+                    }
                 }
             }
         }
@@ -402,6 +420,10 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         }
     }
 
+    // The scan is over: a dependent kernel (launched with programmatic serialization) may start
+    // its own constant-table set-up on the SMs this kernel frees while its last CTAs merge.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+
     // ---- merge the warps ---------------------------------------------------------------------
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -425,45 +447,49 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         o.L[tid] = Ls;
     }
     __syncthreads();
-    float *area = reinterpret_cast<float *>(lut_ptr);  // [kMW][NREP][kHeadStride], reuses the table
-    {
-        const float unscale = 1.0f / (kWScale * lut_alpha);
-        const float f0 = (M0 > -CUDART_INF_F) ? exp2f(M0 - o.M[2 * t]) * unscale : 0.f;
-        const float f1 = (M1 > -CUDART_INF_F) ? exp2f(M1 - o.M[2 * t + 1]) * unscale : 0.f;
-        float *w0 = area + ((size_t)warp * NREP + 2 * t) * kHeadStride + g * 33;
-        float *w1 = w0 + kHeadStride;
-#pragma unroll
-        for (int j = 0; j < 16; j++) {
-            if (2 * t < NREP) {
-                w0[2 * j] = acc[j][0] * f0;
-                w0[2 * j + 1] = acc[j][2] * f0;
-            }
-            if (2 * t + 1 < NREP) {
-                w1[2 * j] = acc[j][1] * f1;
-                w1[2 * j + 1] = acc[j][3] * f1;
-            }
-        }
-    }
-    __syncthreads();
+    float *area = reinterpret_cast<float *>(lut_ptr);  // [kMergeRound][NREP][kHeadStride], reuses the table
     float sums[NREP];
-    {
-        const int d = tid, idx = d + (d >> 5);  // coordinate d sits at g*33 + (d & 31), g = d >> 5
 #pragma unroll
-        for (int r = 0; r < NREP; r++) {
-            float sum = 0.f;
+    for (int r = 0; r < NREP; r++) sums[r] = 0.f;
+    constexpr int kMergeRound = 6;  // warps whose accumulators fit the table's 64 KiB together
+    for (int r0 = 0; r0 < kMW; r0 += kMergeRound) {
+        if (warp >= r0 && warp < r0 + kMergeRound) {
+            const float unscale = 1.0f / (kWScale * lut_alpha);
+            const float f0 = (M0 > -CUDART_INF_F) ? exp2f(M0 - o.M[2 * t]) * unscale : 0.f;
+            const float f1 = (M1 > -CUDART_INF_F) ? exp2f(M1 - o.M[2 * t + 1]) * unscale : 0.f;
+            float *w0 = area + ((size_t)(warp - r0) * NREP + 2 * t) * kHeadStride + g * 33;
+            float *w1 = w0 + kHeadStride;
 #pragma unroll
-            for (int w = 0; w < kMW; w++) sum += area[((size_t)w * NREP + r) * kHeadStride + idx];
-            sums[r] = sum;
+            for (int j = 0; j < 16; j++) {
+                if (2 * t < NREP) {
+                    w0[2 * j] = acc[j][0] * f0;
+                    w0[2 * j + 1] = acc[j][2] * f0;
+                }
+                if (2 * t + 1 < NREP) {
+                    w1[2 * j] = acc[j][1] * f1;
+                    w1[2 * j + 1] = acc[j][3] * f1;
+                }
+            }
         }
-    }
-    __syncthreads();
-    float *s_acc = area;  // [NREP][256]
+        __syncthreads();
+        if (tid < kHd) {
+            const int d = tid, idx = d + (d >> 5);  // coordinate d sits at g*33 + (d & 31), g = d >> 5
 #pragma unroll
-    for (int r = 0; r < NREP; r++) s_acc[r * kHd + tid] = sums[r];
+            for (int r = 0; r < NREP; r++)
+#pragma unroll
+                for (int w = 0; w < kMergeRound; w++)
+                    if (r0 + w < kMW) sums[r] += area[((size_t)w * NREP + r) * kHeadStride + idx];
+        }
+        __syncthreads();
+    }
+    float *s_acc = area;  // [NREP][256]
+    if (tid < kHd)
+#pragma unroll
+        for (int r = 0; r < NREP; r++) s_acc[r * kHd + tid] = sums[r];
     __syncthreads();
 
     const int first_item = meta.item_start[s] + kv * n_chunks;
-    finish_item<NREP>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, true);
+    finish_item<NREP>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, true, o.givens);
 }
 
 template <int NREP, bool QSPLIT>
@@ -486,9 +512,19 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
     }
     const size_t smem = smem_for[dev];
     if (!a.h_tmap_k || !a.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "decode (mma): the cache has no tensor maps");
-    decode_p4_mma_kernel<NREP, QSPLIT><<<m.n_items, kMT, smem, ctx->stream>>>(
-        a, m, alpha, (uint32_t)smem, ctx->d_err, *static_cast<const CUtensorMap *>(a.h_tmap_k),
-        *static_cast<const CUtensorMap *>(a.h_tmap_v));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)m.n_items);
+    cfg.blockDim = dim3(kMT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see griddepcontrol.* in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BK_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_p4_mma_kernel<NREP, QSPLIT>, a, m, alpha, (uint32_t)smem, ctx->d_err,
+                                    *static_cast<const CUtensorMap *>(a.h_tmap_k),
+                                    *static_cast<const CUtensorMap *>(a.h_tmap_v)));
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     return BK_OK;
