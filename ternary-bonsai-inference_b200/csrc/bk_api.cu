@@ -660,7 +660,11 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
         total += list[i].np;
     }
     const int64_t gran = use_mma ? 128 : 64;
-    int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * (use_mma ? 1 : 4) / n_kv);
+    // A launch that already has at least half as many (sequence, kv head) pairs as SMs cannot be
+    // one balanced wave; it is cut into about four waves of equal-sized items instead and the
+    // hardware's in-order CTA dispatch evens out the ragged lengths.
+    const bool many = use_mma && (int64_t)nb * n_kv * 2 > ctx->n_sms;
+    int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * ((use_mma && !many) ? 1 : 4) / n_kv);
     target_items = std::min<int64_t>(target_items, std::max<int64_t>(1, max_items / n_kv));
     int64_t L = (total + target_items - 1) / target_items;
     L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
