@@ -285,6 +285,7 @@ def run_other_workload(args):
         out = torch.zeros((NH, HD), dtype=torch.float32, device=dev)
         gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
         pos_now = [n_total - total_steps]
+        lib_stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
 
         def step(_s):
             for il in range(N_LAYERS):
@@ -294,9 +295,8 @@ def run_other_workload(args):
                     cache.decode_device(il, d_q.offset(il * NH * HD * 4), out.data_ptr(), q_pos=[pos_now[0]])
                 else:
                     cache.decode_device(il, d_q.offset(il * NH * HD * 4), part.data_ptr(), q_pos=[pos_now[0]], partial=True)
-                    ctx.synchronize()                       # library stream -> NCCL (torch stream)
-                    dist.all_gather_into_tensor(gathered.view(-1), part.view(-1))
-                    torch.cuda.current_stream().synchronize()
+                    with torch.cuda.stream(lib_stream):     # NCCL orders itself against the library's stream:
+                        dist.all_gather_into_tensor(gathered.view(-1), part.view(-1))   # no host sync per layer
                     ctx.check(ctx.lib.bk_lse_merge(ctx.h, world, NH, HD, gathered.data_ptr(), out.data_ptr()))
             pos_now[0] += 1
         step_bytes = N_LAYERS * (attn_bytes(mode, n_total) + append_bytes(mode))
