@@ -439,11 +439,13 @@ def main():
     q_stride, kv_stride = NH * HD * 4, NKV * HD * 4
 
     def device_step(s, events=None):
+        # the reference's unit of work: one attention step per layer (append at pos, attend over pos+1)
+        pos = cache.n_pos(0)
         for il in range(N_LAYERS):
-            cache.append_device(il, d_k.offset(s * kv_stride), d_v.offset(s * kv_stride), n_tokens=1)
             if events is not None:
                 events[il][0].record()
-            cache.decode_device(il, d_q.offset((s * N_LAYERS + il) * q_stride), d_out.offset(il * q_stride))
+            cache.step_device(il, d_q.offset((s * N_LAYERS + il) * q_stride), d_k.offset(s * kv_stride),
+                              d_v.offset(s * kv_stride), d_out.offset(il * q_stride), pos)
             if events is not None:
                 events[il][1].record()
 
@@ -537,7 +539,8 @@ def main():
                 "h2d_bytes_per_step": N_LAYERS * (NH + 2 * NKV) * HD * 4, "d2h_bytes_per_step": N_LAYERS * NH * HD * 4,
                 "api": "bk_attn_step_host per layer (host q/k/v in, host out; blocks per layer like the reference)",
                 "out_checksum": checksum},
-        "roofline": {"bound": "hbm", "kernel": "decode_kernel (split-K GQA decode attention)",
+        "roofline": {"bound": "hbm", "kernel": "decode_p4_mma_kernel (split-K GQA decode attention over the 4-bit cache, "
+                               "with the one-token append fused in)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "traffic": None,
                      "algorithmic_bytes_per_launch": alg, "avg_launch_ms": dec_ms_avg,

@@ -623,6 +623,11 @@ void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out
     a.h_tmap_v = c->has_tmaps ? c->tmap_v : nullptr;
     a.layer_pos0 = layer * c->cfg.n_seqs * c->cfg.n_ctx;
     a.n_ctx = c->cfg.n_ctx;
+    a.new_k = a.new_v = nullptr;
+    a.k_rows_w = c->k_rows(layer, 0);
+    a.v_rows_w = c->v_rows(layer, 0);
+    a.k_norms_w = c->k_norms(layer, 0);
+    a.v_norms_w = c->v_norms(layer, 0);
     *out = a;
 }
 
@@ -764,9 +769,29 @@ bk_status bk_attn_step(bk_cache *c, int32_t layer, int32_t seq, int32_t pos, con
         return fail(ctx, BK_ERR_INVALID,
                     "bk_attn_step: pos " + std::to_string(pos) + " is not the next row (" +
                         std::to_string(c->n_pos[c->slab(layer, seq)]) + ")");
+    const int32_t np = pos + 1, qp = pos;
+    // Long 4-bit caches: one launch does both halves of the step (the CTA that scans the last
+    // chunk of each kv head first ropes, quantizes and stores that head's new rows).
+    {
+        DecodeArgs a;
+        fill_decode_args(c, layer, 0, &a);
+        if (decode_entry_uses_mma(ctx, a, np)) {
+            if (!q_dev || !k_dev || !v_dev || !out_dev) return fail(ctx, BK_ERR_INVALID, "bk_attn_step: null argument");
+            if (pos >= c->rope->n_pos) return fail(ctx, BK_ERR_RANGE, "bk_attn_step: position beyond the rope table");
+            bk_status st = bind(ctx);
+            if (st != BK_OK) return st;
+            a.q = q_dev;
+            a.out = out_dev;
+            a.new_k = k_dev;
+            a.new_v = v_dev;
+            const DecodeEntry e{0, seq, np, qp};
+            st = launch_decode_group(ctx, a, &e, 1, true, kMaxItems);
+            if (st == BK_OK) c->n_pos[c->slab(layer, seq)] = np;
+            return st;
+        }
+    }
     bk_status st = bk_append(c, layer, seq, pos, 1, k_dev, v_dev);
     if (st != BK_OK) return st;
-    const int32_t np = pos + 1, qp = pos;
     return decode_impl(c, layer, 1, &seq, &np, &qp, q_dev, out_dev, 0, "bk_attn_step");
 }
 

@@ -44,7 +44,7 @@ constexpr int kMW = 12;                 // warps per CTA
 constexpr int kMT = kMW * 32;
 constexpr int kTile = 16;               // positions per warp tile (the MMA's M)
 constexpr uint32_t kLutBytes = 65536;   // 256 entries x 256 B (128 B used: one word per lane)
-constexpr uint32_t kOtherBytes = 28672; // q halves and fragments + merge bookkeeping (multiple of 1 KiB)
+constexpr uint32_t kOtherBytes = 30720; // q halves and fragments + merge bookkeeping (multiple of 1 KiB)
 constexpr int kHeadStride = 276;        // floats per head in the warp-merge area (bank-conflict free)
 constexpr float kWScale = 16384.0f;     // 2^14: V weights are stored as f16 in (0, 2^14]
 constexpr int kRowBytes = 128;          // 256 coordinates x 4 bit
@@ -60,6 +60,8 @@ struct Other {                          // lives outside the lookup table
     uint2 q_hi_frag[16][32], q_lo_frag[16][32];  // q as B fragments: [k-step][lane], 8-byte conflict-free reads
     float m_w[kMW][8], l_w[kMW][8];
     float sq[8 * kHd];                   // q of the group while it is roped and rotated
+    float new_row[2][kHd];               // the newest token's k and v of this kv head (fused append)
+    float book[16];                      // unscaled centroids (fused append)
     float givens[kHd];                   // (cos, sin) pairs, fetched once (the epilogue needs them again)
     float2 rope_row[kHd / 2];            // (cos, sin) of the q position
     float M[8], L[8];
@@ -229,6 +231,51 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         }
     }
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // ---- fused append: the CTA that scans the last chunk of this kv head stores the head's new K
+    // and V rows first, exactly as the append kernel would (src/forward.rs:259-285; the rope row
+    // of the new token is the q position's).  Its own tile copies come after, so they see the row.
+    if (a.new_k != nullptr && chunk == n_chunks - 1) {
+        if (tid < 16) o.book[tid] = a.book[tid];
+        if (warp < 2) {
+            const float *src = (warp == 0 ? a.new_k : a.new_v) + ((size_t)meta.slot[s] * a.n_kv + kv) * kHd;
+            float *sx = o.new_row[warp];
+            reinterpret_cast<float4 *>(sx)[lane] = reinterpret_cast<const float4 *>(src)[lane];
+            reinterpret_cast<float4 *>(sx)[lane + 32] = reinterpret_cast<const float4 *>(src)[lane + 32];
+        }
+        __syncthreads();  // new rows, centroids, Givens table and rope row are in shared memory
+        if (warp < 2) {
+            float *sx = o.new_row[warp];
+            if (warp == 0 && !a.no_rope) {
+                const int half = a.n_rot >> 1;
+                for (int j = lane; j < half; j += 32) {
+                    float x0 = sx[j], x1 = sx[j + half];
+                    rope_pair(x0, x1, o.rope_row[j]);
+                    sx[j] = x0;
+                    sx[j + half] = x1;
+                }
+                __syncwarp();
+            }
+            float n = 0.f;
+            if (lane == 0) n = serial_norm(sx, kHd);
+            n = __shfl_sync(0xffffffffu, n, 0);
+            const float inv = (n > 1e-12f) ? __fdiv_rn(1.0f, n) : 0.0f;
+            uint64_t packed = 0;
+#pragma unroll
+            for (int pr = 0; pr < 4; pr++) {
+                const int i = lane * 4 + pr;  // pair index: coordinates 2i, 2i+1
+                float r0, r1;
+                givens_fwd(__fmul_rn(sx[2 * i], inv), __fmul_rn(sx[2 * i + 1], inv), o.givens[2 * i], o.givens[2 * i + 1], r0, r1);
+                packed |= (uint64_t)nearest_centroid(r0, o.book, 16) << (4 * (2 * pr));
+                packed |= (uint64_t)nearest_centroid(r1, o.book, 16) << (4 * (2 * pr + 1));
+            }
+            const size_t row = seq_rows + (size_t)(n_pos - 1) * a.n_kv + kv;
+            store_group8<4>((warp == 0 ? a.k_rows_w : a.v_rows_w) + row * kRowBytes, lane, packed);
+            if (lane == 0) (warp == 0 ? a.k_norms_w : a.v_norms_w)[row] = n;
+            __threadfence();
+            asm volatile("fence.proxy.async;\n" ::: "memory");  // generic-proxy stores before the TMA reads below
+        }
+        __syncthreads();
+    }
     // fill the ring now so that the copies fly during the rest of the set-up
     for (int st = 0; st < n_stages; st++)
         if (warp + st * kMW < n_tiles) issue_tile(warp + st * kMW, st);

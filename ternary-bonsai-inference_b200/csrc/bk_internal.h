@@ -168,6 +168,11 @@ struct DecodeArgs {
     // sits in them: position index = layer_pos0 + seq * n_ctx + pos
     const void *h_tmap_k, *h_tmap_v;
     int layer_pos0, n_ctx;
+    // tensor-core path only: when set, the launch also stores the newest token (the fused form of
+    // append + attend): k/v of that token, [n_kv][hd]; its row is n_pos - 1, its rope position q_pos
+    const float *new_k, *new_v;
+    uint8_t *k_rows_w, *v_rows_w;   // writable aliases of k_rows / v_rows
+    float *k_norms_w, *v_norms_w;
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
 

@@ -138,6 +138,10 @@ class AttnCache:
                                                       va.ctypes.data, out.ctypes.data))
         return out
 
+    def step_device(self, il, q_ptr, k_ptr, v_ptr, out_ptr, pos, seq=0):
+        """The attention step on device pointers (asynchronous): append at `pos`, attend over pos+1."""
+        self.ctx.check(self.ctx.lib.bk_attn_step(self.h, il, seq, pos, q_ptr, k_ptr, v_ptr, out_ptr))
+
     # -- dump_kv (src/gdev.rs:1433-1445) ---------------------------------------------
     def dump_kv(self, il, n_pos=None, seq=0, pos0=0):
         """Rows [pos0, pos0+n_pos) as the reference's CPU cache lays them out."""

@@ -480,3 +480,25 @@ def test_planar4_tensor_core_path_other_group_sizes(bk, gpu_ctx, oracle):
         got = cache.attend(0, q)[0]
         assert_close(got, want, f"{n_head}/{n_kv}")
         cache.close()
+
+
+def test_fused_step_on_long_planar4_cache(bk, gpu_ctx, oracle):
+    """On a long 4-bit cache the attention step is one launch (append fused into the decode):
+    the rows it stores and its outputs must match the oracle step by step."""
+    rng = np.random.default_rng(41)
+    n0, steps = 2600, 12
+    k, v = synth_kv(rng, n0 + steps)
+    q = rng.standard_normal((steps, NH, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode("planar4"), n_layers=1, n_ctx=n0 + steps)
+    ref = oracle.cache(MODE_PLANAR, 4, True)
+    cache.append(0, k[:n0], v[:n0])
+    for p in range(n0):
+        ref.append(0, k[p], v[p], p)
+    for t in range(steps):
+        launches = gpu_ctx.launch_count
+        got = bk.full_attention_step(cache, 0, q[t], k[n0 + t], v[n0 + t], n0 + t)
+        assert gpu_ctx.launch_count - launches == 1
+        want = ref.step(0, q[t], k[n0 + t], v[n0 + t], n0 + t, threads=8)
+        assert_close(got, want, f"step {t}")
+    compare_dumps(cache.dump_kv(0, pos0=n0 - 3), {key: val[n0 - 3:] for key, val in ref.dump(0).items()})
+    cache.close()
