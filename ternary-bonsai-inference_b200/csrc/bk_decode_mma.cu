@@ -102,6 +102,18 @@ __device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
     return v;
 }
 
+// Single-instruction exp2 / log2 (2 ulp): the library versions add range fix-ups that this loop
+// does not need (arguments are <= 0 for exp2 up to the 2^14 weight scale, norms are clamped).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_log2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -190,16 +202,26 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     // end of the chunk are whatever follows in the cache (or zeros past its end); their weights
     // are forced to zero below.
     const int gpos0 = a.layer_pos0 + meta.seq_id[s] * a.n_ctx + p0;  // position index in the tensor map
+    uint32_t st_base[kMaxStages];  // this warp's stage addresses
+#pragma unroll
+    for (int i = 0; i < kMaxStages; i++) st_base[i] = stage_addr(i < n_stages ? i : 0);
+    auto stage_of = [&](int st) -> uint32_t {
+        uint32_t r = st_base[0];
+#pragma unroll
+        for (int i = 1; i < kMaxStages; i++) r = (st == i) ? st_base[i] : r;
+        return r;
+    };
+    const uint32_t nb = (uint32_t)(kTile * 4 * a.n_kv);  // norms of 16 positions, every kv head
+    const float *kn_src = a.k_norms + seq_rows + (size_t)p0 * a.n_kv, *vn_src = a.v_norms + seq_rows + (size_t)p0 * a.n_kv;
     auto issue_tile = [&](int tile, int st) {
         if (lane == 0) {
-            const uint32_t bar = bar0 + (uint32_t)st * 8u, dst = stage_addr(st);
-            const uint32_t nb = (uint32_t)(kTile * 4 * a.n_kv);  // norms of 16 positions, every kv head
+            const uint32_t bar = bar0 + (uint32_t)st * 8u, dst = stage_of(st);
             mbar_expect_tx(bar, 2 * kTileBytes + 2 * nb);
             tma_tile(dst, &tm_k, kv, gpos0 + tile * kTile, bar);
             tma_tile(dst + kTileBytes, &tm_v, kv, gpos0 + tile * kTile, bar);
-            const size_t nrow = seq_rows + (size_t)(p0 + tile * kTile) * a.n_kv;
-            tma_bulk(dst + 2 * kTileBytes, a.k_norms + nrow, nb, bar);
-            tma_bulk(dst + 2 * kTileBytes + kNormBytes, a.v_norms + nrow, nb, bar);
+            const uint32_t noff = (uint32_t)(tile * kTile * a.n_kv);
+            tma_bulk(dst + 2 * kTileBytes, kn_src + noff, nb, bar);
+            tma_bulk(dst + 2 * kTileBytes + kNormBytes, vn_src + noff, nb, bar);
         }
     };
     auto wait_tile = [&](int st, uint32_t parity) {
@@ -397,7 +419,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         const int pb = p0 + tile * kTile;
         const bool ok0 = pb + g < p1, ok1 = pb + g + 8 < p1;
         const float s00 = sc[0] * kn[0], s01 = sc[1] * kn[0], s10 = sc[2] * kn[1], s11 = sc[3] * kn[1];
-        const float lv0 = log2f(fmaxf(vn[0], 1e-37f)), lv1 = log2f(fmaxf(vn[1], 1e-37f));
+        const float lv0 = fast_log2(fmaxf(vn[0], 1e-30f)), lv1 = fast_log2(fmaxf(vn[1], 1e-30f));
         const float t00 = ok0 ? s00 + lv0 : -CUDART_INF_F, t01 = ok0 ? s01 + lv0 : -CUDART_INF_F;
         const float t10 = ok1 ? s10 + lv1 : -CUDART_INF_F, t11 = ok1 ? s11 + lv1 : -CUDART_INF_F;
         float mx0 = fmaxf(t00, t10), mx1 = fmaxf(t01, t11);
@@ -409,7 +431,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         const bool grow = (mx0 > M0) || (mx1 > M1);
         if (__any_sync(0xffffffffu, grow)) {
             const float n0 = fmaxf(M0, mx0), n1 = fmaxf(M1, mx1);
-            const float c0 = exp2f(M0 - n0), c1 = exp2f(M1 - n1);  // 0 on the first tile
+            const float c0 = fast_exp2(M0 - n0), c1 = fast_exp2(M1 - n1);  // 0 on the first tile
             l0 *= c0;
             l1 *= c1;
 #pragma unroll
@@ -422,10 +444,10 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             M0 = n0;
             M1 = n1;
         }
-        const float w00 = exp2f(t00 - M0) * kWScale, w01 = exp2f(t01 - M1) * kWScale;
-        const float w10 = exp2f(t10 - M0) * kWScale, w11 = exp2f(t11 - M1) * kWScale;
-        l0 += (ok0 ? exp2f(s00 - M0) : 0.f) + (ok1 ? exp2f(s10 - M0) : 0.f);
-        l1 += (ok0 ? exp2f(s01 - M1) : 0.f) + (ok1 ? exp2f(s11 - M1) : 0.f);
+        const float w00 = fast_exp2(t00 - M0) * kWScale, w01 = fast_exp2(t01 - M1) * kWScale;
+        const float w10 = fast_exp2(t10 - M0) * kWScale, w11 = fast_exp2(t11 - M1) * kWScale;
+        l0 += (ok0 ? fast_exp2(s00 - M0) : 0.f) + (ok1 ? fast_exp2(s10 - M0) : 0.f);
+        l1 += (ok0 ? fast_exp2(s01 - M1) : 0.f) + (ok1 ? fast_exp2(s11 - M1) : 0.f);
         const __half2 pl = __floats2half2_rn(w00, w01), ph = __floats2half2_rn(w10, w11);
         const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
         const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
@@ -460,7 +482,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         uint32_t parity = 0;
         for (int tile = warp; tile < n_tiles; tile += kMW) {
             wait_tile(st, parity);
-            compute_tile(tile, stage_addr(st));
+            compute_tile(tile, stage_of(st));
             __syncwarp();  // every lane has read the stage: lane 0 may refill it
             if (tile + n_stages * kMW < n_tiles) issue_tile(tile + n_stages * kMW, st);
             if (++st == n_stages) { st = 0; parity ^= 1u; }
