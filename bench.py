@@ -542,7 +542,10 @@ def main():
         "roofline": {"bound": "hbm", "kernel": "decode_p4_mma_kernel (split-K GQA decode attention over the 4-bit cache, "
                                "with the one-token append fused in)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "peak_kind": f"of {peak_kind}",
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this
+                     # workload, from the ncu capture summarised in profiles/decode_p4_mma_ctx131072_ncu.md
+                     "traffic": 142.9e6 if (args.mode == "planar4" and args.ctx == 131072) else None,
                      "algorithmic_bytes_per_launch": alg, "avg_launch_ms": dec_ms_avg,
                      "frac_of_8TBs_nominal": achieved / 8000.0},
         "cpu_baseline": cpu, "clocks": clocks,
