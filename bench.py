@@ -286,6 +286,7 @@ def run_other_workload(args):
         gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
         pos_now = [n_total - total_steps]
         lib_stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+        split = par.ContextSplit(cache, dist, rank, world) if (world > 1 and args.exchange == "p2p") else None
 
         def step(_s):
             for il in range(N_LAYERS):
@@ -293,6 +294,8 @@ def run_other_workload(args):
                     cache.append_device(il, dk.ptr, dv.ptr, n_tokens=1, pos=pos_now[0])
                 if world == 1:
                     cache.decode_device(il, d_q.offset(il * NH * HD * 4), out.data_ptr(), q_pos=[pos_now[0]])
+                elif split is not None:
+                    split.attend_device(il, d_q.offset(il * NH * HD * 4), out.data_ptr(), q_pos=pos_now[0])
                 else:
                     cache.decode_device(il, d_q.offset(il * NH * HD * 4), part.data_ptr(), q_pos=[pos_now[0]], partial=True)
                     with torch.cuda.stream(lib_stream):     # NCCL orders itself against the library's stream:
@@ -302,7 +305,9 @@ def run_other_workload(args):
         step_bytes = N_LAYERS * (attn_bytes(mode, n_total) + append_bytes(mode))
         tokens_per_step, scaling = 1, "strong"
         cfg = {"workload": f"splitctx: 1 sequence, context {n_total}, {N_LAYERS} layers, {args.mode}; contiguous context "
-                           f"chunks over {world} GPU(s), per layer one all-gather of (acc, m, l) partials (NCCL) + LSE merge",
+                           f"chunks over {world} GPU(s); per layer the (acc, m, l) partials are exchanged "
+                           + ("through peer memory inside the merge kernel (bk_decode_attn_split)" if split is not None
+                              else "by one NCCL all-gather, then bk_lse_merge"),
                "l2": "%.2f GB of cache per step over all GPUs" % (step_bytes / 1e9)}
     else:  # appendsweep
         cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=4096 * 2)
@@ -381,6 +386,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunk", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=16, help="full-attention layers (16 = qwen35; fewer only to keep a profiler capture small)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="splitctx only: p2p = peer-memory exchange fused with the merge (bk_decode_attn_split); "
+                         "nccl = all-gather of the partials + bk_lse_merge")
     ap.add_argument("--workload", default="decode128k", choices=["decode128k", "batch64", "splitctx", "appendsweep"],
                     help="decode128k: the headline (default).  batch64: 64 sequences, contexts U[2048,16384], sharded "
                          "over the ranks.  splitctx: one 262144-token sequence, context chunks per rank, LSE merge.  "

@@ -200,6 +200,25 @@ BK_API bk_status bk_decode_attn_noalloc(bk_cache *cache, int32_t layer, int32_t 
 BK_API bk_status bk_lse_merge(bk_ctx *ctx, int32_t n_parts, int32_t n_rows, int32_t hd,
                               const float *parts_dev, float *out_dev);
 
+/* Context split with the exchange fused into the merge, over peer memory (NVLink): no reference
+ * counterpart.  Every rank creates a mailbox and hands its 64-byte IPC handle to the other
+ * ranks' processes (any transport); bk_mailbox_open_peers takes all `world` handles in rank order.
+ * bk_decode_attn_split then scans this rank's chunk (rows [0, n_pos) of its cache; q replicated on
+ * every rank, q_pos = the global position), stores its (acc, m, l) rows into every rank's mailbox
+ * with peer stores, waits - bounded; a time-out is reported by bk_synchronize - for the rows of all
+ * ranks carrying `seqno`, and writes the merged [n_head][hd] output on every rank.  Every rank
+ * must make the same sequence of calls with seqno = 1, 2, 3, ...  A rank whose chunk is empty
+ * calls with n_pos = 0. */
+typedef struct bk_mailbox bk_mailbox;
+#define BK_IPC_HANDLE_BYTES 64
+BK_API bk_status bk_mailbox_create(bk_ctx *ctx, int32_t world, int32_t rank, int32_t n_rows, int32_t hd,
+                                   bk_mailbox **out, void *ipc_handle_out);
+BK_API bk_status bk_mailbox_open_peers(bk_mailbox *mailbox, const void *handles);
+BK_API void bk_mailbox_destroy(bk_mailbox *mailbox);
+BK_API bk_status bk_decode_attn_split(bk_cache *cache, int32_t layer, int32_t seq, int32_t n_pos,
+                                      int32_t q_pos, const float *q_dev, float *out_dev,
+                                      bk_mailbox *mailbox, uint32_t seqno);
+
 /* The attention step with the reference's own shape (src/forward.rs:247-375,
  * src/gdev.rs:584-829): rope q and k at `pos`, store k/v at row `pos` (which
  * must equal n_pos), attend over pos+1 rows.  q [n_head][hd], k/v [n_kv][hd],

@@ -59,6 +59,10 @@ SIGNATURES = {
     "bk_decode_attn_partial": (C.c_int, [_vp, _i32, _i32, _pi32, _pi32, _pi32, _vp, _vp]),
     "bk_decode_attn_noalloc": (C.c_int, [_vp, _i32, _i32, _pi32, _pi32, _pi32, _vp, _vp]),
     "bk_lse_merge": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp]),
+    "bk_mailbox_create": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _pp, _vp]),
+    "bk_mailbox_open_peers": (C.c_int, [_vp, _vp]),
+    "bk_mailbox_destroy": (None, [_vp]),
+    "bk_decode_attn_split": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, C.c_uint32]),
     "bk_attn_step": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bk_attn_step_host": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bk_attn_oneshot_host": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),

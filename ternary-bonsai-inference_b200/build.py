@@ -29,6 +29,7 @@ SOURCES = {
     "bk_decode.cu": [],
     "bk_decode_mma.cu": [],
     "bk_noalloc.cu": [],
+    "bk_p2p.cu": [],
     "bk_host_tables.cpp": [],
 }
 HEADERS = ["bk_internal.h", "bk_device.cuh", "bk_decode_common.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]

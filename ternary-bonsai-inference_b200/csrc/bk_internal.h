@@ -21,6 +21,7 @@ constexpr int kMaxRep = 8;             // q heads per kv head the scratch is siz
 constexpr int kPartStride = kHd + 2;   // floats per partial result handed to callers: acc[hd], m, l
 constexpr int kScratchStride = kHd + 4; // floats per partial in the split-K scratch (16-byte aligned rows)
 constexpr int kMmaMinPos = 2048;       // shorter sequences take the generic f32 decode kernel
+constexpr int kMaxWorld = 8;            // ranks a context-split mailbox can connect
 constexpr int kDescSlots = 8;          // launches of bk_append_batch that may be in flight
 constexpr int kDescCap = 4096;         // tokens one bk_append_batch call may carry
 

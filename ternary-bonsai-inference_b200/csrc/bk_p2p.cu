@@ -1,0 +1,200 @@
+// Context split over the GPUs of one node: exchange of the per-chunk partial results through
+// peer memory, fused with their log-sum-exp merge.  No counterpart in the reference (it is
+// single-device); it is the exchange step of "one long sequence, context chunks per GPU".
+//
+// Every rank owns a mailbox (one cudaMalloc, shared with the other ranks' processes through CUDA
+// IPC): two parities x world slots of n_rows x (hd + 2) floats, and two parities x world x n_rows
+// arrival words.  bk_decode_attn_split scans the local chunk into (acc, m, l) rows and then
+// launches ONE kernel of n_rows CTAs: CTA h stores row h into slot [rank] of every rank's
+// mailbox with plain peer stores, publishes it with a system-scope release of the call's sequence
+// number, waits (bounded) until the arrival words of all ranks for row h carry that number, and
+// merges the world rows into out[h].  The transfer is 24.8 KB per rank and layer, so what
+// matters is latency: one launch, no host synchronisation, no collective-library call.
+//
+// The only cross-GPU dependency is between kernels on DIFFERENT GPUs; every wait gives up after
+// kSpinLimit polls and flags the error instead of hanging.  Slots alternate with the parity of
+// the sequence number, so a rank that runs ahead by one call never overwrites rows still being
+// merged.  No TMA and no multicast is used on peer memory.
+#include <cuda/atomic>
+#include <math_constants.h>
+
+#include "bk_internal.h"
+
+struct bk_mailbox {
+    bk_ctx *ctx = nullptr;
+    int world = 0, rank = 0, n_rows = 0, hd = 0;
+    size_t bytes = 0;
+    uint8_t *local = nullptr;           // this rank's mailbox
+    uint8_t *peer[bk::kMaxWorld] = {};  // every rank's mailbox as seen from here ([rank] == local)
+    bool opened[bk::kMaxWorld] = {};
+    float *part = nullptr;              // staging for the local partial rows
+    uint8_t **d_peer = nullptr;         // device copy of peer[]
+};
+
+namespace bk {
+
+namespace {
+
+constexpr int kSpinLimit = 1 << 20;  // polls of one arrival word before giving up (order of a second)
+
+__host__ __device__ inline size_t slot_floats(int n_rows, int hd) { return (size_t)n_rows * (hd + 2); }
+__host__ __device__ inline size_t data_bytes(int world, int n_rows, int hd) {
+    return 2 * (size_t)world * slot_floats(n_rows, hd) * sizeof(float);
+}
+__host__ __device__ inline size_t mailbox_bytes(int world, int n_rows, int hd) {
+    return data_bytes(world, n_rows, hd) + 2 * (size_t)world * n_rows * sizeof(unsigned);
+}
+
+__global__ void __launch_bounds__(256) exchange_merge_kernel(uint8_t *const *peer, int world, int rank, int n_rows,
+                                                             int hd, const float *part, unsigned seqno, float *out,
+                                                             int *err_flag) {
+    const int row = blockIdx.x, tid = threadIdx.x, stride = hd + 2;
+    const unsigned par = seqno & 1u;
+    const size_t slot = slot_floats(n_rows, hd);
+    // ---- send: this rank's row into slot [rank] of every mailbox (its own included) ----------
+    const float *src = part + (size_t)row * stride;
+    for (int r = 0; r < world; r++) {
+        float *dst = reinterpret_cast<float *>(peer[r]) + ((size_t)par * world + rank) * slot + (size_t)row * stride;
+        for (int i = tid; i < stride; i += blockDim.x) dst[i] = src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < world) {
+        unsigned *flag = reinterpret_cast<unsigned *>(peer[tid] + data_bytes(world, n_rows, hd)) +
+                         ((size_t)par * world + rank) * n_rows + row;
+        cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
+        f.store(seqno, cuda::memory_order_release);
+    }
+    // ---- wait for row `row` of every rank (bounded), then merge ------------------------------
+    __shared__ int s_ok;
+    if (tid == 0) s_ok = 1;
+    __syncthreads();
+    if (tid < world) {
+        unsigned *flag = reinterpret_cast<unsigned *>(peer[rank] + data_bytes(world, n_rows, hd)) +
+                         ((size_t)par * world + tid) * n_rows + row;
+        cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
+        int polls = 0;
+        while (f.load(cuda::memory_order_acquire) != seqno) {
+            if (++polls > kSpinLimit) {
+                s_ok = 0;
+                atomicExch(err_flag, 3);
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    const float *mine = reinterpret_cast<const float *>(peer[rank]) + (size_t)par * world * slot + (size_t)row * stride;
+    float M = -CUDART_INF_F;
+    for (int r = 0; r < world; r++) {
+        const volatile float *p = mine + (size_t)r * slot;
+        if (p[hd + 1] > 0.f) M = fmaxf(M, p[hd]);
+    }
+    float Ls = 0.f;
+    for (int r = 0; r < world; r++) {
+        const volatile float *p = mine + (size_t)r * slot;
+        if (p[hd + 1] > 0.f) Ls += p[hd + 1] * expf(p[hd] - M);
+    }
+    for (int d = tid; d < hd; d += blockDim.x) {
+        float sum = 0.f;
+        for (int r = 0; r < world; r++) {
+            const volatile float *p = mine + (size_t)r * slot;
+            if (p[hd + 1] > 0.f) sum = fmaf(p[d], expf(p[hd] - M), sum);
+        }
+        out[(size_t)row * hd + d] = (s_ok && Ls > 0.f) ? sum / Ls : 0.f;
+    }
+}
+
+}  // namespace
+
+}  // namespace bk
+
+using namespace bk;
+
+extern "C" {
+
+bk_status bk_mailbox_create(bk_ctx *ctx, int32_t world, int32_t rank, int32_t n_rows, int32_t hd, bk_mailbox **out,
+                            void *ipc_handle_out) {
+    if (!ctx || !out || !ipc_handle_out) return fail(ctx, BK_ERR_INVALID, "bk_mailbox_create: null argument");
+    *out = nullptr;
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || n_rows < 1 || hd < 1)
+        return fail(ctx, BK_ERR_INVALID, "bk_mailbox_create: bad world/rank/sizes (world <= 8)");
+    static_assert(sizeof(cudaIpcMemHandle_t) == BK_IPC_HANDLE_BYTES, "IPC handle size");
+    bk_status st = bind_device(ctx);
+    if (st != BK_OK) return st;
+    bk_mailbox *m = new (std::nothrow) bk_mailbox();
+    if (!m) return fail(ctx, BK_ERR_OOM, "bk_mailbox_create: host allocation failed");
+    m->ctx = ctx;
+    m->world = world;
+    m->rank = rank;
+    m->n_rows = n_rows;
+    m->hd = hd;
+    m->bytes = mailbox_bytes(world, n_rows, hd);
+    cudaError_t e = cudaMalloc(&m->local, m->bytes);
+    if (e == cudaSuccess) e = cudaMemset(m->local, 0, m->bytes);  // arrival words start at 0: sequence numbers start at 1
+    if (e == cudaSuccess) e = cudaMalloc(&m->part, slot_floats(n_rows, hd) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&m->d_peer, sizeof(uint8_t *) * kMaxWorld);
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(ipc_handle_out), m->local);
+    if (e != cudaSuccess) {
+        bk_mailbox_destroy(m);
+        return cuda_fail(ctx, e, "bk_mailbox_create");
+    }
+    m->peer[rank] = m->local;
+    e = cudaMemcpy(m->d_peer, m->peer, sizeof(uint8_t *) * kMaxWorld, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        bk_mailbox_destroy(m);
+        return cuda_fail(ctx, e, "bk_mailbox_create");
+    }
+    *out = m;
+    return BK_OK;
+}
+
+bk_status bk_mailbox_open_peers(bk_mailbox *m, const void *handles) {
+    if (!m || !handles) return fail(m ? m->ctx : nullptr, BK_ERR_INVALID, "bk_mailbox_open_peers: null argument");
+    bk_ctx *ctx = m->ctx;
+    bk_status st = bind_device(ctx);
+    if (st != BK_OK) return st;
+    const cudaIpcMemHandle_t *h = static_cast<const cudaIpcMemHandle_t *>(handles);
+    for (int r = 0; r < m->world; r++) {
+        if (r == m->rank || m->opened[r]) continue;
+        void *p = nullptr;
+        BK_CUDA(ctx, cudaIpcOpenMemHandle(&p, h[r], cudaIpcMemLazyEnablePeerAccess));
+        m->peer[r] = static_cast<uint8_t *>(p);
+        m->opened[r] = true;
+    }
+    BK_CUDA(ctx, cudaMemcpy(m->d_peer, m->peer, sizeof(uint8_t *) * kMaxWorld, cudaMemcpyHostToDevice));
+    return BK_OK;
+}
+
+void bk_mailbox_destroy(bk_mailbox *m) {
+    if (!m) return;
+    cudaSetDevice(m->ctx->device);
+    cudaStreamSynchronize(m->ctx->stream);
+    for (int r = 0; r < m->world; r++)
+        if (m->opened[r] && m->peer[r]) cudaIpcCloseMemHandle(m->peer[r]);
+    if (m->local) cudaFree(m->local);
+    if (m->part) cudaFree(m->part);
+    if (m->d_peer) cudaFree(m->d_peer);
+    delete m;
+}
+
+bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t n_pos, int32_t q_pos, const float *q_dev,
+                               float *out_dev, bk_mailbox *m, uint32_t seqno) {
+    if (!c || !m) return fail(c ? c->ctx : nullptr, BK_ERR_INVALID, "bk_decode_attn_split: null argument");
+    bk_ctx *ctx = c->ctx;
+    if (m->ctx != ctx) return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_split: mailbox belongs to another context");
+    if (m->n_rows != c->cfg.n_head || m->hd != c->cfg.hd)
+        return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_split: mailbox geometry does not match the cache");
+    if (seqno == 0) return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_split: sequence numbers start at 1");
+    for (int r = 0; r < m->world; r++)
+        if (!m->peer[r]) return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_split: peers are not opened");
+    bk_status st = bk_decode_attn_partial(c, layer, 1, &seq, &n_pos, &q_pos, q_dev, m->part);
+    if (st != BK_OK) return st;
+    exchange_merge_kernel<<<m->n_rows, 256, 0, ctx->stream>>>(m->d_peer, m->world, m->rank, m->n_rows, m->hd, m->part,
+                                                              seqno, out_dev, ctx->d_err);
+    ctx->launches++;
+    BK_CUDA(ctx, cudaGetLastError());
+    return BK_OK;
+}
+
+}  // extern "C"

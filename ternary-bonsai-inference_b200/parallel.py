@@ -72,3 +72,42 @@ def all_gather_partials(dist, part, world):
     dist.all_gather_into_tensor(out.view(-1), part.contiguous().view(-1)) if part.is_cuda else \
         dist.all_gather(list(out.unbind(0)), part.contiguous())
     return out
+
+
+class ContextSplit:
+    """One long sequence split into contiguous context chunks over the ranks, with the exchange of
+    the partial results fused into their merge over peer memory (bk_decode_attn_split) instead
+    of an all-gather.  `cache` holds this rank's chunk (created with rope_positions = the full
+    context).  Handles travel through torch.distributed's object all-gather (any backend)."""
+
+    def __init__(self, cache, dist, rank, world):
+        import ctypes as C
+        from . import _abi
+        self.cache, self.ctx, self.rank, self.world = cache, cache.ctx, rank, world
+        self.seqno = 0
+        handle = (C.c_ubyte * 64)()
+        mb = C.c_void_p()
+        self.ctx.check(self.ctx.lib.bk_mailbox_create(self.ctx.h, world, rank, cache.n_head, cache.hd, C.byref(mb), handle))
+        self.mb = mb
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, bytes(handle))
+        else:
+            handles[0] = bytes(handle)
+        blob = (C.c_ubyte * (64 * world)).from_buffer_copy(b"".join(handles))
+        self.ctx.check(self.ctx.lib.bk_mailbox_open_peers(self.mb, blob))
+        if world > 1:
+            dist.barrier()  # nobody sends before every mailbox is mapped everywhere
+
+    def attend_device(self, il, q_ptr, out_ptr, q_pos, n_pos=None, seq=0):
+        """Scan the local chunk, exchange, merge: every rank ends with the full output."""
+        if n_pos is None:
+            n_pos = self.cache.n_pos(il, seq)
+        self.seqno += 1
+        self.ctx.check(self.ctx.lib.bk_decode_attn_split(self.cache.h, il, seq, n_pos, q_pos, q_ptr, out_ptr,
+                                                         self.mb, self.seqno))
+
+    def close(self):
+        if getattr(self, "mb", None):
+            self.ctx.lib.bk_mailbox_destroy(self.mb)
+            self.mb = None
