@@ -66,7 +66,7 @@ def build(force=False, verbose=False):
     with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
         futs = [ex.submit(_compile, s, e, force, verbose) for s, e in SOURCES.items()]
         results = [f.result() for f in futs]
-    objs = [o for o, _ in results]
+    objs = [o for o, _ in results]  # (a compile error has raised above, before any stale link)
     if verbose:
         for _, log in results:
             sys.stderr.write(log)

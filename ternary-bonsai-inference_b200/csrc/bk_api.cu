@@ -184,6 +184,14 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
     for (int b = 1; b <= kMaxBits; b++) {
         host_codebook(kHd, b, ctx->h_codebooks + (b - 1) * kBookStride);
         ctx->lut_alpha[b] = best_lut_alpha(ctx->h_codebooks + (b - 1) * kBookStride, 1 << b);
+        // the binary-search nearest-centroid of the kernels relies on well separated centroids
+        const float *cb = ctx->h_codebooks + (b - 1) * kBookStride;
+        for (int i = 0; i + 1 < (1 << b); i++)
+            if (!(cb[i + 1] - cb[i] > 1e-5f)) {
+                fail(nullptr, BK_ERR_UNSUPPORTED, "codebook centroids are not separated by more than 1e-5");
+                bk_ctx_destroy(ctx);
+                return BK_ERR_UNSUPPORTED;
+            }
     }
     {
         const char *e1 = getenv("BONSAI_KV_GENERIC"), *e2 = getenv("BONSAI_KV_QSPLIT");

@@ -287,8 +287,8 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                 const int i = lane * 4 + pr;  // pair index: coordinates 2i, 2i+1
                 float r0, r1;
                 givens_fwd(__fmul_rn(sx[2 * i], inv), __fmul_rn(sx[2 * i + 1], inv), o.givens[2 * i], o.givens[2 * i + 1], r0, r1);
-                packed |= (uint64_t)nearest_centroid(r0, o.book, 16) << (4 * (2 * pr));
-                packed |= (uint64_t)nearest_centroid(r1, o.book, 16) << (4 * (2 * pr + 1));
+                packed |= (uint64_t)nearest_centroid_fast<4>(r0, o.book) << (4 * (2 * pr));
+                packed |= (uint64_t)nearest_centroid_fast<4>(r1, o.book) << (4 * (2 * pr + 1));
             }
             const size_t row = seq_rows + (size_t)(n_pos - 1) * a.n_kv + kv;
             store_group8<4>((warp == 0 ? a.k_rows_w : a.v_rows_w) + row * kRowBytes, lane, packed);

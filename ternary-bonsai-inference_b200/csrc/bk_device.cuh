@@ -72,6 +72,24 @@ __device__ __forceinline__ uint32_t nearest_centroid(float v, const float *book,
     return best;
 }
 
+// The same index as nearest_centroid() in BITS + 2 steps instead of 2^BITS.  f32 subtraction is
+// monotone, so along the ascending codebook |v - c_i| falls, then rises: the scan's answer is
+// the last centroid <= v or its right neighbour, the left one on a tie (strict '<').  A plateau
+// (equal rounded distances to two centroids on the same side) would need two centroids closer
+// than an ulp of v; the context checks at creation that every codebook's gaps are above 1e-5,
+// and rotated unit coordinates are below 2 in magnitude.  Non-finite v takes the scan.
+template <int BITS>
+__device__ __forceinline__ uint32_t nearest_centroid_fast(float v, const float *book) {
+    if (!(fabsf(v) < 4.0f)) return nearest_centroid(v, book, 1 << BITS);
+    int lo = 0;
+#pragma unroll
+    for (int step = 1 << (BITS - 1); step >= 1; step >>= 1)
+        if (book[lo + step] <= v) lo += step;
+    const int hi = min(lo + 1, (1 << BITS) - 1);
+    const float d0 = fabsf(__fsub_rn(v, book[lo])), d1 = fabsf(__fsub_rn(v, book[hi]));
+    return (uint32_t)((d1 < d0) ? hi : lo);
+}
+
 // src/kvquant.rs:398: sequential f32 sum of squares then sqrt; 256 dependent adds by design.
 __device__ __forceinline__ float serial_norm(const float *x, int n) {
     float acc = 0.0f;

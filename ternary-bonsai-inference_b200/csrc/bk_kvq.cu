@@ -36,8 +36,8 @@ __global__ void quantize_kernel(int n_vec, const float *x, const float *givens, 
         float r0, r1;
         givens_fwd(__fmul_rn(sx[warp][2 * i], inv), __fmul_rn(sx[warp][2 * i + 1], inv), givens[2 * i],
                    givens[2 * i + 1], r0, r1);
-        word |= (uint64_t)nearest_centroid(r0, sbook, 1 << BITS) << (BITS * (2 * pr));
-        word |= (uint64_t)nearest_centroid(r1, sbook, 1 << BITS) << (BITS * (2 * pr + 1));
+        word |= (uint64_t)nearest_centroid_fast<BITS>(r0, sbook) << (BITS * (2 * pr));
+        word |= (uint64_t)nearest_centroid_fast<BITS>(r1, sbook) << (BITS * (2 * pr + 1));
     }
     store_group8<BITS>(packed + (size_t)vec * 32 * BITS, lane, word);
 }

@@ -502,3 +502,29 @@ def test_fused_step_on_long_planar4_cache(bk, gpu_ctx, oracle):
         assert_close(got, want, f"step {t}")
     compare_dumps(cache.dump_kv(0, pos0=n0 - 3), {key: val[n0 - 3:] for key, val in ref.dump(0).items()})
     cache.close()
+
+
+@pytest.mark.parametrize("bits", range(1, 9))
+def test_nearest_centroid_search_equals_the_reference_scan(bk, gpu_ctx, oracle, bits):
+    """The kernels find the nearest centroid by binary search plus one neighbour check; the
+    reference scans all levels.  Both must pick the same index everywhere, in particular at the
+    centroids themselves, at the midpoints between neighbours and one ulp to either side.
+    Vectors are built so that their rotated unit coordinates land on those values."""
+    pq, opq = bk.PlanarQuant(HD, bits, gpu_ctx), oracle.pq(HD, bits)
+    cb = oracle.codebook(HD, bits).astype(np.float32)
+    mids = ((cb[:-1].astype(np.float64) + cb[1:]) / 2).astype(np.float32)
+    pts = np.concatenate([cb, mids, np.nextafter(mids, np.float32(1)), np.nextafter(mids, np.float32(-1)),
+                          np.nextafter(cb, np.float32(1)), np.nextafter(cb, np.float32(-1)),
+                          np.array([0.0, -0.0, 0.3, -0.3, 0.9, -0.9], np.float32)])
+    rng = np.random.default_rng(bits)
+    rows = []
+    for _ in range(24):
+        target = rng.choice(pts, HD).astype(np.float32)              # wanted rotated unit coordinates
+        x = opq.rotate_inv(target)[:HD]                               # vector whose rotation is about that
+        rows.append(x / max(np.linalg.norm(x), 1e-30))                # unit norm: quantize() scales by ~1
+    x = np.stack(rows).astype(np.float32)
+    packed, norms = pq.quantize(x)
+    for r in range(x.shape[0]):
+        p_ref, n_ref = opq.quantize(x[r])
+        assert np.array_equal(packed[r], p_ref), (bits, r)
+        assert bits_of(norms[r]) == bits_of(n_ref)
