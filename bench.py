@@ -375,6 +375,16 @@ def run_other_workload(args):
 
 # ---------------------------------------------------------------------------------------------
 
+def decode_kernel_name(mode_tag, ctx):
+    """The kernel a decode launch of this workload runs (the library picks it by mode and length)."""
+    if ctx >= 2048 and mode_tag == "planar4":
+        return ("decode_p4_mma_kernel (split-K GQA decode attention over the 4-bit cache, with the one-token "
+                "append fused in)")
+    if ctx >= 2048 and mode_tag == "f16":
+        return "decode_f16_mma_kernel (split-K GQA decode attention over the f16 cache, with the one-token append fused in)"
+    return "decode_kernel (generic f32 split-K GQA decode attention), after append_kernel"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -547,8 +557,7 @@ def main():
                 "h2d_bytes_per_step": N_LAYERS * (NH + 2 * NKV) * HD * 4, "d2h_bytes_per_step": N_LAYERS * NH * HD * 4,
                 "api": "bk_attn_step_host per layer (host q/k/v in, host out; blocks per layer like the reference)",
                 "out_checksum": checksum},
-        "roofline": {"bound": "hbm", "kernel": "decode_p4_mma_kernel (split-K GQA decode attention over the 4-bit cache, "
-                               "with the one-token append fused in)",
+        "roofline": {"bound": "hbm", "kernel": decode_kernel_name(args.mode, args.ctx),
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}",
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this

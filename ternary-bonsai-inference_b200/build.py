@@ -28,11 +28,12 @@ SOURCES = {
     "bk_kvq.cu": ["--fmad=false"],
     "bk_decode.cu": [],
     "bk_decode_mma.cu": [],
+    "bk_decode_f16.cu": [],
     "bk_noalloc.cu": [],
     "bk_p2p.cu": [],
     "bk_host_tables.cpp": [],
 }
-HEADERS = ["bk_internal.h", "bk_device.cuh", "bk_decode_common.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]
+HEADERS = ["bk_internal.h", "bk_device.cuh", "bk_decode_common.cuh", "bk_mma_common.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]
 
 
 def nvcc():

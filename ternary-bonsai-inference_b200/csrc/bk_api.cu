@@ -386,9 +386,9 @@ bk_status bk_cache_create(bk_ctx *ctx, const bk_cache_config *cfg, bk_cache **ou
         return st;
     }
     c->n_pos.assign((size_t)cfg->n_layers * cfg->n_seqs, 0);
-    if (k_kind == ROW_PLANAR && v_kind == ROW_PLANAR && bits == 4) {
-        st = make_p4_tensor_maps(ctx, c->d_k, c->d_v, cfg->n_kv, (size_t)cfg->n_layers * cfg->n_seqs * cfg->n_ctx,
-                                 c->tmap_k, c->tmap_v);
+    if ((k_kind == ROW_PLANAR && v_kind == ROW_PLANAR && bits == 4) || (k_kind == ROW_F16 && v_kind == ROW_F16)) {
+        st = make_tile_tensor_maps(ctx, c->d_k, c->d_v, c->k_row_bytes, cfg->n_kv,
+                                   (size_t)cfg->n_layers * cfg->n_seqs * cfg->n_ctx, c->tmap_k, c->tmap_v);
         if (st != BK_OK) {
             bk_cache_destroy(c);
             return st;
@@ -695,7 +695,9 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
     }
     m.item_start[nb] = items;
     m.n_items = items;
-    return use_mma ? launch_decode_mma(ctx, a, m, ctx->lut_alpha[a.bits], ctx->qsplit) : launch_decode(ctx, a, m);
+    if (!use_mma) return launch_decode(ctx, a, m);
+    return a.k_kind == ROW_F16 ? launch_decode_f16_mma(ctx, a, m, ctx->qsplit)
+                               : launch_decode_p4_mma(ctx, a, m, ctx->lut_alpha[a.bits], ctx->qsplit);
 }
 
 bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos) {

@@ -1,0 +1,445 @@
+// Decode attention over an f16 cache (K and V rows of 256 halfs): tensor-core path.
+//
+// The stored halfs are MMA operands as they are, so the kernel is the 4-bit one without its
+// lookup table: per warp a ring of shared-memory stages, each one tile of 16 positions of one kv
+// head (K 8 KiB + V 8 KiB), filled by the TMA engine as eight tiled copies of 16 rows x 128 bytes
+// (a 3-D tensor map over [position][kv head][512 B]; four column slabs per row because the
+// 128-byte swizzle spans 128 bytes), completion on an mbarrier with a bounded wait.  Fragments
+// come out of the swizzled slabs with ldmatrix (conflict-free: the eight rows of a matrix sit in
+// eight different 16-byte columns):
+//     scores^T[16 pos x 8 heads] = K[16 pos x 256] . Q^T      (A = K via ldmatrix, B = q)
+//     out^T[256 x 8 heads]      += V^T[256 x 16 pos] . W      (A = V via ldmatrix.trans, B = weights)
+// with mma.sync.m16n8k16, f16 in, f32 accumulate.  K and V are exact as stored; q and the V
+// weights (p * 2^14) are each split into f16 hi + lo parts when QSPLIT is set, so both products
+// carry about 22 bits; the softmax runs in f32 in the exp2 domain.  Six of the eight MMA columns
+// are real heads (the GQA group).
+// The CPU path this replaces is src/forward.rs:318-343 (f16 rows widened, f32 dot, f64 softmax sum).
+//
+// Work split, partials and the last-arriver combine are shared with the other decode kernels.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "bk_decode_common.cuh"
+#include "bk_mma_common.cuh"
+
+namespace bk {
+
+namespace {
+
+constexpr int kFW = 12;                  // warps per CTA
+constexpr int kFT = kFW * 32;
+constexpr int kTile = 16;                // positions per warp tile (the MMA's M)
+constexpr int kSlabBytes = kTile * 128;  // 16 rows x 128 B, 128B-swizzled
+constexpr int kSlabs = 4;                // 512-byte rows = 4 slabs
+constexpr int kHalfStage = kSlabs * kSlabBytes;  // one K or V tile: 8 KiB
+constexpr int kStageBytes = 2 * kHalfStage;      // 16 KiB
+constexpr int kMaxStages = 2;
+constexpr int kHeadStride = 276;         // floats per head in the warp-merge area (bank-conflict free)
+constexpr float kWScale = 16384.0f;      // 2^14: V weights are stored as f16 in (0, 2^14]
+
+struct Other {
+    uint2 q_hi_frag[16][32], q_lo_frag[16][32];  // q as B fragments: [k-step][lane]
+    float sq[8 * kHd];                   // q of the group while it is roped
+    float new_row[2][kHd];               // the newest token's k and v of this kv head (fused append)
+    float2 rope_row[kHd / 2];            // (cos, sin) of the q position
+    float m_w[kFW][8], l_w[kFW][8];
+    float M[8], L[8];
+    int last;
+    unsigned long long bar[kFW][kMaxStages];
+};
+
+template <int NREP, bool QSPLIT>
+__global__ void __launch_bounds__(kFT, 1)
+decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *err_flag,
+                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    // ---- shared-memory layout: bookkeeping first, then the ring on a 1 KiB boundary ----------
+    const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    Other &o = *reinterpret_cast<Other *>(smem_raw);
+    const uint32_t ring0 = (base + (uint32_t)sizeof(Other) + 1023u) & ~1023u;
+    const uint32_t ring_end = base + smem_bytes;
+    const int n_stages = ring_end > ring0 ? min((int)((ring_end - ring0) / (uint32_t)(kFW * kStageBytes)), kMaxStages) : 0;
+    if (n_stages < 1) {  // never expected (the host checks the size): report, do not run
+        if (tid == 0) atomicExch(err_flag, 2);
+        return;
+    }
+    const uint32_t bar0 = base + (uint32_t)offsetof(Other, bar) + (uint32_t)(warp * kMaxStages) * 8u;
+    if (lane < kMaxStages) mbar_init(bar0 + lane * 8u, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    __syncthreads();
+
+    // ---- which item ------------------------------------------------------------------------
+    const int item = blockIdx.x;
+    int s = 0;
+    while (s + 1 < meta.n_seqs && meta.item_start[s + 1] <= item) s++;
+    const int n_pos = meta.n_pos[s];
+    const int L = meta.chunk_len;
+    const int n_chunks = (n_pos + L - 1) / L;
+    const int local = item - meta.item_start[s];
+    const int kv = local / n_chunks, chunk = local - kv * n_chunks;
+    const int p0 = chunk * L, p1 = min(p0 + L, n_pos);
+    const int n_tiles = (p1 - p0 + kTile - 1) / kTile;
+    const size_t seq_rows = (size_t)meta.seq_id[s] * a.seq_stride_rows;
+    const int gpos0 = a.layer_pos0 + meta.seq_id[s] * a.n_ctx + p0;  // position index in the tensor map
+
+    auto stage_of = [&](int st) -> uint32_t { return ring0 + (uint32_t)(warp * n_stages + st) * kStageBytes; };
+    auto issue_tile = [&](int tile, int st) {
+        if (lane == 0) {
+            const uint32_t bar = bar0 + (uint32_t)st * 8u, dst = stage_of(st);
+            mbar_expect_tx(bar, kStageBytes);
+            const int pos = gpos0 + tile * kTile;
+#pragma unroll
+            for (int sl = 0; sl < kSlabs; sl++) {
+                tma_tile_x(dst + sl * kSlabBytes, &tm_k, sl * 128, kv, pos, bar);
+                tma_tile_x(dst + kHalfStage + sl * kSlabBytes, &tm_v, sl * 128, kv, pos, bar);
+            }
+        }
+    };
+    auto wait_tile = [&](int st, uint32_t parity) {
+        const uint32_t bar = bar0 + (uint32_t)st * 8u;
+        int polls = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            if (++polls > kWaitPolls) {  // never expected; leave a mark and go on rather than hang
+                if (lane == 0) atomicExch(err_flag, 1);
+                break;
+            }
+        }
+    };
+
+    // ---- constant tables first: with programmatic dependent launch this overlaps the previous
+    // kernel's tail.  q, the newest row and the split-K scratch are read after the wait.
+    if (!a.no_rope) {
+        const int half = a.n_rot >> 1;
+        const float2 *cs = a.rope + (size_t)meta.q_pos[s] * half;
+        for (int i = tid; i < half; i += kFT) o.rope_row[i] = cs[i];
+    }
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+    // ---- fused append: the CTA that scans the last chunk of this kv head stores the head's new K
+    // and V rows first, exactly as the append kernel would (src/forward.rs:259-277: rope on K,
+    // then f32 -> f16 by the reference's own rounding rule).
+    if (a.new_k != nullptr && chunk == n_chunks - 1) {
+        __syncthreads();  // the rope row is in shared memory
+        if (warp < 2) {
+            const float *src = (warp == 0 ? a.new_k : a.new_v) + ((size_t)meta.slot[s] * a.n_kv + kv) * kHd;
+            float *sx = o.new_row[warp];
+            reinterpret_cast<float4 *>(sx)[lane] = reinterpret_cast<const float4 *>(src)[lane];
+            reinterpret_cast<float4 *>(sx)[lane + 32] = reinterpret_cast<const float4 *>(src)[lane + 32];
+            __syncwarp();
+            if (warp == 0 && !a.no_rope) {
+                const int half = a.n_rot >> 1;
+                for (int j = lane; j < half; j += 32) {
+                    float x0 = sx[j], x1 = sx[j + half];
+                    rope_pair(x0, x1, o.rope_row[j]);
+                    sx[j] = x0;
+                    sx[j + half] = x1;
+                }
+                __syncwarp();
+            }
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                w[i] = (uint32_t)f32_to_half_ref(sx[lane * 8 + 2 * i]) | ((uint32_t)f32_to_half_ref(sx[lane * 8 + 2 * i + 1]) << 16);
+            const size_t row = seq_rows + (size_t)(n_pos - 1) * a.n_kv + kv;
+            uint8_t *dst = (warp == 0 ? a.k_rows_w : a.v_rows_w) + row * 512;
+            reinterpret_cast<uint4 *>(dst)[lane] = make_uint4(w[0], w[1], w[2], w[3]);
+            __threadfence();
+            asm volatile("fence.proxy.async;\n" ::: "memory");  // generic-proxy stores before the TMA reads below
+        }
+        __syncthreads();
+    }
+    // fill the ring now so that the copies fly during the rest of the set-up
+    for (int st = 0; st < n_stages; st++)
+        if (warp + st * kFW < n_tiles) issue_tile(warp + st * kFW, st);
+
+    // ---- q: rope, scale, split into f16 hi/lo, laid out as B fragments ---------------------
+    {
+        float *sq = o.sq;  // [NREP][256]
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * kHd;
+        for (int i = tid; i < NREP * kHd; i += kFT) sq[i] = q[i];
+        __syncthreads();  // also: the rope row is complete
+        if (!a.no_rope) {
+            const int half = a.n_rot >> 1;
+            for (int i = tid; i < NREP * half; i += kFT) {
+                const int r = i / half, j = i - r * half;
+                float x0 = sq[r * kHd + j], x1 = sq[r * kHd + j + half];
+                rope_pair(x0, x1, o.rope_row[j]);
+                sq[r * kHd + j] = x0;
+                sq[r * kHd + j + half] = x1;
+            }
+            __syncthreads();
+        }
+        // 1/sqrt(hd) * log2(e): the scores come out in the exp2 domain.
+        // k-step ks covers coordinates 16 ks .. 16 ks + 15; lane (g, t) holds head g's values at
+        // 16 ks + 2t, +1 (b0) and 16 ks + 2t + 8, +9 (b1).
+        const float qscale = rsqrtf((float)kHd) * 1.4426950408889634f;
+        for (int i = tid; i < 16 * 32; i += kFT) {
+            const int ks = i >> 5, ln = i & 31, gg = ln >> 2, tt = ln & 3;
+            const int d0 = 16 * ks + 2 * tt;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            if (gg < NREP) {
+                x[0] = sq[gg * kHd + d0] * qscale;
+                x[1] = sq[gg * kHd + d0 + 1] * qscale;
+                x[2] = sq[gg * kHd + d0 + 8] * qscale;
+                x[3] = sq[gg * kHd + d0 + 9] * qscale;
+            }
+            __half h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                h[e] = __float2half_rn(x[e]);
+                l[e] = __float2half_rn(x[e] - __half2float(h[e]));
+            }
+            auto pack = [](__half lo, __half hi) { return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16); };
+            o.q_hi_frag[ks][ln] = make_uint2(pack(h[0], h[1]), pack(h[2], h[3]));
+            o.q_lo_frag[ks][ln] = make_uint2(pack(l[0], l[1]), pack(l[2], l[3]));
+        }
+        __syncthreads();
+    }
+    const uint32_t qh_addr = base + (uint32_t)offsetof(Other, q_hi_frag) + (uint32_t)lane * 8u;
+    const uint32_t ql_addr = base + (uint32_t)offsetof(Other, q_lo_frag) + (uint32_t)lane * 8u;
+    auto q_frag = [&](uint32_t addr0, int ks, uint32_t &x, uint32_t &y) {
+        asm("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(x), "=r"(y) : "r"(addr0 + (uint32_t)ks * 256u));
+    };
+
+    float acc[16][4];
+#pragma unroll
+    for (int j = 0; j < 16; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    float M0 = -CUDART_INF_F, M1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+    // ldmatrix row addresses of this lane inside a slab.  K (plain): matrices (rows 0-7, chunk c),
+    // (rows 8-15, c), (rows 0-7, c+1), (rows 8-15, c+1).  V (transposed): (rows 0-7, c),
+    // (rows 0-7, c+1), (rows 8-15, c), (rows 8-15, c+1).  Chunk = 16 bytes = 8 coordinates; the
+    // swizzle XORs it with row & 7 = lane & 7.
+    const uint32_t key = (uint32_t)(lane & 7);
+    const uint32_t k_row_off = (uint32_t)((lane & 7) + ((lane >> 3) & 1) * 8) * 128u, k_csel = (uint32_t)(lane >> 4);
+    const uint32_t v_row_off = (uint32_t)((lane & 7) + (lane >> 4) * 8) * 128u, v_csel = (uint32_t)((lane >> 3) & 1);
+
+    auto compute_tile = [&](int tile, uint32_t st_addr) {
+        const int pb = p0 + tile * kTile;
+        if (pb + kTile > p1) {
+            // Ragged last tile of the sequence: the rows past its end hold whatever the cache has
+            // there, possibly non-finite halfs, and 0 * Inf would poison the accumulators.  Zero them.
+            const int valid = p1 - pb;
+            for (int i = lane; i < 2 * kSlabs * kTile * 8; i += 32) {
+                const int slab = i >> 7, r = (i >> 3) & 15, c = i & 7;
+                if (r >= valid)
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(st_addr + (uint32_t)(slab * kSlabBytes + r * 128 + c * 16)), "r"(0u) : "memory");
+            }
+            __syncwarp();
+        }
+        // ---- scores^T = K . Q^T; four independent accumulator chains --------------------------
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        float sc2[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 16; ks++) {
+            const uint32_t addr = st_addr + (uint32_t)((ks >> 2) * kSlabBytes) + k_row_off + ((((uint32_t)(2 * (ks & 3)) + k_csel) ^ key) << 4);
+            uint32_t a0, a1, a2, a3, qx, qy;
+            ldmatrix_x4(addr, a0, a1, a2, a3);
+            q_frag(qh_addr, ks, qx, qy);
+            mma16816((ks & 1) ? sb : sa, a0, a1, a2, a3, qx, qy);
+            if (QSPLIT) {
+                q_frag(ql_addr, ks, qx, qy);
+                mma16816((ks & 1) ? sd : sc2, a0, a1, a2, a3, qx, qy);
+            }
+        }
+        float sc[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) sc[i] = (sa[i] + sb[i]) + (sc2[i] + sd[i]);
+        // ---- online softmax in the exp2 domain ------------------------------------------------
+        const bool ok0 = pb + g < p1, ok1 = pb + g + 8 < p1;
+        const float t00 = ok0 ? sc[0] : -CUDART_INF_F, t01 = ok0 ? sc[1] : -CUDART_INF_F;
+        const float t10 = ok1 ? sc[2] : -CUDART_INF_F, t11 = ok1 ? sc[3] : -CUDART_INF_F;
+        float mx0 = fmaxf(t00, t10), mx1 = fmaxf(t01, t11);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const bool grow = (mx0 > M0) || (mx1 > M1);
+        if (__any_sync(0xffffffffu, grow)) {
+            const float n0 = fmaxf(M0, mx0), n1 = fmaxf(M1, mx1);
+            const float c0 = fast_exp2(M0 - n0), c1 = fast_exp2(M1 - n1);  // 0 on the first tile
+            l0 *= c0;
+            l1 *= c1;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                acc[j][0] *= c0;
+                acc[j][1] *= c1;
+                acc[j][2] *= c0;
+                acc[j][3] *= c1;
+            }
+            M0 = n0;
+            M1 = n1;
+        }
+        const float e00 = fast_exp2(t00 - M0), e01 = fast_exp2(t01 - M1);
+        const float e10 = fast_exp2(t10 - M0), e11 = fast_exp2(t11 - M1);
+        l0 += e00 + e10;
+        l1 += e01 + e11;
+        const float w00 = e00 * kWScale, w01 = e01 * kWScale, w10 = e10 * kWScale, w11 = e11 * kWScale;
+        const __half2 pl = __floats2half2_rn(w00, w01), ph = __floats2half2_rn(w10, w11);
+        const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
+        const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
+        // The weights get a low part as well: V rows are raw activations, and with a peaked softmax
+        // over rows of very different size a single f16 weight (11 bits) would show in the output.
+        uint32_t b0l = 0, b1l = 0;
+        if (QSPLIT) {
+            const float2 fl = __half22float2(pl), fh = __half22float2(ph);
+            const __half2 ql = __floats2half2_rn(w00 - fl.x, w01 - fl.y), qh = __floats2half2_rn(w10 - fh.x, w11 - fh.y);
+            b0l = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ql));
+            b1l = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&qh));
+        }
+        // ---- out^T += V^T . W : MMA j covers coordinates 16j + g (c0, c1) and 16j + g + 8 (c2, c3)
+        const uint32_t v_tile = st_addr + kHalfStage;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const uint32_t addr = v_tile + (uint32_t)((j >> 2) * kSlabBytes) + v_row_off + ((((uint32_t)(2 * (j & 3)) + v_csel) ^ key) << 4);
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4_trans(addr, a0, a1, a2, a3);
+            mma16816(acc[j], a0, a1, a2, a3, b0, b1);
+            if (QSPLIT) mma16816(acc[j], a0, a1, a2, a3, b0l, b1l);
+        }
+    };
+
+    // ---- scan: the warp's tiles are warp, warp + kFW, ...; tile i lives in stage i % n_stages ---
+    {
+        int st = 0;
+        uint32_t parity = 0;
+        for (int tile = warp; tile < n_tiles; tile += kFW) {
+            wait_tile(st, parity);
+            compute_tile(tile, stage_of(st));
+            __syncwarp();  // every lane has read the stage: lane 0 may refill it
+            if (tile + n_stages * kFW < n_tiles) issue_tile(tile + n_stages * kFW, st);
+            if (++st == n_stages) { st = 0; parity ^= 1u; }
+        }
+    }
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+
+    // ---- merge the warps (the ring is free now and holds the merge area) ----------------------
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+    if (g == 0) {
+        o.m_w[warp][2 * t] = M0;
+        o.m_w[warp][2 * t + 1] = M1;
+        o.l_w[warp][2 * t] = l0;
+        o.l_w[warp][2 * t + 1] = l1;
+    }
+    __syncthreads();  // every warp has consumed its last stage
+    if (tid < 8) {
+        float M = -CUDART_INF_F;
+        for (int w = 0; w < kFW; w++) M = fmaxf(M, o.m_w[w][tid]);
+        float Ls = 0.f;
+        for (int w = 0; w < kFW; w++)
+            if (o.m_w[w][tid] > -CUDART_INF_F) Ls += o.l_w[w][tid] * exp2f(o.m_w[w][tid] - M);
+        o.M[tid] = M;
+        o.L[tid] = Ls;
+    }
+    __syncthreads();
+    float *area = reinterpret_cast<float *>(smem_raw + (ring0 - base));  // [kFW][NREP][kHeadStride]
+    {
+        const float unscale = 1.0f / kWScale;
+        const float f0 = (M0 > -CUDART_INF_F) ? exp2f(M0 - o.M[2 * t]) * unscale : 0.f;
+        const float f1 = (M1 > -CUDART_INF_F) ? exp2f(M1 - o.M[2 * t + 1]) * unscale : 0.f;
+        float *w0 = area + ((size_t)warp * NREP + 2 * t) * kHeadStride + g;
+        float *w1 = w0 + kHeadStride;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            if (2 * t < NREP) {
+                w0[16 * j] = acc[j][0] * f0;
+                w0[16 * j + 8] = acc[j][2] * f0;
+            }
+            if (2 * t + 1 < NREP) {
+                w1[16 * j] = acc[j][1] * f1;
+                w1[16 * j + 8] = acc[j][3] * f1;
+            }
+        }
+    }
+    __syncthreads();
+    float sums[NREP];
+#pragma unroll
+    for (int r = 0; r < NREP; r++) sums[r] = 0.f;
+    if (tid < kHd) {
+#pragma unroll
+        for (int r = 0; r < NREP; r++)
+#pragma unroll
+            for (int w = 0; w < kFW; w++) sums[r] += area[((size_t)w * NREP + r) * kHeadStride + tid];
+    }
+    __syncthreads();
+    float *s_acc = area;  // [NREP][256]
+    if (tid < kHd)
+#pragma unroll
+        for (int r = 0; r < NREP; r++) s_acc[r * kHd + tid] = sums[r];
+    __syncthreads();
+
+    const int first_item = meta.item_start[s] + kv * n_chunks;
+    finish_item<NREP>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, false);
+}
+
+template <int NREP, bool QSPLIT>
+bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m) {
+    static size_t smem_for[64] = {};
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (f16 mma): device index above 63");
+    if (smem_for[dev] == 0) {
+        cudaFuncAttributes fa;
+        BK_CUDA(ctx, cudaFuncGetAttributes(&fa, decode_f16_mma_kernel<NREP, QSPLIT>));
+        int optin = 0;
+        BK_CUDA(ctx, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        const size_t dyn = (size_t)optin - fa.sharedSizeBytes;
+        // bookkeeping + alignment slack + one stage per warp, and the merge area must fit the ring
+        const size_t need = sizeof(Other) + 1024 + (size_t)kFW * kStageBytes;
+        static_assert((size_t)kFW * kStageBytes >= (size_t)kFW * 6 * kHeadStride * 4, "merge area does not fit the ring");
+        if (dyn < need) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (f16 mma): not enough shared memory per block on this device");
+        BK_CUDA(ctx, cudaFuncSetAttribute(decode_f16_mma_kernel<NREP, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        smem_for[dev] = dyn;
+    }
+    const size_t smem = smem_for[dev];
+    if (!a.h_tmap_k || !a.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "decode (f16 mma): the cache has no tensor maps");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)m.n_items);
+    cfg.blockDim = dim3(kFT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see griddepcontrol.* in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BK_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_f16_mma_kernel<NREP, QSPLIT>, a, m, (uint32_t)smem, ctx->d_err,
+                                    *static_cast<const CUtensorMap *>(a.h_tmap_k),
+                                    *static_cast<const CUtensorMap *>(a.h_tmap_v)));
+    ctx->launches++;
+    BK_CUDA(ctx, cudaGetLastError());
+    return BK_OK;
+}
+
+}  // namespace
+
+bool decode_f16_mma_supported(const DecodeArgs &a) {
+    const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
+    return a.h_tmap_k && a.h_tmap_v && a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 &&
+           a.v_row_bytes == 512 && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
+}
+
+bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, bool qsplit) {
+    if (m.n_items <= 0) return BK_OK;
+    const int n_rep = a.n_head / a.n_kv;
+#define BK_F16_CASE(R)                                                          \
+    case R:                                                                     \
+        return qsplit ? launch_one<R, true>(ctx, a, m) : launch_one<R, false>(ctx, a, m);
+    switch (n_rep) {
+        BK_F16_CASE(1)
+        BK_F16_CASE(2)
+        BK_F16_CASE(4)
+        BK_F16_CASE(6)
+        default: return fail(ctx, BK_ERR_UNSUPPORTED, "decode (f16 mma): n_head/n_kv must be 1, 2, 4 or 6");
+    }
+#undef BK_F16_CASE
+}
+
+}  // namespace bk

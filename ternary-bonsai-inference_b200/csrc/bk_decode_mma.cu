@@ -35,6 +35,7 @@
 #include <cuda_fp16.h>
 
 #include "bk_decode_common.cuh"
+#include "bk_mma_common.cuh"
 
 namespace bk {
 
@@ -52,7 +53,6 @@ constexpr int kTileBytes = kTile * kRowBytes;   // 2048: one K or V tile, dense 
 constexpr int kNormBytes = 512;                 // norms of 16 positions x up to 8 kv heads (all heads travel)
 constexpr int kStageBytes = 2 * kTileBytes + 2 * kNormBytes;  // K tile, V tile, K norms, V norms; 1 KiB aligned
 constexpr int kMaxStages = 6;
-constexpr int kWaitPolls = 1 << 22;     // mbarrier polls before a wait gives up and flags an error
 
 struct Other {                          // lives outside the lookup table
     __half q_hi[8][kHd];
@@ -70,20 +70,6 @@ struct Other {                          // lives outside the lookup table
 };
 static_assert(sizeof(Other) <= kOtherBytes, "Other does not fit");
 
-__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
-    uint32_t y;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
-    return y;
-}
-
 // Table lookup of packed byte K (0..3) of word x: lane_base holds the table's shared address in
 // its upper two bytes and lane*4 in byte 0; the data byte becomes byte 1 of the address.
 template <int K>
@@ -100,53 +86,6 @@ __device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
-}
-
-// Single-instruction exp2 / log2 (2 ulp): the library versions add range fix-ups that this loop
-// does not need (arguments are <= 0 for exp2 up to the 2^14 weight scale, norms are clamped).
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float fast_log2(float x) {
-    float y;
-    asm("lg2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Plain 1-D bulk copy (the norms of a tile), same completion mechanism.
-__device__ __forceinline__ void tma_bulk(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-// One tile (16 positions x 128 bytes of one kv head) global -> shared through the TMA engine;
-// completion is counted on `bar`.  Coordinates: byte in row (0), kv head, global position.
-__device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap *map, int kv, int pos, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(kv), "r"(pos), "r"(bar)
-        : "memory");
 }
 
 template <int NREP, bool QSPLIT>
@@ -601,10 +540,11 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
 
 }  // namespace
 
-// Tensor maps over the K and V rows of a 4-bit planar cache: dims (128 bytes, n_kv, positions of all
-// layers and sequences), box (128, 1, 16), 128-byte swizzle.  Built once per cache.
-bk_status make_p4_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, int n_kv, size_t total_pos,
-                              void *out_k, void *out_v) {
+// Tensor maps over the K and V rows of a cache whose rows are row_bytes long (128 for 4-bit planar,
+// 512 for f16): dims (row_bytes, n_kv, positions of all layers and sequences), box (128 bytes, 1,
+// 16 positions), 128-byte swizzle.  Built once per cache.
+bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, size_t row_bytes, int n_kv,
+                                size_t total_pos, void *out_k, void *out_v) {
     static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -619,9 +559,10 @@ bk_status make_p4_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_row
         encode = (EncodeFn)fn;
     }
     if (total_pos >= (size_t)1 << 31) return fail(ctx, BK_ERR_UNSUPPORTED, "cache has more than 2^31 positions");
-    const cuuint64_t dims[3] = {(cuuint64_t)kRowBytes, (cuuint64_t)n_kv, (cuuint64_t)total_pos};
-    const cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, (cuuint64_t)kRowBytes * n_kv};
-    const cuuint32_t box[3] = {(cuuint32_t)kRowBytes, 1, (cuuint32_t)kTile};
+    if (row_bytes % 128 != 0) return fail(ctx, BK_ERR_UNSUPPORTED, "tensor maps need rows of a multiple of 128 bytes");
+    const cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)n_kv, (cuuint64_t)total_pos};
+    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)row_bytes * n_kv};
+    const cuuint32_t box[3] = {128, 1, (cuuint32_t)kTile};
     const cuuint32_t estr[3] = {1, 1, 1};
     const void *ptrs[2] = {k_rows, v_rows};
     void *outs[2] = {out_k, out_v};
@@ -635,14 +576,14 @@ bk_status make_p4_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_row
     return BK_OK;
 }
 
-bool decode_mma_supported(const DecodeArgs &a) {
+bool decode_p4_mma_supported(const DecodeArgs &a) {
     const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
     // (the norms of a tile travel as a 16-byte aligned bulk copy: n_ctx * n_kv must be a multiple of 4)
     return a.h_tmap_k && a.h_tmap_v && (a.seq_stride_rows % 4 == 0) && a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && a.bits == 4 &&
            (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
-bk_status launch_decode_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit) {
+bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit) {
     if (m.n_items <= 0) return BK_OK;
     const int n_rep = a.n_head / a.n_kv;
 #define BK_MMA_CASE(R)                                                          \

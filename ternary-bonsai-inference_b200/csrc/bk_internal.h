@@ -87,7 +87,7 @@ struct bk_cache {
     std::vector<int32_t> n_pos;               // [layer][seq]
     std::shared_ptr<bk::RopeTable> rope;
     size_t device_bytes = 0;
-    alignas(64) unsigned char tmap_k[128], tmap_v[128];  // CUtensorMap objects (4-bit planar K+V caches)
+    alignas(64) unsigned char tmap_k[128], tmap_v[128];  // CUtensorMap objects (4-bit planar and f16 K+V caches)
     bool has_tmaps = false;
 
     size_t slab(int layer, int seq) const { return (size_t)layer * cfg.n_seqs + seq; }
@@ -188,11 +188,15 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
                               int max_items);
 bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos);
 bk_status bind_device(bk_ctx *ctx);
-// Tensor-core path for 4-bit planar K and V (bk_decode_mma.cu).  Chunks must be multiples of 128.
-bool decode_mma_supported(const DecodeArgs &a);
-bk_status make_p4_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, int n_kv, size_t total_pos,
-                              void *out_k, void *out_v);
-bk_status launch_decode_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
+// Tensor-core paths: 4-bit planar K and V (bk_decode_mma.cu) and f16 K and V (bk_decode_f16.cu).
+// Chunks must be multiples of 16 positions.
+bool decode_p4_mma_supported(const DecodeArgs &a);
+bool decode_f16_mma_supported(const DecodeArgs &a);
+inline bool decode_mma_supported(const DecodeArgs &a) { return decode_p4_mma_supported(a) || decode_f16_mma_supported(a); }
+bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, size_t row_bytes, int n_kv,
+                                size_t total_pos, void *out_k, void *out_v);
+bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
+bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, bool qsplit);
 bk_status launch_lse_merge(bk_ctx *ctx, int n_parts, int n_rows, int hd, const float *parts, float *out);
 
 bk_status launch_quantize(bk_ctx *ctx, int bits, int n_vec, const float *x, uint8_t *packed, float *norms);

@@ -504,6 +504,79 @@ def test_fused_step_on_long_planar4_cache(bk, gpu_ctx, oracle):
     cache.close()
 
 
+@pytest.mark.parametrize("env", [{"BONSAI_KV_GENERIC": "1"}, {}])
+def test_f16_kernel_variants(bk, oracle, monkeypatch, env):
+    """The f16 cache has the same two decode kernels behind one entry point (tensor cores from 2048
+    positions on).  Lengths hit ragged tiles, single chunks, many chunks and a mixed batch."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    ctx = bk.Context(0)
+    for lens in ([17], [2047], [2048], [2049], [2063, 2064, 2065], [5000], [40000, 3, 2500]):
+        got, want = run_both(bk, ctx, oracle, "f16", MODE_F16, 0, False, lens, seed=sum(lens))
+        assert_close(got, want, f"{env} {lens}")
+    ctx.close()
+
+
+def test_f16_tensor_core_path_other_group_sizes(bk, gpu_ctx, oracle):
+    rng = np.random.default_rng(78)
+    n = 2500
+    for n_head, n_kv in ((4, 4), (8, 4), (8, 2), (16, 2)):
+        k = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
+        v = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
+        q = rng.standard_normal((n_head, HD)).astype(np.float32)
+        cache = bk.AttnCache(gpu_ctx, bk.parse_mode("f16"), n_layers=1, n_ctx=n, n_head=n_head, n_kv=n_kv)
+        cache.append(0, k, v)
+        ref = oracle.cache(MODE_F16, 0, False, n_head=n_head, n_kv=n_kv)
+        for p in range(n):
+            ref.append(0, k[p], v[p], p)
+        want = ref.attend(0, q, n - 1, n, threads=8)
+        got = cache.attend(0, q)[0]
+        assert_close(got, want, f"{n_head}/{n_kv}")
+        cache.close()
+
+
+def test_f16_rows_past_the_end_do_not_leak_in(bk, gpu_ctx, oracle):
+    """The tensor-core kernel copies whole 16-position tiles; rows past n_pos may hold anything,
+    including f16 infinities (1e30 stored as f16), and must not reach the result."""
+    rng = np.random.default_rng(5)
+    n, extra = 2500 + 7, 9
+    k, v = synth_kv(rng, n + extra)
+    k[n:] = np.float32(1e30)
+    v[n:] = np.float32(-1e30)
+    q = rng.standard_normal((NH, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode("f16"), n_layers=1, n_ctx=n + extra)
+    cache.append(0, k, v)
+    ref = oracle.cache(MODE_F16, 0, False)
+    for p in range(n):
+        ref.append(0, k[p], v[p], p)
+    want = ref.attend(0, q, n - 1, n, threads=8)
+    got = cache.attend(0, q[None], n_pos=[n], q_pos=[n - 1])[0]
+    assert np.all(np.isfinite(got))
+    assert_close(got, want)
+    cache.close()
+
+
+def test_fused_step_on_long_f16_cache(bk, gpu_ctx, oracle):
+    """On a long f16 cache the attention step is one launch too; stored rows stay bit-exact."""
+    rng = np.random.default_rng(43)
+    n0, steps = 2600, 12
+    k, v = synth_kv(rng, n0 + steps)
+    q = rng.standard_normal((steps, NH, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode("f16"), n_layers=1, n_ctx=n0 + steps)
+    ref = oracle.cache(MODE_F16, 0, False)
+    cache.append(0, k[:n0], v[:n0])
+    for p in range(n0):
+        ref.append(0, k[p], v[p], p)
+    for t in range(steps):
+        launches = gpu_ctx.launch_count
+        got = bk.full_attention_step(cache, 0, q[t], k[n0 + t], v[n0 + t], n0 + t)
+        assert gpu_ctx.launch_count - launches == 1
+        want = ref.step(0, q[t], k[n0 + t], v[n0 + t], n0 + t, threads=8)
+        assert_close(got, want, f"step {t}")
+    compare_dumps(cache.dump_kv(0, pos0=n0 - 3), {key: val[n0 - 3:] for key, val in ref.dump(0).items()})
+    cache.close()
+
+
 @pytest.mark.parametrize("bits", range(1, 9))
 def test_nearest_centroid_search_equals_the_reference_scan(bk, gpu_ctx, oracle, bits):
     """The kernels find the nearest centroid by binary search plus one neighbour check; the
