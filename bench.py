@@ -215,6 +215,8 @@ def workload_config(args, mode):
     return {"workload": f"decode128k: 1 sequence/GPU, {N_LAYERS} full-attention layers, context {args.ctx}, "
                         f"{args.mode} KV cache, {NH} q / {NKV} kv heads, head_dim {HD}",
             "kv_mode": args.mode, "context": args.ctx, "layers": N_LAYERS, "batch_per_gpu": 1,
+            "step": ("bk_attn_layer_step (q|gate split, q/k RMSNorm, append, attention, sigmoid gate)"
+                     if getattr(args, "step", "attn") == "layer" else "bk_attn_step (append + attention)"),
             "l2": "each step streams %.2f GB of cache, larger than the 126 MB L2 (no flush needed)"
                   % (N_LAYERS * attn_bytes(mode, args.ctx) / 1e9)}
 
@@ -399,6 +401,9 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="splitctx only: p2p = peer-memory exchange fused with the merge (bk_decode_attn_split); "
                          "nccl = all-gather of the partials + bk_lse_merge")
+    ap.add_argument("--step", default="attn", choices=["attn", "layer"],
+                    help="attn: bk_attn_step (the metric's step); layer: bk_attn_layer_step, which also does the "
+                         "q|gate split, the per-head RMSNorm of q and k and the sigmoid gate in the same launch")
     ap.add_argument("--workload", default="decode128k", choices=["decode128k", "batch64", "splitctx", "appendsweep"],
                     help="decode128k: the headline (default).  batch64: 64 sequences, contexts U[2048,16384], sharded "
                          "over the ranks.  splitctx: one 262144-token sequence, context chunks per rank, LSE merge.  "
@@ -449,12 +454,17 @@ def main():
 
     # ---- step inputs, resident in HBM -------------------------------------------------------
     rng = np.random.default_rng(1234 + rank)
-    q_all = rng.standard_normal((total_steps, N_LAYERS, NH, HD), dtype=np.float32)
+    layer_form = args.step == "layer"
+    q_width = 2 * HD if layer_form else HD  # the layer form reads the interleaved [q | gate] projection output
+    q_all = rng.standard_normal((total_steps, N_LAYERS, NH, q_width), dtype=np.float32)
     d_q = ctx.to_device(q_all)
     d_k = ctx.to_device(k_new)
     d_v = ctx.to_device(v_new)
     d_out = ctx.alloc(N_LAYERS * NH * HD * 4)
-    q_stride, kv_stride = NH * HD * 4, NKV * HD * 4
+    q_stride, kv_stride, out_stride = NH * q_width * 4, NKV * HD * 4, NH * HD * 4
+    norm_w = (1.0 + 0.1 * rng.standard_normal((2, HD))).astype(np.float32)
+    d_w = ctx.to_device(norm_w)
+    eps = 1e-6
 
     def device_step(s, events=None):
         # the reference's unit of work: one attention step per layer (append at pos, attend over pos+1)
@@ -462,8 +472,13 @@ def main():
         for il in range(N_LAYERS):
             if events is not None:
                 events[il][0].record()
-            cache.step_device(il, d_q.offset((s * N_LAYERS + il) * q_stride), d_k.offset(s * kv_stride),
-                              d_v.offset(s * kv_stride), d_out.offset(il * q_stride), pos)
+            if layer_form:
+                cache.layer_step_device(il, d_q.offset((s * N_LAYERS + il) * q_stride), d_k.offset(s * kv_stride),
+                                        d_v.offset(s * kv_stride), d_w.ptr, d_w.offset(HD * 4), eps,
+                                        d_out.offset(il * out_stride), pos)
+            else:
+                cache.step_device(il, d_q.offset((s * N_LAYERS + il) * q_stride), d_k.offset(s * kv_stride),
+                                  d_v.offset(s * kv_stride), d_out.offset(il * out_stride), pos)
             if events is not None:
                 events[il][1].record()
 
@@ -504,7 +519,9 @@ def main():
     # ---- e2e: the same steps through the host-buffer entry point ---------------------------------
     for il in range(N_LAYERS):
         cache.set_n_pos(il, 0, final_ctx - args.steps)
-    hq = ctx.pinned((N_LAYERS, NH * HD), np.float32)
+    hq = ctx.pinned((N_LAYERS, NH * q_width), np.float32)
+    hw = ctx.pinned((2, HD), np.float32)
+    hw.array[:] = norm_w
     hk = ctx.pinned((NKV * HD,), np.float32)
     hv = ctx.pinned((NKV * HD,), np.float32)
     hout = ctx.pinned((N_LAYERS, NH * HD), np.float32)
@@ -517,8 +534,12 @@ def main():
         hv.array[:] = v_new[s].ravel()
         pos = cache.n_pos(0)
         for il in range(N_LAYERS):
-            ctx.check(lib.bk_attn_step_host(cache.h, il, 0, pos, hq.ptr + il * q_stride, hk.ptr, hv.ptr,
-                                            hout.ptr + il * q_stride))
+            if layer_form:
+                ctx.check(lib.bk_attn_layer_step_host(cache.h, il, 0, pos, hq.ptr + il * q_stride, hk.ptr, hv.ptr,
+                                                      hw.ptr, hw.ptr + HD * 4, eps, hout.ptr + il * out_stride))
+            else:
+                ctx.check(lib.bk_attn_step_host(cache.h, il, 0, pos, hq.ptr + il * q_stride, hk.ptr, hv.ptr,
+                                                hout.ptr + il * out_stride))
     e2e_s = max_over_ranks(dist, local, time.perf_counter() - t0)
     barrier(dist)
     e2e_tok_s = world * args.steps / e2e_s
@@ -537,7 +558,14 @@ def main():
         kind = {"f32": MODE_F32, "f16": MODE_F16, "planar": MODE_PLANAR}[mode.kind]
         threads = oracle.lib.or_max_threads()
         ref = cpu_fill(oracle, (kind, mode.bits, mode.v_quant), chunks, n0)
-        ts = [cpu_layer_step(ref, q_all[s, 0], k_new[s], v_new[s], n0 + s, threads) for s in range(3)]
+        if layer_form:
+            def cpu_one(s):
+                t0 = time.perf_counter()
+                ref.layer_step(0, q_all[s, 0], k_new[s], v_new[s], norm_w[0], norm_w[1], eps, n0 + s, threads=threads)
+                return time.perf_counter() - t0
+            ts = [cpu_one(s) for s in range(3)]
+        else:
+            ts = [cpu_layer_step(ref, q_all[s, 0], k_new[s], v_new[s], n0 + s, threads) for s in range(3)]
         t_layer = float(np.mean(ts[1:]))
         cpu = {"value": 1.0 / (t_layer * N_LAYERS), "unit": "tokens/s", "cores": min(threads, NH), "kind": "port",
                "sample": f"1 of {N_LAYERS} layers at context {n0} (append + attention, 2 timed steps after 1 warm-up), "
@@ -554,8 +582,10 @@ def main():
         "effective_gbs": world * step_bytes / (ms_step * 1e-3) / 1e9,
         "gpu_launches": launches,
         "e2e": {"value": e2e_tok_s, "unit": "tokens/s",
-                "h2d_bytes_per_step": N_LAYERS * (NH + 2 * NKV) * HD * 4, "d2h_bytes_per_step": N_LAYERS * NH * HD * 4,
-                "api": "bk_attn_step_host per layer (host q/k/v in, host out; blocks per layer like the reference)",
+                "h2d_bytes_per_step": N_LAYERS * ((NH * q_width + 2 * NKV * HD + (2 * HD if layer_form else 0)) * 4),
+                "d2h_bytes_per_step": N_LAYERS * NH * HD * 4,
+                "api": ("bk_attn_layer_step_host" if layer_form else "bk_attn_step_host") +
+                       " per layer (host q/k/v in, host out; blocks per layer like the reference)",
                 "out_checksum": checksum},
         "roofline": {"bound": "hbm", "kernel": decode_kernel_name(args.mode, args.ctx),
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -229,6 +229,28 @@ BK_API bk_status bk_attn_step(bk_cache *cache, int32_t layer, int32_t seq, int32
 BK_API bk_status bk_attn_step_host(bk_cache *cache, int32_t layer, int32_t seq, int32_t pos,
                                    const float *q_host, const float *k_host, const float *v_host,
                                    float *out_host);
+/* The layer form of the step: everything full_attention_layer does between the
+ * q/k/v projections and the output projection (src/forward.rs:237-382;
+ * src/gdev.rs:584-829 with norm_rows / split_qgate / elem mode 4 around it).
+ *   qfull  [n_head][2*hd]  projection output, per head [q | gate] (:237-241)
+ *   kraw, vraw [n_kv][hd]  projection outputs
+ *   q_norm_w, k_norm_w [hd] per-head RMSNorm weights (kernels.rs:97-122), eps
+ *   out    [n_head][hd]    attention * sigmoid(gate), the input of attn_output
+ * On caches that take the tensor-core decode path this is one launch.  The
+ * stored K/V rows equal the reference's bit for bit (the k norm keeps the
+ * reference's summation order). */
+BK_API bk_status bk_attn_layer_step(bk_cache *cache, int32_t layer, int32_t seq, int32_t pos,
+                                    const float *qfull_dev, const float *kraw_dev,
+                                    const float *vraw_dev, const float *q_norm_w_dev,
+                                    const float *k_norm_w_dev, float eps, float *out_dev);
+BK_API bk_status bk_attn_layer_step_host(bk_cache *cache, int32_t layer, int32_t seq, int32_t pos,
+                                         const float *qfull_host, const float *kraw_host,
+                                         const float *vraw_host, const float *q_norm_w_host,
+                                         const float *k_norm_w_host, float eps, float *out_host);
+/* rms_norm_rows (src/kernels.rs:97-122): n_rows rows of row_len (<= 1024)
+ * sharing one weight; bit-exact (sequential sum of squares). */
+BK_API bk_status bk_rms_norm_rows(bk_ctx *ctx, int32_t n_rows, int32_t row_len, const float *x_host,
+                                  const float *w_host, float eps, float *out_host);
 /* Gpu::attn_step (src/vk.rs:1671-1752): one-shot f32 attention over host
  * k/v caches [n_pos][kvheads][hd], no rope; validates sizes like the
  * reference (hd must be 256 here). */

@@ -868,6 +868,51 @@ OR_API int or_attn_step(or_cache *c, size_t il, const float *q, const float *k, 
     return or_attend(c, il, q, pos, pos + 1, out, threads);
 }
 
+/* rms_norm_rows, src/kernels.rs:97-122: rows of row_len sharing one weight;
+ * sequential f32 sum of squares, scale = 1 / sqrt(ss / row_len + eps),
+ * dst = src * scale * w (left to right).  -1 on the reference's two error
+ * cases (weight length, ragged x). */
+OR_API int or_rms_norm_rows(const float *x, size_t x_len, const float *w, size_t w_len, size_t row_len, float eps,
+                            float *out) {
+    if (w_len != row_len) return -1;
+    if (row_len == 0 || x_len % row_len != 0) return -1;
+    for (size_t r = 0; r < x_len / row_len; r++) {
+        const float *src = x + r * row_len;
+        float *dst = out + r * row_len;
+        float ss = 0.0f;
+        for (size_t i = 0; i < row_len; i++) ss += src[i] * src[i];
+        float scale = 1.0f / sqrtf(ss / (float)row_len + eps);
+        for (size_t i = 0; i < row_len; i++) dst[i] = src[i] * scale * w[i];
+    }
+    return 0;
+}
+
+/* sigmoid, src/kernels.rs:162-164. */
+OR_API float or_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+/* full_attention_layer between the projections and the output projection,
+ * src/forward.rs:237-382: split [q | gate] per head (:237-241), per-head
+ * RMSNorm of q and k (:242-245), then the step above (:247-375), then
+ * out *= sigmoid(gate) (:379-382).  qfull [n_head][2*hd]. */
+OR_API int or_attn_layer_step(or_cache *c, size_t il, const float *qfull, const float *kraw, const float *vraw,
+                              const float *q_norm_w, const float *k_norm_w, float eps, size_t pos, float *out,
+                              int threads) {
+    size_t nh = c->n_head, hd = c->hd;
+    float *q = malloc(nh * hd * sizeof(float)), *gate = malloc(nh * hd * sizeof(float));
+    float *qn = malloc(nh * hd * sizeof(float)), *kn = malloc(c->n_kv_elems * sizeof(float));
+    for (size_t h = 0; h < nh; h++) {
+        memcpy(q + h * hd, qfull + h * 2 * hd, hd * sizeof(float));
+        memcpy(gate + h * hd, qfull + h * 2 * hd + hd, hd * sizeof(float));
+    }
+    or_rms_norm_rows(q, nh * hd, q_norm_w, hd, hd, eps, qn);
+    or_rms_norm_rows(kraw, c->n_kv_elems, k_norm_w, hd, hd, eps, kn);
+    int rc = or_attn_step(c, il, qn, kn, vraw, pos, out, threads);
+    if (rc == 0)
+        for (size_t i = 0; i < nh * hd; i++) out[i] *= or_sigmoid(gate[i]);
+    free(q); free(gate); free(qn); free(kn);
+    return rc;
+}
+
 /* Read-only views of the stores, for byte comparison with the device cache. */
 OR_API const float *or_cache_k(const or_cache *c, size_t il) { return c->k[il]; }
 OR_API const float *or_cache_v(const or_cache *c, size_t il) { return c->v[il]; }

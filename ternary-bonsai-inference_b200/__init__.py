@@ -11,14 +11,15 @@ import it with importlib:
 from . import _abi
 from ._abi import BonsaiKvError
 from .device import Context, DeviceBuffer, Event, PinnedArray
-from .forward import AttnCache, attn_step, full_attention_step, n_ctx_env
+from .forward import (AttnCache, attn_step, full_attention_layer_core, full_attention_step, n_ctx_env,
+                      rms_norm_rows)
 from .kvquant import (DEFAULT_HD, F16, F32, KvMode, Planar, PlanarQuant, codebook, f32_to_half,
                       givens_table, half_to_f32, mode_from_env, packed_bytes, parse_mode,
                       quantizers_for, rope_imrope)
 
 __all__ = ["AttnCache", "BonsaiKvError", "Context", "DEFAULT_HD", "DeviceBuffer", "Event", "F16", "F32",
            "KvMode", "PinnedArray", "Planar", "PlanarQuant", "attn_step", "codebook", "f32_to_half",
-           "full_attention_step", "givens_table", "half_to_f32", "mode_from_env", "n_ctx_env",
+           "full_attention_layer_core", "full_attention_step", "givens_table", "half_to_f32", "mode_from_env", "n_ctx_env", "rms_norm_rows",
            "packed_bytes", "parse_mode", "quantizers_for", "rope_imrope"]
 
 

@@ -30,6 +30,7 @@ SOURCES = {
     "bk_decode_mma.cu": [],
     "bk_decode_f16.cu": [],
     "bk_noalloc.cu": [],
+    "bk_layer.cu": ["--fmad=false"],
     "bk_p2p.cu": [],
     "bk_host_tables.cpp": [],
 }

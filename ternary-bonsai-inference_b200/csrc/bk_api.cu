@@ -229,6 +229,7 @@ void bk_ctx_destroy(bk_ctx *ctx) {
     if (ctx->d_err) cudaFree(ctx->d_err);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->d_stage) cudaFree(ctx->d_stage);
+    if (ctx->d_layer) cudaFree(ctx->d_layer);
     if (ctx->h_desc) cudaFreeHost(ctx->h_desc);
     if (ctx->d_desc) cudaFree(ctx->d_desc);
     for (int i = 0; i < kDescSlots; i++)
@@ -632,6 +633,9 @@ void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out
     a.layer_pos0 = layer * c->cfg.n_seqs * c->cfg.n_ctx;
     a.n_ctx = c->cfg.n_ctx;
     a.new_k = a.new_v = nullptr;
+    a.q_stride = a.gate_stride = kHd;
+    a.q_norm_w = a.k_norm_w = a.gate = nullptr;
+    a.eps = 0.f;
     a.k_rows_w = c->k_rows(layer, 0);
     a.v_rows_w = c->v_rows(layer, 0);
     a.k_norms_w = c->k_norms(layer, 0);
@@ -711,7 +715,8 @@ bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos) {
 }  // namespace bk
 
 static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const int32_t *seq_ids, const int32_t *n_pos,
-                             const int32_t *q_pos, const float *q_dev, float *out_dev, int partial, const char *who) {
+                             const int32_t *q_pos, const float *q_dev, float *out_dev, int partial, const char *who,
+                             const float *gate_dev = nullptr, int gate_stride = kHd) {
     if (!c || layer < 0 || layer >= c->cfg.n_layers)
         return fail(c ? c->ctx : nullptr, BK_ERR_INVALID, std::string(who) + ": bad layer");
     bk_ctx *ctx = c->ctx;
@@ -725,6 +730,8 @@ static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const i
     fill_decode_args(c, layer, partial, &a);
     a.q = q_dev;
     a.out = out_dev;
+    a.gate = partial ? nullptr : gate_dev;
+    a.gate_stride = gate_stride;
 
     // Validate everything first, then sort the sequences into the two kernel classes.
     std::vector<DecodeEntry> cls[2];
@@ -825,6 +832,121 @@ bk_status bk_attn_step_host(bk_cache *c, int32_t layer, int32_t seq, int32_t pos
     BK_CUDA(ctx, cudaMemcpyAsync(h_out, d_out, qb, cudaMemcpyDeviceToHost, ctx->stream));
     BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     memcpy(out_host, h_out, qb);
+    return BK_OK;
+}
+
+bk_status bk_attn_layer_step(bk_cache *c, int32_t layer, int32_t seq, int32_t pos, const float *qfull_dev,
+                             const float *kraw_dev, const float *vraw_dev, const float *q_norm_w_dev,
+                             const float *k_norm_w_dev, float eps, float *out_dev) {
+    if (!valid_layer_seq(c, layer, seq)) return fail(c ? c->ctx : nullptr, BK_ERR_INVALID, "bk_attn_layer_step: bad layer/seq");
+    bk_ctx *ctx = c->ctx;
+    if (!qfull_dev || !kraw_dev || !vraw_dev || !q_norm_w_dev || !k_norm_w_dev || !out_dev)
+        return fail(ctx, BK_ERR_INVALID, "bk_attn_layer_step: null argument");
+    if (pos >= c->cfg.n_ctx)
+        return fail(ctx, BK_ERR_RANGE,
+                    "bk_attn_layer_step: position " + std::to_string(pos) + " exceeds context " +
+                        std::to_string(c->cfg.n_ctx) + " (raise BONSAI_CTX)");
+    if (pos != c->n_pos[c->slab(layer, seq)])
+        return fail(ctx, BK_ERR_INVALID,
+                    "bk_attn_layer_step: pos " + std::to_string(pos) + " is not the next row (" +
+                        std::to_string(c->n_pos[c->slab(layer, seq)]) + ")");
+    if (pos >= c->rope->n_pos) return fail(ctx, BK_ERR_RANGE, "bk_attn_layer_step: position beyond the rope table");
+    bk_status st = bind(ctx);
+    if (st != BK_OK) return st;
+    const int32_t np = pos + 1, qp = pos;
+    const int n_head = c->cfg.n_head, n_kv = c->cfg.n_kv;
+    DecodeArgs a;
+    fill_decode_args(c, layer, 0, &a);
+    if (decode_entry_uses_mma(ctx, a, np)) {
+        // One launch: q is read in place from the interleaved projection output and normed in the
+        // kernel's q set-up, the new k row is normed in the fused append, the gate is applied where
+        // the output is written.
+        a.q = qfull_dev;
+        a.q_stride = 2 * kHd;
+        a.q_norm_w = q_norm_w_dev;
+        a.k_norm_w = k_norm_w_dev;
+        a.eps = eps;
+        a.gate = qfull_dev + kHd;
+        a.gate_stride = 2 * kHd;
+        a.out = out_dev;
+        a.new_k = kraw_dev;
+        a.new_v = vraw_dev;
+        const DecodeEntry e{0, seq, np, qp};
+        st = launch_decode_group(ctx, a, &e, 1, true, kMaxItems);
+        if (st == BK_OK) c->n_pos[c->slab(layer, seq)] = np;
+        return st;
+    }
+    // Other caches: norm q and k in one small launch, then append and decode as usual; the gate is
+    // applied by the decode kernel's output stage.
+    const size_t need = (size_t)(n_head + n_kv) * kHd;
+    if (ctx->d_layer_floats < need) {
+        BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->d_layer) cudaFree(ctx->d_layer);
+        ctx->d_layer = nullptr;
+        ctx->d_layer_floats = 0;
+        BK_CUDA(ctx, cudaMalloc((void **)&ctx->d_layer, need * sizeof(float)));
+        ctx->d_layer_floats = need;
+    }
+    float *qn = ctx->d_layer, *kn = ctx->d_layer + (size_t)n_head * kHd;
+    const NormSeg sq{qfull_dev, (size_t)2 * kHd, q_norm_w_dev, qn, n_head};
+    const NormSeg sk{kraw_dev, (size_t)kHd, k_norm_w_dev, kn, n_kv};
+    if ((st = launch_rms_norm_rows(ctx, sq, sk, kHd, eps)) != BK_OK) return st;
+    if ((st = bk_append(c, layer, seq, pos, 1, kn, vraw_dev)) != BK_OK) return st;
+    return decode_impl(c, layer, 1, &seq, &np, &qp, qn, out_dev, 0, "bk_attn_layer_step", qfull_dev + kHd, 2 * kHd);
+}
+
+bk_status bk_attn_layer_step_host(bk_cache *c, int32_t layer, int32_t seq, int32_t pos, const float *qfull_host,
+                                  const float *kraw_host, const float *vraw_host, const float *q_norm_w_host,
+                                  const float *k_norm_w_host, float eps, float *out_host) {
+    if (!valid_layer_seq(c, layer, seq))
+        return fail(c ? c->ctx : nullptr, BK_ERR_INVALID, "bk_attn_layer_step_host: bad layer/seq");
+    bk_ctx *ctx = c->ctx;
+    if (!qfull_host || !kraw_host || !vraw_host || !q_norm_w_host || !k_norm_w_host || !out_host)
+        return fail(ctx, BK_ERR_INVALID, "bk_attn_layer_step_host: null argument");
+    bk_status st = bind(ctx);
+    if (st != BK_OK) return st;
+    const size_t qfb = (size_t)c->cfg.n_head * 2 * kHd * sizeof(float), kb = (size_t)c->cfg.n_kv * kHd * sizeof(float);
+    const size_t wb = kHd * sizeof(float), ob = (size_t)c->cfg.n_head * kHd * sizeof(float);
+    const size_t in_bytes = qfb + 2 * kb + 2 * wb;
+    if ((st = ensure_stage(ctx, in_bytes + ob)) != BK_OK) return st;
+    char *h = (char *)ctx->h_stage, *d = (char *)ctx->d_stage;
+    memcpy(h, qfull_host, qfb);
+    memcpy(h + qfb, kraw_host, kb);
+    memcpy(h + qfb + kb, vraw_host, kb);
+    memcpy(h + qfb + 2 * kb, q_norm_w_host, wb);
+    memcpy(h + qfb + 2 * kb + wb, k_norm_w_host, wb);
+    BK_CUDA(ctx, cudaMemcpyAsync(d, h, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
+    float *d_out = (float *)(d + in_bytes), *h_out = (float *)(h + in_bytes);
+    st = bk_attn_layer_step(c, layer, seq, pos, (const float *)d, (const float *)(d + qfb), (const float *)(d + qfb + kb),
+                            (const float *)(d + qfb + 2 * kb), (const float *)(d + qfb + 2 * kb + wb), eps, d_out);
+    if (st != BK_OK) return st;
+    BK_CUDA(ctx, cudaMemcpyAsync(h_out, d_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    memcpy(out_host, h_out, ob);
+    return BK_OK;
+}
+
+bk_status bk_rms_norm_rows(bk_ctx *ctx, int32_t n_rows, int32_t row_len, const float *x_host, const float *w_host,
+                           float eps, float *out_host) {
+    if (!ctx) return fail(nullptr, BK_ERR_INVALID, "bk_rms_norm_rows: ctx is null");
+    if (n_rows < 0 || row_len < 1 || !x_host || !w_host || !out_host)
+        return fail(ctx, BK_ERR_INVALID, "bk_rms_norm_rows: bad argument");
+    if (row_len > 1024) return fail(ctx, BK_ERR_UNSUPPORTED, "bk_rms_norm_rows: row_len above 1024");
+    if (n_rows == 0) return BK_OK;
+    bk_status st = bind(ctx);
+    if (st != BK_OK) return st;
+    const size_t xb = (size_t)n_rows * row_len * sizeof(float), wb = (size_t)row_len * sizeof(float);
+    if ((st = ensure_stage(ctx, 2 * xb + wb)) != BK_OK) return st;
+    char *h = (char *)ctx->h_stage, *d = (char *)ctx->d_stage;
+    memcpy(h, x_host, xb);
+    memcpy(h + xb, w_host, wb);
+    BK_CUDA(ctx, cudaMemcpyAsync(d, h, xb + wb, cudaMemcpyHostToDevice, ctx->stream));
+    const NormSeg s0{(const float *)d, (size_t)row_len, (const float *)(d + xb), (float *)(d + xb + wb), n_rows};
+    const NormSeg s1{nullptr, 0, nullptr, nullptr, 0};
+    if ((st = launch_rms_norm_rows(ctx, s0, s1, row_len, eps)) != BK_OK) return st;
+    BK_CUDA(ctx, cudaMemcpyAsync(h + xb + wb, d + xb + wb, xb, cudaMemcpyDeviceToHost, ctx->stream));
+    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    memcpy(out_host, h + xb + wb, xb);
     return BK_OK;
 }
 

@@ -6,8 +6,9 @@
 //     last one re-reads every chunk's triple and combines them.  Nobody waits for anybody.
 //   * planar V: the combined accumulator is still in Givens-rotated space and is rotated back
 //     once here (src/forward.rs:349, shaders/attn_out_q.comp:85-91);
-//   * output: acc / L, or the unnormalised (acc, m, l) triple when the caller merges chunks
-//     held by other caches / GPUs itself.
+//   * output: acc / L (times sigmoid(gate) when the layer form of the step passes a gate), or
+//     the unnormalised (acc, m, l) triple when the caller merges chunks held by other caches /
+//     GPUs itself.
 #pragma once
 
 #include <cuda/atomic>
@@ -31,6 +32,16 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
     const bool act = threadIdx.x < 256;
     const int tid0 = act ? tid : (1 << 30);  // loop start that keeps idle threads out of strided loops
     const int warp = tid >> 5, lane = tid & 31;
+    // gate values of this thread's outputs (coordinate tid of every head); the CTA that writes the
+    // output fetches them as early as it knows it is the one, so they travel with the partials
+    const float *gate = (a.gate && !a.partial && act)
+                            ? a.gate + ((size_t)slot * a.n_head + (size_t)kv * NREP) * a.gate_stride + tid : nullptr;
+    float gv[NREP];
+    auto load_gate = [&]() {
+#pragma unroll
+        for (int r = 0; r < NREP; r++) gv[r] = gate ? __ldg(gate + (size_t)r * a.gate_stride) : 0.f;
+    };
+    if (n_chunks <= 1) load_gate();
     if (n_chunks > 1) {
         float *part = a.partials + ((size_t)item * NREP) * kScratchStride;
         for (int i = tid0; i < NREP * kHd; i += nt) {
@@ -74,6 +85,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
             }
         };
         load_batch(0);
+        load_gate();
         // one warp per head: global max, the chunks' rescale factors and the merged l, from one
         // sweep over the (m, l) pairs
         if (warp < NREP) {
@@ -180,9 +192,15 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
         }
     } else {
         float *out = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP) * kHd;
-        for (int i = tid0; i < NREP * kHd; i += nt) {
-            const float Ls = s_L[i / kHd];
-            out[i] = Ls > 0.f ? s_acc[i] / Ls : 0.f;
+        if (act) {
+#pragma unroll
+            for (int r = 0; r < NREP; r++) {
+                const float Ls = s_L[r];
+                float o = Ls > 0.f ? s_acc[r * kHd + tid] / Ls : 0.f;
+                // src/forward.rs:379-382 with src/kernels.rs:162: out *= 1 / (1 + exp(-gate))
+                if (gate) o *= 1.0f / (1.0f + expf(-gv[r]));
+                out[r * kHd + tid] = o;
+            }
         }
     }
 }

@@ -42,6 +42,7 @@ struct Other {
     float sq[8 * kHd];                   // q of the group while it is roped
     float new_row[2][kHd];               // the newest token's k and v of this kv head (fused append)
     float2 rope_row[kHd / 2];            // (cos, sin) of the q position
+    float qw[kHd];                       // q RMSNorm weight (layer form of the step)
     float m_w[kFW][8], l_w[kFW][8];
     float M[8], L[8];
     int last;
@@ -116,6 +117,8 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
         const float2 *cs = a.rope + (size_t)meta.q_pos[s] * half;
         for (int i = tid; i < half; i += kFT) o.rope_row[i] = cs[i];
     }
+    if (a.q_norm_w)
+        for (int i = tid; i < kHd; i += kFT) o.qw[i] = a.q_norm_w[i];
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     // ---- fused append: the CTA that scans the last chunk of this kv head stores the head's new K
@@ -129,6 +132,13 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
             reinterpret_cast<float4 *>(sx)[lane] = reinterpret_cast<const float4 *>(src)[lane];
             reinterpret_cast<float4 *>(sx)[lane + 32] = reinterpret_cast<const float4 *>(src)[lane + 32];
             __syncwarp();
+            if (warp == 0 && a.k_norm_w) {  // per-head RMSNorm of the new k row, bit-exact (src/forward.rs:244-245)
+                float sc = 0.f;
+                if (lane == 0) sc = rms_scale_ref(sx, kHd, a.eps);
+                sc = __shfl_sync(0xffffffffu, sc, 0);
+                for (int i = lane; i < kHd; i += 32) sx[i] = __fmul_rn(__fmul_rn(sx[i], sc), a.k_norm_w[i]);
+                __syncwarp();
+            }
             if (warp == 0 && !a.no_rope) {
                 const int half = a.n_rot >> 1;
                 for (int j = lane; j < half; j += 32) {
@@ -158,9 +168,25 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     // ---- q: rope, scale, split into f16 hi/lo, laid out as B fragments ---------------------
     {
         float *sq = o.sq;  // [NREP][256]
-        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * kHd;
-        for (int i = tid; i < NREP * kHd; i += kFT) sq[i] = q[i];
-        __syncthreads();  // also: the rope row is complete
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * a.q_stride;
+        for (int i = tid; i < NREP * kHd; i += kFT) sq[i] = q[(size_t)(i >> 8) * a.q_stride + (i & 255)];
+        __syncthreads();
+        if (a.q_norm_w) {  // per-head RMSNorm of q (src/forward.rs:242-243); q is not stored, so a tree sum will do
+            if (warp < NREP) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < kHd / 32; j++) {
+                    const float x = sq[warp * kHd + lane + 32 * j];
+                    ss = fmaf(x, x, ss);
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                if (lane == 0) o.M[warp] = 1.0f / sqrtf(ss / (float)kHd + a.eps);
+            }
+            __syncthreads();
+            for (int i = tid; i < NREP * kHd; i += kFT) sq[i] = sq[i] * o.M[i >> 8] * o.qw[i & 255];
+            __syncthreads();
+        }  // also: the rope row is complete
         if (!a.no_rope) {
             const int half = a.n_rot >> 1;
             for (int i = tid; i < NREP * half; i += kFT) {

@@ -55,9 +55,8 @@ constexpr int kStageBytes = 2 * kTileBytes + 2 * kNormBytes;  // K tile, V tile,
 constexpr int kMaxStages = 6;
 
 struct Other {                          // lives outside the lookup table
-    __half q_hi[8][kHd];
-    __half q_lo[8][kHd];
-    uint2 q_hi_frag[16][32], q_lo_frag[16][32];  // q as B fragments: [k-step][lane], 8-byte conflict-free reads
+    uint2 q_hi_frag[16][32], q_lo_frag[16][32];  // q (f16 hi and lo parts) as B fragments: [k-step][lane], 8-byte conflict-free reads
+    float qw[kHd];                       // q RMSNorm weight (layer form of the step)
     float m_w[kMW][8], l_w[kMW][8];
     float sq[8 * kHd];                   // q of the group while it is roped and rotated
     float new_row[2][kHd];               // the newest token's k and v of this kv head (fused append)
@@ -183,6 +182,8 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             const float2 *cs = a.rope + (size_t)meta.q_pos[s] * half;
             for (int i = tid; i < half; i += kMT) o.rope_row[i] = cs[i];
         }
+        if (a.q_norm_w)
+            for (int i = tid; i < kHd; i += kMT) o.qw[i] = a.q_norm_w[i];
         const float c_lo = a.book[lane & 15] * lut_alpha;  // lanes 0..15 hold the 16 scaled centroids
         // the lookup table: entry e -> half2(alpha*c[e & 15], alpha*c[e >> 4]), one copy per lane
         for (int e = warp; e < 256; e += kMW) {
@@ -206,6 +207,13 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         __syncthreads();  // new rows, centroids, Givens table and rope row are in shared memory
         if (warp < 2) {
             float *sx = o.new_row[warp];
+            if (warp == 0 && a.k_norm_w) {  // per-head RMSNorm of the new k row, bit-exact (src/forward.rs:244-245)
+                float sc = 0.f;
+                if (lane == 0) sc = rms_scale_ref(sx, kHd, a.eps);
+                sc = __shfl_sync(0xffffffffu, sc, 0);
+                for (int i = lane; i < kHd; i += 32) sx[i] = __fmul_rn(__fmul_rn(sx[i], sc), a.k_norm_w[i]);
+                __syncwarp();
+            }
             if (warp == 0 && !a.no_rope) {
                 const int half = a.n_rot >> 1;
                 for (int j = lane; j < half; j += 32) {
@@ -245,9 +253,25 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     // bytes of the bookkeeping block, since the table's region is already live) ---------------
     {
         float *sq = o.sq;  // [NREP][256]
-        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * kHd;
-        for (int i = tid; i < NREP * kHd; i += kMT) sq[i] = q[i];
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * a.q_stride;
+        for (int i = tid; i < NREP * kHd; i += kMT) sq[i] = q[(size_t)(i >> 8) * a.q_stride + (i & 255)];
         __syncthreads();  // also: givens / rope row / table are complete
+        if (a.q_norm_w) {  // per-head RMSNorm of q (src/forward.rs:242-243); q is not stored, so a tree sum will do
+            if (warp < NREP) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < kHd / 32; j++) {
+                    const float x = sq[warp * kHd + lane + 32 * j];
+                    ss = fmaf(x, x, ss);
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                if (lane == 0) o.M[warp] = 1.0f / sqrtf(ss / (float)kHd + a.eps);
+            }
+            __syncthreads();
+            for (int i = tid; i < NREP * kHd; i += kMT) sq[i] = sq[i] * o.M[i >> 8] * o.qw[i & 255];
+            __syncthreads();
+        }
         if (!a.no_rope) {
             const int half = a.n_rot >> 1;
             for (int i = tid; i < NREP * half; i += kMT) {
@@ -259,36 +283,32 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             }
             __syncthreads();
         }
-        // 1/sqrt(hd) * log2(e) / alpha: the scores come out in the exp2 domain, alpha undone
+        // 1/sqrt(hd) * log2(e) / alpha: the scores come out in the exp2 domain, alpha undone.
+        // Givens rotation, scale, f16 hi/lo split, written straight into the B-fragment layout:
+        // k-step ks = c*8 + w*2 + bp covers coordinates (2t+c)*32 + w*8 + bp*4 + 0..3 of head g.
         const float qscale = rsqrtf((float)kHd) * 1.4426950408889634f / lut_alpha;
-        for (int i = tid; i < 8 * (kHd / 2); i += kMT) {
-            const int r = i / (kHd / 2), pr = i - r * (kHd / 2);
-            float o0 = 0.f, o1 = 0.f;
-            if (r < NREP) {
-                givens_fwd(sq[r * kHd + 2 * pr], sq[r * kHd + 2 * pr + 1], o.givens[2 * pr], o.givens[2 * pr + 1], o0, o1);
-                o0 *= qscale;
-                o1 *= qscale;
+        for (int i = tid; i < 16 * 32; i += kMT) {
+            const int ks = i >> 5, ln = i & 31, gg = ln >> 2, tt = ln & 3;
+            const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
+            const int d0 = (2 * tt + c) * 32 + w * 8 + bp * 4;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            if (gg < NREP) {
+                givens_fwd(sq[gg * kHd + d0], sq[gg * kHd + d0 + 1], o.givens[d0], o.givens[d0 + 1], x[0], x[1]);
+                givens_fwd(sq[gg * kHd + d0 + 2], sq[gg * kHd + d0 + 3], o.givens[d0 + 2], o.givens[d0 + 3], x[2], x[3]);
             }
-            const __half h0 = __float2half_rn(o0), h1 = __float2half_rn(o1);
-            o.q_hi[r][2 * pr] = h0;
-            o.q_hi[r][2 * pr + 1] = h1;
-            o.q_lo[r][2 * pr] = __float2half_rn(o0 - __half2float(h0));
-            o.q_lo[r][2 * pr + 1] = __float2half_rn(o1 - __half2float(h1));
+            __half h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                x[e] *= qscale;
+                h[e] = __float2half_rn(x[e]);
+                l[e] = __float2half_rn(x[e] - __half2float(h[e]));
+            }
+            auto pack = [](__half lo, __half hi) { return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16); };
+            o.q_hi_frag[ks][ln] = make_uint2(pack(h[0], h[1]), pack(h[2], h[3]));
+            o.q_lo_frag[ks][ln] = make_uint2(pack(l[0], l[1]), pack(l[2], l[3]));
         }
         __syncthreads();
     }
-
-    // ---- q fragments: k-step ks = c*8 + w*2 + bp covers coordinates (2t+c)*32 + w*8 + bp*4 + 0..3
-    if (warp == 0) {  // one warp lays the fragments out (every warp has the same (g, t) view)
-#pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-            const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
-            const int d0 = (2 * t + c) * 32 + w * 8 + bp * 4;
-            o.q_hi_frag[ks][lane] = *reinterpret_cast<const uint2 *>(&o.q_hi[g][d0]);
-            o.q_lo_frag[ks][lane] = *reinterpret_cast<const uint2 *>(&o.q_lo[g][d0]);
-        }
-    }
-    __syncthreads();
     const uint32_t qh_addr = other_addr + (uint32_t)offsetof(Other, q_hi_frag) + (uint32_t)lane * 8u;
     const uint32_t ql_addr = other_addr + (uint32_t)offsetof(Other, q_lo_frag) + (uint32_t)lane * 8u;
     auto q_frag = [&](uint32_t addr0, int ks, uint32_t &x, uint32_t &y) {

@@ -98,6 +98,15 @@ __device__ __forceinline__ float serial_norm(const float *x, int n) {
     return __fsqrt_rn(acc);
 }
 
+// src/kernels.rs:112-116 (rms_norm_rows): sequential f32 sum of squares, then
+// 1 / sqrt(ss / n + eps); the row is then (x * scale) * w, two roundings, left to right (:118).
+__device__ __forceinline__ float rms_scale_ref(const float *x, int n, float eps) {
+    float ss = 0.0f;
+#pragma unroll 16
+    for (int i = 0; i < n; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)n), eps)));
+}
+
 // The `bits`-wide little-endian field stream of src/kvquant.rs:152-165 (for hd = 256 every
 // pack_idx branch of the reference produces exactly this stream): 8 consecutive indices of a
 // row occupy `bits` whole bytes starting at byte (first_index/8)*bits.

@@ -64,6 +64,8 @@ struct bk_ctx {
     size_t h_stage_bytes = 0;
     void *d_stage = nullptr;
     size_t d_stage_bytes = 0;
+    float *d_layer = nullptr;              // normed q and k rows of the layer step (generic decode path)
+    size_t d_layer_floats = 0;
     // split-K scratch of the decode kernel: partial results and arrival counters
     float *d_partials = nullptr;
     unsigned *d_counters = nullptr;
@@ -174,6 +176,17 @@ struct DecodeArgs {
     const float *new_k, *new_v;
     uint8_t *k_rows_w, *v_rows_w;   // writable aliases of k_rows / v_rows
     float *k_norms_w, *v_norms_w;
+    // The layer form of the step (src/forward.rs:237-245, 379-382 around the attention core):
+    //   q_stride    floats between the q rows of consecutive heads (hd, or 2*hd when q is read in
+    //               place from the interleaved [q | gate] projection output); tensor-core path only
+    //   q_norm_w    when set, every q row gets the per-head RMSNorm with this weight [hd] first
+    //               (tensor-core path only; the generic path norms q in a kernel of its own)
+    //   k_norm_w    when set, the fused append norms the new k rows the same way before the rope
+    //   gate        when set (and not partial), out = attention * sigmoid(gate): row of head h at
+    //               gate + (slot * n_head + h) * gate_stride
+    int q_stride, gate_stride;
+    const float *q_norm_w, *k_norm_w, *gate;
+    float eps;
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
 
@@ -197,6 +210,16 @@ bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_r
                                 size_t total_pos, void *out_k, void *out_v);
 bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
 bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, bool qsplit);
+// RMSNorm over rows (bk_layer.cu): up to two row groups per launch, each with its own source
+// stride, weight and contiguous destination.
+struct NormSeg {
+    const float *src;
+    size_t stride;   // floats between consecutive source rows
+    const float *w;  // [row_len]
+    float *dst;      // [n_rows][row_len]
+    int n_rows;
+};
+bk_status launch_rms_norm_rows(bk_ctx *ctx, const NormSeg &s0, const NormSeg &s1, int row_len, float eps);
 bk_status launch_lse_merge(bk_ctx *ctx, int n_parts, int n_rows, int hd, const float *parts, float *out);
 
 bk_status launch_quantize(bk_ctx *ctx, int bits, int n_vec, const float *x, uint8_t *packed, float *norms);

@@ -138,6 +138,27 @@ class AttnCache:
                                                       va.ctypes.data, out.ctypes.data))
         return out
 
+    def layer_step(self, il, qfull, kraw, vraw, q_norm_w, k_norm_w, eps, pos, seq=0):
+        """The layer form of the step on host arrays: qfull [n_head, 2*hd] ([q | gate] per head),
+        kraw/vraw [n_kv, hd], norm weights [hd]; returns attention * sigmoid(gate), [n_head, hd]."""
+        qa = np.ascontiguousarray(qfull, np.float32).ravel()
+        ka = np.ascontiguousarray(kraw, np.float32).ravel()
+        va = np.ascontiguousarray(vraw, np.float32).ravel()
+        qw = np.ascontiguousarray(q_norm_w, np.float32).ravel()
+        kw = np.ascontiguousarray(k_norm_w, np.float32).ravel()
+        assert qa.size == 2 * self.n_head * self.hd and ka.size == self.n_kv_elems and va.size == self.n_kv_elems
+        assert qw.size == self.hd and kw.size == self.hd
+        out = np.zeros((self.n_head, self.hd), np.float32)
+        self.ctx.check(self.ctx.lib.bk_attn_layer_step_host(self.h, il, seq, pos, qa.ctypes.data, ka.ctypes.data,
+                                                            va.ctypes.data, qw.ctypes.data, kw.ctypes.data,
+                                                            float(eps), out.ctypes.data))
+        return out
+
+    def layer_step_device(self, il, qfull_ptr, kraw_ptr, vraw_ptr, q_norm_w_ptr, k_norm_w_ptr, eps, out_ptr, pos, seq=0):
+        """The same on device pointers (asynchronous)."""
+        self.ctx.check(self.ctx.lib.bk_attn_layer_step(self.h, il, seq, pos, qfull_ptr, kraw_ptr, vraw_ptr,
+                                                       q_norm_w_ptr, k_norm_w_ptr, float(eps), out_ptr))
+
     def step_device(self, il, q_ptr, k_ptr, v_ptr, out_ptr, pos, seq=0):
         """The attention step on device pointers (asynchronous): append at `pos`, attend over pos+1."""
         self.ctx.check(self.ctx.lib.bk_attn_step(self.h, il, seq, pos, q_ptr, k_ptr, v_ptr, out_ptr))
@@ -192,6 +213,29 @@ def full_attention_step(cache, il, q, k, v, pos, seq=0):
     """src/forward.rs:247-375: q [n_head*hd] and k [n_kv*hd] RMS-normed, v raw; returns the
     pre-gate attention output [n_head, hd]."""
     return cache.step(il, q, k, v, pos, seq)
+
+
+def full_attention_layer_core(cache, il, qfull, kraw, vraw, q_norm_w, k_norm_w, eps, pos, seq=0):
+    """src/forward.rs:237-382 without the matvecs: split [q | gate], per-head RMSNorm of q and k,
+    both ropes, the cache append, GQA attention and the sigmoid gate.  Returns the input of the
+    output projection, [n_head, hd]."""
+    return cache.layer_step(il, qfull, kraw, vraw, q_norm_w, k_norm_w, eps, pos, seq)
+
+
+def rms_norm_rows(x, w, row_len, eps, ctx=None):
+    """src/kernels.rs:97-122; raises like the reference on a bad weight length or a ragged x."""
+    from .kvquant import default_context
+    c = ctx or default_context()
+    xa = np.ascontiguousarray(x, np.float32).ravel()
+    wa = np.ascontiguousarray(w, np.float32).ravel()
+    if wa.size != row_len:
+        raise _abi.BonsaiKvError(_abi.BK_ERR_INVALID, f"rms_norm_rows: weight len {wa.size} != row_len {row_len}")
+    if xa.size % row_len != 0:
+        raise _abi.BonsaiKvError(_abi.BK_ERR_INVALID, f"rms_norm_rows: x len {xa.size} not divisible by row_len {row_len}")
+    out = np.zeros_like(xa)
+    c.check(c.lib.bk_rms_norm_rows(c.h, xa.size // row_len, row_len, xa.ctypes.data, wa.ctypes.data, float(eps),
+                                   out.ctypes.data))
+    return out
 
 
 def attn_step(ctx, q, kcache, vcache, n_pos, nheads, kvheads, hd):

@@ -28,6 +28,14 @@ def golden():
 
 
 @pytest.fixture(scope="session")
+def layer_golden():
+    """Vectors of tests/golden/gen_layer_golden.py (RMSNorm rows, sigmoid, the layer form of the step)."""
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "layer_golden.npz")
+    return dict(np.load(path))
+
+
+@pytest.fixture(scope="session")
 def bk():
     """The package (its directory name has a '-', hence importlib)."""
     import importlib

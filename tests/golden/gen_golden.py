@@ -280,17 +280,21 @@ def softmax_row(x):
 
 
 # -- forward.rs:247-375 -----------------------------------------------------
-def attention_steps(mode, bits, v_quant, n_tokens, seed):
-    """Run n_tokens decode steps from an empty cache; return per-step outputs and the cache."""
+def attention_steps(mode, bits, v_quant, n_tokens, seed, inputs=None):
+    """Run n_tokens decode steps from an empty cache; return per-step outputs and the cache.
+    `inputs(pos)` may supply the step's (q, k, v) instead of the seeded generator."""
     cb = codebook(HD, bits)[0] if mode == "planar" else None
     giv = givens_table(HD)
     kstore, vstore, knorm, vnorm = [], [], [], []
     outs = []
     scale = F(1.0) / F(np.sqrt(F(HD)))
     for pos in range(n_tokens):
-        q = rand_floats(seed + 3 * pos, N_HEAD * HD)
-        k = rand_floats(seed + 3 * pos + 1, N_KV * HD)
-        v = rand_floats(seed + 3 * pos + 2, N_KV * HD)
+        if inputs is not None:
+            q, k, v = inputs(pos)
+        else:
+            q = rand_floats(seed + 3 * pos, N_HEAD * HD)
+            k = rand_floats(seed + 3 * pos + 1, N_KV * HD)
+            v = rand_floats(seed + 3 * pos + 2, N_KV * HD)
         q = np.concatenate([rope_imrope(q[h * HD:(h + 1) * HD], pos, pos, pos, pos, N_ROT, SECTIONS, FREQ_BASE)
                             for h in range(N_HEAD)])
         k = np.concatenate([rope_imrope(k[h * HD:(h + 1) * HD], pos, pos, pos, pos, N_ROT, SECTIONS, FREQ_BASE)

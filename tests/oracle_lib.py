@@ -59,6 +59,9 @@ def load_oracle():
         "or_append_token": (None, [vp, sz, _f32p, _f32p, sz]),
         "or_attend": (i, [vp, sz, _f32p, sz, sz, _f32p, i]),
         "or_attn_step": (i, [vp, sz, _f32p, _f32p, _f32p, sz, _f32p, i]),
+        "or_rms_norm_rows": (i, [_f32p, sz, _f32p, sz, sz, C.c_float, _f32p]),
+        "or_sigmoid": (C.c_float, [C.c_float]),
+        "or_attn_layer_step": (i, [vp, sz, _f32p, _f32p, _f32p, _f32p, _f32p, C.c_float, sz, _f32p, i]),
         "or_rand_floats": (None, [C.c_uint64, sz, _f32p]),
         "or_max_threads": (i, []),
     }
@@ -115,6 +118,16 @@ class OracleCache:
                                    np.ascontiguousarray(v, np.float32).ravel(), pos, out, threads)
         if rc != 0:
             raise ValueError(f"or_attn_step rc={rc}")
+        return out.reshape(self.n_head, self.hd)
+
+    def layer_step(self, il, qfull, kraw, vraw, q_norm_w, k_norm_w, eps, pos, threads=1):
+        """src/forward.rs:237-382 without the matvecs."""
+        out = np.zeros(self.n_head * self.hd, dtype=np.float32)
+        f = lambda a: np.ascontiguousarray(a, np.float32).ravel()
+        rc = self.lib.or_attn_layer_step(self.h, il, f(qfull), f(kraw), f(vraw), f(q_norm_w), f(k_norm_w), eps, pos,
+                                         out, threads)
+        if rc != 0:
+            raise ValueError(f"or_attn_layer_step rc={rc}")
         return out.reshape(self.n_head, self.hd)
 
     def _view(self, fn, il, count, dtype):
@@ -185,6 +198,18 @@ class Oracle:
         if rc != 0:
             raise ValueError("softmax_rows: length not divisible by row_len")
         return out
+
+    def rms_norm_rows(self, x, w, row_len, eps):
+        x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+        w = np.ascontiguousarray(w, dtype=np.float32).ravel()
+        out = np.zeros_like(x)
+        rc = self.lib.or_rms_norm_rows(x, x.size, w, w.size, row_len, eps, out)
+        if rc != 0:
+            raise ValueError("rms_norm_rows: bad weight length or ragged x")
+        return out
+
+    def sigmoid(self, x):
+        return float(self.lib.or_sigmoid(x))
 
     def pq(self, hd, bits):
         return OraclePQ(self.lib, hd, bits)

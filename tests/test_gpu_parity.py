@@ -601,3 +601,79 @@ def test_nearest_centroid_search_equals_the_reference_scan(bk, gpu_ctx, oracle, 
         p_ref, n_ref = opq.quantize(x[r])
         assert np.array_equal(packed[r], p_ref), (bits, r)
         assert bits_of(norms[r]) == bits_of(n_ref)
+
+
+# ---------------------------------------------------------------------------
+# the layer form of the step: q|gate split, per-head RMSNorm, sigmoid gate
+# ---------------------------------------------------------------------------
+
+def test_rms_norm_rows_bits(bk, gpu_ctx, oracle, layer_golden):
+    """bk_rms_norm_rows against the golden vectors and the oracle, bit for bit; the reference's
+    two error cases (src/kernels.rs:810-811)."""
+    g = layer_golden
+    y = bk.rms_norm_rows(g["rms_small_x"], g["rms_small_w"], 4, 1e-6, ctx=gpu_ctx)
+    assert np.array_equal(bits_of(y), g["rms_small_out"])
+    y = bk.rms_norm_rows(g["rms_rows_x"].view(np.float32), g["rms_rows_w"].view(np.float32), HD, 1e-6, ctx=gpu_ctx)
+    assert np.array_equal(bits_of(y), g["rms_rows_out"])
+    rng = np.random.default_rng(3)
+    for row_len, n_rows in ((256, 28), (128, 48), (1, 5), (1024, 3), (77, 9)):
+        x = (rng.standard_normal(n_rows * row_len) * 3).astype(np.float32)
+        w = rng.standard_normal(row_len).astype(np.float32)
+        got = bk.rms_norm_rows(x, w, row_len, 1e-6, ctx=gpu_ctx)
+        assert np.array_equal(bits_of(got), bits_of(oracle.rms_norm_rows(x, w, row_len, 1e-6))), row_len
+    with pytest.raises(bk.BonsaiKvError):
+        bk.rms_norm_rows(g["rms_small_x"], g["rms_small_w"], 3, 1e-6, ctx=gpu_ctx)
+    with pytest.raises(bk.BonsaiKvError):
+        bk.rms_norm_rows(g["rms_small_x"], g["rms_small_w"][:2], 4, 1e-6, ctx=gpu_ctx)
+
+
+@pytest.mark.parametrize("tag", ["planar4", "f16"])
+def test_layer_step_golden(bk, gpu_ctx, layer_golden, tag):
+    """Three layer steps from an empty cache against the committed vectors."""
+    g = {k[len(f"layer_{tag}_"):]: v for k, v in layer_golden.items() if k.startswith(f"layer_{tag}_")}
+    f = lambda a: a.view(np.float32)
+    n = g["out"].shape[0]
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=16)
+    for pos in range(n):
+        out = bk.full_attention_layer_core(cache, 0, f(g["qfull"])[pos], f(g["kraw"])[pos], f(g["vraw"])[pos],
+                                           f(g["qw"]), f(g["kw"]), 1e-6, pos)
+        assert_close(out.ravel(), f(g["out"])[pos], f"{tag} step {pos}")
+    d = cache.dump_kv(0)
+    if tag == "planar4":
+        assert np.array_equal(d["kq"].reshape(n * 4, -1), g["k"]) and np.array_equal(d["vq"].reshape(n * 4, -1), g["v"])
+        assert np.array_equal(bits_of(d["kn"].ravel()), g["kn"]) and np.array_equal(bits_of(d["vn"].ravel()), g["vn"])
+    else:
+        assert np.array_equal(d["k16"].reshape(n * 4, -1), g["k"]) and np.array_equal(d["v16"].reshape(n * 4, -1), g["v"])
+    cache.close()
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq,n0", [("planar4", MODE_PLANAR, 4, True, 2600), ("f16", MODE_F16, 0, False, 2600),
+                                                 ("planar4", MODE_PLANAR, 4, True, 300), ("f32", MODE_F32, 0, False, 500),
+                                                 ("planar3", MODE_PLANAR, 3, True, 2600), ("planar4k", MODE_PLANAR, 4, False, 700)])
+def test_layer_step_on_a_filled_cache(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0):
+    """Layer steps after a prefill, on caches that take the tensor-core path (one launch per
+    step) and on ones that do not: gated outputs within the bar, stored rows bit-exact."""
+    rng = np.random.default_rng(n0 + bits)
+    steps = 6
+    k, v = synth_kv(rng, n0)
+    qfull = (rng.standard_normal((steps, NH, 2 * HD)) * 2).astype(np.float32)
+    kraw = (rng.standard_normal((steps, NKV, HD)) * 3).astype(np.float32)
+    vraw = rng.standard_normal((steps, NKV, HD)).astype(np.float32)
+    qw = (1 + 0.3 * rng.standard_normal(HD)).astype(np.float32)
+    kw = (1 + 0.3 * rng.standard_normal(HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=n0 + steps)
+    ref = oracle.cache(mode, bits, vq)
+    cache.append(0, k, v)
+    for p in range(n0):
+        ref.append(0, k[p], v[p], p)
+    one_launch = n0 >= 2048 and tag in ("planar4", "f16")
+    for t in range(steps):
+        launches = gpu_ctx.launch_count
+        got = bk.full_attention_layer_core(cache, 0, qfull[t], kraw[t], vraw[t], qw, kw, 1e-6, n0 + t)
+        assert (gpu_ctx.launch_count - launches == 1) == one_launch
+        want = ref.layer_step(0, qfull[t], kraw[t], vraw[t], qw, kw, 1e-6, n0 + t, threads=8)
+        assert_close(got, want, f"{tag} step {t}")
+    compare_dumps(cache.dump_kv(0, pos0=n0 - 2), {key: val[n0 - 2:] for key, val in ref.dump(0).items()})
+    with pytest.raises(bk.BonsaiKvError):  # not the next row
+        bk.full_attention_layer_core(cache, 0, qfull[0], kraw[0], vraw[0], qw, kw, 1e-6, n0)
+    cache.close()

@@ -316,3 +316,61 @@ def test_golden_attention_steps(oracle, golden, tag, mode, bits, vq):
     else:
         assert np.array_equal(bits_of(d["k"].reshape(n * 4, -1)), bits_of(gk))
         assert np.array_equal(bits_of(d["v"].reshape(n * 4, -1)), bits_of(gv))
+
+
+# ---------------------------------------------------------------------------
+# the layer form of the step: q|gate split, per-head RMSNorm, sigmoid gate
+# ---------------------------------------------------------------------------
+
+def test_rms_norm_rows_matches_single_row_math(oracle):
+    """src/kernels.rs:790-811"""
+    x = np.array([1.0, 2.0, 3.0, 4.0, 0.5, -0.5, 2.0, -3.0], np.float32)
+    w = np.array([0.5, 1.0, 1.5, 2.0], np.float32)
+    eps = np.float32(1e-6)
+    y = oracle.rms_norm_rows(x, w, 4, eps)
+    for row in range(2):
+        src = x[4 * row:4 * row + 4]
+        ss = np.float32(0)
+        for v in src:
+            ss = np.float32(ss + v * v)
+        scale = np.float32(1.0) / np.sqrt(np.float32(ss / np.float32(4.0) + eps))
+        for i in range(4):
+            assert abs(y[4 * row + i] - src[i] * scale * w[i]) < 1e-6
+    with pytest.raises(ValueError):
+        oracle.rms_norm_rows(x, w, 3, eps)
+    with pytest.raises(ValueError):
+        oracle.rms_norm_rows(x, w[:2], 4, eps)
+
+
+def test_sigmoid_hits_expected_points(oracle):
+    """src/kernels.rs:834-835"""
+    assert abs(oracle.sigmoid(0.0) - 0.5) < 1e-7
+    assert oracle.sigmoid(-1000.0) == 0.0
+
+
+def test_golden_rms_norm_and_sigmoid(oracle, layer_golden):
+    g = layer_golden
+    y = oracle.rms_norm_rows(g["rms_small_x"], g["rms_small_w"], 4, 1e-6)
+    assert np.array_equal(bits_of(y), g["rms_small_out"])
+    y = oracle.rms_norm_rows(g["rms_rows_x"].view(np.float32), g["rms_rows_w"].view(np.float32), HD, 1e-6)
+    assert np.array_equal(bits_of(y), g["rms_rows_out"])
+    got = np.array([oracle.sigmoid(float(v)) for v in g["sigmoid_in"]], np.float32)
+    assert np.array_equal(bits_of(got), g["sigmoid_out"])
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq", [("planar4", MODE_PLANAR, 4, True), ("f16", MODE_F16, 0, False)])
+def test_golden_layer_steps(oracle, layer_golden, tag, mode, bits, vq):
+    """Three layer steps from an empty cache: gated outputs and stored bytes are bit-equal."""
+    g = {k[len(f"layer_{tag}_"):]: v for k, v in layer_golden.items() if k.startswith(f"layer_{tag}_")}
+    f = lambda a: a.view(np.float32)
+    c = oracle.cache(mode, bits, vq)
+    n = g["out"].shape[0]
+    for pos in range(n):
+        out = c.layer_step(0, f(g["qfull"])[pos], f(g["kraw"])[pos], f(g["vraw"])[pos], f(g["qw"]), f(g["kw"]), 1e-6, pos)
+        assert np.array_equal(bits_of(out.ravel()), g["out"][pos]), (tag, pos)
+    d = c.dump(0)
+    if mode == MODE_PLANAR:
+        assert np.array_equal(d["kq"].reshape(n * 4, -1), g["k"]) and np.array_equal(d["vq"].reshape(n * 4, -1), g["v"])
+        assert np.array_equal(bits_of(d["kn"].ravel()), g["kn"]) and np.array_equal(bits_of(d["vn"].ravel()), g["vn"])
+    else:
+        assert np.array_equal(d["k16"].reshape(n * 4, -1), g["k"]) and np.array_equal(d["v16"].reshape(n * 4, -1), g["v"])
