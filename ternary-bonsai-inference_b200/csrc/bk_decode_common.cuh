@@ -16,17 +16,33 @@
 
 #include "bk_device.cuh"
 #include "bk_internal.h"
+#include "bk_mma_common.cuh"
 
 namespace bk {
 
 constexpr int kFactorCap = 256;  // chunks whose rescale factors are cached in shared memory
 
-template <int NREP>
+// A free region of shared memory through which the last arriver streams the other chunks'
+// triples (the tensor-core kernels pass their drained stage ring): the TMA engine copies them in
+// rounds into the region's two halves, completion on the two mbarriers at `bar` (initialised by
+// the caller with count 1 and not used for anything else).  addr = 0: no region, the combine reads
+// the triples with ordinary loads.
+struct FinishSmem {
+    uint32_t addr = 0;    // shared-window address, 16-byte aligned
+    uint32_t bytes = 0;
+    uint32_t bar = 0;     // shared-window address of two consecutive mbarriers
+    uint8_t *ptr = nullptr;  // the same region as a generic pointer
+    int *err_flag = nullptr;
+};
+
+template <int NREP, bool STREAM = false>
 __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s, int kv, int item, int n_chunks,
                                             int first_item, float *s_acc /* [NREP][kHd] */, float *s_M, float *s_L,
                                             int *s_last, bool v_planar,
-                                            const float *givens = nullptr /* shared-memory copy, if the caller has one */) {
+                                            const float *givens = nullptr /* shared-memory copy, if the caller has one */,
+                                            FinishSmem fs = FinishSmem()) {
     __shared__ float s_f[kFactorCap * NREP];
+    __shared__ float s_scale[8];
     // the first 256 threads work; a larger CTA's remaining threads only take part in the barriers
     const int tid = threadIdx.x, nt = 256;
     const bool act = threadIdx.x < 256;
@@ -61,9 +77,106 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
             const unsigned ticket = cnt.fetch_add(1u, cuda::memory_order_acq_rel);
             *s_last = (ticket == (unsigned)(n_chunks - 1));
         }
+        if (STREAM) asm volatile("fence.proxy.async;\n" ::: "memory");  // this thread's shared-memory traffic before the copies below
         __syncthreads();
         if (!*s_last) return;
         const float *base = a.partials + (size_t)first_item * NREP * kScratchStride;
+        constexpr uint32_t kChunkBytes = NREP * kScratchStride * sizeof(float);
+        const int cap = STREAM ? min((int)((fs.bytes / 2) / kChunkBytes), 32) : 0;  // chunks per half
+        if (STREAM && cap >= 1 && fs.bytes >= (blockDim.x >> 6) * NREP * kHd * sizeof(float)) {
+            // ---- streamed combine: chunks arrive through the TMA engine, two rounds in flight ------
+            const int n_rounds = (n_chunks + cap - 1) / cap;
+            const uint32_t half_bytes = (uint32_t)cap * kChunkBytes;
+            auto issue_round = [&](int rd) {
+                const int c0 = rd * cap, nc = min(cap, n_chunks - c0);
+                const uint32_t bar = fs.bar + (uint32_t)(rd & 1) * 8u, dst = fs.addr + (uint32_t)(rd & 1) * half_bytes;
+                mbar_expect_tx(bar, (uint32_t)nc * kChunkBytes);
+                for (int c = 0; c < nc; c++)
+                    tma_bulk(dst + (uint32_t)c * kChunkBytes, base + (size_t)(c0 + c) * NREP * kScratchStride, kChunkBytes, bar);
+            };
+            if (tid == 0) {
+                // the other CTAs' stores (generic proxy, acquired through the ticket) before the async-proxy reads
+                asm volatile("fence.proxy.async;\n" ::: "memory");
+                issue_round(0);
+                if (n_rounds > 1) issue_round(1);
+            }
+            load_gate();
+            const int n_g = (int)blockDim.x >> 6, rg = tid >> 6, x = tid & 63;  // 64 threads span a row with float4
+            float4 sum[NREP];
+#pragma unroll
+            for (int r = 0; r < NREP; r++) sum[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            float M_run = -CUDART_INF_F, L_run = 0.f;  // warp r < NREP: running max and sum of head r
+            for (int rd = 0; rd < n_rounds; rd++) {
+                const int nc = min(cap, n_chunks - rd * cap);
+                const uint32_t bar = fs.bar + (uint32_t)(rd & 1) * 8u, parity = (uint32_t)(rd >> 1) & 1u;
+                int polls = 0;
+                while (!mbar_try_wait(bar, parity)) {
+                    if (++polls > kWaitPolls) {  // never expected; leave a mark and go on rather than hang
+                        if (tid == 0 && fs.err_flag) atomicExch(fs.err_flag, 3);
+                        break;
+                    }
+                }
+                const float *H = reinterpret_cast<const float *>(fs.ptr + (size_t)(rd & 1) * half_bytes);
+                if (warp < NREP) {  // one warp per head: this round's factors, online in the running max
+                    const int r = warp;
+                    const bool valid = lane < nc;
+                    const float2 ml = valid ? *reinterpret_cast<const float2 *>(H + ((size_t)lane * NREP + r) * kScratchStride + kHd)
+                                            : make_float2(-CUDART_INF_F, 0.f);
+                    float mx = ml.x;
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+                    const float Mn = fmaxf(M_run, mx);
+                    const float fc = ml.x > -CUDART_INF_F ? exp2f(ml.x - Mn) : 0.f;
+                    const float keep = M_run > -CUDART_INF_F ? exp2f(M_run - Mn) : 0.f;
+                    float ls = ml.y * fc;
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, off);
+                    L_run = fmaf(L_run, keep, ls);
+                    M_run = Mn;
+                    if (valid) s_f[lane * NREP + r] = fc;
+                    if (lane == 0) s_scale[r] = keep;
+                }
+                __syncthreads();
+#pragma unroll
+                for (int r = 0; r < NREP; r++) {
+                    const float k = s_scale[r];
+                    sum[r].x *= k; sum[r].y *= k; sum[r].z *= k; sum[r].w *= k;
+                }
+                for (int c = rg; c < nc; c += n_g) {
+#pragma unroll
+                    for (int r = 0; r < NREP; r++) {
+                        const float4 v = reinterpret_cast<const float4 *>(H + ((size_t)c * NREP + r) * kScratchStride)[x];
+                        const float f = s_f[c * NREP + r];
+                        sum[r].x = fmaf(v.x, f, sum[r].x);
+                        sum[r].y = fmaf(v.y, f, sum[r].y);
+                        sum[r].z = fmaf(v.z, f, sum[r].z);
+                        sum[r].w = fmaf(v.w, f, sum[r].w);
+                    }
+                }
+                __syncthreads();  // this half and the factors are free again
+                if (tid == 0 && rd + 2 < n_rounds) issue_round(rd + 2);
+            }
+            if (warp < NREP && lane == 0) {
+                s_M[warp] = M_run;
+                s_L[warp] = L_run;
+            }
+            // the groups' sums meet in the first half (every copy into it has been consumed), fixed order
+            float4 *scratch = reinterpret_cast<float4 *>(fs.ptr);  // [n_g][NREP][64]
+#pragma unroll
+            for (int r = 0; r < NREP; r++) scratch[((size_t)rg * NREP + r) * 64 + x] = sum[r];
+            __syncthreads();
+            if (act) {
+                const float *sf = reinterpret_cast<const float *>(fs.ptr);
+#pragma unroll
+                for (int r = 0; r < NREP; r++) {
+                    float t = 0.f;
+                    for (int g2 = 0; g2 < n_g; g2++) t += sf[((size_t)g2 * NREP + r) * kHd + tid];
+                    s_acc[r * kHd + tid] = t;
+                }
+            }
+            if (tid == 0) a.counters[s * a.n_kv + kv] = 0;  // ready for the next launch
+            __syncthreads();
+        } else {
         // 64 threads span one 256-float row with float4 loads; the four 64-thread groups take
         // every fourth chunk.  The (head, chunk) pairs of a thread form one flat list walked 24
         // independent 16-byte loads at a time.  The first batch is issued before the m/l sweep
@@ -166,6 +279,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
         }
         if (tid == 0) a.counters[s * a.n_kv + kv] = 0;  // ready for the next launch
         __syncthreads();
+        }
     }
 
     if (v_planar) {

@@ -47,6 +47,7 @@ struct Other {
     float M[8], L[8];
     int last;
     unsigned long long bar[kFW][kMaxStages];
+    unsigned long long fin_bar[2];       // the split-K combine's two streaming rounds
 };
 
 template <int NREP, bool QSPLIT>
@@ -69,6 +70,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     }
     const uint32_t bar0 = base + (uint32_t)offsetof(Other, bar) + (uint32_t)(warp * kMaxStages) * 8u;
     if (lane < kMaxStages) mbar_init(bar0 + lane * 8u, 1);
+    if (tid < 2) mbar_init(base + (uint32_t)offsetof(Other, fin_bar) + tid * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     __syncthreads();
 
@@ -120,6 +122,17 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     if (a.q_norm_w)
         for (int i = tid; i < kHd; i += kFT) o.qw[i] = a.q_norm_w[i];
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // q first: its loads are in flight before the tile copies below fill the memory system's queues
+    constexpr int kQPer = (NREP * kHd + kFT - 1) / kFT;
+    float q_reg[kQPer];
+    {
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * a.q_stride;
+#pragma unroll
+        for (int u = 0; u < kQPer; u++) {
+            const int i = tid + u * kFT;
+            q_reg[u] = i < NREP * kHd ? __ldg(q + (size_t)(i >> 8) * a.q_stride + (i & 255)) : 0.f;
+        }
+    }
 
     // ---- fused append: the CTA that scans the last chunk of this kv head stores the head's new K
     // and V rows first, exactly as the append kernel would (src/forward.rs:259-277: rope on K,
@@ -168,8 +181,11 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     // ---- q: rope, scale, split into f16 hi/lo, laid out as B fragments ---------------------
     {
         float *sq = o.sq;  // [NREP][256]
-        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * a.q_stride;
-        for (int i = tid; i < NREP * kHd; i += kFT) sq[i] = q[(size_t)(i >> 8) * a.q_stride + (i & 255)];
+#pragma unroll
+        for (int u = 0; u < kQPer; u++) {
+            const int i = tid + u * kFT;
+            if (i < NREP * kHd) sq[i] = q_reg[u];
+        }
         __syncthreads();
         if (a.q_norm_w) {  // per-head RMSNorm of q (src/forward.rs:242-243); q is not stored, so a tree sum will do
             if (warp < NREP) {
@@ -402,8 +418,14 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
         for (int r = 0; r < NREP; r++) s_acc[r * kHd + tid] = sums[r];
     __syncthreads();
 
+    FinishSmem fs;  // the ring behind the merged accumulator carries the streamed combine
+    fs.addr = ring0 + (uint32_t)(NREP * kHd * sizeof(float));
+    fs.bytes = ring_end - fs.addr;
+    fs.bar = base + (uint32_t)offsetof(Other, fin_bar);
+    fs.ptr = smem_raw + (fs.addr - base);
+    fs.err_flag = err_flag;
     const int first_item = meta.item_start[s] + kv * n_chunks;
-    finish_item<NREP>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, false);
+    finish_item<NREP, true>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, false, nullptr, fs);
 }
 
 template <int NREP, bool QSPLIT>

@@ -66,6 +66,7 @@ struct Other {                          // lives outside the lookup table
     float M[8], L[8];
     int last;
     unsigned long long bar[kMW][kMaxStages];  // one mbarrier per warp and stage
+    unsigned long long fin_bar[2];            // the split-K combine's two streaming rounds
 };
 static_assert(sizeof(Other) <= kOtherBytes, "Other does not fit");
 
@@ -120,6 +121,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     const uint32_t lane_base = lut_addr | (uint32_t)(lane << 2);
     const uint32_t bar0 = other_addr + (uint32_t)offsetof(Other, bar) + (uint32_t)(warp * kMaxStages) * 8u;
     if (lane < kMaxStages) mbar_init(bar0 + lane * 8u, 1);
+    if (tid < 2) mbar_init(other_addr + (uint32_t)offsetof(Other, fin_bar) + tid * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     __syncthreads();
 
@@ -193,6 +195,17 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         }
     }
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // q first: its loads are in flight before the tile copies below fill the memory system's queues
+    constexpr int kQPer = (NREP * kHd + kMT - 1) / kMT;
+    float q_reg[kQPer];
+    {
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * a.q_stride;
+#pragma unroll
+        for (int u = 0; u < kQPer; u++) {
+            const int i = tid + u * kMT;
+            q_reg[u] = i < NREP * kHd ? __ldg(q + (size_t)(i >> 8) * a.q_stride + (i & 255)) : 0.f;
+        }
+    }
     // ---- fused append: the CTA that scans the last chunk of this kv head stores the head's new K
     // and V rows first, exactly as the append kernel would (src/forward.rs:259-285; the rope row
     // of the new token is the q position's).  Its own tile copies come after, so they see the row.
@@ -253,8 +266,11 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     // bytes of the bookkeeping block, since the table's region is already live) ---------------
     {
         float *sq = o.sq;  // [NREP][256]
-        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * a.q_stride;
-        for (int i = tid; i < NREP * kHd; i += kMT) sq[i] = q[(size_t)(i >> 8) * a.q_stride + (i & 255)];
+#pragma unroll
+        for (int u = 0; u < kQPer; u++) {
+            const int i = tid + u * kMT;
+            if (i < NREP * kHd) sq[i] = q_reg[u];
+        }
         __syncthreads();  // also: givens / rope row / table are complete
         if (a.q_norm_w) {  // per-head RMSNorm of q (src/forward.rs:242-243); q is not stored, so a tree sum will do
             if (warp < NREP) {
@@ -516,8 +532,17 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         for (int r = 0; r < NREP; r++) s_acc[r * kHd + tid] = sums[r];
     __syncthreads();
 
+    // Free shared memory for the streamed combine: from behind the merged accumulator (which sits at
+    // the start of the table) to the end of the window if the bookkeeping block lies before the
+    // table, else the rest of the table.
+    FinishSmem fs;
+    fs.addr = lut_addr + (uint32_t)(NREP * kHd * sizeof(float));
+    fs.bytes = (other_addr < lut_addr ? base + smem_bytes : lut_addr + kLutBytes) - fs.addr;
+    fs.bar = other_addr + (uint32_t)offsetof(Other, fin_bar);
+    fs.ptr = smem_raw + (fs.addr - base);
+    fs.err_flag = err_flag;
     const int first_item = meta.item_start[s] + kv * n_chunks;
-    finish_item<NREP>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, true, o.givens);
+    finish_item<NREP, true>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, true, o.givens, fs);
 }
 
 template <int NREP, bool QSPLIT>
