@@ -387,7 +387,7 @@ bk_status bk_cache_create(bk_ctx *ctx, const bk_cache_config *cfg, bk_cache **ou
         return st;
     }
     c->n_pos.assign((size_t)cfg->n_layers * cfg->n_seqs, 0);
-    if ((k_kind == ROW_PLANAR && v_kind == ROW_PLANAR && bits == 4) || (k_kind == ROW_F16 && v_kind == ROW_F16)) {
+    if ((k_kind == ROW_PLANAR && v_kind == ROW_PLANAR && (bits == 4 || bits == 3)) || (k_kind == ROW_F16 && v_kind == ROW_F16)) {
         st = make_tile_tensor_maps(ctx, c->d_k, c->d_v, c->k_row_bytes, cfg->n_kv,
                                    (size_t)cfg->n_layers * cfg->n_seqs * cfg->n_ctx, c->tmap_k, c->tmap_v);
         if (st != BK_OK) {

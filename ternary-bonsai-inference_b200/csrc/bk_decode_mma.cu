@@ -48,11 +48,40 @@ constexpr uint32_t kLutBytes = 65536;   // 256 entries x 256 B (128 B used: one 
 constexpr uint32_t kOtherBytes = 30720; // q halves and fragments + merge bookkeeping (multiple of 1 KiB)
 constexpr int kHeadStride = 276;        // floats per head in the warp-merge area (bank-conflict free)
 constexpr float kWScale = 16384.0f;     // 2^14: V weights are stored as f16 in (0, 2^14]
-constexpr int kRowBytes = 128;          // 256 coordinates x 4 bit
-constexpr int kTileBytes = kTile * kRowBytes;   // 2048: one K or V tile, dense rows, 128B-swizzled
 constexpr int kNormBytes = 512;                 // norms of 16 positions x up to 8 kv heads (all heads travel)
-constexpr int kStageBytes = 2 * kTileBytes + 2 * kNormBytes;  // K tile, V tile, K norms, V norms; 1 KiB aligned
 constexpr int kMaxStages = 6;
+// Per index width (4 or 3 bits): a row is 32 * BITS bytes, a tile 16 dense rows (4-bit tiles land
+// with the 128-byte swizzle, 3-bit tiles plain), a stage = K tile, V tile, K norms, V norms.
+template <int BITS> struct Width {
+    static constexpr int kRowBytes = 32 * BITS;
+    static constexpr int kTileBytes = kTile * kRowBytes;
+    static constexpr int kStageBytes = 2 * kTileBytes + 2 * kNormBytes;  // 5120 / 4096: 1 KiB aligned
+};
+// Which shared-memory row holds the MMA's position row g.  4 bit: g itself (the swizzle spreads
+// the banks).  3 bit: rows are 96 bytes apart and unswizzled; this order makes both the K reads
+// (row g, 8 bytes at 24 t) and the V reads (rows 2t, 2t+1, 4 bytes at 12 g) hit 32 different banks.
+template <int BITS> __device__ __forceinline__ int row_of(int g) {
+    if constexpr (BITS == 3) return (g < 4) ? g : (g ^ 1);  // 0 1 2 3 5 4 7 6
+    else return g;
+}
+// Eight 3-bit indices in the low 24 bits of y -> eight nibbles.
+__device__ __forceinline__ uint32_t expand24(uint32_t y) {
+    y &= 0x00ffffffu;
+    y += (y & 0x00fff000u) * 15u;   // upper four indices up by 4 bits
+    y += (y & 0x0fc00fc0u) * 3u;    // upper two of every four up by 2
+    y += (y & 0x38383838u);         // upper one of every two up by 1
+    return y;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
 
 struct Other {                          // lives outside the lookup table
     uint2 q_hi_frag[16][32], q_lo_frag[16][32];  // q (f16 hi and lo parts) as B fragments: [k-step][lane], 8-byte conflict-free reads
@@ -88,10 +117,12 @@ __device__ __forceinline__ uint4 ldg128(const uint8_t *p) {
     return v;
 }
 
-template <int NREP, bool QSPLIT>
+template <int BITS, int NREP, bool QSPLIT>
 __global__ void __launch_bounds__(kMT, 1)
 decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t smem_bytes, int *err_flag,
                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+    constexpr int kRowBytes = Width<BITS>::kRowBytes, kTileBytes = Width<BITS>::kTileBytes;
+    constexpr int kStageBytes = Width<BITS>::kStageBytes;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -186,10 +217,11 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         }
         if (a.q_norm_w)
             for (int i = tid; i < kHd; i += kMT) o.qw[i] = a.q_norm_w[i];
-        const float c_lo = a.book[lane & 15] * lut_alpha;  // lanes 0..15 hold the 16 scaled centroids
-        // the lookup table: entry e -> half2(alpha*c[e & 15], alpha*c[e >> 4]), one copy per lane
+        constexpr int kIdxMask = (1 << BITS) - 1;
+        const float c_lo = a.book[lane & kIdxMask] * lut_alpha;  // the low lanes hold the scaled centroids
+        // the lookup table: entry e -> half2(alpha*c[low nibble], alpha*c[high nibble]), one copy per lane
         for (int e = warp; e < 256; e += kMW) {
-            const float lo = __shfl_sync(0xffffffffu, c_lo, e & 15), hi = __shfl_sync(0xffffffffu, c_lo, e >> 4);
+            const float lo = __shfl_sync(0xffffffffu, c_lo, e & kIdxMask), hi = __shfl_sync(0xffffffffu, c_lo, (e >> 4) & kIdxMask);
             const __half2 h = __floats2half2_rn(lo, hi);
             *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + lane * 4) = h;
         }
@@ -210,7 +242,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     // and V rows first, exactly as the append kernel would (src/forward.rs:259-285; the rope row
     // of the new token is the q position's).  Its own tile copies come after, so they see the row.
     if (a.new_k != nullptr && chunk == n_chunks - 1) {
-        if (tid < 16) o.book[tid] = a.book[tid];
+        if (tid < (1 << BITS)) o.book[tid] = a.book[tid];
         if (warp < 2) {
             const float *src = (warp == 0 ? a.new_k : a.new_v) + ((size_t)meta.slot[s] * a.n_kv + kv) * kHd;
             float *sx = o.new_row[warp];
@@ -247,11 +279,11 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                 const int i = lane * 4 + pr;  // pair index: coordinates 2i, 2i+1
                 float r0, r1;
                 givens_fwd(__fmul_rn(sx[2 * i], inv), __fmul_rn(sx[2 * i + 1], inv), o.givens[2 * i], o.givens[2 * i + 1], r0, r1);
-                packed |= (uint64_t)nearest_centroid_fast<4>(r0, o.book) << (4 * (2 * pr));
-                packed |= (uint64_t)nearest_centroid_fast<4>(r1, o.book) << (4 * (2 * pr + 1));
+                packed |= (uint64_t)nearest_centroid_fast<BITS>(r0, o.book) << (BITS * (2 * pr));
+                packed |= (uint64_t)nearest_centroid_fast<BITS>(r1, o.book) << (BITS * (2 * pr + 1));
             }
             const size_t row = seq_rows + (size_t)(n_pos - 1) * a.n_kv + kv;
-            store_group8<4>((warp == 0 ? a.k_rows_w : a.v_rows_w) + row * kRowBytes, lane, packed);
+            store_group8<BITS>((warp == 0 ? a.k_rows_w : a.v_rows_w) + row * kRowBytes, lane, packed);
             if (lane == 0) (warp == 0 ? a.k_norms_w : a.v_norms_w)[row] = n;
             __threadfence();
             asm volatile("fence.proxy.async;\n" ::: "memory");  // generic-proxy stores before the TMA reads below
@@ -340,26 +372,50 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         // norms of positions g and g + 8 for this kv head (rows past the chunk are masked below)
         float kn[2], vn[2];
         {
-            const uint32_t na = st_addr + 2 * kTileBytes + (uint32_t)((g * a.n_kv + kv) * 4), step = (uint32_t)(8 * a.n_kv * 4);
+            const uint32_t na = st_addr + 2 * kTileBytes + (uint32_t)((row_of<BITS>(g) * a.n_kv + kv) * 4), step = (uint32_t)(8 * a.n_kv * 4);
             asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(kn[0]) : "r"(na));
             asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(kn[1]) : "r"(na + step));
             asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(vn[0]) : "r"(na + kNormBytes));
             asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(vn[1]) : "r"(na + kNormBytes + step));
         }
-        // swizzled reads: the 16-byte chunk index is XORed with (row & 7); rows g and g + 8 share it
-        const uint32_t k_row = st_addr + g * kRowBytes;
+        // 4 bit: swizzled reads, the 16-byte chunk index is XORed with (row & 7); rows g and g + 8 share it
+        const uint32_t k_row = st_addr + row_of<BITS>(g) * kRowBytes;
         const uint32_t v_tile = st_addr + kTileBytes;
         // ---- scores^T = Kc . Q^T ------------------------------------------------------------
         // four independent accumulator chains (the 16 or 32 MMAs of a tile would otherwise be one
         // dependent chain), summed at the end
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
         float sc2[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
+        // coordinates 64 t .. 64 t + 63 of rows g and g + 8 as eight words of eight nibbles each
+        uint32_t kg[2][4], kh[2][4];
+        if constexpr (BITS == 4) {
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const uint32_t koff = (uint32_t)(((2 * t + c) ^ g) << 4);                 // chunks 2t, 2t+1
+                const uint4 rk_g = lds128(k_row + koff), rk_h = lds128(k_row + 8 * kRowBytes + koff);
+                kg[c][0] = rk_g.x; kg[c][1] = rk_g.y; kg[c][2] = rk_g.z; kg[c][3] = rk_g.w;
+                kh[c][0] = rk_h.x; kh[c][1] = rk_h.y; kh[c][2] = rk_h.z; kh[c][3] = rk_h.w;
+            }
+        } else {
+            // 24 bytes per row: three 8-byte reads, then every 24-bit group widened to a word
+            auto load_row = [&](uint32_t addr, uint32_t (&out)[2][4]) {
+                const uint2 u01 = lds64(addr), u23 = lds64(addr + 8), u45 = lds64(addr + 16);
+                out[0][0] = expand24(u01.x);
+                out[0][1] = expand24(__funnelshift_r(u01.x, u01.y, 24));
+                out[0][2] = expand24(__funnelshift_r(u01.y, u23.x, 16));
+                out[0][3] = expand24(u23.x >> 8);
+                out[1][0] = expand24(u23.y);
+                out[1][1] = expand24(__funnelshift_r(u23.y, u45.x, 24));
+                out[1][2] = expand24(__funnelshift_r(u45.x, u45.y, 16));
+                out[1][3] = expand24(u45.y >> 8);
+            };
+            load_row(k_row + 24 * t, kg);
+            load_row(k_row + 8 * kRowBytes + 24 * t, kh);
+        }
 #pragma unroll
         for (int c = 0; c < 2; c++) {
-            const uint32_t koff = (uint32_t)(((2 * t + c) ^ g) << 4);                 // chunks 2t, 2t+1
-            const uint4 rk_g = lds128(k_row + koff), rk_h = lds128(k_row + 8 * kRowBytes + koff);
-            const uint32_t xg[4] = {rk_g.x, rk_g.y, rk_g.z, rk_g.w};
-            const uint32_t xh[4] = {rk_h.x, rk_h.y, rk_h.z, rk_h.w};
+            const uint32_t(&xg)[4] = kg[c];
+            const uint32_t(&xh)[4] = kh[c];
 #pragma unroll
             for (int w = 0; w < 4; w++) {
                 const int ks = c * 8 + w * 2;
@@ -392,7 +448,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         for (int i = 0; i < 4; i++) sc[i] = (sa[i] + sb[i]) + (sc2[i] + sd[i]);
         // ---- online softmax in the exp2 domain; reference point = max of s + log2||v|| -------
         const int pb = p0 + tile * kTile;
-        const bool ok0 = pb + g < p1, ok1 = pb + g + 8 < p1;
+        const bool ok0 = pb + row_of<BITS>(g) < p1, ok1 = pb + row_of<BITS>(g) + 8 < p1;
         const float s00 = sc[0] * kn[0], s01 = sc[1] * kn[0], s10 = sc[2] * kn[1], s11 = sc[3] * kn[1];
         const float lv0 = fast_log2(fmaxf(vn[0], 1e-30f)), lv1 = fast_log2(fmaxf(vn[1], 1e-30f));
         const float t00 = ok0 ? s00 + lv0 : -CUDART_INF_F, t01 = ok0 ? s01 + lv0 : -CUDART_INF_F;
@@ -427,14 +483,30 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
         const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
         // ---- out^T += Vc^T . W : MMA j covers coordinates 32g + 2j (rows g) and 32g + 2j + 1 (rows g+8)
-        const uint32_t r0 = 2 * t, r1 = 2 * t + 1;  // rows 2t, 2t+1 (and +8: same swizzle), chunk g
-        const uint32_t vo0 = r0 * kRowBytes + (((uint32_t)g ^ (r0 & 7)) << 4), vo1 = r1 * kRowBytes + (((uint32_t)g ^ (r1 & 7)) << 4);
-        const uint4 rv0 = lds128(v_tile + vo0), rv1 = lds128(v_tile + vo1);
-        const uint4 rv2 = lds128(v_tile + 8 * kRowBytes + vo0), rv3 = lds128(v_tile + 8 * kRowBytes + vo1);
-        const uint32_t x0[4] = {rv0.x, rv0.y, rv0.z, rv0.w};
-        const uint32_t x1[4] = {rv1.x, rv1.y, rv1.z, rv1.w};
-        const uint32_t x2[4] = {rv2.x, rv2.y, rv2.z, rv2.w};
-        const uint32_t x3[4] = {rv3.x, rv3.y, rv3.z, rv3.w};
+        // coordinates 32 g .. 32 g + 31 of position rows 2t, 2t+1, 2t+8, 2t+9 as four words each
+        const uint32_t r0 = (uint32_t)row_of<BITS>(2 * t), r1 = (uint32_t)row_of<BITS>(2 * t + 1);
+        uint32_t x0[4], x1[4], x2[4], x3[4];
+        if constexpr (BITS == 4) {  // chunk g of each row; rows r and r + 8 share the swizzle
+            const uint32_t vo0 = r0 * kRowBytes + (((uint32_t)g ^ (r0 & 7)) << 4), vo1 = r1 * kRowBytes + (((uint32_t)g ^ (r1 & 7)) << 4);
+            const uint4 rv0 = lds128(v_tile + vo0), rv1 = lds128(v_tile + vo1);
+            const uint4 rv2 = lds128(v_tile + 8 * kRowBytes + vo0), rv3 = lds128(v_tile + 8 * kRowBytes + vo1);
+            x0[0] = rv0.x; x0[1] = rv0.y; x0[2] = rv0.z; x0[3] = rv0.w;
+            x1[0] = rv1.x; x1[1] = rv1.y; x1[2] = rv1.z; x1[3] = rv1.w;
+            x2[0] = rv2.x; x2[1] = rv2.y; x2[2] = rv2.z; x2[3] = rv2.w;
+            x3[0] = rv3.x; x3[1] = rv3.y; x3[2] = rv3.z; x3[3] = rv3.w;
+        } else {  // 12 bytes per row: three 4-byte reads, widened
+            auto load_v = [&](uint32_t addr, uint32_t (&out)[4]) {
+                const uint32_t u0 = lds32(addr), u1 = lds32(addr + 4), u2 = lds32(addr + 8);
+                out[0] = expand24(u0);
+                out[1] = expand24(__funnelshift_r(u0, u1, 24));
+                out[2] = expand24(__funnelshift_r(u1, u2, 16));
+                out[3] = expand24(u2 >> 8);
+            };
+            load_v(v_tile + r0 * kRowBytes + 12 * g, x0);
+            load_v(v_tile + r1 * kRowBytes + 12 * g, x1);
+            load_v(v_tile + (r0 + 8) * kRowBytes + 12 * g, x2);
+            load_v(v_tile + (r1 + 8) * kRowBytes + 12 * g, x3);
+        }
 #pragma unroll
         for (int w = 0; w < 4; w++) {
             const uint32_t m = 0x0f0f0f0fu;
@@ -545,8 +617,9 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     finish_item<NREP, true>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, true, o.givens, fs);
 }
 
-template <int NREP, bool QSPLIT>
+template <int BITS, int NREP, bool QSPLIT>
 bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha) {
+    constexpr int kStageBytes = Width<BITS>::kStageBytes;
     // Dynamic shared memory: everything the SM allows beyond the kernel's static part.  The kernel
     // lays out table, bookkeeping and as many ring stages as fit (at least 2 are needed).
     static size_t smem_for[64] = {};
@@ -554,13 +627,13 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
     if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (mma): device index above 63");
     if (smem_for[dev] == 0) {
         cudaFuncAttributes fa;
-        BK_CUDA(ctx, cudaFuncGetAttributes(&fa, decode_p4_mma_kernel<NREP, QSPLIT>));
+        BK_CUDA(ctx, cudaFuncGetAttributes(&fa, decode_p4_mma_kernel<BITS, NREP, QSPLIT>));
         int optin = 0;
         BK_CUDA(ctx, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
         const size_t dyn = (size_t)optin - fa.sharedSizeBytes;
         const size_t need = (size_t)kLutBytes + kOtherBytes + 2 * (size_t)kMW * kStageBytes;
         if (dyn < need) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (mma): not enough shared memory per block on this device");
-        BK_CUDA(ctx, cudaFuncSetAttribute(decode_p4_mma_kernel<NREP, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        BK_CUDA(ctx, cudaFuncSetAttribute(decode_p4_mma_kernel<BITS, NREP, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
         smem_for[dev] = dyn;
     }
     const size_t smem = smem_for[dev];
@@ -575,7 +648,7 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    BK_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_p4_mma_kernel<NREP, QSPLIT>, a, m, alpha, (uint32_t)smem, ctx->d_err,
+    BK_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_p4_mma_kernel<BITS, NREP, QSPLIT>, a, m, alpha, (uint32_t)smem, ctx->d_err,
                                     *static_cast<const CUtensorMap *>(a.h_tmap_k),
                                     *static_cast<const CUtensorMap *>(a.h_tmap_v)));
     ctx->launches++;
@@ -604,17 +677,21 @@ bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_r
         encode = (EncodeFn)fn;
     }
     if (total_pos >= (size_t)1 << 31) return fail(ctx, BK_ERR_UNSUPPORTED, "cache has more than 2^31 positions");
-    if (row_bytes % 128 != 0) return fail(ctx, BK_ERR_UNSUPPORTED, "tensor maps need rows of a multiple of 128 bytes");
+    // rows of a multiple of 128 bytes travel as 128-byte swizzled slabs; shorter rows (96 bytes: 3 bit)
+    // as whole dense rows without a swizzle
+    const bool swizzled = row_bytes % 128 == 0;
+    if (!swizzled && (row_bytes % 16 != 0 || row_bytes > 256))
+        return fail(ctx, BK_ERR_UNSUPPORTED, "tensor maps need rows of a multiple of 16 bytes");
     const cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)n_kv, (cuuint64_t)total_pos};
     const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)row_bytes * n_kv};
-    const cuuint32_t box[3] = {128, 1, (cuuint32_t)kTile};
+    const cuuint32_t box[3] = {swizzled ? 128u : (cuuint32_t)row_bytes, 1, (cuuint32_t)kTile};
     const cuuint32_t estr[3] = {1, 1, 1};
     const void *ptrs[2] = {k_rows, v_rows};
     void *outs[2] = {out_k, out_v};
     for (int i = 0; i < 2; i++) {
         const CUresult r = encode(static_cast<CUtensorMap *>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
                                   const_cast<void *>(ptrs[i]), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(ctx, BK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
     }
@@ -624,16 +701,17 @@ bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_r
 bool decode_p4_mma_supported(const DecodeArgs &a) {
     const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
     // (the norms of a tile travel as a 16-byte aligned bulk copy: n_ctx * n_kv must be a multiple of 4)
-    return a.h_tmap_k && a.h_tmap_v && (a.seq_stride_rows % 4 == 0) && a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && a.bits == 4 &&
+    return a.h_tmap_k && a.h_tmap_v && (a.seq_stride_rows % 4 == 0) && a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3) &&
            (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
 bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit) {
     if (m.n_items <= 0) return BK_OK;
     const int n_rep = a.n_head / a.n_kv;
-#define BK_MMA_CASE(R)                                                          \
-    case R:                                                                     \
-        return qsplit ? launch_one<R, true>(ctx, a, m, alpha) : launch_one<R, false>(ctx, a, m, alpha);
+#define BK_MMA_CASE(R)                                                                                     \
+    case R:                                                                                                \
+        if (a.bits == 3) return qsplit ? launch_one<3, R, true>(ctx, a, m, alpha) : launch_one<3, R, false>(ctx, a, m, alpha); \
+        return qsplit ? launch_one<4, R, true>(ctx, a, m, alpha) : launch_one<4, R, false>(ctx, a, m, alpha);
     switch (n_rep) {
         BK_MMA_CASE(1)
         BK_MMA_CASE(2)

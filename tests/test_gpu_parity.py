@@ -505,6 +505,57 @@ def test_fused_step_on_long_planar4_cache(bk, gpu_ctx, oracle):
 
 
 @pytest.mark.parametrize("env", [{"BONSAI_KV_GENERIC": "1"}, {}])
+def test_planar3_kernel_variants(bk, oracle, monkeypatch, env):
+    """The 3-bit cache goes through the same tensor-core kernel (indices widened to nibbles in
+    registers) from 2048 positions on."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    ctx = bk.Context(0)
+    for lens in ([17], [2047], [2048], [2049], [2063, 2064, 2065], [5000], [40000, 3, 2500]):
+        got, want = run_both(bk, ctx, oracle, "planar3", MODE_PLANAR, 3, True, lens, seed=sum(lens) + 3)
+        assert_close(got, want, f"{env} {lens}")
+    ctx.close()
+
+
+def test_planar3_tensor_core_path_other_group_sizes(bk, gpu_ctx, oracle):
+    rng = np.random.default_rng(79)
+    n = 2500
+    for n_head, n_kv in ((4, 4), (8, 4), (8, 2), (16, 2)):
+        k = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
+        v = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
+        q = rng.standard_normal((n_head, HD)).astype(np.float32)
+        cache = bk.AttnCache(gpu_ctx, bk.parse_mode("planar3"), n_layers=1, n_ctx=n, n_head=n_head, n_kv=n_kv)
+        cache.append(0, k, v)
+        ref = oracle.cache(MODE_PLANAR, 3, True, n_head=n_head, n_kv=n_kv)
+        for p in range(n):
+            ref.append(0, k[p], v[p], p)
+        want = ref.attend(0, q, n - 1, n, threads=8)
+        got = cache.attend(0, q)[0]
+        assert_close(got, want, f"{n_head}/{n_kv}")
+        cache.close()
+
+
+def test_fused_step_on_long_planar3_cache(bk, gpu_ctx, oracle):
+    rng = np.random.default_rng(44)
+    n0, steps = 2600, 12
+    k, v = synth_kv(rng, n0 + steps)
+    q = rng.standard_normal((steps, NH, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode("planar3"), n_layers=1, n_ctx=n0 + steps)
+    ref = oracle.cache(MODE_PLANAR, 3, True)
+    cache.append(0, k[:n0], v[:n0])
+    for p in range(n0):
+        ref.append(0, k[p], v[p], p)
+    for t in range(steps):
+        launches = gpu_ctx.launch_count
+        got = bk.full_attention_step(cache, 0, q[t], k[n0 + t], v[n0 + t], n0 + t)
+        assert gpu_ctx.launch_count - launches == 1
+        want = ref.step(0, q[t], k[n0 + t], v[n0 + t], n0 + t, threads=8)
+        assert_close(got, want, f"step {t}")
+    compare_dumps(cache.dump_kv(0, pos0=n0 - 3), {key: val[n0 - 3:] for key, val in ref.dump(0).items()})
+    cache.close()
+
+
+@pytest.mark.parametrize("env", [{"BONSAI_KV_GENERIC": "1"}, {}])
 def test_f16_kernel_variants(bk, oracle, monkeypatch, env):
     """The f16 cache has the same two decode kernels behind one entry point (tensor cores from 2048
     positions on).  Lengths hit ragged tiles, single chunks, many chunks and a mixed batch."""
@@ -666,7 +717,7 @@ def test_layer_step_on_a_filled_cache(bk, gpu_ctx, oracle, tag, mode, bits, vq, 
     cache.append(0, k, v)
     for p in range(n0):
         ref.append(0, k[p], v[p], p)
-    one_launch = n0 >= 2048 and tag in ("planar4", "f16")
+    one_launch = n0 >= 2048 and tag in ("planar4", "planar3", "f16")
     for t in range(steps):
         launches = gpu_ctx.launch_count
         got = bk.full_attention_layer_core(cache, 0, qfull[t], kraw[t], vraw[t], qw, kw, 1e-6, n0 + t)
