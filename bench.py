@@ -591,8 +591,9 @@ def main():
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}",
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this
-                     # workload, from the ncu capture summarised in profiles/decode_p4_mma_ctx131072_ncu.md
-                     "traffic": 142.9e6 if (args.mode == "planar4" and args.ctx == 131072) else None,
+                     # workload, from the ncu captures summarised in profiles/decode_p4_mma_ctx131072_ncu.md
+                     # and profiles/decode_f16_mma_ctx32768_ncu.md (mean of the two captured launches)
+                     "traffic": {("planar4", 131072): 143.4e6, ("f16", 32768): 138.3e6}.get((args.mode, args.ctx)),
                      "algorithmic_bytes_per_launch": alg, "avg_launch_ms": dec_ms_avg,
                      "frac_of_8TBs_nominal": achieved / 8000.0},
         "cpu_baseline": cpu, "clocks": clocks,
