@@ -139,6 +139,22 @@ BK_API bk_status bk_cache_upload(bk_cache *cache, int32_t layer, int32_t seq, in
                                  int32_t n_pos, const void *k_rows_host, const float *k_norms_host,
                                  const void *v_rows_host, const float *v_norms_host);
 
+/* Prompt-cache snapshot of one sequence (all layers) as one self-describing
+ * buffer; restores into any cache of the same KV mode, layer count and head
+ * geometry (n_ctx and n_seqs may differ) and sets n_pos.  No reference
+ * counterpart as a function - the reference's server has no prompt cache
+ * (README.md:218-221) - but the payload is the reference's own row layout,
+ * either one: layout 0 = the CPU stores of src/forward.rs:40-46 (rows, then
+ * norms), layout 1 = the device rows of shaders/kv_store_q.comp:119-123
+ * (packed words + norm word per row).  Header: u32 magic "BKVS", version,
+ * layout, mode kind, bits, v_quant, n_layers, n_kv, hd, 3 reserved, then
+ * n_pos per layer.  bk_cache_snapshot_bytes returns 0 on bad arguments. */
+BK_API size_t bk_cache_snapshot_bytes(const bk_cache *cache, int32_t seq);
+BK_API bk_status bk_cache_snapshot_save(bk_cache *cache, int32_t seq, int32_t layout, void *buf_host,
+                                        size_t buf_bytes, size_t *written);
+BK_API bk_status bk_cache_snapshot_load(bk_cache *cache, int32_t seq, const void *buf_host,
+                                        size_t buf_bytes);
+
 /* ---- append: src/forward.rs:259-285, shaders rope_imrope + kv_store* ------- */
 
 /* One fused kernel: IMROPE on K (all four position ids = rope_pos + i, as

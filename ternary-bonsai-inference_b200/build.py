@@ -33,6 +33,7 @@ SOURCES = {
     "bk_layer.cu": ["--fmad=false"],
     "bk_p2p.cu": [],
     "bk_host_tables.cpp": [],
+    "bk_snapshot.cpp": [],
 }
 HEADERS = ["bk_internal.h", "bk_device.cuh", "bk_decode_common.cuh", "bk_mma_common.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]
 

@@ -138,6 +138,19 @@ class AttnCache:
                                                       va.ctypes.data, out.ctypes.data))
         return out
 
+    def snapshot(self, seq=0, layout=0):
+        """All layers of one sequence as bytes (layout 0: the reference's CPU stores, 1: its device rows)."""
+        n = self.ctx.lib.bk_cache_snapshot_bytes(self.h, seq)
+        buf = np.zeros(max(n, 1), np.uint8)
+        written = C.c_size_t(0)
+        self.ctx.check(self.ctx.lib.bk_cache_snapshot_save(self.h, seq, layout, buf.ctypes.data, n, C.byref(written)))
+        return buf[:written.value].tobytes()
+
+    def restore(self, blob, seq=0):
+        """Load a snapshot taken from a cache of the same mode and head geometry; sets n_pos."""
+        buf = np.frombuffer(blob, np.uint8)
+        self.ctx.check(self.ctx.lib.bk_cache_snapshot_load(self.h, seq, buf.ctypes.data, buf.size))
+
     def layer_step(self, il, qfull, kraw, vraw, q_norm_w, k_norm_w, eps, pos, seq=0):
         """The layer form of the step on host arrays: qfull [n_head, 2*hd] ([q | gate] per head),
         kraw/vraw [n_kv, hd], norm weights [hd]; returns attention * sigmoid(gate), [n_head, hd]."""

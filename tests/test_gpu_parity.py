@@ -728,3 +728,84 @@ def test_layer_step_on_a_filled_cache(bk, gpu_ctx, oracle, tag, mode, bits, vq, 
     with pytest.raises(bk.BonsaiKvError):  # not the next row
         bk.full_attention_layer_core(cache, 0, qfull[0], kraw[0], vraw[0], qw, kw, 1e-6, n0)
     cache.close()
+
+
+# ---------------------------------------------------------------------------
+# prompt-cache snapshots
+# ---------------------------------------------------------------------------
+
+def expected_snapshot(ref_dumps, mode_kind, bits, vq, n_kv, layout):
+    """The snapshot bytes built in numpy from the oracle's stores: header, n_pos per layer, then
+    per layer K and V in the reference's CPU layout (src/forward.rs:40-46) or, for quantized
+    sides, its device rows (shaders/kv_store_q.comp:119-123: packed words then the norm word)."""
+    n_layers = len(ref_dumps)
+    hdr = np.array([0x53564B42, 1, layout, mode_kind, bits, int(vq), n_layers, n_kv, HD, 0, 0, 0], np.uint32)
+    out = [hdr.tobytes(), np.array([d["n"] for d in ref_dumps], np.uint32).tobytes()]
+    for d in ref_dumps:
+        if d["n"] == 0:
+            continue
+        for rows, norms in ((d["k_rows"], d["k_norms"]), (d["v_rows"], d["v_norms"])):
+            flat = np.ascontiguousarray(rows).reshape(d["n"] * n_kv, -1)
+            if norms is None:
+                out.append(flat.tobytes())
+            elif layout == 0:
+                out += [flat.tobytes(), np.ascontiguousarray(norms, np.float32).tobytes()]
+            else:
+                nb = np.ascontiguousarray(norms, np.float32).reshape(-1, 1).view(np.uint8)
+                out.append(np.concatenate([flat.view(np.uint8), nb], axis=1).tobytes())
+    return b"".join(out)
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq", [MODES[0], MODES[1], MODES[2], MODES[3], MODES[4]])
+def test_snapshot_bytes_and_restore(bk, gpu_ctx, oracle, tag, mode, bits, vq):
+    rng = np.random.default_rng(bits + 60)
+    lens = [37, 0, 5]  # per layer
+    kind = {MODE_F32: 0, MODE_F16: 1, MODE_PLANAR: 2}[mode]
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=3, n_ctx=64)
+    ref = oracle.cache(mode, bits, vq, n_layer=3)
+    for il, n in enumerate(lens):
+        if n:
+            k, v = synth_kv(rng, n)
+            cache.append(il, k, v)
+            for p in range(n):
+                ref.append(il, k[p], v[p], p)
+    dumps = []
+    for il, n in enumerate(lens):
+        d = ref.dump(il)
+        if mode == MODE_PLANAR:
+            e = dict(n=n, k_rows=d["kq"], k_norms=d["kn"], v_rows=d["vq"] if vq else d["v"], v_norms=d["vn"] if vq else None)
+        elif mode == MODE_F16:
+            e = dict(n=n, k_rows=d["k16"], k_norms=None, v_rows=d["v16"], v_norms=None)
+        else:
+            e = dict(n=n, k_rows=d["k"], k_norms=None, v_rows=d["v"], v_norms=None)
+        dumps.append(e)
+    blobs = {}
+    for layout in (0, 1):
+        blobs[layout] = cache.snapshot(layout=layout)
+        assert blobs[layout] == expected_snapshot(dumps, kind, bits if mode == MODE_PLANAR else 0,
+                                                  vq if mode == MODE_PLANAR else False, NKV, layout), (tag, layout)
+    # restore into a cache with another context size and several sequences; attend on both
+    q = rng.standard_normal((NH, HD)).astype(np.float32)
+    want = cache.attend(0, q)[0]
+    for layout in (0, 1):
+        other = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=3, n_seqs=2, n_ctx=40)
+        other.restore(blobs[layout], seq=1)
+        assert [other.n_pos(il, 1) for il in range(3)] == lens and other.n_pos(0, 0) == 0
+        got = other.attend(0, q[None], seq_ids=[1])[0]
+        assert np.array_equal(bits_of(got), bits_of(want))
+        compare_dumps(other.dump_kv(0, seq=1), cache.dump_kv(0))
+        other.close()
+    # refusals: other mode, too small a context, truncated or foreign bytes
+    wrong = bk.AttnCache(gpu_ctx, bk.parse_mode("planar5" if tag != "planar5" else "f32"), n_layers=3, n_ctx=64)
+    with pytest.raises(bk.BonsaiKvError):
+        wrong.restore(blobs[0])
+    wrong.close()
+    small = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=3, n_ctx=16)
+    with pytest.raises(bk.BonsaiKvError):
+        small.restore(blobs[0])
+    with pytest.raises(bk.BonsaiKvError):
+        small.restore(blobs[0][:100])
+    with pytest.raises(bk.BonsaiKvError):
+        small.restore(b"\0" * 256)
+    small.close()
+    cache.close()
