@@ -124,7 +124,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def dist_setup(n_gpus):
+def dist_setup(n_gpus, need_nccl=False):
     """Returns (rank, world, local_rank, torch.distributed or None)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world <= 1:
@@ -133,6 +133,18 @@ def dist_setup(n_gpus):
     import torch.distributed as dist
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    # Workloads without a collective on the data path need torch.distributed only for the barrier
+    # and the max over ranks; gloo does that without NCCL's helper threads, which cost the
+    # host-buffer (e2e) path about 10 % when they share the cores.  NCCL is used when asked for
+    # (BONSAI_BENCH_BACKEND=nccl), when the workload exchanges data through it, or if gloo fails.
+    want = os.environ.get("BONSAI_BENCH_BACKEND", "nccl" if need_nccl else "gloo")
+    if want == "gloo":
+        os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")
+        try:
+            dist.init_process_group("gloo")
+            return dist.get_rank(), world, local, dist
+        except Exception as e:  # fall back rather than lose the run
+            print(f"gloo rendezvous failed ({e}); using nccl", file=sys.stderr)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return dist.get_rank(), world, local, dist
 
@@ -141,7 +153,8 @@ def max_over_ranks(dist, local, value):
     if dist is None:
         return value
     import torch
-    t = torch.tensor([value], dtype=torch.float64, device=f"cuda:{local}")
+    dev = "cpu" if dist.get_backend() == "gloo" else f"cuda:{local}"
+    t = torch.tensor([value], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
@@ -230,7 +243,7 @@ def run_other_workload(args):
     par = importlib.import_module("ternary-bonsai-inference_b200.parallel")
     mode = bk.parse_mode(args.mode)
     args.warmup = max(args.warmup, 3)
-    rank, world, local, dist = dist_setup(args.gpus)
+    rank, world, local, dist = dist_setup(args.gpus, need_nccl=(args.workload == "splitctx" and args.exchange == "nccl"))
     ctx = bk.Context(local)
     total_steps = args.steps + args.warmup
     rng = np.random.default_rng(99)          # same plan and data on every rank
