@@ -278,6 +278,33 @@ def run_other_workload(args):
         cfg = {"workload": f"batch64: {n_seqs} sequences, contexts U[2048,16384] (seeded, mean {lens.mean():.0f}), "
                            f"{N_LAYERS} layers, {args.mode}; sequences sharded greedily over {world} GPU(s), no collective",
                "l2": "%.2f GB of cache per step, larger than L2" % (step_bytes / 1e9)}
+    elif args.workload == "prefill":
+        # one prompt of `--ctx` tokens (default here 8192) through all layers in blocks of 512 tokens:
+        # per block and layer one bulk append and one batched causal attention (bk_prefill_step)
+        n_prompt = args.ctx if args.ctx != 131072 else 8192
+        blk = 512
+        cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=n_prompt)
+        k, v = synth_chunk(rng, n_prompt, channels)
+        dk, dv = ctx.to_device(k), ctx.to_device(v)
+        d_q = ctx.to_device(rng.standard_normal((blk, NH, HD), dtype=np.float32))
+        d_out = ctx.alloc(blk * NH * HD * 4)
+
+        def step(_s):
+            cache.reset()
+            for p0 in range(0, n_prompt, blk):
+                m = min(blk, n_prompt - p0)
+                for il in range(N_LAYERS):
+                    cache.prefill_step_device(il, d_q.ptr, dk.offset(p0 * NKV * HD * 4), dv.offset(p0 * NKV * HD * 4),
+                                              d_out.ptr, p0, m)
+        # every block reads the rows before it once: about n^2 / (2 blk) row reads per layer
+        rk, rv = row_bytes(mode)
+        reads = sum(p0 + min(blk, n_prompt - p0) for p0 in range(0, n_prompt, blk))
+        step_bytes = N_LAYERS * (reads * NKV * (rk + rv) + append_bytes(mode, n_prompt) + 2 * n_prompt * NH * HD * 4)
+        tokens_per_step, scaling = n_prompt, "weak"
+        flops = N_LAYERS * 4.0 * NH * HD * sum((p0 + i + 1) for p0 in range(0, n_prompt, blk) for i in range(min(blk, n_prompt - p0)))
+        cfg = {"workload": f"prefill: one prompt of {n_prompt} tokens, blocks of {blk}, {N_LAYERS} layers, {args.mode}; "
+                           f"per block and layer a bulk append and a batched causal attention over the quantized cache",
+               "useful_tflop_per_step": flops / 1e12}
     elif args.workload == "splitctx":
         import torch
         n_total = 262144
@@ -377,6 +404,9 @@ def run_other_workload(args):
     if rank == 0:
         peak, peak_kind = measured_peak()
         gbs = step_bytes / (ms_step * 1e-3) / 1e9
+        if args.workload == "prefill":
+            line["metric"] = "quantized-KV prefill attention prompt tokens/s"
+            line["useful_tflops"] = cfg["useful_tflop_per_step"] / (ms_step * 1e-3)
         line.update({"value": tokens_per_step * 1e3 / ms_step, "ms_per_step": ms_step, "scaling": scaling, "config": cfg,
                      "effective_gbs": gbs, "gpu_launches": ctx.launch_count - launches0,
                      "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s",
@@ -417,7 +447,7 @@ def main():
     ap.add_argument("--step", default="attn", choices=["attn", "layer"],
                     help="attn: bk_attn_step (the metric's step); layer: bk_attn_layer_step, which also does the "
                          "q|gate split, the per-head RMSNorm of q and k and the sigmoid gate in the same launch")
-    ap.add_argument("--workload", default="decode128k", choices=["decode128k", "batch64", "splitctx", "appendsweep"],
+    ap.add_argument("--workload", default="decode128k", choices=["decode128k", "batch64", "splitctx", "appendsweep", "prefill"],
                     help="decode128k: the headline (default).  batch64: 64 sequences, contexts U[2048,16384], sharded "
                          "over the ranks.  splitctx: one 262144-token sequence, context chunks per rank, LSE merge.  "
                          "appendsweep: append throughput for 1..4096 tokens per call")

@@ -245,6 +245,18 @@ BK_API bk_status bk_attn_step(bk_cache *cache, int32_t layer, int32_t seq, int32
 BK_API bk_status bk_attn_step_host(bk_cache *cache, int32_t layer, int32_t seq, int32_t pos,
                                    const float *q_host, const float *k_host, const float *v_host,
                                    float *out_host);
+/* Batched (prefill) form: causal attention of n_tokens consecutive prompt
+ * tokens of one sequence whose K/V rows are already in the cache; token i
+ * (rope position pos0 + i) attends rows 0 .. pos0 + i.  q and out are
+ * [n_tokens][n_head][hd].  Same result as n_tokens successive attention
+ * steps, which is how the reference handles prompts on quantized caches
+ * (src/gdev.rs:1366-1372 refuses the batched pass there; src/forward.rs:247-375
+ * per token).  bk_prefill_step appends the block first (pos0 must be n_pos). */
+BK_API bk_status bk_prefill_attn(bk_cache *cache, int32_t layer, int32_t seq, int32_t pos0,
+                                 int32_t n_tokens, const float *q_dev, float *out_dev);
+BK_API bk_status bk_prefill_step(bk_cache *cache, int32_t layer, int32_t seq, int32_t pos0,
+                                 int32_t n_tokens, const float *q_dev, const float *k_dev,
+                                 const float *v_dev, float *out_dev);
 /* The layer form of the step: everything full_attention_layer does between the
  * q/k/v projections and the output projection (src/forward.rs:237-382;
  * src/gdev.rs:584-829 with norm_rows / split_qgate / elem mode 4 around it).

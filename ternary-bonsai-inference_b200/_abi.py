@@ -68,6 +68,8 @@ SIGNATURES = {
     "bk_cache_snapshot_bytes": (_sz, [_vp, _i32]),
     "bk_cache_snapshot_save": (C.c_int, [_vp, _i32, _i32, _vp, _sz, _vp]),
     "bk_cache_snapshot_load": (C.c_int, [_vp, _i32, _vp, _sz]),
+    "bk_prefill_attn": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "bk_prefill_step": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bk_attn_layer_step": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _f, _vp]),
     "bk_attn_layer_step_host": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _f, _vp]),
     "bk_rms_norm_rows": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _f, _vp]),

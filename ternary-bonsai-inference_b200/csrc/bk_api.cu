@@ -230,6 +230,7 @@ void bk_ctx_destroy(bk_ctx *ctx) {
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->d_stage) cudaFree(ctx->d_stage);
     if (ctx->d_layer) cudaFree(ctx->d_layer);
+    if (ctx->d_prefill) cudaFree(ctx->d_prefill);
     if (ctx->h_desc) cudaFreeHost(ctx->h_desc);
     if (ctx->d_desc) cudaFree(ctx->d_desc);
     for (int i = 0; i < kDescSlots; i++)
@@ -833,6 +834,56 @@ bk_status bk_attn_step_host(bk_cache *c, int32_t layer, int32_t seq, int32_t pos
     BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     memcpy(out_host, h_out, qb);
     return BK_OK;
+}
+
+bk_status bk_prefill_attn(bk_cache *c, int32_t layer, int32_t seq, int32_t pos0, int32_t n_tokens, const float *q_dev,
+                          float *out_dev) {
+    if (!valid_layer_seq(c, layer, seq)) return fail(c ? c->ctx : nullptr, BK_ERR_INVALID, "bk_prefill_attn: bad layer/seq");
+    bk_ctx *ctx = c->ctx;
+    if (pos0 < 0 || n_tokens < 0) return fail(ctx, BK_ERR_INVALID, "bk_prefill_attn: negative position or count");
+    if (n_tokens == 0) return BK_OK;
+    if (!q_dev || !out_dev) return fail(ctx, BK_ERR_INVALID, "bk_prefill_attn: null q/out");
+    const int32_t have = c->n_pos[c->slab(layer, seq)];
+    if ((int64_t)pos0 + n_tokens > have)
+        return fail(ctx, BK_ERR_RANGE,
+                    "bk_prefill_attn: tokens " + std::to_string(pos0) + ".." + std::to_string(pos0 + n_tokens - 1) +
+                        " are not in the cache yet (" + std::to_string(have) + " rows): append them first");
+    if ((int64_t)pos0 + n_tokens > c->rope->n_pos)
+        return fail(ctx, BK_ERR_RANGE, "bk_prefill_attn: position beyond the rope table");
+    bk_status st = bind(ctx);
+    if (st != BK_OK) return st;
+    DecodeArgs a;
+    fill_decode_args(c, layer, 0, &a);
+    a.q = q_dev;
+    a.out = out_dev;
+    if (!ctx->force_generic && prefill_mma_supported(a) && n_tokens >= 4)
+        return launch_prefill_mma(ctx, a, seq, pos0, n_tokens, ctx->lut_alpha[a.bits]);
+    // Other caches and very short blocks: the decode kernels with one entry per token (each token
+    // re-reads the rows it sees).
+    std::vector<int32_t> ids(kMaxSeqsPerLaunch, seq), np(kMaxSeqsPerLaunch), qp(kMaxSeqsPerLaunch);
+    for (int t0 = 0; t0 < n_tokens; t0 += kMaxSeqsPerLaunch) {
+        const int nb = std::min<int>(kMaxSeqsPerLaunch, n_tokens - t0);
+        for (int i = 0; i < nb; i++) {
+            np[i] = pos0 + t0 + i + 1;
+            qp[i] = pos0 + t0 + i;
+        }
+        st = decode_impl(c, layer, nb, ids.data(), np.data(), qp.data(), q_dev + (size_t)t0 * c->cfg.n_head * kHd,
+                         out_dev + (size_t)t0 * c->cfg.n_head * kHd, 0, "bk_prefill_attn");
+        if (st != BK_OK) return st;
+    }
+    return BK_OK;
+}
+
+bk_status bk_prefill_step(bk_cache *c, int32_t layer, int32_t seq, int32_t pos0, int32_t n_tokens, const float *q_dev,
+                          const float *k_dev, const float *v_dev, float *out_dev) {
+    if (!valid_layer_seq(c, layer, seq)) return fail(c ? c->ctx : nullptr, BK_ERR_INVALID, "bk_prefill_step: bad layer/seq");
+    if (pos0 != c->n_pos[c->slab(layer, seq)])
+        return fail(c->ctx, BK_ERR_INVALID,
+                    "bk_prefill_step: pos " + std::to_string(pos0) + " is not the next row (" +
+                        std::to_string(c->n_pos[c->slab(layer, seq)]) + ")");
+    bk_status st = bk_append(c, layer, seq, pos0, n_tokens, k_dev, v_dev);
+    if (st != BK_OK) return st;
+    return bk_prefill_attn(c, layer, seq, pos0, n_tokens, q_dev, out_dev);
 }
 
 bk_status bk_attn_layer_step(bk_cache *c, int32_t layer, int32_t seq, int32_t pos, const float *qfull_dev,

@@ -66,6 +66,8 @@ struct bk_ctx {
     size_t d_stage_bytes = 0;
     float *d_layer = nullptr;              // normed q and k rows of the layer step (generic decode path)
     size_t d_layer_floats = 0;
+    float *d_prefill = nullptr;            // (O, m, l) triples of the prefill attention's context chunks
+    size_t d_prefill_floats = 0;
     // split-K scratch of the decode kernel: partial results and arrival counters
     float *d_partials = nullptr;
     unsigned *d_counters = nullptr;
@@ -220,6 +222,9 @@ struct NormSeg {
     int n_rows;
 };
 bk_status launch_rms_norm_rows(bk_ctx *ctx, const NormSeg &s0, const NormSeg &s1, int row_len, float eps);
+// Batched causal attention of a block of prompt tokens over a 4- or 3-bit planar cache (bk_prefill.cu).
+bool prefill_mma_supported(const DecodeArgs &a);
+bk_status launch_prefill_mma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha);
 bk_status launch_lse_merge(bk_ctx *ctx, int n_parts, int n_rows, int hd, const float *parts, float *out);
 
 bk_status launch_quantize(bk_ctx *ctx, int bits, int n_vec, const float *x, uint8_t *packed, float *norms);

@@ -138,6 +138,23 @@ class AttnCache:
                                                       va.ctypes.data, out.ctypes.data))
         return out
 
+    def prefill_attend(self, il, q, pos0, seq=0):
+        """Causal attention of a block of prompt tokens already in the cache: host q [n, n_head, hd],
+        token i at position pos0 + i; returns [n, n_head, hd]."""
+        qa = np.ascontiguousarray(q, np.float32).reshape(-1, self.n_head, self.hd)
+        n = qa.shape[0]
+        dq = self.ctx.to_device(qa)
+        do = self.ctx.alloc(max(n, 1) * self.n_head * self.hd * 4)
+        self.ctx.check(self.ctx.lib.bk_prefill_attn(self.h, il, seq, pos0, n, dq.ptr, do.ptr))
+        out = do.download((n, self.n_head, self.hd), np.float32)
+        dq.free()
+        do.free()
+        return out
+
+    def prefill_step_device(self, il, q_ptr, k_ptr, v_ptr, out_ptr, pos0, n_tokens, seq=0):
+        """Append a block of tokens and attend causally, device pointers (asynchronous)."""
+        self.ctx.check(self.ctx.lib.bk_prefill_step(self.h, il, seq, pos0, n_tokens, q_ptr, k_ptr, v_ptr, out_ptr))
+
     def snapshot(self, seq=0, layout=0):
         """All layers of one sequence as bytes (layout 0: the reference's CPU stores, 1: its device rows)."""
         n = self.ctx.lib.bk_cache_snapshot_bytes(self.h, seq)

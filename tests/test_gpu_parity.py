@@ -809,3 +809,77 @@ def test_snapshot_bytes_and_restore(bk, gpu_ctx, oracle, tag, mode, bits, vq):
         small.restore(b"\0" * 256)
     small.close()
     cache.close()
+
+
+# ---------------------------------------------------------------------------
+# batched (prefill) attention
+# ---------------------------------------------------------------------------
+
+def prefill_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0, n_tok, seed, n_head=NH, n_kv=NKV, outliers=True):
+    """n0 cached tokens, then a block of n_tok prompt tokens: the batched call against the oracle
+    attending token by token (src/forward.rs:247-375 with q_pos = pos, n_pos = pos + 1)."""
+    rng = np.random.default_rng(seed)
+    n = n0 + n_tok
+    k = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
+    v = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
+    if outliers:
+        ch = rng.choice(HD, size=3, replace=False)
+        k[:, :, ch] *= np.float32(20.0)
+        v[:, :, ch] *= np.float32(20.0)
+    q = rng.standard_normal((n_tok, n_head, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=n, n_head=n_head, n_kv=n_kv)
+    cache.append(0, k, v)
+    ref = oracle.cache(mode, bits, vq, n_head=n_head, n_kv=n_kv)
+    for p in range(n):
+        ref.append(0, k[p], v[p], p)
+    got = cache.prefill_attend(0, q, n0)
+    want = np.stack([ref.attend(0, q[i], n0 + i, n0 + i + 1, threads=8) for i in range(n_tok)])
+    cache.close()
+    return got, want
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq", [MODES[2], MODES[3], MODES[1], MODES[8], MODES[0]])
+@pytest.mark.parametrize("n0,n_tok", [(0, 45), (300, 50), (3000, 100), (37, 3), (0, 1)])
+def test_prefill_attention_equals_token_by_token(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0, n_tok):
+    """planar4 / planar3 take the batched tensor-core kernel (from 4 tokens on), the other modes
+    the decode kernels with one entry per token; every token must meet the decode bar."""
+    got, want = prefill_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0, n_tok, seed=n0 + n_tok + bits)
+    for i in range(n_tok):
+        assert_close(got[i], want[i], f"{tag} n0={n0} token {i}")
+
+
+def test_prefill_other_group_sizes_and_long_context(bk, gpu_ctx, oracle):
+    for n_head, n_kv in ((4, 4), (8, 4), (8, 2)):
+        got, want = prefill_both(bk, gpu_ctx, oracle, "planar4", MODE_PLANAR, 4, True, 500, 70, seed=n_head, n_head=n_head, n_kv=n_kv)
+        assert_close(got, want, f"{n_head}/{n_kv}")
+    got, want = prefill_both(bk, gpu_ctx, oracle, "planar4", MODE_PLANAR, 4, True, 20000, 30, seed=5)
+    assert_close(got, want, "long")
+
+
+def test_prefill_step_appends_then_attends(bk, gpu_ctx, oracle):
+    """bk_prefill_step from the empty cache in blocks: rows bit-exact, outputs within the bar,
+    and refusals for tokens that are not in the cache."""
+    rng = np.random.default_rng(12)
+    n, blk = 130, 50
+    k, v = synth_kv(rng, n)
+    q = rng.standard_normal((n, NH, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode("planar4"), n_layers=1, n_ctx=n)
+    ref = oracle.cache(MODE_PLANAR, 4, True)
+    dq, dk, dv = gpu_ctx.to_device(q), gpu_ctx.to_device(k), gpu_ctx.to_device(v)
+    do = gpu_ctx.alloc(n * NH * HD * 4)
+    with pytest.raises(bk.BonsaiKvError):
+        cache.prefill_attend(0, q[:5], 0)  # nothing appended yet
+    for p0 in range(0, n, blk):
+        m = min(blk, n - p0)
+        cache.prefill_step_device(0, dq.offset(p0 * NH * HD * 4), dk.offset(p0 * NKV * HD * 4), dv.offset(p0 * NKV * HD * 4),
+                                  do.offset(p0 * NH * HD * 4), p0, m)
+    got = do.download((n, NH, HD), np.float32)
+    for p in range(n):
+        want = ref.step(0, q[p], k[p], v[p], p, threads=8)
+        assert_close(got[p], want, f"token {p}")
+    compare_dumps(cache.dump_kv(0), ref.dump(0))
+    with pytest.raises(bk.BonsaiKvError):
+        cache.prefill_step_device(0, dq.ptr, dk.ptr, dv.ptr, do.ptr, 5, 3)  # not the next row
+    for b in (dq, dk, dv, do):
+        b.free()
+    cache.close()
