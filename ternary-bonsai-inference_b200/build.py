@@ -32,11 +32,12 @@ SOURCES = {
     "bk_noalloc.cu": [],
     "bk_layer.cu": ["--fmad=false"],
     "bk_prefill.cu": [],
+    "bk_prefill_umma.cu": [],
     "bk_p2p.cu": [],
     "bk_host_tables.cpp": [],
     "bk_snapshot.cpp": [],
 }
-HEADERS = ["bk_internal.h", "bk_device.cuh", "bk_decode_common.cuh", "bk_mma_common.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]
+HEADERS = ["bk_internal.h", "bk_device.cuh", "bk_decode_common.cuh", "bk_mma_common.cuh", "bk_umma.cuh", os.path.join(ROOT, "include", "bonsai_kv.h")]
 
 
 def nvcc():

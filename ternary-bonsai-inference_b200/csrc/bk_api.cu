@@ -196,6 +196,8 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
     {
         const char *e1 = getenv("BONSAI_KV_GENERIC"), *e2 = getenv("BONSAI_KV_QSPLIT");
         ctx->force_generic = e1 && e1[0] == '1';
+        const char *e3 = getenv("BONSAI_KV_PREFILL");
+        ctx->prefill_umma = !(e3 && std::string(e3) == "mma");  // tcgen05 kernel unless BONSAI_KV_PREFILL=mma
         ctx->qsplit = !(e2 && e2[0] == '0');  // on unless BONSAI_KV_QSPLIT=0
     }
     if ((e = cudaMalloc(&ctx->d_givens, sizeof(ctx->h_givens))) != cudaSuccess) return bail(e, "cudaMalloc givens");
@@ -857,7 +859,8 @@ bk_status bk_prefill_attn(bk_cache *c, int32_t layer, int32_t seq, int32_t pos0,
     a.q = q_dev;
     a.out = out_dev;
     if (!ctx->force_generic && prefill_mma_supported(a) && n_tokens >= 4)
-        return launch_prefill_mma(ctx, a, seq, pos0, n_tokens, ctx->lut_alpha[a.bits]);
+        return ctx->prefill_umma ? launch_prefill_umma(ctx, a, seq, pos0, n_tokens, ctx->lut_alpha[a.bits])
+                                 : launch_prefill_mma(ctx, a, seq, pos0, n_tokens, ctx->lut_alpha[a.bits]);
     // Other caches and very short blocks: the decode kernels with one entry per token (each token
     // re-reads the rows it sees).
     std::vector<int32_t> ids(kMaxSeqsPerLaunch, seq), np(kMaxSeqsPerLaunch), qp(kMaxSeqsPerLaunch);

@@ -57,6 +57,7 @@ struct bk_ctx {
     float h_givens[bk::kHd];
     float h_codebooks[bk::kMaxBits * bk::kBookStride];
     float lut_alpha[bk::kMaxBits + 1] = {};  // per width: scale applied to centroids before f16 rounding
+    bool prefill_umma = true;              // batched attention on tcgen05; BONSAI_KV_PREFILL=mma picks the mma.sync kernel
     bool force_generic = false;            // BONSAI_KV_GENERIC=1: never take the tensor-core path
     bool qsplit = true;                    // q as f16 hi + lo in the tensor-core path (BONSAI_KV_QSPLIT=0: hi only)
     // staging for the *_host entry points (grown on demand)
@@ -225,6 +226,8 @@ bk_status launch_rms_norm_rows(bk_ctx *ctx, const NormSeg &s0, const NormSeg &s1
 // Batched causal attention of a block of prompt tokens over a 4- or 3-bit planar cache (bk_prefill.cu).
 bool prefill_mma_supported(const DecodeArgs &a);
 bk_status launch_prefill_mma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha);
+// The same on tcgen05 tensor cores with the accumulators in tensor memory (bk_prefill_umma.cu).
+bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha);
 bk_status launch_lse_merge(bk_ctx *ctx, int n_parts, int n_rows, int hd, const float *parts, float *out);
 
 bk_status launch_quantize(bk_ctx *ctx, int bits, int n_vec, const float *x, uint8_t *packed, float *norms);

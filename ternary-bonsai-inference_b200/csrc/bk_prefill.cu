@@ -103,7 +103,8 @@ __global__ void __launch_bounds__(kPT, 1) prefill_mma_kernel(PrefillArgs pa) {
 
     // ---- which item ------------------------------------------------------------------------
     const int item = blockIdx.x;
-    const int chunk = item % pa.n_chunks, kv = (item / pa.n_chunks) % a.n_kv, blk = item / (pa.n_chunks * a.n_kv);
+    // the blocks late in the prompt see the most rows: they go first
+    const int chunk = item % pa.n_chunks, kv = (item / pa.n_chunks) % a.n_kv, blk = pa.n_blocks - 1 - item / (pa.n_chunks * a.n_kv);
     const int tok0 = blk * pa.tq, n_tok = min(pa.tq, pa.n_tokens - tok0), n_rows = n_tok * NREP;
     const int vis = pa.pos0 + tok0 + n_tok;  // positions the last token of the block sees
     const int L = ((vis + pa.n_chunks - 1) / pa.n_chunks + kTK - 1) / kTK * kTK;
@@ -126,19 +127,40 @@ __global__ void __launch_bounds__(kPT, 1) prefill_mma_kernel(PrefillArgs pa) {
         float *stage = reinterpret_cast<float *>(k_tile) + warp * kHd;
         const float qscale = rsqrtf((float)kHd) * 1.4426950408889634f / pa.lut_alpha;
         const int half = a.n_rot >> 1;
+        // the next row's q and rope values travel while the current row is processed
+        float xn[8];
+        float2 rn[4];
+        auto prefetch = [&](int r) {
+            if (r < n_rows) {
+                const int tok = tok0 + r / NREP, head = kv * NREP + r % NREP;
+                const float *src = a.q + ((size_t)tok * a.n_head + head) * kHd;
+                const float2 *cs = a.rope + (size_t)(pa.pos0 + tok) * half;
+#pragma unroll
+                for (int i = 0; i < 8; i++) xn[i] = __ldg(src + lane + 32 * i);
+#pragma unroll
+                for (int i = 0; i < 4; i++) rn[i] = (lane + 32 * i < half) ? __ldg(cs + lane + 32 * i) : make_float2(1.f, 0.f);
+            }
+        };
+        prefetch(warp);
         for (int r = warp; r < kQRows; r += kPW) {
             const bool real = r < n_rows;
-            const int tok = tok0 + r / NREP, head = kv * NREP + r % NREP;
             if (real) {
-                const float *src = a.q + ((size_t)tok * a.n_head + head) * kHd;
-                for (int i = lane; i < kHd; i += 32) stage[i] = src[i];
+                float2 rc[4];
+#pragma unroll
+                for (int i = 0; i < 8; i++) stage[lane + 32 * i] = xn[i];
+#pragma unroll
+                for (int i = 0; i < 4; i++) rc[i] = rn[i];
+                prefetch(r + kPW);
                 __syncwarp();
-                const float2 *cs = a.rope + (size_t)(pa.pos0 + tok) * half;
-                for (int j = lane; j < half; j += 32) {
-                    float x0 = stage[j], x1 = stage[j + half];
-                    rope_pair(x0, x1, cs[j]);
-                    stage[j] = x0;
-                    stage[j + half] = x1;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int j = lane + 32 * i;
+                    if (j < half) {
+                        float x0 = stage[j], x1 = stage[j + half];
+                        rope_pair(x0, x1, rc[i]);
+                        stage[j] = x0;
+                        stage[j + half] = x1;
+                    }
                 }
                 __syncwarp();
             }
@@ -446,9 +468,9 @@ bk_status launch_prefill_mma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0
     pa.tq = kQRows / n_rep;
     pa.n_blocks = (n_tokens + pa.tq - 1) / pa.tq;
     pa.lut_alpha = alpha;
-    // enough work items for about two per SM, chunks of at least 256 positions
+    // chunks of at least 256 positions
     const int vis = pos0 + n_tokens;
-    int chunks = (2 * ctx->n_sms + pa.n_blocks * a.n_kv - 1) / (pa.n_blocks * a.n_kv);
+    int chunks = (6 * ctx->n_sms + pa.n_blocks * a.n_kv - 1) / (pa.n_blocks * a.n_kv);  // about six CTAs per SM: the causal triangle leaves them unequal
     chunks = std::max(1, std::min(chunks, std::min(64, vis / 256)));
     pa.n_chunks = chunks;
     if (chunks > 1) {

@@ -1,0 +1,516 @@
+// Batched (prefill) attention over a 4-bit or 3-bit planar cache on the 5th-generation tensor
+// cores: the same work split, operands and arithmetic as bk_prefill.cu (which documents them and
+// stays as the mma.sync form), with both contractions issued as tcgen05.mma and the accumulators
+// in tensor memory.
+//
+// One CTA = 128 query rows (M = 128) of one kv head over one context chunk; 8 warps.  Per tile
+// of 32 positions:
+//   1. all warps dequantize the packed K and V rows once into shared memory as f16 tiles (hi, and
+//      for 4 bit the rounding remainders lo) in the K-major / MN-major 128-byte-swizzled layouts
+//      the tensor cores read directly;
+//   2. one thread issues S[128 x 32] = Q . K^T as 16 K-steps x (q_hi k_hi + q_lo k_hi + q_hi k_lo)
+//      into 32 tensor-memory columns and commits to an mbarrier;
+//   3. warps 0-3 (thread = query row: tensor-memory lane r is row r) read their row of S with
+//      tcgen05.ld, scale by ||k||, apply the causal limit, update the running reference R of
+//      s + log2 ||v|| LAZILY (only when the row maximum exceeds R by more than 8: the weights
+//      p = 2^(t - R) * 64 then stay below 2^14 in f16), rescale their row of O in tensor memory when
+//      R moved, and write the weights as f16 hi + lo into the no-swizzle K-major P tiles;
+//   4. the same thread issues O[128 x 256] += P . V as 2 K-steps x (p_hi v_hi + p_lo v_hi + p_hi v_lo)
+//      into 256 tensor-memory columns (V tile as MN-major B operand) and commits.
+// Every mbarrier wait is bounded (a time-out raises the context's error flag and the kernel runs
+// on to its end, where the tensor memory is always released).  The packed rows of the next tile
+// are fetched into registers while the current one is computed.
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include <algorithm>
+
+#include "bk_device.cuh"
+#include "bk_internal.h"
+#include "bk_mma_common.cuh"
+#include "bk_umma.cuh"
+
+namespace bk {
+
+namespace {
+
+constexpr int kUW = 8, kUT = kUW * 32;
+constexpr int kRows = 128;  // query rows per CTA = tensor-memory lanes
+constexpr int kTK = 32;     // positions per tile
+constexpr float kPScale = 64.0f;
+constexpr float kLazy = 8.0f;  // the reference moves when a row maximum exceeds it by more than this (log2 units)
+
+constexpr uint32_t kQSlab = kRows * 128, kQTile = 4 * kQSlab;  // 16 KiB per 64-coordinate slab, 64 KiB per tile
+constexpr uint32_t kKVSlab = kTK * 128, kKVTile = 4 * kKVSlab;  // 4 KiB, 16 KiB
+constexpr uint32_t kPChunk = (kRows / 8) * 128, kPTile = 4 * kPChunk;  // 2 KiB per 8 positions, 8 KiB
+// offsets from the 1024-byte aligned base
+constexpr uint32_t oQhi = 0, oQlo = kQTile, oKhi = 2 * kQTile, oKlo = oKhi + kKVTile, oVhi = oKlo + kKVTile,
+                   oVlo = oVhi + kKVTile, oPhi = oVlo + kKVTile, oPlo = oPhi + kPTile, oSmall = oPlo + kPTile;
+struct SmallU {
+    float kn[kTK], lv[kTK];  // ||k|| and log2 ||v|| of the tile's positions
+    float givens[kHd];
+    __half table[16], table_lo[16];
+    unsigned long long bar_s, bar_o;
+    uint32_t tmem_slot;
+};
+constexpr uint32_t kUmmaSmem = oSmall + sizeof(SmallU) + 1024;  // + alignment slack
+constexpr uint32_t kTmemCols = 512, kColS = 0, kColO = 32;
+
+__device__ __forceinline__ uint32_t sw_off(int rows, int row, int chunk) {  // as tile_off in bk_prefill.cu
+    return (uint32_t)((chunk >> 3) * rows * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ uint32_t expand24u(uint32_t y) {
+    y &= 0x00ffffffu;
+    y += (y & 0x00fff000u) * 15u;
+    y += (y & 0x0fc00fc0u) * 3u;
+    y += (y & 0x38383838u);
+    return y;
+}
+__device__ __forceinline__ void dequant_store_u(const uint32_t (&w)[4], const __half *table, uint8_t *tile, int row, int chunk0) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        uint32_t h[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const uint32_t lo = (w[j] >> (8 * e)) & 15u, hi = (w[j] >> (8 * e + 4)) & 15u;
+            h[e] = (uint32_t)__half_as_ushort(table[lo]) | ((uint32_t)__half_as_ushort(table[hi]) << 16);
+        }
+        *reinterpret_cast<uint4 *>(tile + sw_off(kTK, row, chunk0 + j)) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+}
+
+// The same with the table in registers: lane i holds (hi | lo << 16) of centroid i & 15, one
+// shuffle looks both parts of an index up, and no shared-memory bank is involved.
+template <bool LO>
+__device__ __forceinline__ void dequant_store_shfl(const uint32_t (&w)[4], uint32_t tab, uint8_t *tile_hi, uint8_t *tile_lo, int row, int chunk0) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const uint32_t v0 = __shfl_sync(0xffffffffu, tab, (w[j] >> (8 * e)) & 15u);
+            const uint32_t v1 = __shfl_sync(0xffffffffu, tab, (w[j] >> (8 * e + 4)) & 15u);
+            h[e] = __byte_perm(v0, v1, 0x5410);
+            l[e] = __byte_perm(v0, v1, 0x7632);
+        }
+        const uint32_t off = sw_off(kTK, row, chunk0 + j);
+        *reinterpret_cast<uint4 *>(tile_hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+        if (LO) *reinterpret_cast<uint4 *>(tile_lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+    }
+}
+
+struct PrefillUArgs {
+    DecodeArgs d;
+    int seq, pos0, n_tokens, tq, n_blocks, n_chunks;
+    float lut_alpha;
+    float *scratch;
+    int *err_flag;
+};
+
+template <int BITS, int NREP>
+__global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const DecodeArgs &a = pa.d;
+    const uint32_t base0 = (uint32_t)__cvta_generic_to_shared(smem_raw), base = (base0 + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - base0);
+    SmallU &ss = *reinterpret_cast<SmallU *>(sm + oSmall);
+    const uint32_t bar_s = base + oSmall + (uint32_t)offsetof(SmallU, bar_s), bar_o = base + oSmall + (uint32_t)offsetof(SmallU, bar_o);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int kRowBytes = 32 * BITS;
+    constexpr bool kLoTiles = BITS == 4;  // see bk_prefill.cu: a 4-bit f16 table is only good to 1e-4
+
+    // ---- which item (as in the mma.sync kernel) ---------------------------------------------
+    const int item = blockIdx.x;
+    // the blocks late in the prompt see the most rows: they go first
+    const int chunk = item % pa.n_chunks, kv = (item / pa.n_chunks) % a.n_kv, blk = pa.n_blocks - 1 - item / (pa.n_chunks * a.n_kv);
+    const int tok0 = blk * pa.tq, n_tok = min(pa.tq, pa.n_tokens - tok0), n_rows = n_tok * NREP;
+    const int vis = pa.pos0 + tok0 + n_tok;
+    const int L = ((vis + pa.n_chunks - 1) / pa.n_chunks + kTK - 1) / kTK * kTK;
+    const int c0 = chunk * L, c1 = min(c0 + L, vis);
+    const int n_tiles = c1 > c0 ? (c1 - c0 + kTK - 1) / kTK : 0;
+
+    // ---- tables, barriers, tensor memory ----------------------------------------------------
+    for (int i = tid; i < kHd; i += kUT) ss.givens[i] = a.givens[i];
+    if (tid < 16) {
+        const float c = a.book[tid & ((1 << BITS) - 1)] * pa.lut_alpha;
+        const __half h = __float2half_rn(c);
+        ss.table[tid] = h;
+        ss.table_lo[tid] = __float2half_rn(c - __half2float(h));
+    }
+    if (tid == 0) {
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    if (warp == 0) tmem_alloc(base + oSmall + (uint32_t)offsetof(SmallU, tmem_slot), kTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = ss.tmem_slot;
+    const uint32_t my_tmem = tmem + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's 32 lanes
+
+    // O starts at zero (it is rescaled before the first product is added)
+    if (warp < 4) {
+        uint32_t z[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) z[j] = 0u;
+        for (int b = 0; b < 8; b++) tmem_st32(my_tmem + kColO + 32 * b, z);
+        tmem_wait_st();
+    }
+
+    // ---- q rows -> the two q tiles (rope, Givens, scale, f16 hi/lo); staged through the K tile ----
+    {
+        float *stage = reinterpret_cast<float *>(sm + oKhi) + warp * kHd;
+        const float qscale = rsqrtf((float)kHd) * 1.4426950408889634f / pa.lut_alpha;
+        const int half = a.n_rot >> 1;
+        // the next row's q and rope values travel while the current row is processed
+        float xn[8];
+        float2 rn[4];
+        auto prefetch = [&](int r) {
+            if (r < n_rows) {
+                const int tok = tok0 + r / NREP, head = kv * NREP + r % NREP;
+                const float *src = a.q + ((size_t)tok * a.n_head + head) * kHd;
+                const float2 *cs = a.rope + (size_t)(pa.pos0 + tok) * half;
+#pragma unroll
+                for (int i = 0; i < 8; i++) xn[i] = __ldg(src + lane + 32 * i);
+#pragma unroll
+                for (int i = 0; i < 4; i++) rn[i] = (lane + 32 * i < half) ? __ldg(cs + lane + 32 * i) : make_float2(1.f, 0.f);
+            }
+        };
+        prefetch(warp);
+        for (int r = warp; r < kRows; r += kUW) {
+            const bool real = r < n_rows;
+            if (real) {
+                float2 rc[4];
+#pragma unroll
+                for (int i = 0; i < 8; i++) stage[lane + 32 * i] = xn[i];
+#pragma unroll
+                for (int i = 0; i < 4; i++) rc[i] = rn[i];
+                prefetch(r + kUW);
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int j = lane + 32 * i;
+                    if (j < half) {
+                        float x0 = stage[j], x1 = stage[j + half];
+                        rope_pair(x0, x1, rc[i]);
+                        stage[j] = x0;
+                        stage[j + half] = x1;
+                    }
+                }
+                __syncwarp();
+            }
+            uint32_t hw[4], lw[4];
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                float o0 = 0.f, o1 = 0.f;
+                if (real) {
+                    const int d = 8 * lane + 2 * p;
+                    givens_fwd(stage[d], stage[d + 1], ss.givens[d], ss.givens[d + 1], o0, o1);
+                    o0 *= qscale;
+                    o1 *= qscale;
+                }
+                const __half h0 = __float2half_rn(o0), h1 = __float2half_rn(o1);
+                const __half l0 = __float2half_rn(o0 - __half2float(h0)), l1 = __float2half_rn(o1 - __half2float(h1));
+                hw[p] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+                lw[p] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+            }
+            const uint32_t off = sw_off(kRows, r, lane);
+            *reinterpret_cast<uint4 *>(sm + oQhi + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            *reinterpret_cast<uint4 *>(sm + oQlo + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            __syncwarp();
+        }
+    }
+
+    __syncthreads();  // the staging area becomes the K tile
+
+    // ---- per-thread share of a packed tile: position tid / 8, coordinates 32 (tid % 8) .. + 31 ----
+    const int my_row = tid >> 3, my_c = tid & 7;
+    const size_t seq_rows = (size_t)pa.seq * a.seq_stride_rows;
+    uint32_t pk[4], pv[4];
+    float pn = 0.f;
+    auto fetch = [&](int tile) {
+        const int pos = min(c0 + tile * kTK + my_row, a.n_ctx - 1);
+        const size_t row = seq_rows + (size_t)pos * a.n_kv + kv;
+        const uint8_t *kr = a.k_rows + row * kRowBytes, *vr = a.v_rows + row * kRowBytes;
+        if constexpr (BITS == 4) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4 *>(kr) + my_c), y = __ldg(reinterpret_cast<const uint4 *>(vr) + my_c);
+            pk[0] = x.x; pk[1] = x.y; pk[2] = x.z; pk[3] = x.w;
+            pv[0] = y.x; pv[1] = y.y; pv[2] = y.z; pv[3] = y.w;
+        } else {
+            const uint32_t *k3 = reinterpret_cast<const uint32_t *>(kr) + 3 * my_c, *v3 = reinterpret_cast<const uint32_t *>(vr) + 3 * my_c;
+            pk[0] = __ldg(k3); pk[1] = __ldg(k3 + 1); pk[2] = __ldg(k3 + 2); pk[3] = 0;
+            pv[0] = __ldg(v3); pv[1] = __ldg(v3 + 1); pv[2] = __ldg(v3 + 2); pv[3] = 0;
+        }
+        if (tid < 2 * kTK) {
+            const int p2 = min(c0 + tile * kTK + (tid & (kTK - 1)), a.n_ctx - 1);
+            pn = __ldg((tid < kTK ? a.k_norms : a.v_norms) + seq_rows + (size_t)p2 * a.n_kv + kv);
+        }
+    };
+    auto widen = [&](uint32_t (&w)[4]) {
+        if constexpr (BITS == 3) {
+            const uint32_t u0 = w[0], u1 = w[1], u2 = w[2];
+            w[0] = expand24u(u0);
+            w[1] = expand24u(__funnelshift_r(u0, u1, 24));
+            w[2] = expand24u(__funnelshift_r(u1, u2, 16));
+            w[3] = expand24u(u2 >> 8);
+        }
+    };
+    auto wait_bar = [&](uint32_t bar, uint32_t parity) {
+        int polls = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            if (++polls > kWaitPolls) {  // never expected; leave a mark and go on rather than hang
+                if (lane == 0) atomicExch(pa.err_flag, 4);
+                break;
+            }
+        }
+    };
+
+    // this thread's query row (warps 0-3): causal limit, running reference and sum
+    const int my_q = (warp & 3) * 32 + lane;
+    const int lim = (warp < 4 && my_q < n_rows) ? pa.pos0 + tok0 + my_q / NREP + 1 : 0;
+    float R = -CUDART_INF_F, lsum = 0.f;
+    const uint32_t tab = (uint32_t)__half_as_ushort(ss.table[lane & 15]) | ((uint32_t)__half_as_ushort(ss.table_lo[lane & 15]) << 16);
+    const uint32_t idesc_s = umma_idesc_f16(kRows, kTK, 0, 0), idesc_o = umma_idesc_f16(kRows, kHd, 0, 1);
+
+    if (n_tiles > 0) fetch(0);
+    for (int tile = 0; tile < n_tiles; tile++) {
+        const uint32_t parity = (uint32_t)tile & 1u;
+        // ---- 1. dequantize (the previous tile's products are complete: bar_o was awaited) ----------
+        widen(pk);
+        widen(pv);
+        dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKlo, my_row, 4 * my_c);
+        dequant_store_shfl<kLoTiles>(pv, tab, sm + oVhi, sm + oVlo, my_row, 4 * my_c);
+        if (tid < kTK) ss.kn[tid] = pn;
+        else if (tid < 2 * kTK) ss.lv[tid - kTK] = fast_log2(fmaxf(pn, 1e-30f));
+        if (tile + 1 < n_tiles) fetch(tile + 1);
+        fence_smem_to_async_proxy();
+        __syncthreads();
+
+        // ---- 2. S = Q . K^T ------------------------------------------------------------------------
+        if (tid == 0) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < 16; ks++) {
+                const uint32_t qo = (uint32_t)(ks >> 2) * kQSlab + (uint32_t)(ks & 3) * 32u;
+                const uint32_t ko = (uint32_t)(ks >> 2) * kKVSlab + (uint32_t)(ks & 3) * 32u;
+                const uint64_t qh = umma_smem_desc(base + oQhi + qo, 16, 1024, kUmmaSwizzle128);
+                const uint64_t ql = umma_smem_desc(base + oQlo + qo, 16, 1024, kUmmaSwizzle128);
+                const uint64_t kh = umma_smem_desc(base + oKhi + ko, 16, 1024, kUmmaSwizzle128);
+                umma_f16_ss(tmem + kColS, qh, kh, idesc_s, ks > 0);
+                umma_f16_ss(tmem + kColS, ql, kh, idesc_s, true);
+                if constexpr (kLoTiles) {
+                    const uint64_t kl = umma_smem_desc(base + oKlo + ko, 16, 1024, kUmmaSwizzle128);
+                    umma_f16_ss(tmem + kColS, qh, kl, idesc_s, true);
+                }
+            }
+            umma_commit(bar_s);
+        }
+        __syncwarp();
+
+        // ---- 3. softmax: thread = query row ---------------------------------------------------------
+        if (warp < 4) {
+            wait_bar(bar_s, parity);
+            tc_fence_after_sync();
+            uint32_t sr[32];
+            tmem_ld32(my_tmem + kColS, sr);
+            const int pb = c0 + tile * kTK;
+            float t[32];
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float s = __uint_as_float(sr[j]) * ss.kn[j];
+                sr[j] = __float_as_uint(s);
+                const int p = pb + j;
+                t[j] = (p < c1 && p < lim) ? s + ss.lv[j] : -CUDART_INF_F;
+                mx = fmaxf(mx, t[j]);
+            }
+            // lazy reference: move it only when this row's maximum ran ahead by more than kLazy
+            const bool move = mx > -CUDART_INF_F && (R == -CUDART_INF_F || mx > R + kLazy);
+            if (__any_sync(0xffffffffu, move)) {  // tensor-memory traffic is warp-collective
+                const float newR = move ? mx : R;
+                const float f = (move && R > -CUDART_INF_F) ? fast_exp2(R - newR) : (move ? 0.f : 1.f);
+                lsum *= f;
+                for (int b = 0; b < 8; b++) {
+                    uint32_t o[32];
+                    tmem_ld32(my_tmem + kColO + 32 * b, o);
+#pragma unroll
+                    for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
+                    tmem_st32(my_tmem + kColO + 32 * b, o);
+                }
+                tmem_wait_st();
+                R = newR;
+            }
+            const float ref = R > -CUDART_INF_F ? R : 0.f;
+            // weights: chunk c = positions 8c .. 8c+7 -> 16 bytes at c * 2048 + (row / 8) * 128 + (row % 8) * 16
+            uint8_t *p_hi = sm + oPhi + (my_q >> 3) * 128 + (my_q & 7) * 16, *p_lo = sm + oPlo + (my_q >> 3) * 128 + (my_q & 7) * 16;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t hw[4], lw[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int j = 8 * c + 2 * e;
+                    const float w0 = fast_exp2(t[j] - ref) * kPScale, w1 = fast_exp2(t[j + 1] - ref) * kPScale;
+                    if (t[j] > -CUDART_INF_F) lsum += fast_exp2(__uint_as_float(sr[j]) - ref);
+                    if (t[j + 1] > -CUDART_INF_F) lsum += fast_exp2(__uint_as_float(sr[j + 1]) - ref);
+                    const __half2 h = __floats2half2_rn(w0, w1);
+                    const float2 hf = __half22float2(h);
+                    const __half2 l = __floats2half2_rn(w0 - hf.x, w1 - hf.y);
+                    hw[e] = *reinterpret_cast<const uint32_t *>(&h);
+                    lw[e] = *reinterpret_cast<const uint32_t *>(&l);
+                }
+                *reinterpret_cast<uint4 *>(p_hi + c * kPChunk) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                *reinterpret_cast<uint4 *>(p_lo + c * kPChunk) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            }
+            tc_fence_before_sync();
+            fence_smem_to_async_proxy();
+        }
+        __syncthreads();
+
+        // ---- 4. O += P . V ----------------------------------------------------------------------------
+        if (tid == 0) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++) {
+                const uint64_t ph = umma_smem_desc(base + oPhi + kk * 2 * kPChunk, kPChunk, 128, kUmmaSwizzleNone);
+                const uint64_t pl = umma_smem_desc(base + oPlo + kk * 2 * kPChunk, kPChunk, 128, kUmmaSwizzleNone);
+                const uint64_t vh = umma_smem_desc(base + oVhi + kk * 2048, kKVSlab, 1024, kUmmaSwizzle128);
+                umma_f16_ss(tmem + kColO, ph, vh, idesc_o, true);
+                umma_f16_ss(tmem + kColO, pl, vh, idesc_o, true);
+                if constexpr (kLoTiles) {
+                    const uint64_t vl = umma_smem_desc(base + oVlo + kk * 2048, kKVSlab, 1024, kUmmaSwizzle128);
+                    umma_f16_ss(tmem + kColO, ph, vl, idesc_o, true);
+                }
+            }
+            umma_commit(bar_o);
+        }
+        __syncwarp();
+        wait_bar(bar_o, parity);  // everybody: the tiles and the P buffers may be overwritten, O may be rescaled
+        tc_fence_after_sync();
+    }
+
+    // ---- epilogue: thread = query row ------------------------------------------------------------------
+    if (warp < 4) {  // every lane takes part in the warp-collective tensor-memory loads, rows past the block only skip the stores
+        const bool real = my_q < n_rows;
+        const size_t out_row = real ? (size_t)(tok0 + my_q / NREP) * a.n_head + kv * NREP + my_q % NREP : 0;
+        const float unscale = 1.0f / (kPScale * pa.lut_alpha);
+        const bool whole = pa.n_chunks == 1;
+        const float mul = whole ? (lsum > 0.f ? unscale / lsum : 0.f) : unscale;
+        float *dst = whole ? a.out + out_row * kHd : pa.scratch + (out_row * pa.n_chunks + chunk) * (kHd + 2);
+        for (int b = 0; b < 8; b++) {
+            uint32_t o[32];
+            tmem_ld32(my_tmem + kColO + 32 * b, o);
+            if (real) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const int d = 32 * b + j;
+                    float o0 = __uint_as_float(o[j]) * mul, o1 = __uint_as_float(o[j + 1]) * mul;
+                    if (whole) {
+                        float r0, r1;
+                        givens_inv(o0, o1, ss.givens[d], ss.givens[d + 1], r0, r1);
+                        o0 = r0;
+                        o1 = r1;
+                    }
+                    *reinterpret_cast<float2 *>(dst + d) = make_float2(o0, o1);
+                }
+            }
+        }
+        if (real && !whole) {
+            dst[kHd] = R;
+            dst[kHd + 1] = lsum;
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+// One CTA of 128 threads per output row: merge the chunks' triples, rotate back, write.
+__global__ void __launch_bounds__(128) prefill_umma_merge_kernel(const float *scratch, const float *givens, int n_chunks, float *out) {
+    const size_t row = blockIdx.x;
+    const int pr = threadIdx.x;
+    const float *basep = scratch + row * n_chunks * (kHd + 2);
+    float M = -CUDART_INF_F;
+    for (int c = 0; c < n_chunks; c++) M = fmaxf(M, basep[(size_t)c * (kHd + 2) + kHd]);
+    float a0 = 0.f, a1 = 0.f, Ls = 0.f;
+    for (int c = 0; c < n_chunks; c++) {
+        const float *p = basep + (size_t)c * (kHd + 2);
+        const float m = p[kHd];
+        if (!(m > -CUDART_INF_F)) continue;
+        const float f = exp2f(m - M);
+        const float2 v = *reinterpret_cast<const float2 *>(p + 2 * pr);
+        a0 = fmaf(v.x, f, a0);
+        a1 = fmaf(v.y, f, a1);
+        Ls = fmaf(p[kHd + 1], f, Ls);
+    }
+    const float inv = Ls > 0.f ? 1.0f / Ls : 0.f;
+    float o0, o1;
+    givens_inv(a0 * inv, a1 * inv, givens[2 * pr], givens[2 * pr + 1], o0, o1);
+    *reinterpret_cast<float2 *>(out + row * kHd + 2 * pr) = make_float2(o0, o1);
+}
+
+template <int BITS, int NREP>
+bk_status launch_umma_one(bk_ctx *ctx, const PrefillUArgs &pa) {
+    static bool configured[64] = {};
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "prefill: device index above 63");
+    if (!configured[dev]) {
+        BK_CUDA(ctx, cudaFuncSetAttribute(prefill_umma_kernel<BITS, NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmem));
+        configured[dev] = true;
+    }
+    const int grid = pa.n_blocks * pa.d.n_kv * pa.n_chunks;
+    prefill_umma_kernel<BITS, NREP><<<grid, kUT, kUmmaSmem, ctx->stream>>>(pa);
+    ctx->launches++;
+    BK_CUDA(ctx, cudaGetLastError());
+    if (pa.n_chunks > 1) {
+        prefill_umma_merge_kernel<<<pa.n_tokens * pa.d.n_head, 128, 0, ctx->stream>>>(pa.scratch, pa.d.givens, pa.n_chunks, pa.d.out);
+        ctx->launches++;
+        BK_CUDA(ctx, cudaGetLastError());
+    }
+    return BK_OK;
+}
+
+}  // namespace
+
+bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha) {
+    if (n_tokens <= 0) return BK_OK;
+    const int n_rep = a.n_head / a.n_kv;
+    PrefillUArgs pa{};
+    pa.d = a;
+    pa.seq = seq;
+    pa.pos0 = pos0;
+    pa.n_tokens = n_tokens;
+    pa.tq = kRows / n_rep;
+    pa.n_blocks = (n_tokens + pa.tq - 1) / pa.tq;
+    pa.lut_alpha = alpha;
+    pa.err_flag = ctx->d_err;
+    const int vis = pos0 + n_tokens;
+    int chunks = (6 * ctx->n_sms + pa.n_blocks * a.n_kv - 1) / (pa.n_blocks * a.n_kv);  // about six CTAs per SM: the causal triangle leaves them unequal
+    chunks = std::max(1, std::min(chunks, std::min(64, vis / 256)));
+    pa.n_chunks = chunks;
+    if (chunks > 1) {
+        const size_t need = (size_t)n_tokens * a.n_head * chunks * (kHd + 2);
+        if (ctx->d_prefill_floats < need) {
+            BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            if (ctx->d_prefill) cudaFree(ctx->d_prefill);
+            ctx->d_prefill = nullptr;
+            ctx->d_prefill_floats = 0;
+            BK_CUDA(ctx, cudaMalloc((void **)&ctx->d_prefill, need * sizeof(float)));
+            ctx->d_prefill_floats = need;
+        }
+        pa.scratch = ctx->d_prefill;
+    }
+#define BK_PU_CASE(R)                                                                            \
+    case R:                                                                                      \
+        return a.bits == 3 ? launch_umma_one<3, R>(ctx, pa) : launch_umma_one<4, R>(ctx, pa);
+    switch (n_rep) {
+        BK_PU_CASE(1)
+        BK_PU_CASE(2)
+        BK_PU_CASE(4)
+        BK_PU_CASE(6)
+        default: return fail(ctx, BK_ERR_UNSUPPORTED, "prefill: n_head/n_kv must be 1, 2, 4 or 6");
+    }
+#undef BK_PU_CASE
+}
+
+}  // namespace bk

@@ -848,6 +848,25 @@ def test_prefill_attention_equals_token_by_token(bk, gpu_ctx, oracle, tag, mode,
         assert_close(got[i], want[i], f"{tag} n0={n0} token {i}")
 
 
+@pytest.mark.parametrize("tag,mode,bits,vq", [MODES[2], MODES[3]])
+def test_prefill_mma_sync_variant_and_empty_chunks(bk, oracle, monkeypatch, tag, mode, bits, vq):
+    """The batched kernel exists twice: on tcgen05 with tensor-memory accumulators (default) and
+    on mma.sync (BONSAI_KV_PREFILL=mma, read when the context is created).  A 700-token prompt
+    from the empty cache gives two context chunks, of which the second is empty for the early
+    query blocks; both kernels must handle it."""
+    for env in ("mma", None):
+        if env:
+            monkeypatch.setenv("BONSAI_KV_PREFILL", env)
+        else:
+            monkeypatch.delenv("BONSAI_KV_PREFILL", raising=False)
+        ctx = bk.Context(0)
+        for n0, n_tok in ((0, 700), (300, 50), (3000, 100)):
+            got, want = prefill_both(bk, ctx, oracle, tag, mode, bits, vq, n0, n_tok, seed=n0 + 7)
+            for i in range(n_tok):
+                assert_close(got[i], want[i], f"{env} {tag} n0={n0} token {i}")
+        ctx.close()
+
+
 def test_prefill_other_group_sizes_and_long_context(bk, gpu_ctx, oracle):
     for n_head, n_kv in ((4, 4), (8, 4), (8, 2)):
         got, want = prefill_both(bk, gpu_ctx, oracle, "planar4", MODE_PLANAR, 4, True, 500, 70, seed=n_head, n_head=n_head, n_kv=n_kv)
