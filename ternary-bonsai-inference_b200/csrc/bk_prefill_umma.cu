@@ -54,7 +54,7 @@ struct SmallU {
     uint32_t tmem_slot;
 };
 constexpr uint32_t kUmmaSmem = oSmall + sizeof(SmallU) + 1024;  // + alignment slack
-constexpr uint32_t kTmemCols = 512, kColS = 0, kColO = 32;
+constexpr uint32_t kTmemCols = 512, kColS = 0, kColO = 64;  // S: 32 (+32 for the k_lo term) columns, O: 256
 
 __device__ __forceinline__ uint32_t sw_off(int rows, int row, int chunk) {  // as tile_off in bk_prefill.cu
     return (uint32_t)((chunk >> 3) * rows * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
@@ -82,7 +82,8 @@ __device__ __forceinline__ void dequant_store_u(const uint32_t (&w)[4], const __
 // The same with the table in registers: lane i holds (hi | lo << 16) of centroid i & 15, one
 // shuffle looks both parts of an index up, and no shared-memory bank is involved.
 template <bool LO>
-__device__ __forceinline__ void dequant_store_shfl(const uint32_t (&w)[4], uint32_t tab, uint8_t *tile_hi, uint8_t *tile_lo, int row, int chunk0) {
+__device__ __forceinline__ void dequant_store_shfl(const uint32_t (&w)[4], uint32_t tab, uint8_t *tile_hi, uint8_t *tile_lo, int rows,
+                                                   int row_hi, int row_lo, int chunk0) {
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         uint32_t h[4], l[4];
@@ -93,9 +94,8 @@ __device__ __forceinline__ void dequant_store_shfl(const uint32_t (&w)[4], uint3
             h[e] = __byte_perm(v0, v1, 0x5410);
             l[e] = __byte_perm(v0, v1, 0x7632);
         }
-        const uint32_t off = sw_off(kTK, row, chunk0 + j);
-        *reinterpret_cast<uint4 *>(tile_hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
-        if (LO) *reinterpret_cast<uint4 *>(tile_lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+        *reinterpret_cast<uint4 *>(tile_hi + sw_off(rows, row_hi, chunk0 + j)) = make_uint4(h[0], h[1], h[2], h[3]);
+        if (LO) *reinterpret_cast<uint4 *>(tile_lo + sw_off(rows, row_lo, chunk0 + j)) = make_uint4(l[0], l[1], l[2], l[3]);
     }
 }
 
@@ -118,6 +118,11 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int kRowBytes = 32 * BITS;
     constexpr bool kLoTiles = BITS == 4;  // see bk_prefill.cu: a 4-bit f16 table is only good to 1e-4
+    // The K operand holds k_hi in rows 0-31 of every slab and, for 4 bit, k_lo in rows 32-63: one MMA
+    // with N = 64 then yields q_hi k_hi and q_hi k_lo side by side (q is re-read from shared memory
+    // once instead of twice, and that read is what an N = 32 MMA waits for).
+    constexpr int kKRows = kLoTiles ? 64 : 32;
+    constexpr uint32_t kKSlab = kKRows * 128;
 
     // ---- which item (as in the mma.sync kernel) ---------------------------------------------
     const int item = blockIdx.x;
@@ -271,42 +276,40 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
     const int lim = (warp < 4 && my_q < n_rows) ? pa.pos0 + tok0 + my_q / NREP + 1 : 0;
     float R = -CUDART_INF_F, lsum = 0.f;
     const uint32_t tab = (uint32_t)__half_as_ushort(ss.table[lane & 15]) | ((uint32_t)__half_as_ushort(ss.table_lo[lane & 15]) << 16);
-    const uint32_t idesc_s = umma_idesc_f16(kRows, kTK, 0, 0), idesc_o = umma_idesc_f16(kRows, kHd, 0, 1);
+    const uint32_t idesc_s = umma_idesc_f16(kRows, kTK, 0, 0), idesc_s2 = umma_idesc_f16(kRows, kKRows, 0, 0);
+    const uint32_t idesc_o = umma_idesc_f16(kRows, kHd, 0, 1);
 
     if (n_tiles > 0) fetch(0);
     for (int tile = 0; tile < n_tiles; tile++) {
         const uint32_t parity = (uint32_t)tile & 1u;
-        // ---- 1. dequantize (the previous tile's products are complete: bar_o was awaited) ----------
+        // ---- 1. dequantize K (the previous tile's products are complete: bar_o was awaited) --------
         widen(pk);
-        widen(pv);
-        dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKlo, my_row, 4 * my_c);
-        dequant_store_shfl<kLoTiles>(pv, tab, sm + oVhi, sm + oVlo, my_row, 4 * my_c);
+        dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, 4 * my_c);
         if (tid < kTK) ss.kn[tid] = pn;
         else if (tid < 2 * kTK) ss.lv[tid - kTK] = fast_log2(fmaxf(pn, 1e-30f));
-        if (tile + 1 < n_tiles) fetch(tile + 1);
         fence_smem_to_async_proxy();
         __syncthreads();
 
-        // ---- 2. S = Q . K^T ------------------------------------------------------------------------
+        // ---- 2. S = Q . K^T, and V is dequantized while it runs ---------------------------------------
         if (tid == 0) {
             tc_fence_after_sync();
 #pragma unroll
             for (int ks = 0; ks < 16; ks++) {
                 const uint32_t qo = (uint32_t)(ks >> 2) * kQSlab + (uint32_t)(ks & 3) * 32u;
-                const uint32_t ko = (uint32_t)(ks >> 2) * kKVSlab + (uint32_t)(ks & 3) * 32u;
+                const uint32_t ko = (uint32_t)(ks >> 2) * kKSlab + (uint32_t)(ks & 3) * 32u;
                 const uint64_t qh = umma_smem_desc(base + oQhi + qo, 16, 1024, kUmmaSwizzle128);
                 const uint64_t ql = umma_smem_desc(base + oQlo + qo, 16, 1024, kUmmaSwizzle128);
-                const uint64_t kh = umma_smem_desc(base + oKhi + ko, 16, 1024, kUmmaSwizzle128);
-                umma_f16_ss(tmem + kColS, qh, kh, idesc_s, ks > 0);
-                umma_f16_ss(tmem + kColS, ql, kh, idesc_s, true);
-                if constexpr (kLoTiles) {
-                    const uint64_t kl = umma_smem_desc(base + oKlo + ko, 16, 1024, kUmmaSwizzle128);
-                    umma_f16_ss(tmem + kColS, qh, kl, idesc_s, true);
-                }
+                const uint64_t kd = umma_smem_desc(base + oKhi + ko, 16, 1024, kUmmaSwizzle128);
+                umma_f16_ss(tmem + kColS, qh, kd, idesc_s2, ks > 0);  // columns 0-31: q_hi k_hi, 32-63: q_hi k_lo
+                umma_f16_ss(tmem + kColS, ql, kd, idesc_s, true);     // columns 0-31 += q_lo k_hi
             }
             umma_commit(bar_s);
         }
         __syncwarp();
+        widen(pv);
+        dequant_store_shfl<kLoTiles>(pv, tab, sm + oVhi, sm + oVlo, kTK, my_row, my_row, 4 * my_c);
+        if (tile + 1 < n_tiles) fetch(tile + 1);
+        fence_smem_to_async_proxy();
 
         // ---- 3. softmax: thread = query row ---------------------------------------------------------
         if (warp < 4) {
@@ -314,6 +317,12 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
             tc_fence_after_sync();
             uint32_t sr[32];
             tmem_ld32(my_tmem + kColS, sr);
+            if constexpr (kLoTiles) {
+                uint32_t s2[32];
+                tmem_ld32(my_tmem + kColS + 32, s2);
+#pragma unroll
+                for (int j = 0; j < 32; j++) sr[j] = __float_as_uint(__uint_as_float(sr[j]) + __uint_as_float(s2[j]));
+            }
             const int pb = c0 + tile * kTK;
             float t[32];
             float mx = -CUDART_INF_F;
@@ -397,23 +406,35 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
         const bool whole = pa.n_chunks == 1;
         const float mul = whole ? (lsum > 0.f ? unscale / lsum : 0.f) : unscale;
         float *dst = whole ? a.out + out_row * kHd : pa.scratch + (out_row * pa.n_chunks + chunk) * (kHd + 2);
+        // 32 rows x 32 columns at a time through a padded shared-memory block, so that the global
+        // stores of a warp cover one row's 128 bytes instead of 32 rows' 8 bytes
+        float *stg = reinterpret_cast<float *>(sm + oKhi) + (warp & 3) * (32 * 33);
+        const int wrow0 = (warp & 3) * 32;
         for (int b = 0; b < 8; b++) {
             uint32_t o[32];
             tmem_ld32(my_tmem + kColO + 32 * b, o);
-            if (real) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int d = 32 * b + j;
-                    float o0 = __uint_as_float(o[j]) * mul, o1 = __uint_as_float(o[j + 1]) * mul;
-                    if (whole) {
-                        float r0, r1;
-                        givens_inv(o0, o1, ss.givens[d], ss.givens[d + 1], r0, r1);
-                        o0 = r0;
-                        o1 = r1;
-                    }
-                    *reinterpret_cast<float2 *>(dst + d) = make_float2(o0, o1);
+            for (int j = 0; j < 32; j += 2) {
+                const int d = 32 * b + j;
+                float o0 = __uint_as_float(o[j]) * mul, o1 = __uint_as_float(o[j + 1]) * mul;
+                if (whole) {
+                    float r0, r1;
+                    givens_inv(o0, o1, ss.givens[d], ss.givens[d + 1], r0, r1);
+                    o0 = r0;
+                    o1 = r1;
                 }
+                stg[lane * 33 + j] = o0;
+                stg[lane * 33 + j + 1] = o1;
             }
+            __syncwarp();
+            for (int rr = 0; rr < 32; rr++) {
+                const int q = wrow0 + rr;
+                if (q >= n_rows) break;
+                const size_t orow = (size_t)(tok0 + q / NREP) * a.n_head + kv * NREP + q % NREP;
+                float *drow = whole ? a.out + orow * kHd : pa.scratch + (orow * pa.n_chunks + chunk) * (kHd + 2);
+                drow[32 * b + lane] = stg[rr * 33 + lane];
+            }
+            __syncwarp();
         }
         if (real && !whole) {
             dst[kHd] = R;
@@ -485,7 +506,7 @@ bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos
     pa.lut_alpha = alpha;
     pa.err_flag = ctx->d_err;
     const int vis = pos0 + n_tokens;
-    int chunks = (6 * ctx->n_sms + pa.n_blocks * a.n_kv - 1) / (pa.n_blocks * a.n_kv);  // about six CTAs per SM: the causal triangle leaves them unequal
+    int chunks = (4 * ctx->n_sms + pa.n_blocks * a.n_kv - 1) / (pa.n_blocks * a.n_kv);  // about four CTAs per SM: the causal triangle leaves them unequal
     chunks = std::max(1, std::min(chunks, std::min(64, vis / 256)));
     pa.n_chunks = chunks;
     if (chunks > 1) {
