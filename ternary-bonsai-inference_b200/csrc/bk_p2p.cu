@@ -155,6 +155,19 @@ bk_status bk_mailbox_open_peers(bk_mailbox *m, const void *handles) {
     bk_status st = bind_device(ctx);
     if (st != BK_OK) return st;
     const cudaIpcMemHandle_t *h = static_cast<const cudaIpcMemHandle_t *>(handles);
+    // Direct peer access to every other visible GPU, so that the mapped mailboxes are reached over
+    // NVLink whatever else the process has (or has not) initialised; "already enabled" and GPUs
+    // without a peer path are not errors here (the open below reports a real failure).
+    {
+        int n_dev = 0;
+        if (cudaGetDeviceCount(&n_dev) == cudaSuccess)
+            for (int d = 0; d < n_dev; d++) {
+                int can = 0;
+                if (d == ctx->device || cudaDeviceCanAccessPeer(&can, ctx->device, d) != cudaSuccess || !can) continue;
+                cudaDeviceEnablePeerAccess(d, 0);
+            }
+        cudaGetLastError();
+    }
     for (int r = 0; r < m->world; r++) {
         if (r == m->rank || m->opened[r]) continue;
         void *p = nullptr;
