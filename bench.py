@@ -332,6 +332,11 @@ def run_other_workload(args):
 
         def step(_s):
             for il in range(N_LAYERS):
+                if split is not None:  # one launch per rank and layer: append (tail owner), scan, exchange, merge
+                    own = rank == owner
+                    split.step_device(il, d_q.offset(il * NH * HD * 4), dk.ptr if own else None, dv.ptr if own else None,
+                                      out.data_ptr(), q_pos=pos_now[0])
+                    continue
                 if rank == owner:
                     cache.append_device(il, dk.ptr, dv.ptr, n_tokens=1, pos=pos_now[0])
                 if world == 1:

@@ -234,6 +234,13 @@ BK_API void bk_mailbox_destroy(bk_mailbox *mailbox);
 BK_API bk_status bk_decode_attn_split(bk_cache *cache, int32_t layer, int32_t seq, int32_t n_pos,
                                       int32_t q_pos, const float *q_dev, float *out_dev,
                                       bk_mailbox *mailbox, uint32_t seqno);
+/* The whole step of a split sequence in one launch per rank: the rank that owns
+ * the tail passes the new token's k/v [n_kv][hd] (they become its next row, roped
+ * at q_pos), every other rank passes NULL; then as bk_decode_attn_split over
+ * the rank's rows.  No reference counterpart (single-device reference). */
+BK_API bk_status bk_attn_step_split(bk_cache *cache, int32_t layer, int32_t seq, int32_t q_pos,
+                                    const float *q_dev, const float *k_dev, const float *v_dev,
+                                    float *out_dev, bk_mailbox *mailbox, uint32_t seqno);
 
 /* The attention step with the reference's own shape (src/forward.rs:247-375,
  * src/gdev.rs:584-829): rope q and k at `pos`, store k/v at row `pos` (which

@@ -70,6 +70,7 @@ SIGNATURES = {
     "bk_cache_snapshot_load": (C.c_int, [_vp, _i32, _vp, _sz]),
     "bk_prefill_attn": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "bk_prefill_step": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "bk_attn_step_split": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "bk_attn_layer_step": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _f, _vp]),
     "bk_attn_layer_step_host": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _f, _vp]),
     "bk_rms_norm_rows": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _f, _vp]),

@@ -639,6 +639,10 @@ void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out
     a.q_stride = a.gate_stride = kHd;
     a.q_norm_w = a.k_norm_w = a.gate = nullptr;
     a.eps = 0.f;
+    a.xch_peer = nullptr;
+    a.xch_world = a.xch_rank = 0;
+    a.xch_seqno = 0;
+    a.xch_err = ctx->d_err;
     a.k_rows_w = c->k_rows(layer, 0);
     a.v_rows_w = c->v_rows(layer, 0);
     a.k_norms_w = c->k_norms(layer, 0);
@@ -754,6 +758,36 @@ static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const i
         }
     return BK_OK;
 }
+
+namespace bk {
+bk_status decode_with_exchange(bk_cache *c, int layer, int seq, int n_pos, int q_pos, const float *q_dev, float *out_dev,
+                               uint8_t *const *d_peer, int world, int rank, unsigned seqno, const float *new_k,
+                               const float *new_v) {
+    bk_ctx *ctx = c->ctx;
+    bk_status st = bind(ctx);
+    if (st != BK_OK) return st;
+    DecodeArgs a;
+    fill_decode_args(c, layer, 0, &a);
+    if (new_k) {  // this rank owns the tail: the new token becomes row n_pos - 1 (already counted in n_pos)
+        if (decode_entry_uses_mma(ctx, a, n_pos)) {
+            a.new_k = new_k;
+            a.new_v = new_v;
+        } else {  // caches without the fused append: store first (n_pos is one ahead of the cache's count)
+            if ((st = bk_append(c, layer, seq, q_pos, 1, new_k, new_v)) != BK_OK) return st;
+        }
+    }
+    a.q = q_dev;
+    a.out = out_dev;
+    a.xch_peer = d_peer;
+    a.xch_world = world;
+    a.xch_rank = rank;
+    a.xch_seqno = seqno;
+    DecodeEntry e;
+    if ((st = check_decode_entry(c, layer, 0, &seq, &n_pos, &q_pos, "bk_decode_attn_split", &e)) != BK_OK) return st;
+    if (e.np <= 0) return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_split: empty chunk on the fused path");
+    return launch_decode_group(ctx, a, &e, 1, decode_entry_uses_mma(ctx, a, e.np), kMaxItems);
+}
+}  // namespace bk
 
 extern "C" {
 

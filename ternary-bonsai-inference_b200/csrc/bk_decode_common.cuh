@@ -294,7 +294,65 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
         }
         __syncthreads();
     }
-    if (a.partial) {
+    if (a.xch_peer) {
+        // ---- context split: send this kv head's rows to every rank, wait for everybody's, merge ----
+        __shared__ int s_ok;
+        constexpr int kStride = kHd + 2;
+        constexpr int kXchSpin = 1 << 20;  // polls of one arrival word before giving up (order of a second)
+        const int world = a.xch_world, rank = a.xch_rank, n_rows = a.n_head, row0 = kv * NREP;
+        const unsigned seqno = a.xch_seqno, par = seqno & 1u;
+        const size_t slot_f = (size_t)n_rows * kStride, data_b = 2 * (size_t)world * slot_f * sizeof(float);
+        for (int r = 0; r < world; r++) {
+            float *dst = reinterpret_cast<float *>(a.xch_peer[r]) + ((size_t)par * world + rank) * slot_f + (size_t)row0 * kStride;
+            for (int i = tid0; i < NREP * kStride; i += nt) {
+                const int rr = i / kStride, c = i - rr * kStride;
+                dst[i] = c < kHd ? s_acc[rr * kHd + c] : (c == kHd ? s_M[rr] * 0.6931471805599453f : s_L[rr]);
+            }
+        }
+        if (tid == 0) s_ok = 1;
+        __threadfence_system();
+        __syncthreads();
+        if (tid < world * NREP) {
+            const int r = tid / NREP, rr = tid - r * NREP;
+            unsigned *flag = reinterpret_cast<unsigned *>(a.xch_peer[r] + data_b) + ((size_t)par * world + rank) * n_rows + row0 + rr;
+            cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
+            f.store(seqno, cuda::memory_order_release);
+            // ... and wait for row rr of rank r in this rank's own mailbox
+            unsigned *mine = reinterpret_cast<unsigned *>(a.xch_peer[rank] + data_b) + ((size_t)par * world + r) * n_rows + row0 + rr;
+            cuda::atomic_ref<unsigned, cuda::thread_scope_system> g(*mine);
+            int polls = 0;
+            while (g.load(cuda::memory_order_acquire) != seqno) {
+                if (++polls > kXchSpin) {  // never expected; leave a mark and go on rather than hang
+                    s_ok = 0;
+                    if (a.xch_err) atomicExch(a.xch_err, 3);
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+        __syncthreads();
+        const float *mbox = reinterpret_cast<const float *>(a.xch_peer[rank]) + (size_t)par * world * slot_f + (size_t)row0 * kStride;
+        float *out = a.out + ((size_t)slot * a.n_head + row0) * kHd;
+        if (act) {
+            for (int rr = 0; rr < NREP; rr++) {
+                float Mx = -CUDART_INF_F;
+                for (int r = 0; r < world; r++) {
+                    const volatile float *p = mbox + (size_t)r * slot_f + (size_t)rr * kStride;
+                    if (p[kHd + 1] > 0.f) Mx = fmaxf(Mx, p[kHd]);
+                }
+                float Ls = 0.f, sum = 0.f;
+                for (int r = 0; r < world; r++) {
+                    const volatile float *p = mbox + (size_t)r * slot_f + (size_t)rr * kStride;
+                    if (p[kHd + 1] > 0.f) {
+                        const float f = expf(p[kHd] - Mx);
+                        Ls = fmaf(p[kHd + 1], f, Ls);
+                        sum = fmaf(p[tid], f, sum);
+                    }
+                }
+                out[rr * kHd + tid] = (s_ok && Ls > 0.f) ? sum / Ls : 0.f;
+            }
+        }
+    } else if (a.partial) {
         float *out = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP) * kPartStride;
         for (int i = tid0; i < NREP * kHd; i += nt) {
             const int r = i / kHd, d = i - r * kHd;

@@ -190,6 +190,14 @@ struct DecodeArgs {
     int q_stride, gate_stride;
     const float *q_norm_w, *k_norm_w, *gate;
     float eps;
+    // Context split over several GPUs (bk_p2p.cu): when xch_peer is set, the CTA that finishes a
+    // kv head does not write its rows to `out` but sends them (acc, m in ln units, l) to slot
+    // [xch_rank] of every rank's mailbox, publishes them with the call's sequence number, waits
+    // (bounded) for the same rows of every rank and writes their log-sum-exp merge to `out`.
+    uint8_t *const *xch_peer;
+    int xch_world, xch_rank;
+    unsigned xch_seqno;
+    int *xch_err;
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
 
@@ -204,6 +212,11 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
                               int max_items);
 bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos);
 bk_status bind_device(bk_ctx *ctx);
+// One sequence's decode attention whose finishing CTAs exchange and merge their rows through the
+// ranks' mailboxes (bk_api.cu; used by bk_decode_attn_split).
+bk_status decode_with_exchange(bk_cache *c, int layer, int seq, int n_pos, int q_pos, const float *q_dev, float *out_dev,
+                               uint8_t *const *d_peer, int world, int rank, unsigned seqno,
+                               const float *new_k = nullptr, const float *new_v = nullptr);
 // Tensor-core paths: 4-bit planar K and V (bk_decode_mma.cu) and f16 K and V (bk_decode_f16.cu).
 // Chunks must be multiples of 16 positions.
 bool decode_p4_mma_supported(const DecodeArgs &a);

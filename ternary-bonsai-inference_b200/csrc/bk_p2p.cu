@@ -18,6 +18,8 @@
 #include <cuda/atomic>
 #include <math_constants.h>
 
+#include <cstdlib>
+
 #include "bk_internal.h"
 
 struct bk_mailbox {
@@ -201,6 +203,11 @@ bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t 
     if (seqno == 0) return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_split: sequence numbers start at 1");
     for (int r = 0; r < m->world; r++)
         if (!m->peer[r]) return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_split: peers are not opened");
+    // A rank with rows to scan does everything in the decode launch: the CTA that finishes a kv head
+    // sends, waits and merges that head's rows itself.  An empty chunk has no such CTA and goes the
+    // two-step way (zero rows, then the exchange kernel); both speak the same mailbox protocol.
+    if (n_pos > 0 && !getenv("BONSAI_KV_SPLIT_UNFUSED"))
+        return decode_with_exchange(c, layer, seq, n_pos, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, seqno);
     bk_status st = bk_decode_attn_partial(c, layer, 1, &seq, &n_pos, &q_pos, q_dev, m->part);
     if (st != BK_OK) return st;
     exchange_merge_kernel<<<m->n_rows, 256, 0, ctx->stream>>>(m->d_peer, m->world, m->rank, m->n_rows, m->hd, m->part,
@@ -208,6 +215,33 @@ bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t 
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     return BK_OK;
+}
+
+bk_status bk_attn_step_split(bk_cache *c, int32_t layer, int32_t seq, int32_t q_pos, const float *q_dev,
+                             const float *k_dev, const float *v_dev, float *out_dev, bk_mailbox *m, uint32_t seqno) {
+    if (!c || !m) return fail(c ? c->ctx : nullptr, BK_ERR_INVALID, "bk_attn_step_split: null argument");
+    bk_ctx *ctx = c->ctx;
+    if (layer < 0 || layer >= c->cfg.n_layers || seq < 0 || seq >= c->cfg.n_seqs)
+        return fail(ctx, BK_ERR_INVALID, "bk_attn_step_split: bad layer/seq");
+    const bool owner = k_dev != nullptr;
+    if (owner && !v_dev) return fail(ctx, BK_ERR_INVALID, "bk_attn_step_split: k without v");
+    int32_t &np = c->n_pos[c->slab(layer, seq)];
+    if (!owner) return bk_decode_attn_split(c, layer, seq, np, q_pos, q_dev, out_dev, m, seqno);
+    if (np >= c->cfg.n_ctx)
+        return fail(ctx, BK_ERR_RANGE, "bk_attn_step_split: the local chunk is full (raise BONSAI_CTX)");
+    if (m->ctx != ctx || m->n_rows != c->cfg.n_head || m->hd != c->cfg.hd || seqno == 0)
+        return fail(ctx, BK_ERR_INVALID, "bk_attn_step_split: mailbox does not match, or sequence number 0");
+    for (int r = 0; r < m->world; r++)
+        if (!m->peer[r]) return fail(ctx, BK_ERR_INVALID, "bk_attn_step_split: peers are not opened");
+    if (q_pos < 0 || q_pos >= c->rope->n_pos) return fail(ctx, BK_ERR_RANGE, "bk_attn_step_split: position beyond the rope table");
+    // on caches that take the tensor-core kernels the row is stored by the decode launch itself
+    DecodeArgs a;
+    fill_decode_args(c, layer, 0, &a);
+    const bool fused_append = decode_entry_uses_mma(ctx, a, np + 1);
+    bk_status st = decode_with_exchange(c, layer, seq, np + 1, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, seqno,
+                                        k_dev, v_dev);
+    if (st == BK_OK && fused_append) np += 1;  // (the other route went through bk_append, which counted it)
+    return st;
 }
 
 }  // extern "C"

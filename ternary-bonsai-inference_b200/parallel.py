@@ -107,6 +107,13 @@ class ContextSplit:
         self.ctx.check(self.ctx.lib.bk_decode_attn_split(self.cache.h, il, seq, n_pos, q_pos, q_ptr, out_ptr,
                                                          self.mb, self.seqno))
 
+    def step_device(self, il, q_ptr, k_ptr, v_ptr, out_ptr, q_pos, seq=0):
+        """The whole step in one launch per rank: the tail owner passes the new token's k/v
+        device pointers (appended as its next row, roped at q_pos), the others pass None."""
+        self.seqno += 1
+        self.ctx.check(self.ctx.lib.bk_attn_step_split(self.cache.h, il, seq, q_pos, q_ptr, k_ptr, v_ptr, out_ptr,
+                                                       self.mb, self.seqno))
+
     def close(self):
         if getattr(self, "mb", None):
             self.ctx.lib.bk_mailbox_destroy(self.mb)

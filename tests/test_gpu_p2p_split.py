@@ -33,9 +33,11 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, out_q):
+def _rank_main(rank, world, port, out_q, variant="attend"):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    if variant == "unfused":
+        os.environ["BONSAI_KV_SPLIT_UNFUSED"] = "1"
     dist.init_process_group("gloo", rank=rank, world_size=world)
     ok, worst = True, 0.0
     try:
@@ -65,10 +67,15 @@ def _rank_main(rank, world, port, out_q):
         for s in range(steps):
             pos = n0 + s
             for il in range(layers):
-                if rank == owner:
-                    mine.append(il, k[pos], v[pos], pos=pos)
                 d_q = ctx.to_device(q[s, il])
-                split.attend_device(il, d_q.ptr, d_out.ptr, q_pos=pos)
+                if variant == "step":      # one launch per rank: the tail owner's append is part of it
+                    d_k, d_v = ctx.to_device(k[pos]), ctx.to_device(v[pos])
+                    own = rank == owner
+                    split.step_device(il, d_q.ptr, d_k.ptr if own else None, d_v.ptr if own else None, d_out.ptr, q_pos=pos)
+                else:
+                    if rank == owner:
+                        mine.append(il, k[pos], v[pos], pos=pos)
+                    split.attend_device(il, d_q.ptr, d_out.ptr, q_pos=pos)
                 got = d_out.download((NH, HD), np.float32)   # synchronises: reports a timed-out wait
                 d_q.free()
                 if whole:
@@ -87,12 +94,15 @@ def _rank_main(rank, world, port, out_q):
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-def test_split_context_over_peer_memory():
+@pytest.mark.parametrize("variant", ["attend", "step", "unfused"])
+def test_split_context_over_peer_memory(variant):
+    """attend: exchange and merge inside the decode launch's finishing CTAs; step: the tail owner's
+    append in the same launch too; unfused: partial rows, then the separate exchange kernel."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, variant)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(2)]
