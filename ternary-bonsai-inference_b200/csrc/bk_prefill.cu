@@ -124,7 +124,8 @@ __global__ void __launch_bounds__(kPT, 1) prefill_mma_kernel(PrefillArgs pa) {
     // ---- q rows: rope at the token's position, Givens rotation, scale, f16 hi/lo into the two
     // q tiles (a warp per row, staged through the K tile area) ---------------------------------
     {
-        float *stage = reinterpret_cast<float *>(k_tile) + warp * kHd;
+        float *stage = reinterpret_cast<float *>(k_tile) + warp * (kHd + 8);  // rows are padded by one float per 32 (see pad())
+        auto pad = [](int i) { return i + (i >> 5); };  // lanes 8 coordinates apart land in different banks
         const float qscale = rsqrtf((float)kHd) * 1.4426950408889634f / pa.lut_alpha;
         const int half = a.n_rot >> 1;
         // the next row's q and rope values travel while the current row is processed
@@ -147,7 +148,7 @@ __global__ void __launch_bounds__(kPT, 1) prefill_mma_kernel(PrefillArgs pa) {
             if (real) {
                 float2 rc[4];
 #pragma unroll
-                for (int i = 0; i < 8; i++) stage[lane + 32 * i] = xn[i];
+                for (int i = 0; i < 8; i++) stage[pad(lane + 32 * i)] = xn[i];
 #pragma unroll
                 for (int i = 0; i < 4; i++) rc[i] = rn[i];
                 prefetch(r + kPW);
@@ -156,10 +157,10 @@ __global__ void __launch_bounds__(kPT, 1) prefill_mma_kernel(PrefillArgs pa) {
                 for (int i = 0; i < 4; i++) {
                     const int j = lane + 32 * i;
                     if (j < half) {
-                        float x0 = stage[j], x1 = stage[j + half];
+                        float x0 = stage[pad(j)], x1 = stage[pad(j + half)];
                         rope_pair(x0, x1, rc[i]);
-                        stage[j] = x0;
-                        stage[j + half] = x1;
+                        stage[pad(j)] = x0;
+                        stage[pad(j + half)] = x1;
                     }
                 }
                 __syncwarp();
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(kPT, 1) prefill_mma_kernel(PrefillArgs pa) {
                 float o0 = 0.f, o1 = 0.f;
                 if (real) {
                     const int d = 8 * lane + 2 * p;
-                    givens_fwd(stage[d], stage[d + 1], sm.givens[d], sm.givens[d + 1], o0, o1);
+                    givens_fwd(stage[pad(d)], stage[pad(d + 1)], sm.givens[d], sm.givens[d + 1], o0, o1);
                     o0 *= qscale;
                     o1 *= qscale;
                 }
