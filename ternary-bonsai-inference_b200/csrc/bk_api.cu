@@ -892,9 +892,11 @@ bk_status bk_prefill_attn(bk_cache *c, int32_t layer, int32_t seq, int32_t pos0,
     fill_decode_args(c, layer, 0, &a);
     a.q = q_dev;
     a.out = out_dev;
-    if (!ctx->force_generic && prefill_mma_supported(a) && n_tokens >= 4)
-        return ctx->prefill_umma ? launch_prefill_umma(ctx, a, seq, pos0, n_tokens, ctx->lut_alpha[a.bits])
-                                 : launch_prefill_mma(ctx, a, seq, pos0, n_tokens, ctx->lut_alpha[a.bits]);
+    if (!ctx->force_generic && n_tokens >= 4) {
+        const float alpha = a.bits ? ctx->lut_alpha[a.bits] : 1.0f;
+        if (ctx->prefill_umma && prefill_umma_supported(a)) return launch_prefill_umma(ctx, a, seq, pos0, n_tokens, alpha);
+        if (prefill_mma_supported(a)) return launch_prefill_mma(ctx, a, seq, pos0, n_tokens, alpha);
+    }
     // Other caches and very short blocks: the decode kernels with one entry per token (each token
     // re-reads the rows it sees).
     std::vector<int32_t> ids(kMaxSeqsPerLaunch, seq), np(kMaxSeqsPerLaunch), qp(kMaxSeqsPerLaunch);

@@ -240,6 +240,7 @@ bk_status launch_rms_norm_rows(bk_ctx *ctx, const NormSeg &s0, const NormSeg &s1
 bool prefill_mma_supported(const DecodeArgs &a);
 bk_status launch_prefill_mma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha);
 // The same on tcgen05 tensor cores with the accumulators in tensor memory (bk_prefill_umma.cu).
+bool prefill_umma_supported(const DecodeArgs &a);  // planar4 / planar3 / f16 caches
 bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha);
 bk_status launch_lse_merge(bk_ctx *ctx, int n_parts, int n_rows, int hd, const float *parts, float *out);
 

@@ -51,6 +51,7 @@ struct SmallU {
     float givens[kHd];
     __half table[16], table_lo[16];
     unsigned long long bar_s, bar_o;
+    unsigned long long bar_t[2];  // f16 caches: the TMA engine fills two K/V stages
     uint32_t tmem_slot;
 };
 constexpr uint32_t kUmmaSmem = oSmall + sizeof(SmallU) + 1024;  // + alignment slack
@@ -108,7 +109,8 @@ struct PrefillUArgs {
 };
 
 template <int BITS, int NREP>
-__global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
+__global__ void __launch_bounds__(kUT, 1)
+prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const DecodeArgs &a = pa.d;
     const uint32_t base0 = (uint32_t)__cvta_generic_to_shared(smem_raw), base = (base0 + 1023u) & ~1023u;
@@ -116,7 +118,11 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
     SmallU &ss = *reinterpret_cast<SmallU *>(sm + oSmall);
     const uint32_t bar_s = base + oSmall + (uint32_t)offsetof(SmallU, bar_s), bar_o = base + oSmall + (uint32_t)offsetof(SmallU, bar_o);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    constexpr int kRowBytes = 32 * BITS;
+    // BITS = 16 stands for an f16 cache: its rows ARE the operands, so the TMA engine drops them into
+    // two shared-memory stages in the swizzled layout and nothing is dequantized (no table, no norms,
+    // no Givens rotation); everything else is the same kernel.
+    constexpr bool kF16 = BITS == 16;
+    constexpr int kRowBytes = kF16 ? 512 : 32 * BITS;
     constexpr bool kLoTiles = BITS == 4;  // see bk_prefill.cu: a 4-bit f16 table is only good to 1e-4
     // The K operand holds k_hi in rows 0-31 of every slab and, for 4 bit, k_lo in rows 32-63: one MMA
     // with N = 64 then yields q_hi k_hi and q_hi k_lo side by side (q is re-read from shared memory
@@ -137,14 +143,21 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
     // ---- tables, barriers, tensor memory ----------------------------------------------------
     for (int i = tid; i < kHd; i += kUT) ss.givens[i] = a.givens[i];
     if (tid < 16) {
-        const float c = a.book[tid & ((1 << BITS) - 1)] * pa.lut_alpha;
+        const float c = kF16 ? 0.f : a.book[tid & ((1 << (kF16 ? 4 : BITS)) - 1)] * pa.lut_alpha;
         const __half h = __float2half_rn(c);
         ss.table[tid] = h;
         ss.table_lo[tid] = __float2half_rn(c - __half2float(h));
     }
+    if (kF16 && tid < kTK) {  // no norms: ||k|| = 1, log2 ||v|| = 0
+        ss.kn[tid] = 1.f;
+        ss.lv[tid] = 0.f;
+    }
+    const uint32_t bar_t = base + oSmall + (uint32_t)offsetof(SmallU, bar_t);
     if (tid == 0) {
         mbar_init(bar_s, 1);
         mbar_init(bar_o, 1);
+        mbar_init(bar_t, 1);
+        mbar_init(bar_t + 8, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     if (warp == 0) tmem_alloc(base + oSmall + (uint32_t)offsetof(SmallU, tmem_slot), kTmemCols);
@@ -212,7 +225,12 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
                 float o0 = 0.f, o1 = 0.f;
                 if (real) {
                     const int d = 8 * lane + 2 * p;
-                    givens_fwd(stage[pad(d)], stage[pad(d + 1)], ss.givens[d], ss.givens[d + 1], o0, o1);
+                    if constexpr (kF16) {
+                        o0 = stage[pad(d)];
+                        o1 = stage[pad(d + 1)];
+                    } else {
+                        givens_fwd(stage[pad(d)], stage[pad(d + 1)], ss.givens[d], ss.givens[d + 1], o0, o1);
+                    }
                     o0 *= qscale;
                     o1 *= qscale;
                 }
@@ -228,6 +246,7 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
         }
     }
 
+    fence_smem_to_async_proxy();  // (f16: the TMA engine writes where the staging rows were)
     __syncthreads();  // the staging area becomes the K tile
 
     // ---- per-thread share of a packed tile: position tid / 8, coordinates 32 (tid % 8) .. + 31 ----
@@ -236,6 +255,7 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
     uint32_t pk[4], pv[4];
     float pn = 0.f;
     auto fetch = [&](int tile) {
+        if constexpr (kF16) return;
         const int pos = min(c0 + tile * kTK + my_row, a.n_ctx - 1);
         const size_t row = seq_rows + (size_t)pos * a.n_kv + kv;
         const uint8_t *kr = a.k_rows + row * kRowBytes, *vr = a.v_rows + row * kRowBytes;
@@ -243,7 +263,7 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
             const uint4 x = __ldg(reinterpret_cast<const uint4 *>(kr) + my_c), y = __ldg(reinterpret_cast<const uint4 *>(vr) + my_c);
             pk[0] = x.x; pk[1] = x.y; pk[2] = x.z; pk[3] = x.w;
             pv[0] = y.x; pv[1] = y.y; pv[2] = y.z; pv[3] = y.w;
-        } else {
+        } else if constexpr (BITS == 3) {
             const uint32_t *k3 = reinterpret_cast<const uint32_t *>(kr) + 3 * my_c, *v3 = reinterpret_cast<const uint32_t *>(vr) + 3 * my_c;
             pk[0] = __ldg(k3); pk[1] = __ldg(k3 + 1); pk[2] = __ldg(k3 + 2); pk[3] = 0;
             pv[0] = __ldg(v3); pv[1] = __ldg(v3 + 1); pv[2] = __ldg(v3 + 2); pv[3] = 0;
@@ -280,16 +300,52 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
     const uint32_t idesc_s = umma_idesc_f16(kRows, kTK, 0, 0), idesc_s2 = umma_idesc_f16(kRows, kKRows, 0, 0);
     const uint32_t idesc_o = umma_idesc_f16(kRows, kHd, 0, 1);
 
-    if (n_tiles > 0) fetch(0);
+    // f16: one thread has the TMA engine copy tile `tile` (32 rows x 512 bytes of K and of V, as
+    // 16 boxes of 16 rows x 128 bytes) into stage st; completion on bar_t[st].
+    auto issue_tma = [&](int tile, int st) {
+        const uint32_t bar = bar_t + (uint32_t)st * 8u, dstk = base + oKhi + (uint32_t)st * 2u * kKVTile, dstv = dstk + kKVTile;
+        mbar_expect_tx(bar, 2 * kKVTile);
+        const int gpos = a.layer_pos0 + pa.seq * a.n_ctx + c0 + tile * kTK;
+#pragma unroll
+        for (int sl = 0; sl < 4; sl++)
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                tma_tile_x(dstk + sl * kKVSlab + hf * 2048, &tm_k, sl * 128, kv, gpos + 16 * hf, bar);
+                tma_tile_x(dstv + sl * kKVSlab + hf * 2048, &tm_v, sl * 128, kv, gpos + 16 * hf, bar);
+            }
+    };
+    if constexpr (kF16) {
+        if (tid == 0 && n_tiles > 0) issue_tma(0, 0);
+    } else {
+        if (n_tiles > 0) fetch(0);
+    }
     for (int tile = 0; tile < n_tiles; tile++) {
         const uint32_t parity = (uint32_t)tile & 1u;
-        // ---- 1. dequantize K (the previous tile's products are complete: bar_o was awaited) --------
-        widen(pk);
-        dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, 4 * my_c);
-        if (tid < kTK) ss.kn[tid] = pn;
-        else if (tid < 2 * kTK) ss.lv[tid - kTK] = fast_log2(fmaxf(pn, 1e-30f));
-        fence_smem_to_async_proxy();
-        __syncthreads();
+        const int st = kF16 ? (tile & 1) : 0;
+        const uint32_t k_off = kF16 ? oKhi + (uint32_t)st * 2u * kKVTile : oKhi, v_off = kF16 ? k_off + kKVTile : oVhi;
+        if constexpr (kF16) {
+            // ---- 1. the next tile starts travelling (its stage was released when bar_o was awaited);
+            // this tile has landed; rows past the chunk's end may hold anything and are zeroed
+            if (tid == 0 && tile + 1 < n_tiles) issue_tma(tile + 1, st ^ 1);
+            wait_bar(bar_t + (uint32_t)st * 8u, (uint32_t)(tile >> 1) & 1u);
+            const int valid = c1 - (c0 + tile * kTK);
+            if (valid < kTK) {
+                for (int i = tid; i < 2 * 4 * kTK * 8; i += kUT) {
+                    const int tl = i >> 10, slab = (i >> 8) & 3, r = (i >> 3) & 31, c = i & 7;
+                    if (r >= valid) *reinterpret_cast<uint4 *>(sm + k_off + tl * kKVTile + slab * kKVSlab + r * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            fence_smem_to_async_proxy();
+            __syncthreads();
+        } else {
+            // ---- 1. dequantize K (the previous tile's products are complete: bar_o was awaited) --------
+            widen(pk);
+            dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, 4 * my_c);
+            if (tid < kTK) ss.kn[tid] = pn;
+            else if (tid < 2 * kTK) ss.lv[tid - kTK] = fast_log2(fmaxf(pn, 1e-30f));
+            fence_smem_to_async_proxy();
+            __syncthreads();
+        }
 
         // ---- 2. S = Q . K^T, and V is dequantized while it runs ---------------------------------------
         if (tid == 0) {
@@ -300,17 +356,19 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
                 const uint32_t ko = (uint32_t)(ks >> 2) * kKSlab + (uint32_t)(ks & 3) * 32u;
                 const uint64_t qh = umma_smem_desc(base + oQhi + qo, 16, 1024, kUmmaSwizzle128);
                 const uint64_t ql = umma_smem_desc(base + oQlo + qo, 16, 1024, kUmmaSwizzle128);
-                const uint64_t kd = umma_smem_desc(base + oKhi + ko, 16, 1024, kUmmaSwizzle128);
+                const uint64_t kd = umma_smem_desc(base + k_off + ko, 16, 1024, kUmmaSwizzle128);
                 umma_f16_ss(tmem + kColS, qh, kd, idesc_s2, ks > 0);  // columns 0-31: q_hi k_hi, 32-63: q_hi k_lo
                 umma_f16_ss(tmem + kColS, ql, kd, idesc_s, true);     // columns 0-31 += q_lo k_hi
             }
             umma_commit(bar_s);
         }
         __syncwarp();
-        widen(pv);
-        dequant_store_shfl<kLoTiles>(pv, tab, sm + oVhi, sm + oVlo, kTK, my_row, my_row, 4 * my_c);
-        if (tile + 1 < n_tiles) fetch(tile + 1);
-        fence_smem_to_async_proxy();
+        if constexpr (!kF16) {
+            widen(pv);
+            dequant_store_shfl<kLoTiles>(pv, tab, sm + oVhi, sm + oVlo, kTK, my_row, my_row, 4 * my_c);
+            if (tile + 1 < n_tiles) fetch(tile + 1);
+            fence_smem_to_async_proxy();
+        }
 
         // ---- 3. softmax: thread = query row ---------------------------------------------------------
         if (warp < 4) {
@@ -384,7 +442,7 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
             for (int kk = 0; kk < 2; kk++) {
                 const uint64_t ph = umma_smem_desc(base + oPhi + kk * 2 * kPChunk, kPChunk, 128, kUmmaSwizzleNone);
                 const uint64_t pl = umma_smem_desc(base + oPlo + kk * 2 * kPChunk, kPChunk, 128, kUmmaSwizzleNone);
-                const uint64_t vh = umma_smem_desc(base + oVhi + kk * 2048, kKVSlab, 1024, kUmmaSwizzle128);
+                const uint64_t vh = umma_smem_desc(base + v_off + kk * 2048, kKVSlab, 1024, kUmmaSwizzle128);
                 umma_f16_ss(tmem + kColO, ph, vh, idesc_o, true);
                 umma_f16_ss(tmem + kColO, pl, vh, idesc_o, true);
                 if constexpr (kLoTiles) {
@@ -418,7 +476,7 @@ __global__ void __launch_bounds__(kUT, 1) prefill_umma_kernel(PrefillUArgs pa) {
             for (int j = 0; j < 32; j += 2) {
                 const int d = 32 * b + j;
                 float o0 = __uint_as_float(o[j]) * mul, o1 = __uint_as_float(o[j + 1]) * mul;
-                if (whole) {
+                if (whole && !kF16) {
                     float r0, r1;
                     givens_inv(o0, o1, ss.givens[d], ss.givens[d + 1], r0, r1);
                     o0 = r0;
@@ -466,8 +524,8 @@ __global__ void __launch_bounds__(128) prefill_umma_merge_kernel(const float *sc
         Ls = fmaf(p[kHd + 1], f, Ls);
     }
     const float inv = Ls > 0.f ? 1.0f / Ls : 0.f;
-    float o0, o1;
-    givens_inv(a0 * inv, a1 * inv, givens[2 * pr], givens[2 * pr + 1], o0, o1);
+    float o0 = a0 * inv, o1 = a1 * inv;
+    if (givens) givens_inv(a0 * inv, a1 * inv, givens[2 * pr], givens[2 * pr + 1], o0, o1);  // planar V only
     *reinterpret_cast<float2 *>(out + row * kHd + 2 * pr) = make_float2(o0, o1);
 }
 
@@ -481,11 +539,14 @@ bk_status launch_umma_one(bk_ctx *ctx, const PrefillUArgs &pa) {
         configured[dev] = true;
     }
     const int grid = pa.n_blocks * pa.d.n_kv * pa.n_chunks;
-    prefill_umma_kernel<BITS, NREP><<<grid, kUT, kUmmaSmem, ctx->stream>>>(pa);
+    if (!pa.d.h_tmap_k || !pa.d.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "prefill: the cache has no tensor maps");
+    prefill_umma_kernel<BITS, NREP><<<grid, kUT, kUmmaSmem, ctx->stream>>>(pa, *static_cast<const CUtensorMap *>(pa.d.h_tmap_k),
+                                                                          *static_cast<const CUtensorMap *>(pa.d.h_tmap_v));
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     if (pa.n_chunks > 1) {
-        prefill_umma_merge_kernel<<<pa.n_tokens * pa.d.n_head, 128, 0, ctx->stream>>>(pa.scratch, pa.d.givens, pa.n_chunks, pa.d.out);
+        prefill_umma_merge_kernel<<<pa.n_tokens * pa.d.n_head, 128, 0, ctx->stream>>>(pa.scratch, BITS == 16 ? nullptr : pa.d.givens,
+                                                                                      pa.n_chunks, pa.d.out);
         ctx->launches++;
         BK_CUDA(ctx, cudaGetLastError());
     }
@@ -493,6 +554,13 @@ bk_status launch_umma_one(bk_ctx *ctx, const PrefillUArgs &pa) {
 }
 
 }  // namespace
+
+bool prefill_umma_supported(const DecodeArgs &a) {
+    const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
+    const bool planar = a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3);
+    const bool f16 = a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 && a.v_row_bytes == 512;
+    return (planar || f16) && a.h_tmap_k && a.h_tmap_v && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
+}
 
 bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha) {
     if (n_tokens <= 0) return BK_OK;
@@ -524,6 +592,7 @@ bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos
     }
 #define BK_PU_CASE(R)                                                                            \
     case R:                                                                                      \
+        if (a.k_kind == ROW_F16) return launch_umma_one<16, R>(ctx, pa);                         \
         return a.bits == 3 ? launch_umma_one<3, R>(ctx, pa) : launch_umma_one<4, R>(ctx, pa);
     switch (n_rep) {
         BK_PU_CASE(1)

@@ -841,14 +841,14 @@ def prefill_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0, n_tok, seed, n_he
 @pytest.mark.parametrize("tag,mode,bits,vq", [MODES[2], MODES[3], MODES[1], MODES[8], MODES[0]])
 @pytest.mark.parametrize("n0,n_tok", [(0, 45), (300, 50), (3000, 100), (37, 3), (0, 1)])
 def test_prefill_attention_equals_token_by_token(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0, n_tok):
-    """planar4 / planar3 take the batched tensor-core kernel (from 4 tokens on), the other modes
-    the decode kernels with one entry per token; every token must meet the decode bar."""
+    """planar4 / planar3 / f16 take the batched tensor-core kernel (from 4 tokens on), the other
+    modes the decode kernels with one entry per token; every token must meet the decode bar."""
     got, want = prefill_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0, n_tok, seed=n0 + n_tok + bits)
     for i in range(n_tok):
         assert_close(got[i], want[i], f"{tag} n0={n0} token {i}")
 
 
-@pytest.mark.parametrize("tag,mode,bits,vq", [MODES[2], MODES[3]])
+@pytest.mark.parametrize("tag,mode,bits,vq", [MODES[2], MODES[3], MODES[1]])
 def test_prefill_mma_sync_variant_and_empty_chunks(bk, oracle, monkeypatch, tag, mode, bits, vq):
     """The batched kernel exists twice: on tcgen05 with tensor-memory accumulators (default) and
     on mma.sync (BONSAI_KV_PREFILL=mma, read when the context is created).  A 700-token prompt
