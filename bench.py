@@ -271,8 +271,7 @@ def run_other_workload(args):
         def step(_s):
             for il in range(N_LAYERS):
                 if n_local:
-                    cache.append_batch_device(il, dk.ptr, dv.ptr, n_local)
-                    cache.decode_device(il, d_q.offset(il * n_local * NH * HD * 4), d_out.ptr, n_seqs=n_local)
+                    cache.step_batch_device(il, d_q.offset(il * n_local * NH * HD * 4), dk.ptr, dv.ptr, d_out.ptr, n_local)
         step_bytes = N_LAYERS * sum(attn_bytes(mode, int(lens[i])) + append_bytes(mode) for i in range(n_seqs))
         tokens_per_step, scaling = n_seqs, "strong"
         cfg = {"workload": f"batch64: {n_seqs} sequences, contexts U[2048,16384] (seeded, mean {lens.mean():.0f}), "

@@ -252,6 +252,14 @@ BK_API bk_status bk_attn_step(bk_cache *cache, int32_t layer, int32_t seq, int32
 BK_API bk_status bk_attn_step_host(bk_cache *cache, int32_t layer, int32_t seq, int32_t pos,
                                    const float *q_host, const float *k_host, const float *v_host,
                                    float *out_host);
+/* The attention step for a batch of independent sequences (no counterpart in
+ * the single-sequence reference; the per-sequence semantics are bk_attn_step's):
+ * sequence seq_ids[i] (NULL: i) gets one new token at its next position;
+ * q [n_seqs][n_head][hd], k/v [n_seqs][n_kv][hd], out [n_seqs][n_head][hd].
+ * One launch when every sequence is long enough for a tensor-core kernel. */
+BK_API bk_status bk_attn_step_batch(bk_cache *cache, int32_t layer, int32_t n_seqs,
+                                    const int32_t *seq_ids, const float *q_dev, const float *k_dev,
+                                    const float *v_dev, float *out_dev);
 /* Batched (prefill) form: causal attention of n_tokens consecutive prompt
  * tokens of one sequence whose K/V rows are already in the cache; token i
  * (rope position pos0 + i) attends rows 0 .. pos0 + i.  q and out are

@@ -68,6 +68,7 @@ SIGNATURES = {
     "bk_cache_snapshot_bytes": (_sz, [_vp, _i32]),
     "bk_cache_snapshot_save": (C.c_int, [_vp, _i32, _i32, _vp, _sz, _vp]),
     "bk_cache_snapshot_load": (C.c_int, [_vp, _i32, _vp, _sz]),
+    "bk_attn_step_batch": (C.c_int, [_vp, _i32, _i32, _pi32, _vp, _vp, _vp, _vp]),
     "bk_prefill_attn": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "bk_prefill_step": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bk_attn_step_split": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, C.c_uint32]),

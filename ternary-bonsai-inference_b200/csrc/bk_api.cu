@@ -21,8 +21,8 @@ namespace bk {
 // round almost exactly and the tensor-core path loses nothing to the f16 table.
 static float best_lut_alpha(const float *book, int n) {
     float best_a = 1.0f, best_e = 1e30f;
-    for (int i = 0; i < 4096; i++) {
-        const float al = 1.0f + (float)i / 4096.0f;
+    for (int i = 0; i < 65536; i++) {  // (one binade covers every alignment of the f16 grid)
+        const float al = 1.0f + (float)i / 65536.0f;
         float worst = 0.f;
         for (int k = 0; k < n; k++) {
             const float c = book[k];
@@ -870,6 +870,47 @@ bk_status bk_attn_step_host(bk_cache *c, int32_t layer, int32_t seq, int32_t pos
     BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     memcpy(out_host, h_out, qb);
     return BK_OK;
+}
+
+bk_status bk_attn_step_batch(bk_cache *c, int32_t layer, int32_t n_seqs, const int32_t *seq_ids, const float *q_dev,
+                             const float *k_dev, const float *v_dev, float *out_dev) {
+    if (!c || layer < 0 || layer >= c->cfg.n_layers) return fail(c ? c->ctx : nullptr, BK_ERR_INVALID, "bk_attn_step_batch: bad layer");
+    bk_ctx *ctx = c->ctx;
+    if (n_seqs < 0) return fail(ctx, BK_ERR_INVALID, "bk_attn_step_batch: negative count");
+    if (n_seqs == 0) return BK_OK;
+    if (!q_dev || !k_dev || !v_dev || !out_dev) return fail(ctx, BK_ERR_INVALID, "bk_attn_step_batch: null argument");
+    bk_status st = bind(ctx);
+    if (st != BK_OK) return st;
+    DecodeArgs a;
+    fill_decode_args(c, layer, 0, &a);
+    // One launch when every sequence takes a tensor-core kernel (which stores the new rows itself);
+    // otherwise the batched append and the batched decode, two launches.
+    bool all_fused = n_seqs <= kMaxSeqsPerLaunch;
+    std::vector<DecodeEntry> list((size_t)n_seqs);
+    for (int i = 0; i < n_seqs && all_fused; i++) {
+        const int s = seq_ids ? seq_ids[i] : i;
+        if (s < 0 || s >= c->cfg.n_seqs) return fail(ctx, BK_ERR_INVALID, "bk_attn_step_batch: bad sequence id");
+        for (int j = 0; seq_ids && j < i; j++)
+            if (seq_ids[j] == s) return fail(ctx, BK_ERR_INVALID, "bk_attn_step_batch: duplicate sequence id");
+        const int np = c->n_pos[c->slab(layer, s)];
+        if (np + 1 > c->cfg.n_ctx)
+            return fail(ctx, BK_ERR_RANGE, "bk_attn_step_batch: sequence " + std::to_string(s) + " is full (raise BONSAI_CTX)");
+        if (np >= c->rope->n_pos) return fail(ctx, BK_ERR_RANGE, "bk_attn_step_batch: position beyond the rope table");
+        all_fused = decode_entry_uses_mma(ctx, a, np + 1);
+        list[i] = DecodeEntry{i, s, np + 1, np};
+    }
+    if (all_fused) {
+        a.q = q_dev;
+        a.out = out_dev;
+        a.new_k = k_dev;
+        a.new_v = v_dev;
+        st = launch_decode_group(ctx, a, list.data(), n_seqs, true, kMaxItems);
+        if (st != BK_OK) return st;
+        for (int i = 0; i < n_seqs; i++) c->n_pos[c->slab(layer, list[i].seq)]++;
+        return BK_OK;
+    }
+    if ((st = bk_append_batch(c, layer, n_seqs, seq_ids, nullptr, k_dev, v_dev)) != BK_OK) return st;
+    return decode_impl(c, layer, n_seqs, seq_ids, nullptr, nullptr, q_dev, out_dev, 0, "bk_attn_step_batch");
 }
 
 bk_status bk_prefill_attn(bk_cache *c, int32_t layer, int32_t seq, int32_t pos0, int32_t n_tokens, const float *q_dev,

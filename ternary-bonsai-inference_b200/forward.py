@@ -138,6 +138,11 @@ class AttnCache:
                                                       va.ctypes.data, out.ctypes.data))
         return out
 
+    def step_batch_device(self, il, q_ptr, k_ptr, v_ptr, out_ptr, n_seqs, seq_ids=None):
+        """One new token for each of n_seqs independent sequences: append + attend (asynchronous)."""
+        sp, _s = _i32_array(seq_ids) or (None, None)
+        self.ctx.check(self.ctx.lib.bk_attn_step_batch(self.h, il, n_seqs, sp, q_ptr, k_ptr, v_ptr, out_ptr))
+
     def prefill_attend(self, il, q, pos0, seq=0):
         """Causal attention of a block of prompt tokens already in the cache: host q [n, n_head, hd],
         token i at position pos0 + i; returns [n, n_head, hd]."""

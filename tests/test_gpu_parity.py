@@ -902,3 +902,39 @@ def test_prefill_step_appends_then_attends(bk, gpu_ctx, oracle):
     for b in (dq, dk, dv, do):
         b.free()
     cache.close()
+
+
+def test_batched_step_one_launch_and_mixed_lengths(bk, gpu_ctx, oracle):
+    """bk_attn_step_batch: a batch of long planar4 sequences is one launch per step (the decode
+    kernel stores the new rows); a batch with a short sequence goes through append + decode.
+    Rows bit-exact and outputs within the bar either way."""
+    rng = np.random.default_rng(21)
+    for lens, one_launch in (([4100, 6000, 9000], True), ([4100, 40, 6000], False)):
+        n_seqs, steps = len(lens), 3
+        cache = bk.AttnCache(gpu_ctx, bk.parse_mode("planar4"), n_layers=1, n_seqs=n_seqs, n_ctx=max(lens) + steps)
+        refs = []
+        for s, n in enumerate(lens):
+            k, v = synth_kv(rng, n)
+            cache.append(0, k, v, seq=s)
+            ref = oracle.cache(MODE_PLANAR, 4, True)
+            for p in range(n):
+                ref.append(0, k[p], v[p], p)
+            refs.append(ref)
+        for t in range(steps):
+            q = rng.standard_normal((n_seqs, NH, HD)).astype(np.float32)
+            k = rng.standard_normal((n_seqs, NKV, HD)).astype(np.float32)
+            v = rng.standard_normal((n_seqs, NKV, HD)).astype(np.float32)
+            dq, dk, dv = gpu_ctx.to_device(q), gpu_ctx.to_device(k), gpu_ctx.to_device(v)
+            do = gpu_ctx.alloc(n_seqs * NH * HD * 4)
+            launches = gpu_ctx.launch_count
+            cache.step_batch_device(0, dq.ptr, dk.ptr, dv.ptr, do.ptr, n_seqs)
+            assert (gpu_ctx.launch_count - launches == 1) == one_launch
+            got = do.download((n_seqs, NH, HD), np.float32)
+            for s in range(n_seqs):
+                want = refs[s].step(0, q[s], k[s], v[s], lens[s] + t, threads=8)
+                assert_close(got[s], want, f"{lens} seq {s} step {t}")
+            for b in (dq, dk, dv, do):
+                b.free()
+        for s in range(n_seqs):
+            compare_dumps(cache.dump_kv(0, seq=s, pos0=lens[s] - 1), {key: val[lens[s] - 1:] for key, val in refs[s].dump(0).items()})
+        cache.close()
