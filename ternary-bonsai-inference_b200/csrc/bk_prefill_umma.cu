@@ -1,25 +1,27 @@
-// Batched (prefill) attention over a 4-bit or 3-bit planar cache on the 5th-generation tensor
-// cores: the same work split, operands and arithmetic as bk_prefill.cu (which documents them and
-// stays as the mma.sync form), with both contractions issued as tcgen05.mma and the accumulators
-// in tensor memory.
+// Batched (prefill) attention over a 4-bit or 3-bit planar cache, or an f16 cache, on the
+// 5th-generation tensor cores: the same work split, operands and arithmetic as bk_prefill.cu
+// (which documents them and stays as the mma.sync form), with both contractions issued as
+// tcgen05.mma and the accumulators in tensor memory.
 //
 // One CTA = 128 query rows (M = 128) of one kv head over one context chunk; 8 warps.  Per tile
 // of 32 positions:
-//   1. all warps dequantize the packed K and V rows once into shared memory as f16 tiles (hi, and
-//      for 4 bit the rounding remainders lo) in the K-major / MN-major 128-byte-swizzled layouts
-//      the tensor cores read directly;
-//   2. one thread issues S[128 x 32] = Q . K^T as 16 K-steps x (q_hi k_hi + q_lo k_hi + q_hi k_lo)
-//      into 32 tensor-memory columns and commits to an mbarrier;
+//   1. all warps dequantize the packed K rows once into shared memory as f16 (for 4 bit also the
+//      rounding remainders, as rows 32-63 of the same K-major, 128-byte-swizzled operand tile);
+//   2. one thread issues S[128 x 32] = Q . K^T as 16 K-steps x (q_hi [k_hi; k_lo] with N = 64, then
+//      q_lo k_hi with N = 32) into tensor-memory columns and commits to an mbarrier; while those
+//      MMAs run, all warps dequantize V (hi and lo tiles, read later as the MN-major B operand);
 //   3. warps 0-3 (thread = query row: tensor-memory lane r is row r) read their row of S with
 //      tcgen05.ld, scale by ||k||, apply the causal limit, update the running reference R of
 //      s + log2 ||v|| LAZILY (only when the row maximum exceeds R by more than 8: the weights
 //      p = 2^(t - R) * 64 then stay below 2^14 in f16), rescale their row of O in tensor memory when
 //      R moved, and write the weights as f16 hi + lo into the no-swizzle K-major P tiles;
 //   4. the same thread issues O[128 x 256] += P . V as 2 K-steps x (p_hi v_hi + p_lo v_hi + p_hi v_lo)
-//      into 256 tensor-memory columns (V tile as MN-major B operand) and commits.
+//      into 256 tensor-memory columns and commits.
+// f16 caches (BITS = 16) skip the dequantization: the TMA engine drops their rows, which are the
+// operands as stored, into two shared-memory stages through the cache's swizzled tensor maps.
 // Every mbarrier wait is bounded (a time-out raises the context's error flag and the kernel runs
 // on to its end, where the tensor memory is always released).  The packed rows of the next tile
-// are fetched into registers while the current one is computed.
+// are fetched into registers (f16: into the other stage) while the current one is computed.
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
@@ -67,21 +69,9 @@ __device__ __forceinline__ uint32_t expand24u(uint32_t y) {
     y += (y & 0x38383838u);
     return y;
 }
-__device__ __forceinline__ void dequant_store_u(const uint32_t (&w)[4], const __half *table, uint8_t *tile, int row, int chunk0) {
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        uint32_t h[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const uint32_t lo = (w[j] >> (8 * e)) & 15u, hi = (w[j] >> (8 * e + 4)) & 15u;
-            h[e] = (uint32_t)__half_as_ushort(table[lo]) | ((uint32_t)__half_as_ushort(table[hi]) << 16);
-        }
-        *reinterpret_cast<uint4 *>(tile + sw_off(kTK, row, chunk0 + j)) = make_uint4(h[0], h[1], h[2], h[3]);
-    }
-}
-
-// The same with the table in registers: lane i holds (hi | lo << 16) of centroid i & 15, one
-// shuffle looks both parts of an index up, and no shared-memory bank is involved.
+// 32 coordinates (four words of eight nibbles) -> 32 halfs as four 16-byte chunks of a tile row.
+// The table sits in registers: lane i holds (hi | lo << 16) of centroid i & 15, one shuffle looks
+// both parts of an index up, and no shared-memory bank is involved.
 template <bool LO>
 __device__ __forceinline__ void dequant_store_shfl(const uint32_t (&w)[4], uint32_t tab, uint8_t *tile_hi, uint8_t *tile_lo, int rows,
                                                    int row_hi, int row_lo, int chunk0) {
