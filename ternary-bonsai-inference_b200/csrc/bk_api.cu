@@ -863,10 +863,12 @@ bk_status bk_attn_step_host(bk_cache *c, int32_t layer, int32_t seq, int32_t pos
     memcpy(h + qb, k_host, kb);
     memcpy(h + qb + kb, v_host, kb);
     BK_CUDA(ctx, cudaMemcpyAsync(d, h, qb + 2 * kb, cudaMemcpyHostToDevice, ctx->stream));
-    float *d_out = (float *)(d + qb + 2 * kb), *h_out = (float *)(h + qb + 2 * kb);
-    st = bk_attn_step(c, layer, seq, pos, (const float *)d, (const float *)(d + qb), (const float *)(d + qb + kb), d_out);
+    // The output goes straight into the pinned staging buffer (device-addressable under unified
+    // addressing): the CTAs that finish the kv heads write their 6 KB over the bus themselves, which
+    // saves the copy-back call of a step that is all latency.
+    float *h_out = (float *)(h + qb + 2 * kb);
+    st = bk_attn_step(c, layer, seq, pos, (const float *)d, (const float *)(d + qb), (const float *)(d + qb + kb), h_out);
     if (st != BK_OK) return st;
-    BK_CUDA(ctx, cudaMemcpyAsync(h_out, d_out, qb, cudaMemcpyDeviceToHost, ctx->stream));
     BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     memcpy(out_host, h_out, qb);
     return BK_OK;
@@ -1047,11 +1049,10 @@ bk_status bk_attn_layer_step_host(bk_cache *c, int32_t layer, int32_t seq, int32
     memcpy(h + qfb + 2 * kb, q_norm_w_host, wb);
     memcpy(h + qfb + 2 * kb + wb, k_norm_w_host, wb);
     BK_CUDA(ctx, cudaMemcpyAsync(d, h, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
-    float *d_out = (float *)(d + in_bytes), *h_out = (float *)(h + in_bytes);
+    float *h_out = (float *)(h + in_bytes);  // written by the kernel directly (see bk_attn_step_host)
     st = bk_attn_layer_step(c, layer, seq, pos, (const float *)d, (const float *)(d + qfb), (const float *)(d + qfb + kb),
-                            (const float *)(d + qfb + 2 * kb), (const float *)(d + qfb + 2 * kb + wb), eps, d_out);
+                            (const float *)(d + qfb + 2 * kb), (const float *)(d + qfb + 2 * kb + wb), eps, h_out);
     if (st != BK_OK) return st;
-    BK_CUDA(ctx, cudaMemcpyAsync(h_out, d_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
     BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     memcpy(out_host, h_out, ob);
     return BK_OK;
