@@ -355,6 +355,54 @@ def run_other_workload(args):
                            + ("through peer memory inside the merge kernel (bk_decode_attn_split)" if split is not None
                               else "by one NCCL all-gather, then bk_lse_merge"),
                "l2": "%.2f GB of cache per step over all GPUs" % (step_bytes / 1e9)}
+    elif args.workload == "pq2":
+        # The four PQ2_0 projections of a full-attention layer, one token: wq [12288 x 5120] (q | gate),
+        # wk and wv [1024 x 5120], wo [5120 x 6144]; 16 layers with their own weights (446 MB, larger than L2).
+        shapes = [("wq", 2 * NH * HD, 5120), ("wk", NKV * HD, 5120), ("wv", NKV * HD, 5120), ("wo", 5120, NH * HD)]
+        n_tok = 1
+        tensors, host_payloads = [], []
+        for il in range(N_LAYERS):
+            for name, n_rows, ne0 in shapes:
+                nb = ne0 // 128
+                raw = rng.integers(0, 256, size=(n_rows, nb, 34), dtype=np.uint8)
+                raw[..., :2] = (0.01 + rng.random((n_rows, nb))).astype(np.float16).view(np.uint8).reshape(n_rows, nb, 2)
+                tensors.append((bk.Pq2Tensor(ctx, raw.reshape(-1), ne0), n_rows, ne0))
+                if il == 0:
+                    host_payloads.append((raw.reshape(-1), n_rows, ne0))
+        hx = {ne0: rng.standard_normal((n_tok, ne0), dtype=np.float32) for ne0 in (5120, NH * HD)}
+        dx = {ne0: ctx.to_device(v) for ne0, v in hx.items()}
+        d_y = ctx.alloc(n_tok * 2 * NH * HD * 4)
+
+        def step(_s):
+            for t, _n, ne0 in tensors:
+                t.matvec_device(dx[ne0].ptr, d_y.ptr, n_tok)
+        step_bytes = sum(t.payload_bytes for t, _n, _e in tensors)
+        tokens_per_step, scaling = n_tok, "weak"
+        cfg = {"workload": f"pq2: wq/wk/wv/wo of {N_LAYERS} full-attention layers, {n_tok} token(s), weights resident "
+                           f"({step_bytes / 1e6:.0f} MB streamed per step, larger than L2)"}
+
+        def pq2_extras():
+            """e2e through the host-buffer call, and the oracle's scalar matvec on one layer (x 16)."""
+            for t, n_rows, ne0 in tensors[:4]:
+                t.matmul_n(hx[ne0], n_tok)
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                for t, n_rows, ne0 in tensors:
+                    t.matmul_n(hx[ne0], n_tok)
+            e2e = args.steps * n_tok / (time.perf_counter() - t0)
+            out = {"e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": N_LAYERS * (3 * 5120 + NH * HD) * 4 * n_tok,
+                           "d2h_bytes_per_step": N_LAYERS * sum(n for _p, n, _e in host_payloads) * 4 * n_tok}}
+            if not args.no_cpu_baseline:
+                sys.path.insert(0, os.path.join(ROOT, "tests"))
+                from oracle_lib import load_oracle
+                orc = load_oracle()
+                t0 = time.perf_counter()
+                for pl, n_rows, ne0 in host_payloads:
+                    orc.pq2_matmul(pl, ne0, 0, n_rows, hx[ne0], n_tok)
+                dt = time.perf_counter() - t0
+                out["cpu_baseline"] = {"value": n_tok / (dt * N_LAYERS), "unit": "tokens/s", "cores": 1, "kind": "port",
+                                       "sample": "the four tensors of one layer through the oracle's scalar row dot, time x 16"}
+            return out
     else:  # appendsweep
         cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=4096 * 2)
         k, v = synth_chunk(rng, 4096, channels)
@@ -411,12 +459,18 @@ def run_other_workload(args):
         if args.workload == "prefill":
             line["metric"] = "quantized-KV prefill attention prompt tokens/s"
             line["useful_tflops"] = cfg["useful_tflop_per_step"] / (ms_step * 1e-3)
+        if args.workload == "pq2":
+            line["metric"] = "PQ2_0 attention-projection matvec tokens/s"
+            line.update(pq2_extras())
         line.update({"value": tokens_per_step * 1e3 / ms_step, "ms_per_step": ms_step, "scaling": scaling, "config": cfg,
                      "effective_gbs": gbs, "gpu_launches": ctx.launch_count - launches0,
                      "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s",
                                   "frac": gbs / world / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
                                   "note": "whole step (append + decode of every layer) per GPU, not one kernel"},
                      "clocks": clocks})
+        if args.workload == "pq2":
+            line["roofline"]["note"] = ("pq2_matvec_kernel, every launch of the step: payload bytes (the algorithmic "
+                                        "bytes: each weight byte once) over the step's device time")
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -451,7 +505,7 @@ def main():
     ap.add_argument("--step", default="attn", choices=["attn", "layer"],
                     help="attn: bk_attn_step (the metric's step); layer: bk_attn_layer_step, which also does the "
                          "q|gate split, the per-head RMSNorm of q and k and the sigmoid gate in the same launch")
-    ap.add_argument("--workload", default="decode128k", choices=["decode128k", "batch64", "splitctx", "appendsweep", "prefill"],
+    ap.add_argument("--workload", default="decode128k", choices=["decode128k", "batch64", "splitctx", "appendsweep", "prefill", "pq2"],
                     help="decode128k: the headline (default).  batch64: 64 sequences, contexts U[2048,16384], sharded "
                          "over the ranks.  splitctx: one 262144-token sequence, context chunks per rank, LSE merge.  "
                          "appendsweep: append throughput for 1..4096 tokens per call")

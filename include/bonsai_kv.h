@@ -294,6 +294,27 @@ BK_API bk_status bk_attn_layer_step_host(bk_cache *cache, int32_t layer, int32_t
  * sharing one weight; bit-exact (sequential sum of squares). */
 BK_API bk_status bk_rms_norm_rows(bk_ctx *ctx, int32_t n_rows, int32_t row_len, const float *x_host,
                                   const float *w_host, float eps, float *out_host);
+/* PQ2_0 ternary rows (src/kernels.rs:204-211): ceil(ne0 / 128) blocks of 34
+ * bytes (f16 scale + 128 two-bit codes, weight = (code - 1) * scale). */
+BK_API size_t bk_pq2_row_bytes(int64_t ne0);
+/* pq2_matvec_range / pq2_matmul_n (src/kernels.rs:265-330, 333-420; the device
+ * form is Gpu::matvec_pq2, shaders/pq2_matvec_fused.comp):
+ * y[t * n_rows + r] = sum_j x[t * ne0 + j] * W[base_row + r][j] for n_tok
+ * activations.  payload_dev is the tensor's whole contiguous data in device
+ * memory (rows back to back, bk_pq2_row_bytes apart; 16-byte alignment of the
+ * first row of the range lets the TMA engine stream it, any even address
+ * works); like the reference the call fails (BK_ERR_RANGE) when the rows asked
+ * for do not lie inside payload_bytes.  Four tokens share one pass over the
+ * weights.  The sum runs on the tensor cores with x as f16 hi + lo, so it
+ * differs from the reference's scalar path by rounding order, like the
+ * reference's own AVX2 path (src/kernels.rs:652-660). */
+BK_API bk_status bk_pq2_matvec(bk_ctx *ctx, const void *payload_dev, size_t payload_bytes, int64_t ne0,
+                               int64_t base_row, int64_t n_rows, const float *x_dev, int32_t n_tok,
+                               float *y_dev);
+/* The same with host x and y (weights stay resident in device memory). */
+BK_API bk_status bk_pq2_matvec_host(bk_ctx *ctx, const void *payload_dev, size_t payload_bytes,
+                                    int64_t ne0, int64_t base_row, int64_t n_rows, const float *x_host,
+                                    int32_t n_tok, float *y_host);
 /* Gpu::attn_step (src/vk.rs:1671-1752): one-shot f32 attention over host
  * k/v caches [n_pos][kvheads][hd], no rope; validates sizes like the
  * reference (hd must be 256 here). */

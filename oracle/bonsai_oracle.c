@@ -943,3 +943,66 @@ OR_API int or_max_threads(void) {
     long n = sysconf(_SC_NPROCESSORS_ONLN);
     return n > 0 ? (int)n : 1;
 }
+
+/* ---- PQ2_0 ternary rows (src/kernels.rs:204-330, 333-420, 631-650) ---------------------- */
+
+/* pq2_row_bytes, src/kernels.rs:208-211. */
+OR_API size_t or_pq2_row_bytes(size_t ne0) { return ((ne0 + 127) / 128) * 34; }
+
+/* decode_pq2_0_row, src/kernels.rs:213-229: (code - 1) * scale, codes two bits each, least
+ * significant first, one f16 scale per 128. */
+OR_API void or_pq2_decode_row(const uint8_t *raw, size_t ne0, float *out) {
+    size_t n = 0;
+    for (size_t block = 0; block < (ne0 + 127) / 128; block++) {
+        const uint8_t *b = raw + block * 34;
+        const float scale = or_half_to_f32((uint16_t)(b[0] | (b[1] << 8)));
+        for (size_t j = 0; j < 128 && block * 128 + j < ne0; j++) {
+            const int code = (b[2 + j / 4] >> ((j % 4) * 2)) & 3;
+            out[n++] = (float)(code - 1) * scale;
+        }
+    }
+}
+
+/* row_dot_scalar, src/kernels.rs:633-650: per block a sequential f32 sum of x * (code - 1), then
+ * acc += scale * block_acc.  (The reference's AVX2 path, 652-760, is the same sum in another
+ * order; its own test bounds the difference by 1e-4 relative, src/kernels.rs:855-906.) */
+static float pq2_row_dot(const uint8_t *raw, size_t ne0, const float *x) {
+    float acc = 0.0f;
+    for (size_t block = 0; block < (ne0 + 127) / 128; block++) {
+        const uint8_t *b = raw + block * 34;
+        const float scale = or_half_to_f32((uint16_t)(b[0] | (b[1] << 8)));
+        const size_t start = block * 128, end = start + 128 < ne0 ? start + 128 : ne0;
+        float block_acc = 0.0f;
+        for (size_t j = start; j < end; j++) {
+            const int code = (b[2 + (j - start) / 4] >> (((j - start) % 4) * 2)) & 3;
+            block_acc += x[j] * (float)(code - 1);
+        }
+        acc += scale * block_acc;
+    }
+    return acc;
+}
+
+/* dot_pq2_0_row, src/kernels.rs:234-263: the dot against the DECODED row (weights scaled first),
+ * another rounding order the reference ships; -1 when the row is outside the payload. */
+OR_API int or_pq2_dot_row(const uint8_t *payload, size_t payload_len, size_t ne0, size_t row, const float *x, float *out) {
+    const size_t rb = or_pq2_row_bytes(ne0);
+    if ((row + 1) * rb > payload_len) return -1;
+    float *w = (float *)malloc(ne0 * sizeof(float));
+    or_pq2_decode_row(payload + row * rb, ne0, w);
+    float acc = 0.0f;
+    for (size_t j = 0; j < ne0; j++) acc += x[j] * w[j];
+    free(w);
+    *out = acc;
+    return 0;
+}
+
+/* pq2_matvec_range / pq2_matmul_n, src/kernels.rs:265-330, 333-420 (scalar row dot):
+ * y[t * n_rows + r] = x[t] . W[base_row + r].  -1: rows outside the payload. */
+OR_API int or_pq2_matmul(const uint8_t *payload, size_t payload_len, size_t ne0, size_t base_row, size_t n_rows, const float *x,
+                         size_t n_tok, float *y) {
+    const size_t rb = or_pq2_row_bytes(ne0);
+    if ((base_row + n_rows) * rb > payload_len) return -1;
+    for (size_t r = 0; r < n_rows; r++)
+        for (size_t t = 0; t < n_tok; t++) y[t * n_rows + r] = pq2_row_dot(payload + (base_row + r) * rb, ne0, x + t * ne0);
+    return 0;
+}

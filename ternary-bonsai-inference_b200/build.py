@@ -31,6 +31,7 @@ SOURCES = {
     "bk_decode_f16.cu": [],
     "bk_noalloc.cu": [],
     "bk_layer.cu": ["--fmad=false"],
+    "bk_pq2.cu": [],
     "bk_prefill.cu": [],
     "bk_prefill_umma.cu": [],
     "bk_p2p.cu": [],

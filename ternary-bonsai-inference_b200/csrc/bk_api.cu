@@ -1082,6 +1082,68 @@ bk_status bk_rms_norm_rows(bk_ctx *ctx, int32_t n_rows, int32_t row_len, const f
     return BK_OK;
 }
 
+/* ---- PQ2_0 ternary matvec -------------------------------------------------- */
+
+size_t bk_pq2_row_bytes(int64_t ne0) { return ne0 > 0 ? pq2_row_bytes(ne0) : 0; }
+
+static bk_status pq2_check(bk_ctx *ctx, const char *who, const void *payload, size_t payload_bytes, int64_t ne0, int64_t base_row,
+                           int64_t n_rows, int32_t n_tok, const void *x, const void *y) {
+    if (!ctx) return fail(nullptr, BK_ERR_INVALID, std::string(who) + ": ctx is null");
+    if (ne0 < 1 || ne0 > (1 << 24) || base_row < 0 || n_rows < 0 || n_tok < 0)
+        return fail(ctx, BK_ERR_INVALID, std::string(who) + ": bad sizes");
+    if (n_rows > 0 && n_tok > 0 && (!payload || !x || !y)) return fail(ctx, BK_ERR_INVALID, std::string(who) + ": null argument");
+    if ((uintptr_t)payload % 2 != 0) return fail(ctx, BK_ERR_INVALID, std::string(who) + ": payload must be 2-byte aligned");
+    const size_t rb = pq2_row_bytes(ne0);
+    // the reference's range check (src/kernels.rs:288-299): the rows asked for must lie inside the payload
+    const unsigned __int128 need = (unsigned __int128)(base_row + n_rows) * rb;
+    if (need > payload_bytes)
+        return fail(ctx, BK_ERR_RANGE, std::string(who) + ": rows " + std::to_string(base_row) + ".." + std::to_string(base_row + n_rows) +
+                                           " need " + std::to_string((unsigned long long)need) + " bytes, payload is " +
+                                           std::to_string(payload_bytes));
+    if (n_rows > (int64_t)INT32_MAX - 16) return fail(ctx, BK_ERR_UNSUPPORTED, std::string(who) + ": too many rows for one call");
+    return BK_OK;
+}
+
+static bk_status pq2_run(bk_ctx *ctx, const uint8_t *payload, int64_t ne0, int64_t base_row, int64_t n_rows, const float *x_dev,
+                         int32_t n_tok, float *y_dev) {
+    const uint8_t *rows = payload + (size_t)base_row * pq2_row_bytes(ne0);
+    for (int t0 = 0; t0 < n_tok; t0 += 4) {  // four tokens share one pass over the weights
+        const int nt = std::min(4, n_tok - t0);
+        bk_status st = launch_pq2_matvec(ctx, rows, (int)ne0, (int)n_rows, x_dev + (size_t)t0 * ne0, nt, y_dev + (size_t)t0 * n_rows, (int)n_rows);
+        if (st != BK_OK) return st;
+    }
+    return BK_OK;
+}
+
+bk_status bk_pq2_matvec(bk_ctx *ctx, const void *payload_dev, size_t payload_bytes, int64_t ne0, int64_t base_row, int64_t n_rows,
+                        const float *x_dev, int32_t n_tok, float *y_dev) {
+    bk_status st = pq2_check(ctx, "bk_pq2_matvec", payload_dev, payload_bytes, ne0, base_row, n_rows, n_tok, x_dev, y_dev);
+    if (st != BK_OK) return st;
+    if (n_rows == 0 || n_tok == 0) return BK_OK;
+    if ((st = bind(ctx)) != BK_OK) return st;
+    return pq2_run(ctx, (const uint8_t *)payload_dev, ne0, base_row, n_rows, x_dev, n_tok, y_dev);
+}
+
+bk_status bk_pq2_matvec_host(bk_ctx *ctx, const void *payload_dev, size_t payload_bytes, int64_t ne0, int64_t base_row,
+                             int64_t n_rows, const float *x_host, int32_t n_tok, float *y_host) {
+    bk_status st = pq2_check(ctx, "bk_pq2_matvec_host", payload_dev, payload_bytes, ne0, base_row, n_rows, n_tok, x_host, y_host);
+    if (st != BK_OK) return st;
+    if (n_rows == 0 || n_tok == 0) return BK_OK;
+    if ((st = bind(ctx)) != BK_OK) return st;
+    const size_t xb = (size_t)n_tok * ne0 * sizeof(float), yb = (size_t)n_tok * n_rows * sizeof(float);
+    const size_t xpad = (xb + 255) / 256 * 256;
+    if ((st = ensure_stage(ctx, xpad + yb)) != BK_OK) return st;
+    char *h = (char *)ctx->h_stage, *d = (char *)ctx->d_stage;
+    memcpy(h, x_host, xb);
+    BK_CUDA(ctx, cudaMemcpyAsync(d, h, xb, cudaMemcpyHostToDevice, ctx->stream));
+    // y is written straight into the pinned staging buffer by the kernel
+    if ((st = pq2_run(ctx, (const uint8_t *)payload_dev, ne0, base_row, n_rows, (const float *)d, n_tok, (float *)(h + xpad))) != BK_OK)
+        return st;
+    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    memcpy(y_host, h + xpad, yb);
+    return BK_OK;
+}
+
 bk_status bk_attn_oneshot_host(bk_ctx *ctx, const float *q_host, const float *k_host, const float *v_host,
                                int32_t n_pos, int32_t nheads, int32_t kvheads, int32_t hd, float *out_host) {
     if (!ctx) return fail(nullptr, BK_ERR_INVALID, "bk_attn_oneshot_host: ctx is null");

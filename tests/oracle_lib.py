@@ -63,6 +63,10 @@ def load_oracle():
         "or_sigmoid": (C.c_float, [C.c_float]),
         "or_attn_layer_step": (i, [vp, sz, _f32p, _f32p, _f32p, _f32p, _f32p, C.c_float, sz, _f32p, i]),
         "or_rand_floats": (None, [C.c_uint64, sz, _f32p]),
+        "or_pq2_row_bytes": (sz, [sz]),
+        "or_pq2_decode_row": (None, [_u8p, sz, _f32p]),
+        "or_pq2_dot_row": (i, [_u8p, sz, sz, sz, _f32p, _f32p]),
+        "or_pq2_matmul": (i, [_u8p, sz, sz, sz, sz, _f32p, sz, _f32p]),
         "or_max_threads": (i, []),
     }
     for name in ("or_cache_k", "or_cache_v", "or_cache_k16", "or_cache_v16", "or_cache_kq",
@@ -210,6 +214,36 @@ class Oracle:
 
     def sigmoid(self, x):
         return float(self.lib.or_sigmoid(x))
+
+    # ---- PQ2_0 ternary rows (src/kernels.rs:204-420) ----
+    def pq2_row_bytes(self, ne0):
+        return int(self.lib.or_pq2_row_bytes(ne0))
+
+    def pq2_decode_row(self, raw, ne0):
+        raw = np.ascontiguousarray(raw, dtype=np.uint8)
+        out = np.zeros(ne0, np.float32)
+        self.lib.or_pq2_decode_row(raw, ne0, out)
+        return out
+
+    def pq2_dot_row(self, payload, ne0, row, x):
+        payload = np.ascontiguousarray(payload, dtype=np.uint8)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        if x.size != ne0:
+            raise ValueError("dot_pq2_0_row: x length")
+        out = np.zeros(1, np.float32)
+        if self.lib.or_pq2_dot_row(payload, payload.size, ne0, row, x, out) != 0:
+            raise ValueError("dot_pq2_0_row: row outside the payload")
+        return float(out[0])
+
+    def pq2_matmul(self, payload, ne0, base_row, n_rows, x, n_tok=1):
+        payload = np.ascontiguousarray(payload, dtype=np.uint8)
+        x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+        if x.size != n_tok * ne0:
+            raise ValueError("pq2_matmul_n: x length")
+        y = np.zeros(n_tok * n_rows, np.float32)
+        if self.lib.or_pq2_matmul(payload, payload.size, ne0, base_row, n_rows, x, n_tok, y) != 0:
+            raise ValueError("pq2_matmul_n: row range exceeds payload")
+        return y.reshape(n_tok, n_rows)
 
     def pq(self, hd, bits):
         return OraclePQ(self.lib, hd, bits)
