@@ -304,10 +304,11 @@ BK_API size_t bk_pq2_row_bytes(int64_t ne0);
  * memory (rows back to back, bk_pq2_row_bytes apart; 16-byte alignment of the
  * first row of the range lets the TMA engine stream it, any even address
  * works); like the reference the call fails (BK_ERR_RANGE) when the rows asked
- * for do not lie inside payload_bytes.  Four tokens share one pass over the
- * weights.  The sum runs on the tensor cores with x as f16 hi + lo, so it
- * differs from the reference's scalar path by rounding order, like the
- * reference's own AVX2 path (src/kernels.rs:652-660). */
+ * for do not lie inside payload_bytes.  Two tokens share one pass over the
+ * weights.  The block sums run on the integer tensor cores with x in 25-bit
+ * fixed point and are exact; the result differs from the reference's scalar
+ * path by the rounding order across blocks, like the reference's own AVX2
+ * path (src/kernels.rs:652-660). */
 BK_API bk_status bk_pq2_matvec(bk_ctx *ctx, const void *payload_dev, size_t payload_bytes, int64_t ne0,
                                int64_t base_row, int64_t n_rows, const float *x_dev, int32_t n_tok,
                                float *y_dev);

@@ -1107,8 +1107,8 @@ static bk_status pq2_check(bk_ctx *ctx, const char *who, const void *payload, si
 static bk_status pq2_run(bk_ctx *ctx, const uint8_t *payload, int64_t ne0, int64_t base_row, int64_t n_rows, const float *x_dev,
                          int32_t n_tok, float *y_dev) {
     const uint8_t *rows = payload + (size_t)base_row * pq2_row_bytes(ne0);
-    for (int t0 = 0; t0 < n_tok; t0 += 4) {  // four tokens share one pass over the weights
-        const int nt = std::min(4, n_tok - t0);
+    for (int t0 = 0; t0 < n_tok; t0 += 2) {  // two tokens share one pass over the weights
+        const int nt = std::min(2, n_tok - t0);
         bk_status st = launch_pq2_matvec(ctx, rows, (int)ne0, (int)n_rows, x_dev + (size_t)t0 * ne0, nt, y_dev + (size_t)t0 * n_rows, (int)n_rows);
         if (st != BK_OK) return st;
     }

@@ -8,23 +8,23 @@
 //   * a CTA owns tiles of 16 consecutive rows; a tile is one contiguous byte range of the
 //     payload, which the TMA engine copies into a ring of shared-memory stages (one bulk copy
 //     per tile, completion on an mbarrier);
-//   * the codes go to the tensor cores as they are.  A 32-bit word holds 16 codes; `w & mask`
-//     with a two-bit mask in each 16-bit half is a pair of f16 SUBNORMALS of value
-//     code * 2^(p-24) (p = the bit position of the code in its half), so one AND makes the A
-//     operand of two weights, with no subtraction, table or conversion; five masks on w and
-//     three on w >> 6 cover the 16 codes of the word.  The activation that multiplies such a
-//     weight is scaled by 2^(15-p) when the CTA stages x (after x is normalised by a power of two
-//     so that nothing overflows), which makes every product code * x * 2^-9 exactly;
-//   * x is split into f16 hi + lo (22 significant bits) and takes two B columns per token, so
-//     m16n8k16 carries up to 4 tokens; the order of the 16 k slots of an MMA is free, and it is
-//     chosen so that a lane's A registers come from its own two words of the block;
-//   * the "- 1" of the code is the block sum of x, computed once per CTA: per block and row
-//     y += scale * (sum x code - sum x), as the reference's scalar path groups it
+//   * the codes go to the integer tensor cores as they are.  A 32-bit word holds 16 codes, four
+//     per byte; `w & 0x03030303 << 2m` is four unsigned bytes of value 4^m * code, the A operand
+//     of mma.m16n8k32.u8.s8 for four weights, with no shift, table or conversion: 16 ANDs and 4
+//     MMAs per lane and block cover two rows x 32 weights;
+//   * x becomes fixed point when the CTA stages it: X = round(x * 2^(24-e)) with 2^e the power of
+//     two above max|x|; the activation that meets a code in byte slot m is B = X * 4^(3-m), so
+//     every product is 64 * code * X, and B is split into four balanced base-256 digits, one B
+//     column each (two tokens per MMA).  The order of the 32 k slots of an MMA is free, and it
+//     is chosen so that a lane's A registers come from its own two words of the block;
+//   * the "- 1" of the code is the per-block digit sum of B, an integer computed once per CTA, so
+//     the block sums sum (code - 1) * X are EXACT integers; they turn into floats only to be
+//     scaled by the block's f16 scale and added up, as the reference's scalar path groups it
 //     (src/kernels.rs:633-650);
 //   * the 8 warps of a CTA split the blocks of a row between them and add up through shared
-//     memory.
-// The result differs from the reference's scalar path by the summation order and the 22-bit x,
-// like its own AVX2 path does (src/kernels.rs:652-660 gives 1e-6 relative for that one).
+//     memory, where the four digit sums are joined.
+// The result differs from the reference's scalar path by the summation order across blocks and
+// the 2^-25 max|x| grid of X, less than its own AVX2 path does (src/kernels.rs:652-660).
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
@@ -39,6 +39,8 @@ namespace {
 constexpr int kPqThreads = 256, kPqWarps = 8, kPqTileRows = 16;
 constexpr int kPqQK = 128, kPqBlockBytes = 34;
 constexpr int kPqMaxStages = 4;
+constexpr int kPqRedBytes = 2 * kPqWarps * 32 * 16;  // two buffers of [warp][lane][4] partial sums
+constexpr int kPqFrac = 24;                          // X = round(x * 2^(kPqFrac - e))
 
 struct Pq2Args {
     const uint8_t *rows;  // first row of the range
@@ -50,31 +52,35 @@ struct Pq2Args {
     int *err_flag;
 };
 
-// k-step -> (code index inside a 16-bit half, bit position).  Steps 0-4 mask the word itself,
-// steps 5-7 the word shifted right by 6.
-__host__ __device__ constexpr int pq_code_of_step(int ks) { return ks < 5 ? 4 - ks : 12 - ks; }
-__host__ __device__ constexpr int pq_pos_of_step(int ks) { return ks < 5 ? 8 - 2 * ks : 18 - 2 * ks; }
-__host__ __device__ constexpr int pq_step_of_code(int i) { return i < 5 ? 4 - i : 12 - i; }
+// D (s32) += A (u8, 16 x 32, row) . B (s8, 32 x 8, col).  No side effects: the compiler may schedule it.
+__device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Shared memory: barriers (at 0) | per-token 2^e | partial sums | digit sums [nb][8] | x digits | stages
+__host__ __device__ inline uint32_t pq_off_dsum() { return 128u + kPqRedBytes; }
+__host__ __device__ inline uint32_t pq_off_x(int nb) { return (pq_off_dsum() + (uint32_t)nb * 32u + 127u) / 128u * 128u; }
+__host__ __device__ inline uint32_t pq_off_stage(int nb, int nt) { return pq_off_x(nb) + (uint32_t)(4 * nt) * nb * 128u; }
 
 template <int NT>
 __global__ void __launch_bounds__(kPqThreads) pq2_matvec_kernel(const Pq2Args a) {
     extern __shared__ __align__(128) uint8_t sm[];
-    constexpr int kCols = 2 * NT;
+    constexpr int kCols = 4 * NT;  // four base-256 digits per token
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int nb = a.nb;
-    // layout: barriers (at 0) | per-token scale | block sums | cross-warp sums | x fragments | stages
     float *inv_s = reinterpret_cast<float *>(sm + 64);
-    float *red = reinterpret_cast<float *>(sm + 128);                      // [8 warps][32 lanes][2]
-    float *bsum = reinterpret_cast<float *>(sm + 128 + kPqWarps * 32 * 8);  // [NT][nb]
-    const uint32_t off_x = (uint32_t)((128 + kPqWarps * 32 * 8 + NT * nb * 4 + 127) / 128 * 128);
-    const uint32_t off_st = off_x + (uint32_t)(kCols * nb * 256);
-    __half *xf = reinterpret_cast<__half *>(sm + off_x);
+    float *red = reinterpret_cast<float *>(sm + 128);  // [2][8 warps][32 lanes][4]
+    int *dsum = reinterpret_cast<int *>(sm + pq_off_dsum());
+    const uint32_t off_x = pq_off_x(nb), off_st = pq_off_stage(nb, NT);
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(sm);
 
     if (tid == 0) {
         for (int s = 0; s < a.stages; s++) mbar_init(sbase + 8u * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
+    for (int i = tid; i < nb * 8; i += kPqThreads) dsum[i] = 0;
     __syncthreads();
 
     const size_t tile_bytes = (size_t)kPqTileRows * a.row_bytes;
@@ -89,11 +95,13 @@ __global__ void __launch_bounds__(kPqThreads) pq2_matvec_kernel(const Pq2Args a)
         for (int s = 0; s < a.stages; s++) issue(blockIdx.x + s * gridDim.x, s);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-    // ---- x: power-of-two normalisation, block sums, f16 hi/lo fragments ---------------------------
+    // ---- x: power-of-two normalisation, fixed point, balanced digits, digit sums -------------------
+    // Element jj of a block (32 t + 16 r + 4 q + m: word 2t + r of the block, byte q, slot m) lands in
+    // byte q of the word [col][block][t][m][r]; a lane's 8 words of a block are 32 contiguous bytes.
     for (int tok = 0; tok < NT; tok++) {
         const float *xr = a.x + (size_t)tok * a.ne0;
-        float am = 0.f;
         const bool real = tok < a.n_tok;  // columns past n_tok are zeros
+        float am = 0.f;
         for (int j = tid; real && j < a.ne0; j += kPqThreads) am = fmaxf(am, fabsf(xr[j]));
         for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
         if (lane == 0) red[warp] = am;
@@ -103,32 +111,51 @@ __global__ void __launch_bounds__(kPqThreads) pq2_matvec_kernel(const Pq2Args a)
             for (int w = 0; w < kPqWarps; w++) m = fmaxf(m, red[w]);
             int e = 0;
             if (m > 0.f && m < CUDART_INF_F) frexpf(m, &e);  // m = f * 2^e, f in [0.5, 1)
-            red[kPqWarps] = ldexpf(1.0f, -e);
-            inv_s[tok] = ldexpf(1.0f, e);
+            red[kPqWarps] = ldexpf(1.0f, kPqFrac - e);
+            inv_s[tok] = ldexpf(1.0f, e - kPqFrac - 6);  // the products carry 4^3
         }
         __syncthreads();
         const float s = red[kPqWarps];
         for (int b = warp; b < nb; b += kPqWarps) {
-            float part = 0.f;
+            int ds[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int jj = lane + 32 * q, j = b * kPqQK + jj;
-                const float xv = (real && j < a.ne0) ? xr[j] * s : 0.f;
-                part += xv;
-                const int tt = jj >> 5, r = (jj >> 4) & 1, e = (jj >> 3) & 1, ks = pq_step_of_code(jj & 7);
-                const float xp = xv * (float)(1 << (15 - pq_pos_of_step(ks)));
-                const __half hi = __float2half_rn(xp);
-                const __half lo = __float2half_rn(xp - __half2float(hi));
-                const int base = ((((b * 4 + tt) * 8 + ks) * 2 + r) * 2 + e);
-                xf[(size_t)(2 * tok) * nb * 128 + base] = hi;
-                xf[(size_t)(2 * tok + 1) * nb * 128 + base] = lo;
+            for (int i = 0; i < 4; i++) {
+                const int jj = lane + 32 * i, j = b * kPqQK + jj;
+                const float xv = (real && j < a.ne0) ? xr[j] * s : 0.f;  // |xv| < 2^24
+                const int tt = jj >> 5, r = (jj >> 4) & 1, q = (jj >> 2) & 3, m = jj & 3;
+                int B = __float2int_rn(xv) << (2 * (3 - m));
+                uint8_t *dst = sm + off_x + ((((size_t)(4 * tok) * nb + b) * 4 + tt) * 8 + m * 2 + r) * 4 + q;
+#pragma unroll
+                for (int d = 0; d < 4; d++) {
+                    const int dg = (int)(int8_t)(B & 0xff);
+                    B = (B - dg) >> 8;
+                    dst[(size_t)d * nb * 128] = (uint8_t)dg;
+                    ds[d] += dg << (2 * m);
+                }
             }
-            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (lane == 0) bsum[tok * nb + b] = part;
+#pragma unroll
+            for (int d = 0; d < 4; d++) {
+                int v = ds[d];
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) dsum[b * 8 + 4 * tok + d] = v;
+            }
         }
         __syncthreads();
     }
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+
+    // per-lane constants of the weight reads: rows g and g + 8, this lane's 8 bytes of a block
+    uint32_t w_off[2], w_sh[2], s_off[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        s_off[h] = (uint32_t)(g + 8 * h) * a.row_bytes + (uint32_t)warp * kPqBlockBytes;
+        const uint32_t oc = s_off[h] + 2u + 8u * t;
+        w_off[h] = oc & ~3u;         // the warp's next block is 8 * 34 = 272 bytes on: the alignment stays
+        w_sh[h] = (oc & 2u) * 8u;
+    }
+    const bool has_x = g < kCols;
+    const uint32_t x_lane = off_x + ((uint32_t)(g * nb + warp) * 4 + t) * 32;
+    const uint32_t d_lane = pq_off_dsum() + (uint32_t)warp * 32 + 8u * t;
 
     uint32_t phase = 0;  // one parity bit per stage
     int it = 0;
@@ -153,54 +180,59 @@ __global__ void __launch_bounds__(kPqThreads) pq2_matvec_kernel(const Pq2Args a)
             __syncthreads();
         }
 
-        float tot0 = 0.f, tot1 = 0.f;
-        for (int b = warp; b < nb; b += kPqWarps) {
-            // this lane's two words of the block, for rows g and g + 8
+        float tot[4] = {0.f, 0.f, 0.f, 0.f};  // rows g (0, 1) and g + 8 (2, 3), digit columns 2t and 2t + 1
+        uint32_t step = 0;
+#pragma unroll 2
+        for (int b = warp; b < nb; b += kPqWarps, step += 1) {
             uint32_t w[2][2];
             float sc[2];
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                const uint32_t o = (uint32_t)(g + 8 * h) * a.row_bytes + (uint32_t)b * kPqBlockBytes;
-                sc[h] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(stage + o)));
-                const uint32_t oc = o + 2u + 8u * t, al = oc & ~3u, sh = (oc & 2u) * 8u;
-                const uint32_t w0 = *reinterpret_cast<const uint32_t *>(stage + al), w1 = *reinterpret_cast<const uint32_t *>(stage + al + 4),
-                               w2 = *reinterpret_cast<const uint32_t *>(stage + al + 8);
-                w[h][0] = __funnelshift_r(w0, w1, sh);
-                w[h][1] = __funnelshift_r(w1, w2, sh);
+                const uint8_t *pw = stage + w_off[h] + step * (kPqWarps * kPqBlockBytes);
+                const uint32_t w0 = *reinterpret_cast<const uint32_t *>(pw), w1 = *reinterpret_cast<const uint32_t *>(pw + 4),
+                               w2 = *reinterpret_cast<const uint32_t *>(pw + 8);
+                w[h][0] = __funnelshift_r(w0, w1, w_sh[h]);
+                w[h][1] = __funnelshift_r(w1, w2, w_sh[h]);
+                sc[h] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(stage + s_off[h] + step * (kPqWarps * kPqBlockBytes))));
             }
-            uint4 bx[4] = {};
-            if (g < kCols) {
-                const uint4 *p = reinterpret_cast<const uint4 *>(sm + off_x + ((size_t)(g * nb + b) * 4 + t) * 64);
-                bx[0] = p[0]; bx[1] = p[1]; bx[2] = p[2]; bx[3] = p[3];
+            uint4 bx0 = make_uint4(0, 0, 0, 0), bx1 = bx0;
+            if (has_x) {
+                const uint4 *px = reinterpret_cast<const uint4 *>(sm + x_lane + step * (kPqWarps * 128));
+                bx0 = px[0];
+                bx1 = px[1];
             }
-            const uint32_t *bw = reinterpret_cast<const uint32_t *>(bx);
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) {
-                const int p = pq_pos_of_step(ks);
-                const uint32_t m = (3u << p) | (3u << (p + 16));
-                const int shv = ks < 5 ? 0 : 6;
-                mma16816(c, (w[0][0] >> shv) & m, (w[1][0] >> shv) & m, (w[0][1] >> shv) & m, (w[1][1] >> shv) & m, bw[2 * ks], bw[2 * ks + 1]);
-            }
-            const float sx = t < NT ? bsum[t * nb + b] : 0.f;
-            tot0 = fmaf(sc[0], fmaf(512.f, c[0] + c[1], -sx), tot0);
-            tot1 = fmaf(sc[1], fmaf(512.f, c[2] + c[3], -sx), tot1);
+            const int2 dsv = *reinterpret_cast<const int2 *>(sm + d_lane + step * (kPqWarps * 32));
+            int c[4] = {0, 0, 0, 0};
+            imma_u8s8(c, w[0][0] & 0x03030303u, w[1][0] & 0x03030303u, w[0][1] & 0x03030303u, w[1][1] & 0x03030303u, bx0.x, bx0.y);
+            imma_u8s8(c, w[0][0] & 0x0c0c0c0cu, w[1][0] & 0x0c0c0c0cu, w[0][1] & 0x0c0c0c0cu, w[1][1] & 0x0c0c0c0cu, bx0.z, bx0.w);
+            imma_u8s8(c, w[0][0] & 0x30303030u, w[1][0] & 0x30303030u, w[0][1] & 0x30303030u, w[1][1] & 0x30303030u, bx1.x, bx1.y);
+            imma_u8s8(c, w[0][0] & 0xc0c0c0c0u, w[1][0] & 0xc0c0c0c0u, w[0][1] & 0xc0c0c0c0u, w[1][1] & 0xc0c0c0c0u, bx1.z, bx1.w);
+            tot[0] = fmaf(sc[0], (float)(c[0] - dsv.x), tot[0]);
+            tot[1] = fmaf(sc[0], (float)(c[1] - dsv.y), tot[1]);
+            tot[2] = fmaf(sc[1], (float)(c[2] - dsv.x), tot[2]);
+            tot[3] = fmaf(sc[1], (float)(c[3] - dsv.y), tot[3]);
         }
-        red[(warp * 32 + lane) * 2] = tot0;
-        red[(warp * 32 + lane) * 2 + 1] = tot1;
-        __syncthreads();
-        if (tid < kPqTileRows * NT) {
-            const int r = tid & 15, tok = tid >> 4;
-            const int ln = (r & 7) * 4 + tok, h = r >> 3;
-            float sum = 0.f;
-#pragma unroll
-            for (int wp = 0; wp < kPqWarps; wp++) sum += red[(wp * 32 + ln) * 2 + h];
-            if (r < rows_here && tok < a.n_tok) a.y[(size_t)tok * a.y_stride + (size_t)tile * kPqTileRows + r] = sum * inv_s[tok];
-        }
-        __syncthreads();  // the stage and the sums may be overwritten
+        float *rd = red + (it & 1) * (kPqWarps * 128);  // two buffers: one barrier per tile
+        *reinterpret_cast<float4 *>(rd + (warp * 32 + lane) * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
+        __syncthreads();  // the tile's partial sums are in place, and nobody reads the stage any more
         if (tid == 0) {
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             issue(tile + a.stages * (int)gridDim.x, st);
+        }
+        if (tid < kPqTileRows * NT) {
+            // row r of token tok: digit d sits with lane (r % 8, 2 tok + d / 2), register 2 (r / 8) + d % 2
+            const int r = tid & 15, tok = tid >> 4;
+            float dsumf[4];
+#pragma unroll
+            for (int d = 0; d < 4; d++) {
+                const int ln = (r & 7) * 4 + 2 * tok + (d >> 1), reg = 2 * (r >> 3) + (d & 1);
+                float sum = 0.f;
+#pragma unroll
+                for (int wp = 0; wp < kPqWarps; wp++) sum += rd[(wp * 32 + ln) * 4 + reg];
+                dsumf[d] = sum;
+            }
+            const float v = ((dsumf[3] * 256.f + dsumf[2]) * 256.f + dsumf[1]) * 256.f + dsumf[0];
+            if (r < rows_here && tok < a.n_tok) a.y[(size_t)tok * a.y_stride + (size_t)tile * kPqTileRows + r] = v * inv_s[tok];
         }
     }
 }
@@ -228,7 +260,7 @@ bk_status launch_nt(bk_ctx *ctx, const Pq2Args &a, int grid, size_t smem) {
 
 size_t pq2_row_bytes(int64_t ne0) { return (size_t)((ne0 + kPqQK - 1) / kPqQK) * kPqBlockBytes; }
 
-// rows: device pointer to row 0 of the range; x [n_tok][ne0]; y [n_tok][y_stride], n_tok 1..4.
+// rows: device pointer to row 0 of the range; x [n_tok][ne0]; y [n_tok][y_stride], n_tok 1..2.
 bk_status launch_pq2_matvec(bk_ctx *ctx, const uint8_t *rows, int ne0, int n_rows, const float *x, int n_tok, float *y, int y_stride) {
     if (n_rows <= 0 || n_tok <= 0) return BK_OK;
     Pq2Args a{};
@@ -246,8 +278,8 @@ bk_status launch_pq2_matvec(bk_ctx *ctx, const uint8_t *rows, int ne0, int n_row
     const size_t tile_bytes = (size_t)kPqTileRows * a.row_bytes;
     a.stage_stride = (int)((tile_bytes + 16 + 127) / 128 * 128);
     a.bulk = ((uintptr_t)rows % 16 == 0) ? 1 : 0;  // 16 rows are a multiple of 16 bytes whatever ne0
-    const int nt = n_tok <= 1 ? 1 : (n_tok == 2 ? 2 : 4);
-    const size_t fixed = (size_t)((128 + kPqWarps * 32 * 8 + nt * a.nb * 4 + 127) / 128 * 128) + (size_t)2 * nt * a.nb * 256;
+    const int nt = n_tok <= 1 ? 1 : 2;
+    const size_t fixed = pq_off_stage(a.nb, nt);
     const size_t limit = 227 * 1024;
     if (fixed + 2 * (size_t)a.stage_stride > limit)
         return fail(ctx, BK_ERR_UNSUPPORTED, "pq2_matvec: rows too long for two shared-memory stages of 16 rows");
@@ -261,8 +293,7 @@ bk_status launch_pq2_matvec(bk_ctx *ctx, const uint8_t *rows, int ne0, int n_row
     const size_t smem = fixed + (size_t)a.stages * a.stage_stride;
     const int grid = std::min(a.n_tiles, ctx->n_sms * ctas);
     if (nt == 1) return launch_nt<1>(ctx, a, grid, smem);
-    if (nt == 2) return launch_nt<2>(ctx, a, grid, smem);
-    return launch_nt<4>(ctx, a, grid, smem);
+    return launch_nt<2>(ctx, a, grid, smem);
 }
 
 }  // namespace bk
