@@ -36,10 +36,10 @@ namespace bk {
 
 namespace {
 
-constexpr int kPqThreads = 256, kPqWarps = 8, kPqTileRows = 16;
+constexpr int kPqGroupThreads = 256, kPqWarps = 8, kPqTileRows = 16;  // a group: 8 warps on one tile
+constexpr int kPqMaxGroups = 4, kPqGroupStages = 2;
 constexpr int kPqQK = 128, kPqBlockBytes = 34;
-constexpr int kPqMaxStages = 4;
-constexpr int kPqRedBytes = 2 * kPqWarps * 32 * 16;  // two buffers of [warp][lane][4] partial sums
+constexpr int kPqRedBytes = kPqMaxGroups * 2 * kPqWarps * kPqTileRows * 2 * 4;  // per group two buffers of [warp][row][token]
 constexpr int kPqFrac = 24;                          // X = round(x * 2^(kPqFrac - e))
 
 struct Pq2Args {
@@ -47,7 +47,9 @@ struct Pq2Args {
     const float *x;       // [n_tok][ne0]
     float *y;             // [n_tok][y_stride]
     int ne0, nb, row_bytes, n_rows, n_tiles, y_stride, n_tok;
-    int stages, stage_stride;  // stage_stride: bytes between stages (tile bytes + slack, 128-byte multiple)
+    int stage_stride;  // bytes between stages (tile bytes + slack, 128-byte multiple)
+    int groups;        // groups of 8 warps that stream tiles (the CTA always has kPqMaxGroups of them to stage x)
+    int stages;        // stages per group: kPqGroupStages, or 1 for rows so long that two do not fit
     int bulk;                  // 1: tiles start on 16-byte boundaries, the TMA engine may copy them
     int *err_flag;
 };
@@ -59,40 +61,46 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Shared memory: barriers (at 0) | per-token 2^e | partial sums | digit sums [nb][8] | x digits | stages
-__host__ __device__ inline uint32_t pq_off_dsum() { return 128u + kPqRedBytes; }
+// Shared memory: barriers (at 0) | per-token 2^e (at 128) | partial sums (at 256) | digit sums [nb][8] | x digits | stages
+__host__ __device__ inline uint32_t pq_off_dsum() { return 256u + kPqRedBytes; }
 __host__ __device__ inline uint32_t pq_off_x(int nb) { return (pq_off_dsum() + (uint32_t)nb * 32u + 127u) / 128u * 128u; }
 __host__ __device__ inline uint32_t pq_off_stage(int nb, int nt) { return pq_off_x(nb) + (uint32_t)(4 * nt) * nb * 128u; }
 
 template <int NT>
-__global__ void __launch_bounds__(kPqThreads) pq2_matvec_kernel(const Pq2Args a) {
+__global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_kernel(const Pq2Args a) {
     extern __shared__ __align__(128) uint8_t sm[];
     constexpr int kCols = 4 * NT;  // four base-256 digits per token
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    // all threads stage x; then every group of 8 warps streams its own tiles through its own stages
+    const int tid_all = threadIdx.x, warp_all = tid_all >> 5, n_threads = blockDim.x, n_warps = n_threads >> 5, n_groups = a.groups;
+    const int grp = warp_all / kPqWarps, warp = warp_all % kPqWarps, tid = tid_all % kPqGroupThreads;
+    const int lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int nb = a.nb;
-    float *inv_s = reinterpret_cast<float *>(sm + 64);
-    float *red = reinterpret_cast<float *>(sm + 128);  // [2][8 warps][32 lanes][4]
+    float *inv_s = reinterpret_cast<float *>(sm + 128);
+    float *red = reinterpret_cast<float *>(sm + 256);
     int *dsum = reinterpret_cast<int *>(sm + pq_off_dsum());
     const uint32_t off_x = pq_off_x(nb), off_st = pq_off_stage(nb, NT);
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(sm);
 
-    if (tid == 0) {
-        for (int s = 0; s < a.stages; s++) mbar_init(sbase + 8u * s, 1);
+    if (tid_all == 0) {
+        for (int s = 0; s < kPqMaxGroups * kPqGroupStages; s++) mbar_init(sbase + 8u * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    for (int i = tid; i < nb * 8; i += kPqThreads) dsum[i] = 0;
+    for (int i = tid_all; i < nb * 8; i += n_threads) dsum[i] = 0;
     __syncthreads();
 
     const size_t tile_bytes = (size_t)kPqTileRows * a.row_bytes;
-    auto issue = [&](int tile, int st) {  // one thread
+    // the it-th tile of this group; consecutive groups and CTAs take consecutive tiles
+    auto tile_of = [&](int it) { return (it * (int)gridDim.x + (int)blockIdx.x) * n_groups + grp; };
+    auto issue = [&](int it) {  // one thread of the group
+        const int tile = tile_of(it), st = grp * a.stages + it % a.stages;
         if (!a.bulk || tile >= a.n_tiles || (tile + 1) * kPqTileRows > a.n_rows) return;
         const uint32_t bar = sbase + 8u * st;
         mbar_expect_tx(bar, (uint32_t)tile_bytes);
         tma_bulk(sbase + off_st + (uint32_t)st * a.stage_stride, a.rows + (size_t)tile * tile_bytes, (uint32_t)tile_bytes, bar);
     };
     // The weights do not depend on the kernel before this one: the first copies start at once.
-    if (tid == 0)
-        for (int s = 0; s < a.stages; s++) issue(blockIdx.x + s * gridDim.x, s);
+    if (tid == 0 && grp < n_groups)
+        for (int s = 0; s < a.stages; s++) issue(s);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     // ---- x: power-of-two normalisation, fixed point, balanced digits, digit sums -------------------
@@ -102,21 +110,21 @@ __global__ void __launch_bounds__(kPqThreads) pq2_matvec_kernel(const Pq2Args a)
         const float *xr = a.x + (size_t)tok * a.ne0;
         const bool real = tok < a.n_tok;  // columns past n_tok are zeros
         float am = 0.f;
-        for (int j = tid; real && j < a.ne0; j += kPqThreads) am = fmaxf(am, fabsf(xr[j]));
+        for (int j = tid_all; real && j < a.ne0; j += n_threads) am = fmaxf(am, fabsf(xr[j]));
         for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        if (lane == 0) red[warp] = am;
+        if (lane == 0) red[warp_all] = am;
         __syncthreads();
-        if (tid == 0) {
+        if (tid_all == 0) {
             float m = 0.f;
-            for (int w = 0; w < kPqWarps; w++) m = fmaxf(m, red[w]);
+            for (int w = 0; w < n_warps; w++) m = fmaxf(m, red[w]);
             int e = 0;
             if (m > 0.f && m < CUDART_INF_F) frexpf(m, &e);  // m = f * 2^e, f in [0.5, 1)
-            red[kPqWarps] = ldexpf(1.0f, kPqFrac - e);
+            red[32] = ldexpf(1.0f, kPqFrac - e);
             inv_s[tok] = ldexpf(1.0f, e - kPqFrac - 6);  // the products carry 4^3
         }
         __syncthreads();
-        const float s = red[kPqWarps];
-        for (int b = warp; b < nb; b += kPqWarps) {
+        const float s = red[32];
+        for (int b = warp_all; b < nb; b += n_warps) {
             int ds[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -157,27 +165,31 @@ __global__ void __launch_bounds__(kPqThreads) pq2_matvec_kernel(const Pq2Args a)
     const uint32_t x_lane = off_x + ((uint32_t)(g * nb + warp) * 4 + t) * 32;
     const uint32_t d_lane = pq_off_dsum() + (uint32_t)warp * 32 + 8u * t;
 
-    uint32_t phase = 0;  // one parity bit per stage
-    int it = 0;
-    for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x, it++) {
-        const int st = it % a.stages;
+    if (grp >= n_groups) return;  // helped to stage x; no tiles for this group
+    auto group_sync = [&]() { asm volatile("bar.sync %0, %1;\n" ::"r"(1 + grp), "r"(kPqGroupThreads) : "memory"); };
+    float *red_g = red + grp * (2 * kPqWarps * kPqTileRows * 2);
+    uint32_t phase = 0;  // one parity bit per stage of the group
+    for (int it = 0;; it++) {
+        const int tile = tile_of(it);
+        if (tile >= a.n_tiles) break;
+        const int sl = it % a.stages, st = grp * a.stages + sl;
         const uint8_t *stage = sm + off_st + (size_t)st * a.stage_stride;
         const int rows_here = min(kPqTileRows, a.n_rows - tile * kPqTileRows);
         if (a.bulk && rows_here == kPqTileRows) {
             int polls = 0;
-            while (!mbar_try_wait(sbase + 8u * st, (phase >> st) & 1u)) {
+            while (!mbar_try_wait(sbase + 8u * st, (phase >> sl) & 1u)) {
                 if (++polls > kWaitPolls) {  // never expected: leave a mark rather than hang
                     if (lane == 0) atomicExch(a.err_flag, 5);
                     break;
                 }
             }
-            phase ^= 1u << st;
+            phase ^= 1u << sl;
         } else {  // a ragged last tile or an unaligned payload: ordinary 2-byte loads
             const uint16_t *src = reinterpret_cast<const uint16_t *>(a.rows + (size_t)tile * tile_bytes);
             uint16_t *dst = reinterpret_cast<uint16_t *>(sm + off_st + (size_t)st * a.stage_stride);
             const int n2 = rows_here * a.row_bytes / 2;
-            for (int i = tid; i < n2; i += kPqThreads) dst[i] = __ldg(src + i);
-            __syncthreads();
+            for (int i = tid; i < n2; i += kPqGroupThreads) dst[i] = __ldg(src + i);
+            group_sync();
         }
 
         float tot[4] = {0.f, 0.f, 0.f, 0.f};  // rows g (0, 1) and g + 8 (2, 3), digit columns 2t and 2t + 1
@@ -202,37 +214,36 @@ __global__ void __launch_bounds__(kPqThreads) pq2_matvec_kernel(const Pq2Args a)
                 bx1 = px[1];
             }
             const int2 dsv = *reinterpret_cast<const int2 *>(sm + d_lane + step * (kPqWarps * 32));
-            int c[4] = {0, 0, 0, 0};
+            int c[4] = {-dsv.x, -dsv.y, -dsv.x, -dsv.y}, c2[4] = {0, 0, 0, 0};  // two chains; the "- 1" goes in as the start value
             imma_u8s8(c, w[0][0] & 0x03030303u, w[1][0] & 0x03030303u, w[0][1] & 0x03030303u, w[1][1] & 0x03030303u, bx0.x, bx0.y);
-            imma_u8s8(c, w[0][0] & 0x0c0c0c0cu, w[1][0] & 0x0c0c0c0cu, w[0][1] & 0x0c0c0c0cu, w[1][1] & 0x0c0c0c0cu, bx0.z, bx0.w);
+            imma_u8s8(c2, w[0][0] & 0x0c0c0c0cu, w[1][0] & 0x0c0c0c0cu, w[0][1] & 0x0c0c0c0cu, w[1][1] & 0x0c0c0c0cu, bx0.z, bx0.w);
             imma_u8s8(c, w[0][0] & 0x30303030u, w[1][0] & 0x30303030u, w[0][1] & 0x30303030u, w[1][1] & 0x30303030u, bx1.x, bx1.y);
-            imma_u8s8(c, w[0][0] & 0xc0c0c0c0u, w[1][0] & 0xc0c0c0c0u, w[0][1] & 0xc0c0c0c0u, w[1][1] & 0xc0c0c0c0u, bx1.z, bx1.w);
-            tot[0] = fmaf(sc[0], (float)(c[0] - dsv.x), tot[0]);
-            tot[1] = fmaf(sc[0], (float)(c[1] - dsv.y), tot[1]);
-            tot[2] = fmaf(sc[1], (float)(c[2] - dsv.x), tot[2]);
-            tot[3] = fmaf(sc[1], (float)(c[3] - dsv.y), tot[3]);
+            imma_u8s8(c2, w[0][0] & 0xc0c0c0c0u, w[1][0] & 0xc0c0c0c0u, w[0][1] & 0xc0c0c0c0u, w[1][1] & 0xc0c0c0c0u, bx1.z, bx1.w);
+            tot[0] = fmaf(sc[0], (float)(c[0] + c2[0]), tot[0]);
+            tot[1] = fmaf(sc[0], (float)(c[1] + c2[1]), tot[1]);
+            tot[2] = fmaf(sc[1], (float)(c[2] + c2[2]), tot[2]);
+            tot[3] = fmaf(sc[1], (float)(c[3] + c2[3]), tot[3]);
         }
-        float *rd = red + (it & 1) * (kPqWarps * 128);  // two buffers: one barrier per tile
-        *reinterpret_cast<float4 *>(rd + (warp * 32 + lane) * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
-        __syncthreads();  // the tile's partial sums are in place, and nobody reads the stage any more
+        // join the four digits: this lane's two columns, then the lane pair (t even: digits 0 1, t odd: 2 3)
+        float v0 = fmaf(tot[1], 256.f, tot[0]), v1 = fmaf(tot[3], 256.f, tot[2]);
+        v0 = fmaf(__shfl_xor_sync(0xffffffffu, v0, 1), 65536.f, v0);  // meaningful on even t only
+        v1 = fmaf(__shfl_xor_sync(0xffffffffu, v1, 1), 65536.f, v1);
+        float *rd = red_g + (it & 1) * (kPqWarps * kPqTileRows * 2);  // [warp][row][token]; two buffers: one barrier per tile
+        if ((t & 1) == 0 && (t >> 1) < NT) {
+            rd[(warp * kPqTileRows + g) * 2 + (t >> 1)] = v0;
+            rd[(warp * kPqTileRows + g + 8) * 2 + (t >> 1)] = v1;
+        }
+        group_sync();  // the tile's partial sums are in place, and nobody of the group reads the stage any more
         if (tid == 0) {
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            issue(tile + a.stages * (int)gridDim.x, st);
+            issue(it + a.stages);
         }
         if (tid < kPqTileRows * NT) {
-            // row r of token tok: digit d sits with lane (r % 8, 2 tok + d / 2), register 2 (r / 8) + d % 2
             const int r = tid & 15, tok = tid >> 4;
-            float dsumf[4];
+            float sum = 0.f;
 #pragma unroll
-            for (int d = 0; d < 4; d++) {
-                const int ln = (r & 7) * 4 + 2 * tok + (d >> 1), reg = 2 * (r >> 3) + (d & 1);
-                float sum = 0.f;
-#pragma unroll
-                for (int wp = 0; wp < kPqWarps; wp++) sum += rd[(wp * 32 + ln) * 4 + reg];
-                dsumf[d] = sum;
-            }
-            const float v = ((dsumf[3] * 256.f + dsumf[2]) * 256.f + dsumf[1]) * 256.f + dsumf[0];
-            if (r < rows_here && tok < a.n_tok) a.y[(size_t)tok * a.y_stride + (size_t)tile * kPqTileRows + r] = v * inv_s[tok];
+            for (int wp = 0; wp < kPqWarps; wp++) sum += rd[(wp * kPqTileRows + r) * 2 + tok];
+            if (r < rows_here && tok < a.n_tok) a.y[(size_t)tok * a.y_stride + (size_t)tile * kPqTileRows + r] = sum * inv_s[tok];
         }
     }
 }
@@ -242,7 +253,7 @@ bk_status launch_nt(bk_ctx *ctx, const Pq2Args &a, int grid, size_t smem) {
     BK_CUDA(ctx, cudaFuncSetAttribute(pq2_matvec_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kPqThreads);
+    cfg.blockDim = dim3((unsigned)(kPqGroupThreads * kPqMaxGroups));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -281,17 +292,17 @@ bk_status launch_pq2_matvec(bk_ctx *ctx, const uint8_t *rows, int ne0, int n_row
     const int nt = n_tok <= 1 ? 1 : 2;
     const size_t fixed = pq_off_stage(a.nb, nt);
     const size_t limit = 227 * 1024;
-    if (fixed + 2 * (size_t)a.stage_stride > limit)
-        return fail(ctx, BK_ERR_UNSUPPORTED, "pq2_matvec: rows too long for two shared-memory stages of 16 rows");
-    // two CTAs per SM when four stages of each fit, else one CTA with as many stages as fit
-    int ctas = 2;
-    a.stages = kPqMaxStages;
-    if (2 * (fixed + (size_t)kPqMaxStages * a.stage_stride + 1024) > limit + 1024) {
-        ctas = 1;
-        a.stages = (int)std::min<size_t>(kPqMaxStages, (limit - fixed) / a.stage_stride);
-    }
-    const size_t smem = fixed + (size_t)a.stages * a.stage_stride;
-    const int grid = std::min(a.n_tiles, ctx->n_sms * ctas);
+    a.stages = fixed + (size_t)kPqGroupStages * a.stage_stride <= limit ? kPqGroupStages : 1;
+    const size_t per_group = (size_t)a.stages * a.stage_stride;
+    if (fixed + per_group > limit)
+        return fail(ctx, BK_ERR_UNSUPPORTED, "pq2_matvec: rows too long for a shared-memory stage of 16 rows");
+    // One CTA per SM; it runs as many groups of 8 warps (each with its own tiles and stages) as the
+    // matrix has tiles for and shared memory has room for.
+    int groups = (int)std::min<size_t>(kPqMaxGroups, (limit - fixed) / per_group);
+    groups = std::max(1, std::min(groups, (a.n_tiles + ctx->n_sms - 1) / ctx->n_sms));
+    a.groups = groups;
+    const size_t smem = fixed + (size_t)groups * per_group;
+    const int grid = std::min((a.n_tiles + groups - 1) / groups, ctx->n_sms);
     if (nt == 1) return launch_nt<1>(ctx, a, grid, smem);
     return launch_nt<2>(ctx, a, grid, smem);
 }
