@@ -312,6 +312,18 @@ BK_API size_t bk_pq2_row_bytes(int64_t ne0);
 BK_API bk_status bk_pq2_matvec(bk_ctx *ctx, const void *payload_dev, size_t payload_bytes, int64_t ne0,
                                int64_t base_row, int64_t n_rows, const float *x_dev, int32_t n_tok,
                                float *y_dev);
+/* Up to four row ranges of tensors with the same ne0 against the same x in ONE
+ * launch (attn_q, attn_k and attn_v of a layer: src/forward.rs:219-236 makes
+ * three matvec calls on one input); range s writes y_dev [n_tok][n_rows].  No
+ * reference counterpart as a call; results equal the separate calls bit for bit. */
+typedef struct bk_pq2_seg {
+    const void *payload_dev;
+    size_t payload_bytes;
+    int64_t base_row, n_rows;
+    float *y_dev;
+} bk_pq2_seg;
+BK_API bk_status bk_pq2_matvec_multi(bk_ctx *ctx, int32_t n_seg, const bk_pq2_seg *segs, int64_t ne0,
+                                     const float *x_dev, int32_t n_tok);
 /* The same with host x and y (weights stay resident in device memory). */
 BK_API bk_status bk_pq2_matvec_host(bk_ctx *ctx, const void *payload_dev, size_t payload_bytes,
                                     int64_t ne0, int64_t base_row, int64_t n_rows, const float *x_host,

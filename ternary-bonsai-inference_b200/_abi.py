@@ -77,6 +77,7 @@ SIGNATURES = {
     "bk_rms_norm_rows": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _f, _vp]),
     "bk_pq2_row_bytes": (_sz, [_i64]),
     "bk_pq2_matvec": (C.c_int, [_vp, _vp, _sz, _i64, _i64, _i64, _vp, _i32, _vp]),
+    "bk_pq2_matvec_multi": (C.c_int, [_vp, _i32, _vp, _i64, _vp, _i32]),
     "bk_pq2_matvec_host": (C.c_int, [_vp, _vp, _sz, _i64, _i64, _i64, _vp, _i32, _vp]),
     "bk_attn_oneshot_host": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "bk_kvq_packed_len": (_sz, [_i32, _i32]),

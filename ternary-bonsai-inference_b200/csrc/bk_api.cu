@@ -1104,15 +1104,42 @@ static bk_status pq2_check(bk_ctx *ctx, const char *who, const void *payload, si
     return BK_OK;
 }
 
-static bk_status pq2_run(bk_ctx *ctx, const uint8_t *payload, int64_t ne0, int64_t base_row, int64_t n_rows, const float *x_dev,
-                         int32_t n_tok, float *y_dev) {
-    const uint8_t *rows = payload + (size_t)base_row * pq2_row_bytes(ne0);
-    for (int t0 = 0; t0 < n_tok; t0 += 2) {  // two tokens share one pass over the weights
-        const int nt = std::min(2, n_tok - t0);
-        bk_status st = launch_pq2_matvec(ctx, rows, (int)ne0, (int)n_rows, x_dev + (size_t)t0 * ne0, nt, y_dev + (size_t)t0 * n_rows, (int)n_rows);
+// y of range s: [n_tok][n_rows_s]; two tokens share one pass over the weights
+static bk_status pq2_run_multi(bk_ctx *ctx, int n_seg, const bk_pq2_seg *segs, int64_t ne0, const float *x_dev, int32_t n_tok) {
+    const size_t rb = pq2_row_bytes(ne0);
+    for (int t0 = 0; t0 < n_tok; t0 += 2) {
+        const uint8_t *rows[4];
+        float *y[4];
+        int n_rows[4];
+        for (int i = 0; i < n_seg; i++) {
+            rows[i] = (const uint8_t *)segs[i].payload_dev + (size_t)segs[i].base_row * rb;
+            n_rows[i] = (int)segs[i].n_rows;
+            y[i] = segs[i].y_dev + (size_t)t0 * segs[i].n_rows;
+        }
+        bk_status st = launch_pq2_matvec(ctx, n_seg, rows, n_rows, y, (int)ne0, x_dev + (size_t)t0 * ne0, std::min(2, n_tok - t0));
         if (st != BK_OK) return st;
     }
     return BK_OK;
+}
+
+static bk_status pq2_run(bk_ctx *ctx, const uint8_t *payload, int64_t ne0, int64_t base_row, int64_t n_rows, const float *x_dev,
+                         int32_t n_tok, float *y_dev) {
+    const bk_pq2_seg seg{payload, 0, base_row, n_rows, y_dev};
+    return pq2_run_multi(ctx, 1, &seg, ne0, x_dev, n_tok);
+}
+
+bk_status bk_pq2_matvec_multi(bk_ctx *ctx, int32_t n_seg, const bk_pq2_seg *segs, int64_t ne0, const float *x_dev, int32_t n_tok) {
+    if (!ctx) return fail(nullptr, BK_ERR_INVALID, "bk_pq2_matvec_multi: ctx is null");
+    if (n_seg < 0 || n_seg > 4 || (n_seg > 0 && !segs)) return fail(ctx, BK_ERR_INVALID, "bk_pq2_matvec_multi: 0..4 row ranges");
+    for (int i = 0; i < n_seg; i++) {
+        bk_status st = pq2_check(ctx, "bk_pq2_matvec_multi", segs[i].payload_dev, segs[i].payload_bytes, ne0, segs[i].base_row,
+                                 segs[i].n_rows, n_tok, x_dev, segs[i].y_dev);
+        if (st != BK_OK) return st;
+    }
+    if (n_seg == 0 || n_tok == 0) return BK_OK;
+    bk_status st = bind(ctx);
+    if (st != BK_OK) return st;
+    return pq2_run_multi(ctx, n_seg, segs, ne0, x_dev, n_tok);
 }
 
 bk_status bk_pq2_matvec(bk_ctx *ctx, const void *payload_dev, size_t payload_bytes, int64_t ne0, int64_t base_row, int64_t n_rows,

@@ -237,9 +237,10 @@ struct NormSeg {
 };
 bk_status launch_rms_norm_rows(bk_ctx *ctx, const NormSeg &s0, const NormSeg &s1, int row_len, float eps);
 
-// PQ2_0 ternary rows (bk_pq2.cu): bytes per row, and y[t][r] = x[t] . row r for up to 4 tokens a launch.
+// PQ2_0 ternary rows (bk_pq2.cu): bytes per row, and y[t][r] = x[t] . row r for up to 2 tokens and 4 row ranges a launch.
 size_t pq2_row_bytes(int64_t ne0);
-bk_status launch_pq2_matvec(bk_ctx *ctx, const uint8_t *rows, int ne0, int n_rows, const float *x, int n_tok, float *y, int y_stride);
+bk_status launch_pq2_matvec(bk_ctx *ctx, int n_seg, const uint8_t *const *rows, const int *n_rows, float *const *y, int ne0,
+                            const float *x, int n_tok);
 // Batched causal attention of a block of prompt tokens over a 4- or 3-bit planar cache (bk_prefill.cu).
 bool prefill_mma_supported(const DecodeArgs &a);
 bk_status launch_prefill_mma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha);

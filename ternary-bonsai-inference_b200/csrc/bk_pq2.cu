@@ -12,8 +12,8 @@
 //     per byte; `w & 0x03030303 << 2m` is four unsigned bytes of value 4^m * code, the A operand
 //     of mma.m16n8k32.u8.s8 for four weights, with no shift, table or conversion: 16 ANDs and 4
 //     MMAs per lane and block cover two rows x 32 weights;
-//   * x becomes fixed point when the CTA stages it: X = round(x * 2^(24-e)) with 2^e the power of
-//     two above max|x|; the activation that meets a code in byte slot m is B = X * 4^(3-m), so
+//   * x becomes fixed point when the CTA stages it: per block of 128, X = round(x * 2^(24-e)) with
+//     2^e the power of two above the block's max|x| (2^e then rides on the block's f16 scale); the activation that meets a code in byte slot m is B = X * 4^(3-m), so
 //     every product is 64 * code * X, and B is split into four balanced base-256 digits, one B
 //     column each (two tokens per MMA).  The order of the 32 k slots of an MMA is free, and it
 //     is chosen so that a lane's A registers come from its own two words of the block;
@@ -24,7 +24,7 @@
 //   * the 8 warps of a CTA split the blocks of a row between them and add up through shared
 //     memory, where the four digit sums are joined.
 // The result differs from the reference's scalar path by the summation order across blocks and
-// the 2^-25 max|x| grid of X, less than its own AVX2 path does (src/kernels.rs:652-660).
+// the 2^-25 (block max|x|) grid of X, less than its own AVX2 path does (src/kernels.rs:652-660).
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
@@ -37,20 +37,23 @@ namespace bk {
 namespace {
 
 constexpr int kPqGroupThreads = 256, kPqWarps = 8, kPqTileRows = 16;  // a group: 8 warps on one tile
-constexpr int kPqMaxGroups = 4, kPqGroupStages = 2;
+constexpr int kPqMaxGroups = 4, kPqGroupStages = 2, kPqMaxSegs = 4;
 constexpr int kPqQK = 128, kPqBlockBytes = 34;
 constexpr int kPqRedBytes = kPqMaxGroups * 2 * kPqWarps * kPqTileRows * 2 * 4;  // per group two buffers of [warp][row][token]
 constexpr int kPqFrac = 24;                          // X = round(x * 2^(kPqFrac - e))
 
 struct Pq2Args {
-    const uint8_t *rows;  // first row of the range
-    const float *x;       // [n_tok][ne0]
-    float *y;             // [n_tok][y_stride]
-    int ne0, nb, row_bytes, n_rows, n_tiles, y_stride, n_tok;
+    // up to kPqMaxSegs row ranges (of tensors with the same ne0) share x and one launch
+    const uint8_t *rows[kPqMaxSegs];  // first row of each range
+    float *y[kPqMaxSegs];             // [n_tok][seg_rows]
+    int seg_rows[kPqMaxSegs];
+    int seg_tile0[kPqMaxSegs + 1];    // first tile of each range in the launch's tile order
+    const float *x;                   // [n_tok][ne0]
+    int ne0, nb, row_bytes, n_tiles, n_tok;
     int stage_stride;  // bytes between stages (tile bytes + slack, 128-byte multiple)
     int groups;        // groups of 8 warps that stream tiles (the CTA always has kPqMaxGroups of them to stage x)
     int stages;        // stages per group: kPqGroupStages, or 1 for rows so long that two do not fit
-    int bulk;                  // 1: tiles start on 16-byte boundaries, the TMA engine may copy them
+    int bulk;                  // bit s: the tiles of range s start on 16-byte boundaries, the TMA engine may copy them
     int *err_flag;
 };
 
@@ -61,9 +64,9 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Shared memory: barriers (at 0) | per-token 2^e (at 128) | partial sums (at 256) | digit sums [nb][8] | x digits | stages
+// Shared memory: barriers (at 0) | partial sums (at 256) | digit sums [nb][8] | block scales [2][nb] | x digits | stages
 __host__ __device__ inline uint32_t pq_off_dsum() { return 256u + kPqRedBytes; }
-__host__ __device__ inline uint32_t pq_off_x(int nb) { return (pq_off_dsum() + (uint32_t)nb * 32u + 127u) / 128u * 128u; }
+__host__ __device__ inline uint32_t pq_off_x(int nb) { return (pq_off_dsum() + (uint32_t)nb * 40u + 127u) / 128u * 128u; }
 __host__ __device__ inline uint32_t pq_off_stage(int nb, int nt) { return pq_off_x(nb) + (uint32_t)(4 * nt) * nb * 128u; }
 
 template <int NT>
@@ -75,9 +78,9 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
     const int grp = warp_all / kPqWarps, warp = warp_all % kPqWarps, tid = tid_all % kPqGroupThreads;
     const int lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int nb = a.nb;
-    float *inv_s = reinterpret_cast<float *>(sm + 128);
     float *red = reinterpret_cast<float *>(sm + 256);
     int *dsum = reinterpret_cast<int *>(sm + pq_off_dsum());
+    float *bscale = reinterpret_cast<float *>(sm + pq_off_dsum() + (uint32_t)nb * 32u);  // [2][nb]
     const uint32_t off_x = pq_off_x(nb), off_st = pq_off_stage(nb, NT);
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(sm);
 
@@ -90,66 +93,71 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
 
     const size_t tile_bytes = (size_t)kPqTileRows * a.row_bytes;
     // the it-th tile of this group; consecutive groups and CTAs take consecutive tiles
+    auto seg_of = [&](int tile) {
+        int sg = 0;
+#pragma unroll
+        for (int i = 1; i < kPqMaxSegs; i++) sg += (tile >= a.seg_tile0[i]) ? 1 : 0;  // unused ranges start at n_tiles
+        return sg;
+    };
     auto tile_of = [&](int it) { return (it * (int)gridDim.x + (int)blockIdx.x) * n_groups + grp; };
     auto issue = [&](int it) {  // one thread of the group
         const int tile = tile_of(it), st = grp * a.stages + it % a.stages;
-        if (!a.bulk || tile >= a.n_tiles || (tile + 1) * kPqTileRows > a.n_rows) return;
+        if (tile >= a.n_tiles) return;
+        const int sg = seg_of(tile), lt = tile - a.seg_tile0[sg];
+        if (!((a.bulk >> sg) & 1) || (lt + 1) * kPqTileRows > a.seg_rows[sg]) return;
         const uint32_t bar = sbase + 8u * st;
         mbar_expect_tx(bar, (uint32_t)tile_bytes);
-        tma_bulk(sbase + off_st + (uint32_t)st * a.stage_stride, a.rows + (size_t)tile * tile_bytes, (uint32_t)tile_bytes, bar);
+        tma_bulk(sbase + off_st + (uint32_t)st * a.stage_stride, a.rows[sg] + (size_t)lt * tile_bytes, (uint32_t)tile_bytes, bar);
     };
     // The weights do not depend on the kernel before this one: the first copies start at once.
     if (tid == 0 && grp < n_groups)
         for (int s = 0; s < a.stages; s++) issue(s);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-    // ---- x: power-of-two normalisation, fixed point, balanced digits, digit sums -------------------
+    // ---- x: per block a power-of-two scale, fixed point, balanced digits, digit sums --------------
+    // One warp per (token, block): X = round(x * 2^(24 - e)) with 2^e the power of two above the
+    // block's max |x|; the block's 2^(e - 24 - 6) (the products carry 4^3) multiplies its f16 scale.
     // Element jj of a block (32 t + 16 r + 4 q + m: word 2t + r of the block, byte q, slot m) lands in
     // byte q of the word [col][block][t][m][r]; a lane's 8 words of a block are 32 contiguous bytes.
-    for (int tok = 0; tok < NT; tok++) {
+    for (int unit = warp_all; unit < NT * nb; unit += n_warps) {
+        const int tok = unit / nb, b = unit - tok * nb;
         const float *xr = a.x + (size_t)tok * a.ne0;
         const bool real = tok < a.n_tok;  // columns past n_tok are zeros
-        float am = 0.f;
-        for (int j = tid_all; real && j < a.ne0; j += n_threads) am = fmaxf(am, fabsf(xr[j]));
-        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        if (lane == 0) red[warp_all] = am;
-        __syncthreads();
-        if (tid_all == 0) {
-            float m = 0.f;
-            for (int w = 0; w < n_warps; w++) m = fmaxf(m, red[w]);
-            int e = 0;
-            if (m > 0.f && m < CUDART_INF_F) frexpf(m, &e);  // m = f * 2^e, f in [0.5, 1)
-            red[32] = ldexpf(1.0f, kPqFrac - e);
-            inv_s[tok] = ldexpf(1.0f, e - kPqFrac - 6);  // the products carry 4^3
+        float xv[4], am = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int j = b * kPqQK + lane + 32 * i;
+            xv[i] = (real && j < a.ne0) ? xr[j] : 0.f;
+            am = fmaxf(am, fabsf(xv[i]));
         }
-        __syncthreads();
-        const float s = red[32];
-        for (int b = warp_all; b < nb; b += n_warps) {
-            int ds[4] = {0, 0, 0, 0};
+        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        int e = 0;
+        if (am > 0.f && am < CUDART_INF_F) frexpf(am, &e);  // am = f * 2^e, f in [0.5, 1)
+        const float s = ldexpf(1.0f, kPqFrac - e);
+        int ds[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int jj = lane + 32 * i, j = b * kPqQK + jj;
-                const float xv = (real && j < a.ne0) ? xr[j] * s : 0.f;  // |xv| < 2^24
-                const int tt = jj >> 5, r = (jj >> 4) & 1, q = (jj >> 2) & 3, m = jj & 3;
-                int B = __float2int_rn(xv) << (2 * (3 - m));
-                uint8_t *dst = sm + off_x + ((((size_t)(4 * tok) * nb + b) * 4 + tt) * 8 + m * 2 + r) * 4 + q;
-#pragma unroll
-                for (int d = 0; d < 4; d++) {
-                    const int dg = (int)(int8_t)(B & 0xff);
-                    B = (B - dg) >> 8;
-                    dst[(size_t)d * nb * 128] = (uint8_t)dg;
-                    ds[d] += dg << (2 * m);
-                }
-            }
+        for (int i = 0; i < 4; i++) {
+            const int jj = lane + 32 * i;
+            const int tt = jj >> 5, r = (jj >> 4) & 1, q = (jj >> 2) & 3, m = jj & 3;
+            int B = __float2int_rn(xv[i] * s) << (2 * (3 - m));  // |x s| < 2^24
+            uint8_t *dst = sm + off_x + ((((size_t)(4 * tok) * nb + b) * 4 + tt) * 8 + m * 2 + r) * 4 + q;
 #pragma unroll
             for (int d = 0; d < 4; d++) {
-                int v = ds[d];
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) dsum[b * 8 + 4 * tok + d] = v;
+                const int dg = (int)(int8_t)(B & 0xff);
+                B = (B - dg) >> 8;
+                dst[(size_t)d * nb * 128] = (uint8_t)dg;
+                ds[d] += dg << (2 * m);
             }
         }
-        __syncthreads();
+#pragma unroll
+        for (int d = 0; d < 4; d++) {
+            int v = ds[d];
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) dsum[b * 8 + 4 * tok + d] = v;
+        }
+        if (lane == 0) bscale[tok * nb + b] = ldexpf(1.0f, e - kPqFrac - 6);
     }
+    __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
     // per-lane constants of the weight reads: rows g and g + 8, this lane's 8 bytes of a block
@@ -164,6 +172,7 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
     const bool has_x = g < kCols;
     const uint32_t x_lane = off_x + ((uint32_t)(g * nb + warp) * 4 + t) * 32;
     const uint32_t d_lane = pq_off_dsum() + (uint32_t)warp * 32 + 8u * t;
+    const uint32_t bs_lane = pq_off_dsum() + (uint32_t)nb * 32u + (uint32_t)((t >> 1) * nb + warp) * 4u;
 
     if (grp >= n_groups) return;  // helped to stage x; no tiles for this group
     auto group_sync = [&]() { asm volatile("bar.sync %0, %1;\n" ::"r"(1 + grp), "r"(kPqGroupThreads) : "memory"); };
@@ -174,8 +183,9 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
         if (tile >= a.n_tiles) break;
         const int sl = it % a.stages, st = grp * a.stages + sl;
         const uint8_t *stage = sm + off_st + (size_t)st * a.stage_stride;
-        const int rows_here = min(kPqTileRows, a.n_rows - tile * kPqTileRows);
-        if (a.bulk && rows_here == kPqTileRows) {
+        const int sg = seg_of(tile), lt = tile - a.seg_tile0[sg];
+        const int rows_here = min(kPqTileRows, a.seg_rows[sg] - lt * kPqTileRows);
+        if (((a.bulk >> sg) & 1) && rows_here == kPqTileRows) {
             int polls = 0;
             while (!mbar_try_wait(sbase + 8u * st, (phase >> sl) & 1u)) {
                 if (++polls > kWaitPolls) {  // never expected: leave a mark rather than hang
@@ -185,7 +195,7 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
             }
             phase ^= 1u << sl;
         } else {  // a ragged last tile or an unaligned payload: ordinary 2-byte loads
-            const uint16_t *src = reinterpret_cast<const uint16_t *>(a.rows + (size_t)tile * tile_bytes);
+            const uint16_t *src = reinterpret_cast<const uint16_t *>(a.rows[sg] + (size_t)lt * tile_bytes);
             uint16_t *dst = reinterpret_cast<uint16_t *>(sm + off_st + (size_t)st * a.stage_stride);
             const int n2 = rows_here * a.row_bytes / 2;
             for (int i = tid; i < n2; i += kPqGroupThreads) dst[i] = __ldg(src + i);
@@ -214,6 +224,9 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
                 bx1 = px[1];
             }
             const int2 dsv = *reinterpret_cast<const int2 *>(sm + d_lane + step * (kPqWarps * 32));
+            const float bs = *reinterpret_cast<const float *>(sm + bs_lane + step * (kPqWarps * 4));
+            sc[0] *= bs;
+            sc[1] *= bs;
             int c[4] = {-dsv.x, -dsv.y, -dsv.x, -dsv.y}, c2[4] = {0, 0, 0, 0};  // two chains; the "- 1" goes in as the start value
             imma_u8s8(c, w[0][0] & 0x03030303u, w[1][0] & 0x03030303u, w[0][1] & 0x03030303u, w[1][1] & 0x03030303u, bx0.x, bx0.y);
             imma_u8s8(c2, w[0][0] & 0x0c0c0c0cu, w[1][0] & 0x0c0c0c0cu, w[0][1] & 0x0c0c0c0cu, w[1][1] & 0x0c0c0c0cu, bx0.z, bx0.w);
@@ -243,7 +256,7 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
             float sum = 0.f;
 #pragma unroll
             for (int wp = 0; wp < kPqWarps; wp++) sum += rd[(wp * kPqTileRows + r) * 2 + tok];
-            if (r < rows_here && tok < a.n_tok) a.y[(size_t)tok * a.y_stride + (size_t)tile * kPqTileRows + r] = sum * inv_s[tok];
+            if (r < rows_here && tok < a.n_tok) a.y[sg][(size_t)tok * a.seg_rows[sg] + (size_t)lt * kPqTileRows + r] = sum;
         }
     }
 }
@@ -271,24 +284,34 @@ bk_status launch_nt(bk_ctx *ctx, const Pq2Args &a, int grid, size_t smem) {
 
 size_t pq2_row_bytes(int64_t ne0) { return (size_t)((ne0 + kPqQK - 1) / kPqQK) * kPqBlockBytes; }
 
-// rows: device pointer to row 0 of the range; x [n_tok][ne0]; y [n_tok][y_stride], n_tok 1..2.
-bk_status launch_pq2_matvec(bk_ctx *ctx, const uint8_t *rows, int ne0, int n_rows, const float *x, int n_tok, float *y, int y_stride) {
-    if (n_rows <= 0 || n_tok <= 0) return BK_OK;
+// Up to four row ranges with the same ne0 (rows[s]: device pointer to the first row, n_rows[s] rows,
+// y[s] [n_tok][n_rows[s]]); x [n_tok][ne0], n_tok 1..2.
+bk_status launch_pq2_matvec(bk_ctx *ctx, int n_seg, const uint8_t *const *rows, const int *n_rows, float *const *y, int ne0,
+                            const float *x, int n_tok) {
+    if (n_tok <= 0) return BK_OK;
     Pq2Args a{};
-    a.rows = rows;
     a.x = x;
-    a.y = y;
     a.ne0 = ne0;
     a.nb = (ne0 + kPqQK - 1) / kPqQK;
     a.row_bytes = a.nb * kPqBlockBytes;
-    a.n_rows = n_rows;
     a.n_tok = n_tok;
-    a.n_tiles = (n_rows + kPqTileRows - 1) / kPqTileRows;
-    a.y_stride = y_stride;
     a.err_flag = ctx->d_err;
+    int tiles = 0, used = 0;
+    for (int sgi = 0; sgi < n_seg && used < kPqMaxSegs; sgi++) {
+        if (n_rows[sgi] <= 0) continue;
+        a.rows[used] = rows[sgi];
+        a.y[used] = y[sgi];
+        a.seg_rows[used] = n_rows[sgi];
+        a.seg_tile0[used] = tiles;
+        if ((uintptr_t)rows[sgi] % 16 == 0) a.bulk |= 1 << used;  // 16 rows are a multiple of 16 bytes whatever ne0
+        tiles += (n_rows[sgi] + kPqTileRows - 1) / kPqTileRows;
+        used++;
+    }
+    for (int sgi = used; sgi <= kPqMaxSegs; sgi++) a.seg_tile0[sgi] = tiles;
+    a.n_tiles = tiles;
+    if (tiles == 0) return BK_OK;
     const size_t tile_bytes = (size_t)kPqTileRows * a.row_bytes;
     a.stage_stride = (int)((tile_bytes + 16 + 127) / 128 * 128);
-    a.bulk = ((uintptr_t)rows % 16 == 0) ? 1 : 0;  // 16 rows are a multiple of 16 bytes whatever ne0
     const int nt = n_tok <= 1 ? 1 : 2;
     const size_t fixed = pq_off_stage(a.nb, nt);
     const size_t limit = 227 * 1024;

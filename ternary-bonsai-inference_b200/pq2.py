@@ -5,6 +5,8 @@ is its GGUF payload, rows back to back, each row ceil(ne0 / 128) blocks of 34 by
 128 two-bit codes, weight = (code - 1) * scale).  The payload is uploaded once and stays in
 device memory; every product streams it once per group of four activations.
 """
+import ctypes as C
+
 import numpy as np
 
 from . import _abi
@@ -33,6 +35,20 @@ def pack_pq2(codes, scales):
     out[..., :2] = sc.view(np.uint8).reshape(n_rows, nb, 2)
     out[..., 2:] = qs
     return out.reshape(-1)
+
+
+class _Seg(C.Structure):
+    _fields_ = [("payload_dev", C.c_void_p), ("payload_bytes", C.c_size_t), ("base_row", C.c_int64), ("n_rows", C.c_int64),
+                ("y_dev", C.c_void_p)]
+
+
+def pq2_matvec_multi_device(ctx, tensors, x_ptr, y_ptrs, n_tok=1):
+    """Up to four tensors with the same ne0 against one x in one launch (the q, k and v projections
+    of a layer); y_ptrs[i] receives [n_tok, tensors[i].n_rows].  Asynchronous, device pointers."""
+    segs = (_Seg * len(tensors))()
+    for sg, t, yp in zip(segs, tensors, y_ptrs):
+        sg.payload_dev, sg.payload_bytes, sg.base_row, sg.n_rows, sg.y_dev = t.buf.ptr, t.payload_bytes, 0, t.n_rows, yp
+    ctx.check(ctx.lib.bk_pq2_matvec_multi(ctx.h, len(tensors), C.cast(segs, C.c_void_p), tensors[0].ne0, x_ptr, n_tok))
 
 
 class Pq2Tensor:

@@ -105,7 +105,7 @@ def test_gpu_pq2_matvec_matches_oracle(oracle, bk, gpu_ctx, ne0, n_rows, n_tok):
     norm = np.abs(x.astype(np.float64)) @ np.abs(w).T
     truth = x.astype(np.float64) @ w.T
     assert np.all(np.abs(got - want) <= TOL * norm + 1e-30), f"max {np.max(np.abs(got - want) / (norm + 1e-30)):.3e}"
-    assert np.max(np.abs(got - truth) / (norm + 1e-30)) <= 2e-6  # 22-bit activations, f32 sums
+    assert np.max(np.abs(got - truth) / (norm + 1e-30)) <= 2e-6  # exact block sums of 25-bit fixed-point x, f32 sums across blocks
     t.free()
 
 
@@ -154,7 +154,7 @@ def test_gpu_pq2_properties_at_model_size(bk, gpu_ctx):
     scales = (0.01 + rng.random((n_rows, nb))).astype(np.float16)
     t = bk.Pq2Tensor(gpu_ctx, bk.pack_pq2(codes, scales), ne0)
     y = t.matvec(x[0])
-    # a power-of-two factor on x passes through exactly (the kernel normalises x by a power of two)
+    # a power-of-two factor on x passes through exactly (the kernel normalises every block of x by a power of two)
     assert np.array_equal(t.matvec(x[0] * np.float32(1024.0)), y * np.float32(1024.0))
     assert np.array_equal(t.matvec(x[0] * np.float32(2.0 ** -20)), y * np.float32(2.0 ** -20))
     # rows are independent: any row range equals the slice of the whole product
@@ -164,3 +164,26 @@ def test_gpu_pq2_properties_at_model_size(bk, gpu_ctx):
     w = dense(codes[rows], scales[rows], ne0)
     assert np.max(np.abs(y[rows] - w @ x[0].astype(np.float64)) / (np.abs(w) @ np.abs(x[0]).astype(np.float64))) <= 2e-6
     t.free()
+
+
+@pytest.mark.gpu
+def test_gpu_pq2_multi_equals_separate_calls(bk, gpu_ctx):
+    """attn_q, attn_k, attn_v shapes on one x in one launch: bit-equal to three launches."""
+    ne0 = 5120
+    rng = np.random.default_rng(7)
+    tensors = []
+    for n_rows in (12288, 1024, 1000):
+        payload, _, _, _ = synth(bk, n_rows, n_rows, ne0, 1)
+        tensors.append(bk.Pq2Tensor(gpu_ctx, payload, ne0))
+    for n_tok in (1, 2, 3):
+        x = rng.standard_normal((n_tok, ne0)).astype(np.float32)
+        dx = gpu_ctx.to_device(x)
+        ys = [gpu_ctx.alloc(n_tok * t.n_rows * 4) for t in tensors]
+        bk.pq2_matvec_multi_device(gpu_ctx, tensors, dx.ptr, [y.ptr for y in ys], n_tok)
+        for t, y in zip(tensors, ys):
+            got = y.download((n_tok, t.n_rows), np.float32)
+            assert np.array_equal(got, t.matmul_n(x, n_tok))
+            y.free()
+        dx.free()
+    for t in tensors:
+        t.free()
