@@ -476,6 +476,9 @@ def run_other_workload(args):
         if args.workload == "pq2":
             line["roofline"]["note"] = ("pq2_matvec_kernel, every launch of the step: payload bytes (the algorithmic "
                                         "bytes: each weight byte once) over the step's device time")
+            # dram__bytes_read.sum + dram__bytes_write.sum of one layer's two launches (19.55 + 8.41 MB, writes 0),
+            # profiles/pq2_matvec_attn_projections_ncu.md, times the layers of a step
+            line["roofline"]["traffic"] = N_LAYERS * 27.96e6
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
