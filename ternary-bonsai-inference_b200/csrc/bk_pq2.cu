@@ -263,7 +263,11 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
 
 template <int NT>
 bk_status launch_nt(bk_ctx *ctx, const Pq2Args &a, int grid, size_t smem) {
-    BK_CUDA(ctx, cudaFuncSetAttribute(pq2_matvec_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static int opted_in_device = -1;  // the opt-in is per device and costs a driver call: once is enough
+    if (opted_in_device != ctx->device) {
+        BK_CUDA(ctx, cudaFuncSetAttribute(pq2_matvec_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        opted_in_device = ctx->device;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)(kPqGroupThreads * kPqMaxGroups));
