@@ -92,14 +92,15 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
     __syncthreads();
 
     const size_t tile_bytes = (size_t)kPqTileRows * a.row_bytes;
-    // the it-th tile of this group; consecutive groups and CTAs take consecutive tiles
     auto seg_of = [&](int tile) {
         int sg = 0;
 #pragma unroll
         for (int i = 1; i < kPqMaxSegs; i++) sg += (tile >= a.seg_tile0[i]) ? 1 : 0;  // unused ranges start at n_tiles
         return sg;
     };
-    auto tile_of = [&](int it) { return (it * (int)gridDim.x + (int)blockIdx.x) * n_groups + grp; };
+    // the it-th tile of this group: consecutive CTAs take consecutive tiles, group after group, so a last
+    // partial round spreads over all SMs (few groups busy on each) instead of filling some of them
+    auto tile_of = [&](int it) { return (it * n_groups + grp) * (int)gridDim.x + (int)blockIdx.x; };
     auto issue = [&](int it) {  // one thread of the group
         const int tile = tile_of(it), st = grp * a.stages + it % a.stages;
         if (tile >= a.n_tiles) return;
@@ -329,7 +330,7 @@ bk_status launch_pq2_matvec(bk_ctx *ctx, int n_seg, const uint8_t *const *rows, 
     groups = std::max(1, std::min(groups, (a.n_tiles + ctx->n_sms - 1) / ctx->n_sms));
     a.groups = groups;
     const size_t smem = fixed + (size_t)groups * per_group;
-    const int grid = std::min((a.n_tiles + groups - 1) / groups, ctx->n_sms);
+    const int grid = std::min(a.n_tiles, ctx->n_sms);
     if (nt == 1) return launch_nt<1>(ctx, a, grid, smem);
     return launch_nt<2>(ctx, a, grid, smem);
 }
