@@ -381,10 +381,10 @@ def run_other_workload(args):
                 wq, wk, wv, wo = (t for t, _n, _e in tensors[4 * il:4 * il + 4])
                 bk.pq2_matvec_multi_device(ctx, [wq, wk, wv], dx[5120].ptr, [d_y.ptr, d_yk.ptr, d_yv.ptr], n_tok)
                 wo.matvec_device(dx[NH * HD].ptr, d_y.ptr, n_tok)
-        step_bytes = sum(t.payload_bytes for t, _n, _e in tensors)
-        tokens_per_step, scaling = n_tok, "weak"
+        step_bytes = world * sum(t.payload_bytes for t, _n, _e in tensors)   # every rank is a replica with its own token
+        tokens_per_step, scaling = n_tok * world, "weak"
         cfg = {"workload": f"pq2: wq+wk+wv (one launch) and wo of {N_LAYERS} full-attention layers, {n_tok} token(s), weights resident "
-                           f"({step_bytes / 1e6:.0f} MB streamed per step, larger than L2)"}
+                           f"({step_bytes / world / 1e6:.0f} MB streamed per step and GPU, larger than L2)"}
 
         def pq2_extras():
             """e2e through the host-buffer call, and the oracle's scalar matvec on one layer (x 16)."""
@@ -466,7 +466,8 @@ def run_other_workload(args):
             line["useful_tflops"] = cfg["useful_tflop_per_step"] / (ms_step * 1e-3)
         if args.workload == "pq2":
             line["metric"] = "PQ2_0 attention-projection matvec tokens/s"
-            line.update(pq2_extras())
+            if world == 1:   # the host-buffer loop and the CPU arm are single-process measurements
+                line.update(pq2_extras())
         line.update({"value": tokens_per_step * 1e3 / ms_step, "ms_per_step": ms_step, "scaling": scaling, "config": cfg,
                      "effective_gbs": gbs, "gpu_launches": ctx.launch_count - launches0,
                      "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s",
@@ -478,7 +479,7 @@ def run_other_workload(args):
                                         "bytes: each weight byte once) over the step's device time")
             # dram__bytes_read.sum + dram__bytes_write.sum of one layer's two launches (19.55 + 8.41 MB, writes 0),
             # profiles/pq2_matvec_attn_projections_ncu.md, times the layers of a step
-            line["roofline"]["traffic"] = N_LAYERS * 27.96e6
+            line["roofline"]["traffic"] = N_LAYERS * 27.96e6   # per GPU, like `achieved`
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
