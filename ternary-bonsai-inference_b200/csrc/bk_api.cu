@@ -199,6 +199,9 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
         const char *e3 = getenv("BONSAI_KV_PREFILL");
         ctx->prefill_umma = !(e3 && std::string(e3) == "mma");  // tcgen05 kernel unless BONSAI_KV_PREFILL=mma
         ctx->qsplit = !(e2 && e2[0] == '0');  // on unless BONSAI_KV_QSPLIT=0
+        const char *e5 = getenv("BONSAI_KV_DYN"), *e6 = getenv("BONSAI_KV_DIST");
+        ctx->dyn_tiles = e5 ? atoi(e5) : 1;
+        ctx->dist_combine = !(e6 && e6[0] == '0');
     }
     if ((e = cudaMalloc(&ctx->d_givens, sizeof(ctx->h_givens))) != cudaSuccess) return bail(e, "cudaMalloc givens");
     if ((e = cudaMalloc(&ctx->d_codebooks, sizeof(ctx->h_codebooks))) != cudaSuccess)
@@ -382,9 +385,9 @@ bk_status bk_cache_create(bk_ctx *ctx, const bk_cache_config *cfg, bk_cache **ou
     };
     if ((st = alloc((void **)&c->d_k, rows * c->k_row_bytes)) != BK_OK ||
         (st = alloc((void **)&c->d_v, rows * c->v_row_bytes)) != BK_OK ||
-        // norms carry one tile (16 positions) of slack: the tensor-core decode copies whole tiles
-        (k_kind == ROW_PLANAR && (st = alloc((void **)&c->d_kn, (rows + 16 * cfg->n_kv) * 4)) != BK_OK) ||
-        (v_kind == ROW_PLANAR && (st = alloc((void **)&c->d_vn, (rows + 16 * cfg->n_kv) * 4)) != BK_OK) ||
+        // norms carry one tile (32 positions) of slack: the tensor-core decode copies whole tiles
+        (k_kind == ROW_PLANAR && (st = alloc((void **)&c->d_kn, (rows + 32 * cfg->n_kv) * 4)) != BK_OK) ||
+        (v_kind == ROW_PLANAR && (st = alloc((void **)&c->d_vn, (rows + 32 * cfg->n_kv) * 4)) != BK_OK) ||
         (st = get_rope(ctx, cfg->n_rot, cfg->freq_base, rope_n, &c->rope)) != BK_OK) {
         bk_cache_destroy(c);
         return st;
@@ -392,7 +395,7 @@ bk_status bk_cache_create(bk_ctx *ctx, const bk_cache_config *cfg, bk_cache **ou
     c->n_pos.assign((size_t)cfg->n_layers * cfg->n_seqs, 0);
     if ((k_kind == ROW_PLANAR && v_kind == ROW_PLANAR && (bits == 4 || bits == 3)) || (k_kind == ROW_F16 && v_kind == ROW_F16)) {
         st = make_tile_tensor_maps(ctx, c->d_k, c->d_v, c->k_row_bytes, cfg->n_kv,
-                                   (size_t)cfg->n_layers * cfg->n_seqs * cfg->n_ctx, c->tmap_k, c->tmap_v);
+                                   (size_t)cfg->n_layers * cfg->n_seqs * cfg->n_ctx, k_kind == ROW_F16 ? 16 : 32, c->tmap_k, c->tmap_v);
         if (st != BK_OK) {
             bk_cache_destroy(c);
             return st;
@@ -643,6 +646,7 @@ void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out
     a.xch_world = a.xch_rank = 0;
     a.xch_seqno = 0;
     a.xch_err = ctx->d_err;
+    a.dyn = a.dist = 0;
     a.k_rows_w = c->k_rows(layer, 0);
     a.v_rows_w = c->v_rows(layer, 0);
     a.k_norms_w = c->k_norms(layer, 0);
@@ -707,8 +711,12 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
     m.item_start[nb] = items;
     m.n_items = items;
     if (!use_mma) return launch_decode(ctx, a, m);
-    return a.k_kind == ROW_F16 ? launch_decode_f16_mma(ctx, a, m, ctx->qsplit)
-                               : launch_decode_p4_mma(ctx, a, m, ctx->lut_alpha[a.bits], ctx->qsplit);
+    DecodeArgs a2 = a;
+    a2.dyn = ctx->dyn_tiles;
+    // every CTA holds a whole SM, so a launch of at most n_sms items is resident all at once
+    a2.dist = (ctx->dist_combine && items <= ctx->n_sms && !a.xch_peer) ? 1 : 0;
+    return a.k_kind == ROW_F16 ? launch_decode_f16_mma(ctx, a2, m, ctx->qsplit)
+                               : launch_decode_p4_mma(ctx, a2, m, ctx->lut_alpha[a.bits], ctx->qsplit);
 }
 
 bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos) {

@@ -21,6 +21,23 @@
 namespace bk {
 
 constexpr int kFactorCap = 256;  // chunks whose rescale factors are cached in shared memory
+constexpr int kDistSpin = 1 << 21;  // polls of the arrival counter before the slice combine gives up
+
+// Per-CTA time stamps for tuning builds (-DBK_PHASE): stamp i of CTA b lands in g_phase[b][i].
+#ifdef BK_PHASE
+static __device__ unsigned long long g_phase[1024][16];
+__device__ __forceinline__ unsigned long long phase_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define BK_STAMP(i)                                                                       \
+    do {                                                                                  \
+        if (threadIdx.x == 0 && blockIdx.x < 1024) g_phase[blockIdx.x][i] = phase_timer(); \
+    } while (0)
+#else
+#define BK_STAMP(i)
+#endif
 
 // A free region of shared memory through which the last arriver streams the other chunks'
 // triples (the tensor-core kernels pass their drained stage ring): the TMA engine copies them in
@@ -34,6 +51,147 @@ struct FinishSmem {
     uint8_t *ptr = nullptr;  // the same region as a generic pointer
     int *err_flag = nullptr;
 };
+
+// The slice form of the split-K combine.  When every CTA of a (sequence, kv head) is resident at
+// the same time (the launcher sets DecodeArgs::dist only then), nobody leaves after publishing:
+// each CTA waits (bounded) until all n_chunks triples are in the scratch and then combines ONE
+// slice of the output - all heads of the group, `D` consecutive coordinates - from every chunk's
+// triple: one L2 round trip of a few hundred 16-byte loads per CTA instead of one CTA walking
+// through all the triples.  The slices are whole Givens pairs, so the inverse rotation, the
+// division by l and the gate happen here too.  `red` is free shared memory (16-byte aligned, at
+// least 16 KiB); s_f holds kFactorCap * NREP floats.  Returns false when the wait ran out.
+template <int NREP>
+__device__ __forceinline__ bool combine_slice(const DecodeArgs &a, int slot, int kv, int my_chunk, int n_chunks,
+                                              const float *base /* first chunk's triple */, float *red, float *s_f,
+                                              float *s_M, float *s_L, int *s_flag, unsigned *counter, bool v_planar,
+                                              const float *givens, int *err_flag) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        cuda::atomic_ref<unsigned, cuda::thread_scope_device> cnt(*counter);
+        int polls = 0, ok = 1;
+        while (cnt.load(cuda::memory_order_acquire) < (unsigned)n_chunks) {
+            if (++polls > kDistSpin) {  // never expected: leave a mark, write nothing
+                ok = 0;
+                if (err_flag) atomicExch(err_flag, 6);
+                break;
+            }
+        }
+        *s_flag = ok;
+    }
+    __syncthreads();
+    BK_STAMP(7);
+    if (!*s_flag) return false;
+    const int D4 = (kHd / 4 + n_chunks - 1) / n_chunks;  // 16-byte columns per head in a slice
+    const int D = 4 * D4, n_slices = (kHd + D - 1) / D;
+    if (my_chunk >= n_slices) return true;
+    const int d0 = my_chunk * D, d4 = min(D4, (kHd - d0) >> 2), dn = 4 * d4;
+    const int n_col = NREP * d4;                     // 16-byte columns of this slice (<= 192 for two chunks)
+    const int n_grp = max(1, 256 / n_col);           // thread groups; group g takes chunks g, g + n_grp, ...
+    const bool act = tid < n_grp * n_col;
+    const int grp = tid / n_col, col = tid - grp * n_col, r_col = col / d4, j_col = col - r_col * d4;
+    // the data loads go out first: they and the (m, l) sweep below share one round trip
+    constexpr int kPre = 4;
+    float4 pre[kPre];
+    const float *src = base + (size_t)r_col * kScratchStride + d0 + 4 * j_col;
+#pragma unroll
+    for (int u = 0; u < kPre; u++) {
+        const int c = grp + u * n_grp;
+        pre[u] = (act && c < n_chunks) ? __ldcg(reinterpret_cast<const float4 *>(src + (size_t)c * NREP * kScratchStride))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float *gate = (a.gate && !a.partial) ? a.gate + ((size_t)slot * a.n_head + (size_t)kv * NREP) * a.gate_stride + d0 : nullptr;
+    float gv = 0.f;
+    if (gate && tid < NREP * dn) gv = __ldg(gate + (size_t)(tid / dn) * a.gate_stride + (tid % dn));
+    if (warp < NREP) {  // one warp per head: global max, every chunk's factor, the merged l
+        const int r = warp;
+        constexpr int kPer = kFactorCap / 32;
+        float2 ml[kPer];
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int u = 0; u < kPer; u++) {
+            const int c = lane + 32 * u;
+            ml[u] = make_float2(-CUDART_INF_F, 0.f);
+            if (c < n_chunks) ml[u] = __ldcg(reinterpret_cast<const float2 *>(base + ((size_t)c * NREP + r) * kScratchStride + kHd));
+            M = fmaxf(M, ml[u].x);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        float Lsum = 0.f;
+#pragma unroll
+        for (int u = 0; u < kPer; u++) {
+            const int c = lane + 32 * u;
+            const float f = ml[u].x > -CUDART_INF_F ? exp2f(ml[u].x - M) : 0.f;
+            Lsum = fmaf(ml[u].y, f, Lsum);
+            if (c < n_chunks) s_f[c * NREP + r] = f;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, off);
+        if (lane == 0) {
+            s_M[r] = M;
+            s_L[r] = Lsum;
+        }
+    }
+    __syncthreads();
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (act) {
+        for (int c0 = grp; c0 < n_chunks; c0 += kPre * n_grp) {
+            if (c0 > grp) {
+#pragma unroll
+                for (int u = 0; u < kPre; u++) {
+                    const int c = c0 + u * n_grp;
+                    pre[u] = c < n_chunks ? __ldcg(reinterpret_cast<const float4 *>(src + (size_t)c * NREP * kScratchStride))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kPre; u++) {
+                const int c = c0 + u * n_grp;
+                const float f = c < n_chunks ? s_f[c * NREP + r_col] : 0.f;
+                if (f != 0.f) {  // an empty chunk's accumulator is never looked at
+                    sum.x = fmaf(pre[u].x, f, sum.x);
+                    sum.y = fmaf(pre[u].y, f, sum.y);
+                    sum.z = fmaf(pre[u].z, f, sum.z);
+                    sum.w = fmaf(pre[u].w, f, sum.w);
+                }
+            }
+        }
+        reinterpret_cast<float4 *>(red)[grp * n_col + col] = sum;
+    }
+    __syncthreads();
+    float *res = red + (size_t)4 * n_grp * n_col;  // [NREP][dn], fixed summation order over the groups
+    if (tid < NREP * dn) {
+        const int r = tid / dn, d = tid - r * dn;
+        float t = 0.f;
+        for (int g2 = 0; g2 < n_grp; g2++) t += red[((size_t)g2 * n_col + r * d4 + (d >> 2)) * 4 + (d & 3)];
+        res[tid] = t;
+    }
+    __syncthreads();
+    if (tid < NREP * dn) {
+        const int r = tid / dn, d = tid - r * dn;
+        float o = res[tid];
+        if (v_planar) {  // undo the Givens rotation: coordinate d0 + d and its partner (src/forward.rs:349)
+            const int pr = (d0 + d) >> 1;
+            const float c = givens[2 * pr], sn = givens[2 * pr + 1];
+            float o0, o1;
+            givens_inv(res[r * dn + (d & ~1)], res[r * dn + (d | 1)], c, sn, o0, o1);
+            o = (d & 1) ? o1 : o0;
+        }
+        if (a.partial) {
+            a.out[((size_t)slot * a.n_head + (size_t)kv * NREP + r) * kPartStride + d0 + d] = o;
+        } else {
+            const float Ls = s_L[r];
+            o = Ls > 0.f ? o / Ls : 0.f;
+            if (gate) o *= 1.0f / (1.0f + expf(-gv));
+            a.out[((size_t)slot * a.n_head + (size_t)kv * NREP + r) * kHd + d0 + d] = o;
+        }
+    }
+    if (a.partial && my_chunk == 0 && tid < NREP) {
+        float *po = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP + tid) * kPartStride;
+        po[kHd] = s_M[tid] * 0.6931471805599453f;  // log2 -> ln
+        po[kHd + 1] = s_L[tid];
+    }
+    return true;
+}
 
 template <int NREP, bool STREAM = false>
 __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s, int kv, int item, int n_chunks,
@@ -79,6 +237,25 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
         }
         if (STREAM) asm volatile("fence.proxy.async;\n" ::: "memory");  // this thread's shared-memory traffic before the copies below
         __syncthreads();
+        BK_STAMP(6);
+        if (STREAM && a.dist && fs.ptr && fs.bytes >= 20480 && n_chunks <= kFactorCap) {
+            // every CTA of this (sequence, kv head) stays and combines one slice of the output
+            const float *base0 = a.partials + (size_t)first_item * NREP * kScratchStride;
+            combine_slice<NREP>(a, slot, kv, item - first_item, n_chunks, base0, reinterpret_cast<float *>(fs.ptr), s_f, s_M,
+                                s_L, s_last, &a.counters[s * a.n_kv + kv], v_planar, givens ? givens : a.givens, fs.err_flag);
+            BK_STAMP(8);
+            __syncthreads();  // every load of this CTA has been consumed
+            if (tid == 0) {
+                // the last CTA to get here knows that everybody has seen the full count: reset for the next launch
+                cuda::atomic_ref<unsigned, cuda::thread_scope_device> done(a.counters[kCtrDone + s * a.n_kv + kv]);
+                if (done.fetch_add(1u, cuda::memory_order_acq_rel) == (unsigned)(n_chunks - 1)) {
+                    a.counters[s * a.n_kv + kv] = 0;
+                    a.counters[kCtrTile + s * a.n_kv + kv] = 0;
+                    a.counters[kCtrDone + s * a.n_kv + kv] = 0;
+                }
+            }
+            return;
+        }
         if (!*s_last) return;
         const float *base = a.partials + (size_t)first_item * NREP * kScratchStride;
         constexpr uint32_t kChunkBytes = NREP * kScratchStride * sizeof(float);
@@ -174,7 +351,10 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
                     s_acc[r * kHd + tid] = t;
                 }
             }
-            if (tid == 0) a.counters[s * a.n_kv + kv] = 0;  // ready for the next launch
+            if (tid == 0) {  // ready for the next launch
+                a.counters[s * a.n_kv + kv] = 0;
+                a.counters[kCtrTile + s * a.n_kv + kv] = 0;
+            }
             __syncthreads();
         } else {
         // 64 threads span one 256-float row with float4 loads; the four 64-thread groups take
@@ -277,7 +457,10 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
             }
             __syncthreads();
         }
-        if (tid == 0) a.counters[s * a.n_kv + kv] = 0;  // ready for the next launch
+        if (tid == 0) {  // ready for the next launch
+            a.counters[s * a.n_kv + kv] = 0;
+            a.counters[kCtrTile + s * a.n_kv + kv] = 0;
+        }
         __syncthreads();
         }
     }

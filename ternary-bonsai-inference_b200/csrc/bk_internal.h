@@ -22,6 +22,10 @@ constexpr int kPartStride = kHd + 2;   // floats per partial result handed to ca
 constexpr int kScratchStride = kHd + 4; // floats per partial in the split-K scratch (16-byte aligned rows)
 constexpr int kMmaMinPos = 2048;       // shorter sequences take the generic f32 decode kernel
 constexpr int kMaxWorld = 8;            // ranks a context-split mailbox can connect
+// The counters of the split-K scratch, per (sequence in the launch, kv head) pair i (i < 512):
+// [i] arrival tickets, [kCtrTile + i] tiles claimed from the pair's pool (tensor-core kernels),
+// [kCtrDone + i] CTAs that have finished the slice combine.  All read zero between launches.
+constexpr int kCtrTile = 512, kCtrDone = 1024, kCtrTotal = 1536;
 constexpr int kDescSlots = 8;          // launches of bk_append_batch that may be in flight
 constexpr int kDescCap = 4096;         // tokens one bk_append_batch call may carry
 
@@ -60,6 +64,7 @@ struct bk_ctx {
     bool prefill_umma = true;              // batched attention on tcgen05; BONSAI_KV_PREFILL=mma picks the mma.sync kernel
     bool force_generic = false;            // BONSAI_KV_GENERIC=1: never take the tensor-core path
     bool qsplit = true;                    // q as f16 hi + lo in the tensor-core path (BONSAI_KV_QSPLIT=0: hi only)
+    int dyn_tiles = 1; bool dist_combine = true;  // BONSAI_KV_DYN=0 / BONSAI_KV_DIST=0 switch them off
     // staging for the *_host entry points (grown on demand)
     void *h_stage = nullptr;
     size_t h_stage_bytes = 0;
@@ -92,7 +97,7 @@ struct bk_cache {
     std::vector<int32_t> n_pos;               // [layer][seq]
     std::shared_ptr<bk::RopeTable> rope;
     size_t device_bytes = 0;
-    alignas(64) unsigned char tmap_k[128], tmap_v[128];  // CUtensorMap objects (4-bit planar and f16 K+V caches)
+    alignas(64) unsigned char tmap_k[128], tmap_v[128];  // CUtensorMap objects (4/3-bit planar: boxes of 32 positions; f16 K+V: 16)
     bool has_tmaps = false;
 
     size_t slab(int layer, int seq) const { return (size_t)layer * cfg.n_seqs + seq; }
@@ -198,6 +203,12 @@ struct DecodeArgs {
     int xch_world, xch_rank;
     unsigned xch_seqno;
     int *xch_err;
+    // Set by launch_decode_group for the tensor-core kernels:
+    //   dyn   the warps of a (sequence, kv head) draw their tiles from one shared pool (a counter in
+    //         the scratch) instead of a fixed share, so that a CTA that starts late takes less
+    //   dist  every CTA of the launch is resident at once (items <= SMs): the split-K combine is
+    //         done in slices by all CTAs of a kv head instead of by the last one to arrive
+    int dyn, dist;
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
 
@@ -223,7 +234,7 @@ bool decode_p4_mma_supported(const DecodeArgs &a);
 bool decode_f16_mma_supported(const DecodeArgs &a);
 inline bool decode_mma_supported(const DecodeArgs &a) { return decode_p4_mma_supported(a) || decode_f16_mma_supported(a); }
 bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, size_t row_bytes, int n_kv,
-                                size_t total_pos, void *out_k, void *out_v);
+                                size_t total_pos, int box_rows, void *out_k, void *out_v);
 bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
 bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, bool qsplit);
 // RMSNorm over rows (bk_layer.cu): up to two row groups per launch, each with its own source

@@ -30,7 +30,7 @@ namespace bk {
 namespace {
 
 constexpr int kStaticItems = 512;     // work items one call may create
-constexpr int kStaticCounters = 1024; // (sequence-in-call, kv head) pairs: 64 x 16
+constexpr int kStaticCounters = kCtrTotal; // three counters per (sequence-in-call, kv head) pair, up to 512 pairs
 constexpr int kStaticSeqs = kMaxSeqsPerLaunch;
 
 // The scratch itself.  In host code these names are only handles for the runtime: the device
