@@ -213,7 +213,7 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
         return bail(e, "upload codebooks");
     const size_t part_bytes = (size_t)kMaxItems * kMaxRep * kScratchStride * sizeof(float);
     if ((e = cudaMalloc(&ctx->d_partials, part_bytes)) != cudaSuccess) return bail(e, "cudaMalloc partials");
-    const size_t cnt_bytes = (size_t)kMaxSeqsPerLaunch * 64 * sizeof(unsigned);
+    const size_t cnt_bytes = (size_t)kCtrTotal * sizeof(unsigned);
     if ((e = cudaMalloc(&ctx->d_counters, cnt_bytes)) != cudaSuccess) return bail(e, "cudaMalloc counters");
     if ((e = cudaMemset(ctx->d_counters, 0, cnt_bytes)) != cudaSuccess) return bail(e, "clear counters");
     if ((e = cudaMalloc(&ctx->d_err, sizeof(int))) != cudaSuccess) return bail(e, "cudaMalloc error flag");
@@ -647,6 +647,8 @@ void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out
     a.xch_seqno = 0;
     a.xch_err = ctx->d_err;
     a.dyn = a.dist = 0;
+    a.counters_other = nullptr;
+    a.other_n = 0;
     a.k_rows_w = c->k_rows(layer, 0);
     a.v_rows_w = c->v_rows(layer, 0);
     a.k_norms_w = c->k_norms(layer, 0);
@@ -713,6 +715,15 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
     if (!use_mma) return launch_decode(ctx, a, m);
     DecodeArgs a2 = a;
     a2.dyn = ctx->dyn_tiles;
+    if (a.counters == ctx->d_counters) {  // (a caller with its own scratch clears it itself before every call)
+        const int set = ctx->ctr_set;
+        a2.counters = ctx->d_counters + (size_t)kCtrSet * (1 + set);
+        a2.counters_other = ctx->d_counters + (size_t)kCtrSet * (2 - set);
+        a2.other_n = ctx->ctr_dirty[1 - set];
+        ctx->ctr_dirty[set] = std::max(ctx->ctr_dirty[set], nb * n_kv);
+        ctx->ctr_dirty[1 - set] = 0;
+        ctx->ctr_set = 1 - set;
+    }
     // every CTA holds a whole SM, so a launch of at most n_sms items is resident all at once
     a2.dist = (ctx->dist_combine && items <= ctx->n_sms && !a.xch_peer) ? 1 : 0;
     return a.k_kind == ROW_F16 ? launch_decode_f16_mma(ctx, a2, m, ctx->qsplit)

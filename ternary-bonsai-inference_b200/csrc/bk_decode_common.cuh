@@ -244,17 +244,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
             combine_slice<NREP>(a, slot, kv, item - first_item, n_chunks, base0, reinterpret_cast<float *>(fs.ptr), s_f, s_M,
                                 s_L, s_last, &a.counters[s * a.n_kv + kv], v_planar, givens ? givens : a.givens, fs.err_flag);
             BK_STAMP(8);
-            __syncthreads();  // every load of this CTA has been consumed
-            if (tid == 0) {
-                // the last CTA to get here knows that everybody has seen the full count: reset for the next launch
-                cuda::atomic_ref<unsigned, cuda::thread_scope_device> done(a.counters[kCtrDone + s * a.n_kv + kv]);
-                if (done.fetch_add(1u, cuda::memory_order_acq_rel) == (unsigned)(n_chunks - 1)) {
-                    a.counters[s * a.n_kv + kv] = 0;
-                    a.counters[kCtrTile + s * a.n_kv + kv] = 0;
-                    a.counters[kCtrDone + s * a.n_kv + kv] = 0;
-                }
-            }
-            return;
+            return;  // (the counter is cleared by the launch after the next one)
         }
         if (!*s_last) return;
         const float *base = a.partials + (size_t)first_item * NREP * kScratchStride;
@@ -351,10 +341,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
                     s_acc[r * kHd + tid] = t;
                 }
             }
-            if (tid == 0) {  // ready for the next launch
-                a.counters[s * a.n_kv + kv] = 0;
-                a.counters[kCtrTile + s * a.n_kv + kv] = 0;
-            }
+            if (tid == 0) a.counters[s * a.n_kv + kv] = 0;  // ready for the next launch
             __syncthreads();
         } else {
         // 64 threads span one 256-float row with float4 loads; the four 64-thread groups take
@@ -457,10 +444,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
             }
             __syncthreads();
         }
-        if (tid == 0) {  // ready for the next launch
-            a.counters[s * a.n_kv + kv] = 0;
-            a.counters[kCtrTile + s * a.n_kv + kv] = 0;
-        }
+        if (tid == 0) a.counters[s * a.n_kv + kv] = 0;  // ready for the next launch
         __syncthreads();
         }
     }

@@ -122,6 +122,9 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     if (a.q_norm_w)
         for (int i = tid; i < kHd; i += kFT) o.qw[i] = a.q_norm_w[i];
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // the counter set of the next launch: whatever the launch before the previous one left there goes now
+    if (blockIdx.x == 0 && a.counters_other)
+        for (int i = tid; i < a.other_n; i += blockDim.x) a.counters_other[i] = 0;
     // q first: its loads are in flight before the tile copies below fill the memory system's queues
     constexpr int kQPer = (NREP * kHd + kFT - 1) / kFT;
     float q_reg[kQPer];

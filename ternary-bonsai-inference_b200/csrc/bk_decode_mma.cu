@@ -25,10 +25,9 @@
 //     merged into one byte so that a lookup yields one coordinate at two positions.  The
 //     softmax weights move from the accumulator layout to the B layout with two movmatrix
 //     transposes.  Six of the eight MMA columns are real heads (the GQA group);
-//   * keeps q in registers as B fragments.  Every warp prepares them by itself (a lane owns 64
-//     consecutive coordinates of one head, which is exactly what its fragments cover, so rope,
-//     Givens rotation, scaling and the f16 hi/lo split need no other lane), and after the
-//     dependency wait no warp waits for another one before the scan is over.
+//   * keeps q in registers as B fragments (prepared once by the whole CTA through shared memory):
+//     no shared-memory read of q in the scan, and from the start of the scan to its end no warp
+//     waits for another one.
 // Scores and the softmax stay in f32.  The codebook is scaled by a constant alpha before
 // rounding to f16 (chosen on the host so that all centroids round almost exactly); q is split
 // into f16 hi + lo parts when QSPLIT is set; V weights are p * ||v|| referenced to the running
@@ -244,17 +243,20 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     BK_STAMP(0);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     BK_STAMP(1);
+    // the counter set of the next launch: whatever the launch before the previous one left there goes now
+    if (blockIdx.x == 0 && a.counters_other)
+        for (int i = tid; i < a.other_n; i += blockDim.x) a.counters_other[i] = 0;
 
-    // ---- q first: its loads are in flight before the tile copies fill the memory system's queues.
-    // Lane (g, t) owns coordinates 64 t .. 64 t + 63 of head g: the B fragments of k-step
-    // ks = c*8 + w*2 + bp are its coordinates c*32 + w*8 + bp*4 + 0..3.
-    float qx[64];
+
+    // ---- q first: its loads are in flight before the tile copies fill the memory system's queues
+    constexpr int kQPer = (NREP * kHd + kMT - 1) / kMT;
+    float q_reg[kQPer];
     {
-        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP + min(g, NREP - 1)) * a.q_stride + 64 * t;
+        const float *q = a.q + ((size_t)meta.slot[s] * a.n_head + (size_t)kv * NREP) * a.q_stride;
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const float4 v = __ldg(reinterpret_cast<const float4 *>(q) + i);
-            qx[4 * i] = v.x; qx[4 * i + 1] = v.y; qx[4 * i + 2] = v.z; qx[4 * i + 3] = v.w;
+        for (int u = 0; u < kQPer; u++) {
+            const int i = tid + u * kMT;
+            q_reg[u] = i < NREP * kHd ? __ldg(q + (size_t)(i >> 8) * a.q_stride + (i & 255)) : 0.f;
         }
     }
     // ---- fill the ring: warp w starts with tiles w, w + 8, ... of the chunk
@@ -266,6 +268,85 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         if (in_stage[st] >= 0) issue_tile(lt, st);
     }
     int i_next = n_stages;  // fixed shares (dyn off): the warp's next tile is warp + 8 i_next
+    // ---- q: per-head RMSNorm (layer form), rope, Givens rotation, scale, split into f16 hi/lo, written in the
+    // MMA's B-fragment layout and then fetched by every lane into registers.  The scratch for this is the
+    // unused upper half of the table's 256-byte slots (the table itself fills only the lower halves):
+    // slot h, word x is at table + 256 h + 128 + 4 x.  sq[i] takes slots 0..47, the fragments slots 64..127.
+    uint32_t qh[16][2], ql[QSPLIT ? 16 : 1][2];
+    {
+        auto sq = [&](int i) -> float & { return *reinterpret_cast<float *>(lut_ptr + (i >> 5) * 256 + 128 + (i & 31) * 4); };
+        auto frag = [&](int lo_part, int j) -> uint2 & {  // j = k-step * 32 + lane
+            return *reinterpret_cast<uint2 *>(lut_ptr + (64 + 32 * lo_part + (j >> 4)) * 256 + 128 + (j & 15) * 8);
+        };
+#pragma unroll
+        for (int u = 0; u < kQPer; u++) {
+            const int i = tid + u * kMT;
+            if (i < NREP * kHd) sq(i) = q_reg[u];
+        }
+        __syncthreads();
+        if (a.q_norm_w) {  // per-head RMSNorm of q (src/forward.rs:242-243); q is not stored, so a tree sum will do
+            if (warp < NREP) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < kHd / 32; j++) {
+                    const float x = sq(warp * kHd + lane + 32 * j);
+                    ss = fmaf(x, x, ss);
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                if (lane == 0) o.M[warp] = 1.0f / sqrtf(ss / (float)kHd + a.eps);
+            }
+            __syncthreads();
+            for (int i = tid; i < NREP * kHd; i += kMT) sq(i) = sq(i) * o.M[i >> 8] * o.qw[i & 255];
+            __syncthreads();
+        }
+        if (!a.no_rope) {
+            const int half = a.n_rot >> 1;
+            for (int i = tid; i < NREP * half; i += kMT) {
+                const int r = i / half, j = i - r * half;
+                float x0 = sq(r * kHd + j), x1 = sq(r * kHd + j + half);
+                rope_pair(x0, x1, o.rope_row[j]);
+                sq(r * kHd + j) = x0;
+                sq(r * kHd + j + half) = x1;
+            }
+            __syncthreads();
+        }
+        // 1/sqrt(hd) * log2(e) / alpha: the scores come out in the exp2 domain, alpha undone.
+        // k-step ks = c*8 + w*2 + bp covers coordinates (2t+c)*32 + w*8 + bp*4 + 0..3 of head g.
+        const float qscale = rsqrtf((float)kHd) * 1.4426950408889634f / lut_alpha;
+        for (int i = tid; i < 16 * 32; i += kMT) {
+            const int ks = i >> 5, ln = i & 31, gg = ln >> 2, tt = ln & 3;
+            const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
+            const int d0 = (2 * tt + c) * 32 + w * 8 + bp * 4;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            if (gg < NREP) {
+                givens_fwd(sq(gg * kHd + d0), sq(gg * kHd + d0 + 1), o.givens[d0], o.givens[d0 + 1], x[0], x[1]);
+                givens_fwd(sq(gg * kHd + d0 + 2), sq(gg * kHd + d0 + 3), o.givens[d0 + 2], o.givens[d0 + 3], x[2], x[3]);
+            }
+            __half h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                x[e] *= qscale;
+                h[e] = __float2half_rn(x[e]);
+                l[e] = __float2half_rn(x[e] - __half2float(h[e]));
+            }
+            frag(0, i) = make_uint2(pack_h2(h[0], h[1]), pack_h2(h[2], h[3]));
+            frag(1, i) = make_uint2(pack_h2(l[0], l[1]), pack_h2(l[2], l[3]));
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < 16; ks++) {
+            const uint2 v = frag(0, ks * 32 + lane);
+            qh[ks][0] = v.x;
+            qh[ks][1] = v.y;
+            if constexpr (QSPLIT) {
+                const uint2 u = frag(1, ks * 32 + lane);
+                ql[ks][0] = u.x;
+                ql[ks][1] = u.y;
+            }
+        }
+    }
+    BK_STAMP(2);
     // ---- fused append: warps 0 and 1 of the CTA that scans the last chunk of this kv head store the
     // head's new K and V rows, exactly as the append kernel would (src/forward.rs:259-285; the rope
     // row of the new token is the q position's).  Only the chunk's last tile sees those rows; it is
@@ -320,68 +401,6 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             asm volatile("bar.sync 1, 64;\n" ::: "memory");      // the V row of warp 1 is stored too
             asm volatile("fence.proxy.async;\n" ::: "memory");
             inject = true;
-        }
-    }
-    BK_STAMP(2);
-
-    // ---- q: per-head RMSNorm (layer form), rope, Givens rotation, scale, f16 hi/lo, all inside the lane
-    uint32_t qh[16][2], ql[QSPLIT ? 16 : 1][2];
-    {
-        if (a.q_norm_w) {  // src/forward.rs:242-243; q is not stored, so a tree sum will do
-            float ss = 0.f;
-#pragma unroll
-            for (int j = 0; j < 64; j++) ss = fmaf(qx[j], qx[j], ss);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-            const float sc = 1.0f / sqrtf(ss / (float)kHd + a.eps);
-#pragma unroll
-            for (int j = 0; j < 64; j++) qx[j] = qx[j] * sc * o.qw[64 * t + j];
-        }
-        if (!a.no_rope) {
-            const int half = a.n_rot >> 1;
-            if (half == 32) {  // n_rot = 64: both coordinates of every pair belong to lane t = 0
-                if (t == 0) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) rope_pair(qx[j], qx[j + 32], o.rope_row[j]);
-                }
-            } else {  // half = 64 or 128 (checked on the host): the partner sits in lane t ^ (half / 64)
-                const int dt = half >> 6;
-#pragma unroll
-                for (int j = 0; j < 64; j++) {
-                    const float other = __shfl_xor_sync(0xffffffffu, qx[j], dt);
-                    const int d = 64 * t + j;
-                    if (d < half) {
-                        const float2 cs = o.rope_row[d];
-                        qx[j] = __fsub_rn(__fmul_rn(qx[j], cs.x), __fmul_rn(other, cs.y));
-                    } else if (d < 2 * half) {
-                        const float2 cs = o.rope_row[d - half];
-                        qx[j] = __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(qx[j], cs.x));
-                    }
-                }
-            }
-        }
-        // 1/sqrt(hd) * log2(e) / alpha: the scores come out in the exp2 domain, alpha undone.
-        const float qscale = (g < NREP) ? rsqrtf((float)kHd) * 1.4426950408889634f / lut_alpha : 0.f;
-#pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-            const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
-            const int j0 = c * 32 + w * 8 + bp * 4, d0 = 64 * t + j0;
-            float x[4];
-            givens_fwd(qx[j0], qx[j0 + 1], o.givens[d0], o.givens[d0 + 1], x[0], x[1]);
-            givens_fwd(qx[j0 + 2], qx[j0 + 3], o.givens[d0 + 2], o.givens[d0 + 3], x[2], x[3]);
-            __half h[4], l[4];
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                x[e] *= qscale;
-                h[e] = __float2half_rn(x[e]);
-                l[e] = __float2half_rn(x[e] - __half2float(h[e]));
-            }
-            qh[ks][0] = pack_h2(h[0], h[1]);
-            qh[ks][1] = pack_h2(h[2], h[3]);
-            if constexpr (QSPLIT) {
-                ql[ks][0] = pack_h2(l[0], l[1]);
-                ql[ks][1] = pack_h2(l[2], l[3]);
-            }
         }
     }
     BK_STAMP(3);
@@ -527,6 +546,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         for (int m = 0; m < 2; m++) {
             // coordinates 32 g .. 32 g + 31 of position rows 2t, 2t+1, 2t+8, 2t+9 of this row block, four words each
             const uint32_t v_blk = v_tile + (uint32_t)(16 * m * kRowBytes);
+            const uint32_t bm0 = m ? b0[1] : b0[0], bm1 = m ? b1[1] : b1[0];
             uint32_t x0[4], x1[4], x2[4], x3[4];
             if constexpr (BITS == 4) {  // chunk g of each row; rows r and r + 8 share the swizzle
                 const uint32_t vo0 = r0 * kRowBytes + (((uint32_t)g ^ (r0 & 7)) << 4), vo1 = r1 * kRowBytes + (((uint32_t)g ^ (r1 & 7)) << 4);
@@ -555,13 +575,13 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                 const uint32_t lo01 = (x0[w] & msk) | ((x1[w] & msk) << 4), hi01 = ((x0[w] >> 4) & msk) | (x1[w] & ~msk);
                 const uint32_t lo23 = (x2[w] & msk) | ((x3[w] & msk) << 4), hi23 = ((x2[w] >> 4) & msk) | (x3[w] & ~msk);
                 mma16816(acc[4 * w + 0], lut<0>(lo01, lane_base), lut<0>(hi01, lane_base), lut<0>(lo23, lane_base),
-                         lut<0>(hi23, lane_base), b0[m], b1[m]);
+                         lut<0>(hi23, lane_base), bm0, bm1);
                 mma16816(acc[4 * w + 1], lut<1>(lo01, lane_base), lut<1>(hi01, lane_base), lut<1>(lo23, lane_base),
-                         lut<1>(hi23, lane_base), b0[m], b1[m]);
+                         lut<1>(hi23, lane_base), bm0, bm1);
                 mma16816(acc[4 * w + 2], lut<2>(lo01, lane_base), lut<2>(hi01, lane_base), lut<2>(lo23, lane_base),
-                         lut<2>(hi23, lane_base), b0[m], b1[m]);
+                         lut<2>(hi23, lane_base), bm0, bm1);
                 mma16816(acc[4 * w + 3], lut<3>(lo01, lane_base), lut<3>(hi01, lane_base), lut<3>(lo23, lane_base),
-                         lut<3>(hi23, lane_base), b0[m], b1[m]);
+                         lut<3>(hi23, lane_base), bm0, bm1);
             }
         }
     };

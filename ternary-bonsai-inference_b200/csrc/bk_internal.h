@@ -22,10 +22,12 @@ constexpr int kPartStride = kHd + 2;   // floats per partial result handed to ca
 constexpr int kScratchStride = kHd + 4; // floats per partial in the split-K scratch (16-byte aligned rows)
 constexpr int kMmaMinPos = 2048;       // shorter sequences take the generic f32 decode kernel
 constexpr int kMaxWorld = 8;            // ranks a context-split mailbox can connect
-// The counters of the split-K scratch, per (sequence in the launch, kv head) pair i (i < 512):
-// [i] arrival tickets, [kCtrTile + i] tiles claimed from the pair's pool (tensor-core kernels),
-// [kCtrDone + i] CTAs that have finished the slice combine.  All read zero between launches.
-constexpr int kCtrTile = 512, kCtrDone = 1024, kCtrTotal = 1536;
+// The arrival counters of the split-K scratch, one per (sequence in the launch, kv head) pair i (i < 512),
+// in three sets of kCtrSet: set 0 for the generic kernel, whose last arriver puts its counter back to zero;
+// sets 1 and 2 for the tensor-core kernels, which alternate between them from launch to launch: a launch
+// counts in one set and clears what the launch before the previous one left in the other, so that no CTA
+// has to stay behind to reset anything.
+constexpr int kCtrSet = 512, kCtrTotal = 3 * kCtrSet;
 constexpr int kDescSlots = 8;          // launches of bk_append_batch that may be in flight
 constexpr int kDescCap = 4096;         // tokens one bk_append_batch call may carry
 
@@ -77,6 +79,8 @@ struct bk_ctx {
     // split-K scratch of the decode kernel: partial results and arrival counters
     float *d_partials = nullptr;
     unsigned *d_counters = nullptr;
+    int ctr_set = 0;               // which of the two tensor-core counter sets the next launch counts in
+    int ctr_dirty[2] = {0, 0};     // entries of each set that a launch has left non-zero
     int *d_err = nullptr;          // set by a kernel whose bounded wait ran out; read by bk_synchronize
     int n_sms = 148;
     std::vector<std::shared_ptr<bk::RopeTable>> ropes;
@@ -97,7 +101,7 @@ struct bk_cache {
     std::vector<int32_t> n_pos;               // [layer][seq]
     std::shared_ptr<bk::RopeTable> rope;
     size_t device_bytes = 0;
-    alignas(64) unsigned char tmap_k[128], tmap_v[128];  // CUtensorMap objects (4/3-bit planar: boxes of 32 positions; f16 K+V: 16)
+    alignas(64) unsigned char tmap_k[128], tmap_v[128];  // CUtensorMap objects (4/3-bit planar and f16 K+V caches): boxes of 16 positions
     bool has_tmaps = false;
 
     size_t slab(int layer, int seq) const { return (size_t)layer * cfg.n_seqs + seq; }
@@ -208,7 +212,11 @@ struct DecodeArgs {
     //         the scratch) instead of a fixed share, so that a CTA that starts late takes less
     //   dist  every CTA of the launch is resident at once (items <= SMs): the split-K combine is
     //         done in slices by all CTAs of a kv head instead of by the last one to arrive
+    //   counters_other / other_n  the counter set the next launch will count in, and how many of its
+    //         entries an earlier launch has left non-zero: CTA 0 clears them
     int dyn, dist;
+    unsigned *counters_other;
+    int other_n;
 };
 bk_status launch_decode(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m);
 
