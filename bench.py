@@ -13,7 +13,12 @@ far more than the 126 MB L2, so no separate L2 flush is needed.
 
 With N > 1 (torchrun, one rank per GPU) every rank decodes its own independent sequence of
 the same shape: sequences shard across GPUs with no collective on the data path (weak
-scaling); torch.distributed is used only for the barrier and the max over ranks.
+scaling); torch.distributed is used only for the barrier and the max over ranks.  After the
+headline pass the same process group also runs the two configurations that shard ONE job over
+the GPUs - 64 sequences split over the ranks, and one 262144-token sequence cut into context
+chunks whose partial results meet through peer memory - for a few steps each and reports them
+under `sharded` (with each one's own 1-GPU time measured on rank 0 in the same run, and a
+small split-context self-check against a whole cache).
 
 Prints one JSON line.  `value` is device-resident throughput (CUDA events on the library's
 stream, max over ranks), `e2e` the same step through the host-buffer entry point
@@ -39,6 +44,22 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 NH, NKV, HD = 24, 4, 256
 N_LAYERS = 16  # --layers overrides it for small profiling runs
 FALLBACK_HBM_GBS = 6650.0
+
+
+class Mode:
+    """BONSAI_KV mode string -> (kind, bits, v_quant), the reference's table (src/kvquant.rs:515-543).
+    Used by the reference arm, which must not load the CUDA library."""
+    def __init__(self, text):
+        t = text or ""
+        self.kind, self.bits, self.v_quant = "f32", 0, False
+        if t in ("f16", "fp16", "half"):
+            self.kind = "f16"
+            return
+        k_only = t.endswith("k")
+        body = t[:-1] if k_only else t
+        for prefix in ("planar", "iso"):
+            if body.startswith(prefix) and body[len(prefix):].isdigit() and 1 <= int(body[len(prefix):]) <= 8:
+                self.kind, self.bits, self.v_quant = "planar", int(body[len(prefix):]), not k_only
 
 
 def row_bytes(mode):
@@ -238,6 +259,202 @@ def workload_config(args, mode):
 # secondary workloads (the other sharded configurations; same JSON shape, no CPU arm)
 # ---------------------------------------------------------------------------------------------
 
+
+def build_batch64(bk, par, ctx, mode, rank, world, total_steps, mode_name):
+    """64 sequences, contexts U[2048,16384] (seeded), sharded greedily by length over the ranks."""
+    rng = np.random.default_rng(99)          # same plan and data on every rank
+    channels = rng.choice(HD, size=3, replace=False)
+    n_seqs = 64
+    lens = rng.integers(2048, 16385, n_seqs)
+    mine = par.shard_sequences(lens, world)[rank]
+    n_local = len(mine)
+    n_ctx = int(lens.max()) + total_steps
+    cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=max(n_local, 1), n_ctx=n_ctx)
+    k, v = synth_chunk(rng, 16384, channels)
+    dk, dv = ctx.to_device(k), ctx.to_device(v)
+    for j, i in enumerate(mine):
+        for il in range(N_LAYERS):
+            cache.append_device(il, dk.ptr, dv.ptr, n_tokens=int(lens[i]), seq=j)
+    ctx.synchronize()
+    d_q = ctx.to_device(rng.standard_normal((N_LAYERS, max(n_local, 1), NH, HD), dtype=np.float32))
+    d_out = ctx.alloc(max(n_local, 1) * NH * HD * 4)
+
+    def step(_s):
+        for il in range(N_LAYERS):
+            if n_local:
+                cache.step_batch_device(il, d_q.offset(il * n_local * NH * HD * 4), dk.ptr, dv.ptr, d_out.ptr, n_local)
+
+    def cleanup():
+        cache.close()
+        for b in (dk, dv, d_q, d_out):
+            b.free()
+    step_bytes = N_LAYERS * sum(attn_bytes(mode, int(lens[i])) + append_bytes(mode) for i in range(n_seqs))
+    cfg = {"workload": f"batch64: {n_seqs} sequences, contexts U[2048,16384] (seeded, mean {lens.mean():.0f}), "
+                       f"{N_LAYERS} layers, {mode_name}; sequences sharded greedily over {world} GPU(s), no collective",
+           "l2": "%.2f GB of cache per step, larger than L2" % (step_bytes / 1e9)}
+    return step, step_bytes, n_seqs, "strong", cfg, cleanup
+
+
+def build_splitctx(bk, par, ctx, mode, rank, world, local, dist, total_steps, mode_name, exchange):
+    """One 262144-token sequence, contiguous context chunks per rank, the partial results exchanged per layer."""
+    import torch
+    rng = np.random.default_rng(99)
+    channels = rng.choice(HD, size=3, replace=False)
+    n_total = 262144
+    chunks = par.split_context(n_total - total_steps, world)
+    b, e = chunks[rank]
+    owner = par.tail_owner(chunks)
+    cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=(e - b) + total_steps, rope_positions=n_total)
+    k, v = synth_chunk(rng, 8192, channels)
+    dk, dv = ctx.to_device(k), ctx.to_device(v)
+    for il in range(N_LAYERS):
+        p = b
+        while p < e:
+            n = min(8192, e - p)
+            cache.append_device(il, dk.ptr, dv.ptr, n_tokens=n, pos=p)
+            p += n
+    ctx.synchronize()
+    d_q = ctx.to_device(rng.standard_normal((N_LAYERS, NH, HD), dtype=np.float32))
+    dev = torch.device("cuda", local)
+    part = torch.zeros((NH, HD + 2), dtype=torch.float32, device=dev)
+    out = torch.zeros((NH, HD), dtype=torch.float32, device=dev)
+    gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
+    pos_now = [n_total - total_steps]
+    lib_stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+    split = par.ContextSplit(cache, dist, rank, world) if (world > 1 and exchange == "p2p") else None
+
+    def step(_s):
+        for il in range(N_LAYERS):
+            if split is not None:  # one launch per rank and layer: append (tail owner), scan, exchange, merge
+                own = rank == owner
+                split.step_device(il, d_q.offset(il * NH * HD * 4), dk.ptr if own else None, dv.ptr if own else None,
+                                  out.data_ptr(), q_pos=pos_now[0])
+                continue
+            if world == 1:
+                cache.step_device(il, d_q.offset(il * NH * HD * 4), dk.ptr, dv.ptr, out.data_ptr(), pos_now[0])
+                continue
+            if rank == owner:
+                cache.append_device(il, dk.ptr, dv.ptr, n_tokens=1, pos=pos_now[0])
+            cache.decode_device(il, d_q.offset(il * NH * HD * 4), part.data_ptr(), q_pos=[pos_now[0]], partial=True)
+            with torch.cuda.stream(lib_stream):     # NCCL orders itself against the library's stream:
+                dist.all_gather_into_tensor(gathered.view(-1), part.view(-1))   # no host sync per layer
+            ctx.check(ctx.lib.bk_lse_merge(ctx.h, world, NH, HD, gathered.data_ptr(), out.data_ptr()))
+        pos_now[0] += 1
+
+    def cleanup():
+        if split is not None:
+            split.close()
+        cache.close()
+        for bf in (dk, dv, d_q):
+            bf.free()
+    step_bytes = N_LAYERS * (attn_bytes(mode, n_total) + append_bytes(mode))
+    cfg = {"workload": f"splitctx: 1 sequence, context {n_total}, {N_LAYERS} layers, {mode_name}; contiguous context "
+                       f"chunks over {world} GPU(s); per layer the (acc, m, l) partials are exchanged "
+                       + ("through peer memory inside the decode launch (bk_attn_step_split)" if split is not None
+                          else ("by one NCCL all-gather, then bk_lse_merge" if world > 1 else "- one GPU, nothing to exchange")),
+           "l2": "%.2f GB of cache per step over all GPUs" % (step_bytes / 1e9)}
+    return step, step_bytes, 1, "strong", cfg, cleanup
+
+
+def timed_steps(ctx, dist, local, step, steps, warmup):
+    """Device time of `steps` steps after `warmup`: CUDA events on the library's stream, barriers on both
+    sides, max over the ranks.  Returns ms per step."""
+    for s_ in range(warmup):
+        step(s_)
+    ctx.synchronize()
+    barrier(dist)
+    ev0, ev1 = ctx.event(), ctx.event()
+    ev0.record()
+    for s_ in range(steps):
+        step(s_)
+    ev1.record()
+    ctx.synchronize()
+    barrier(dist)
+    return max_over_ranks(dist, local, ev0.elapsed_ms(ev1)) / steps
+
+
+def splitctx_self_check(bk, par, ctx, dist, rank, world):
+    """The split-context step against a whole cache, on a small side case (6003 rows, one layer, two steps):
+    every rank's merged output is compared with rank 0's whole-cache output; returns the worst |difference|
+    over the ranks (on every rank)."""
+    rng = np.random.default_rng(3)       # same stream on every rank
+    n0, steps = 6003, 2
+    n_total = n0 + steps
+    k = rng.standard_normal((n_total, NKV, HD), dtype=np.float32)
+    v = rng.standard_normal((n_total, NKV, HD), dtype=np.float32)
+    k[:, :, [9, 100, 222]] *= np.float32(20.0)
+    v[:, :, [9, 100, 222]] *= np.float32(20.0)
+    q = rng.standard_normal((steps, NH, HD), dtype=np.float32)
+    chunks = par.split_context(n0, world)
+    b, e = chunks[rank]
+    owner = par.tail_owner(chunks)
+    mode = bk.parse_mode("planar4")
+    mine = bk.AttnCache(ctx, mode, n_layers=1, n_ctx=max(e - b, 0) + steps, rope_positions=n_total)
+    whole = bk.AttnCache(ctx, mode, n_layers=1, n_ctx=n_total) if rank == 0 else None
+    if e > b:
+        mine.append(0, k[b:e], v[b:e], pos=b)
+    if whole:
+        whole.append(0, k[:n0], v[:n0])
+    split = par.ContextSplit(mine, dist, rank, world)
+    d_out = ctx.alloc(NH * HD * 4)
+    worst = 0.0
+    for s in range(steps):
+        pos = n0 + s
+        d_q, d_k, d_v = ctx.to_device(q[s]), ctx.to_device(k[pos]), ctx.to_device(v[pos])
+        own = rank == owner
+        split.step_device(0, d_q.ptr, d_k.ptr if own else None, d_v.ptr if own else None, d_out.ptr, q_pos=pos)
+        got = d_out.download((NH, HD), np.float32)
+        want = whole.step(0, q[s], k[pos], v[pos], pos) if whole else None
+        box = [want]
+        dist.broadcast_object_list(box, src=0)
+        err = float(np.max(np.abs(got - box[0])))
+        errs = [None] * world
+        dist.all_gather_object(errs, err)
+        worst = max(worst, max(errs))
+        for bf in (d_q, d_k, d_v):
+            bf.free()
+    split.close()
+    mine.close()
+    if whole:
+        whole.close()
+    return worst
+
+
+def run_sharded(bk, ctx, mode, mode_name, rank, world, local, dist, steps=5, warmup=3):
+    """The two configurations that shard one job over the ranks, each with its own 1-GPU time (rank 0 alone,
+    same run) so that the speed-up needs no second record.  Returns the `sharded` object of the JSON line."""
+    par = importlib.import_module("ternary-bonsai-inference_b200.parallel")
+    total = steps + warmup
+    out = {}
+    for name in ("batch64", "splitctx"):
+        def build(r, w, d):
+            if name == "batch64":
+                return build_batch64(bk, par, ctx, mode, r, w, total, mode_name)
+            return build_splitctx(bk, par, ctx, mode, r, w, local, d, total, mode_name, "p2p")
+        n1 = None
+        if rank == 0:   # this workload on one GPU: rank 0 alone, the others wait at the barrier below
+            step, step_bytes, tokens, _sc, _cfg, cleanup = build(0, 1, None)
+            ms1 = timed_steps(ctx, None, local, step, steps, warmup)
+            cleanup()
+            n1 = {"tokens_per_s": tokens * 1e3 / ms1, "ms_per_step": ms1, "effective_gbs": step_bytes / ms1 / 1e6}
+        entry = {"n1": n1}
+        if world > 1:
+            barrier(dist)
+            step, step_bytes, tokens, scaling, cfg, cleanup = build(rank, world, dist)
+            ms = timed_steps(ctx, dist, local, step, steps, warmup)
+            cleanup()
+            entry.update({"tokens_per_s": tokens * 1e3 / ms, "ms_per_step": ms, "effective_gbs": step_bytes / ms / 1e6,
+                          "scaling": scaling, "workload": cfg["workload"], "steps": steps, "warmup": warmup})
+            if n1:
+                entry["speedup_vs_own_n1"] = n1["ms_per_step"] / ms
+                entry["efficiency_vs_own_n1"] = n1["ms_per_step"] / ms / world
+            if name == "splitctx":
+                entry["exchange"] = "p2p"
+                entry["check_max_abs"] = splitctx_self_check(bk, par, ctx, dist, rank, world)
+        out[name] = entry
+    return out
+
+
 def run_other_workload(args):
     bk = importlib.import_module("ternary-bonsai-inference_b200")
     par = importlib.import_module("ternary-bonsai-inference_b200.parallel")
@@ -253,30 +470,7 @@ def run_other_workload(args):
             "dtype": "f32", "data": "synthetic"}
 
     if args.workload == "batch64":
-        n_seqs = 64
-        lens = rng.integers(2048, 16385, n_seqs)
-        mine = par.shard_sequences(lens, world)[rank]
-        n_local = len(mine)
-        n_ctx = int(lens.max()) + total_steps
-        cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=max(n_local, 1), n_ctx=n_ctx)
-        k, v = synth_chunk(rng, 16384, channels)
-        dk, dv = ctx.to_device(k), ctx.to_device(v)
-        for j, i in enumerate(mine):
-            for il in range(N_LAYERS):
-                cache.append_device(il, dk.ptr, dv.ptr, n_tokens=int(lens[i]), seq=j)
-        ctx.synchronize()
-        d_q = ctx.to_device(rng.standard_normal((N_LAYERS, max(n_local, 1), NH, HD), dtype=np.float32))
-        d_out = ctx.alloc(max(n_local, 1) * NH * HD * 4)
-
-        def step(_s):
-            for il in range(N_LAYERS):
-                if n_local:
-                    cache.step_batch_device(il, d_q.offset(il * n_local * NH * HD * 4), dk.ptr, dv.ptr, d_out.ptr, n_local)
-        step_bytes = N_LAYERS * sum(attn_bytes(mode, int(lens[i])) + append_bytes(mode) for i in range(n_seqs))
-        tokens_per_step, scaling = n_seqs, "strong"
-        cfg = {"workload": f"batch64: {n_seqs} sequences, contexts U[2048,16384] (seeded, mean {lens.mean():.0f}), "
-                           f"{N_LAYERS} layers, {args.mode}; sequences sharded greedily over {world} GPU(s), no collective",
-               "l2": "%.2f GB of cache per step, larger than L2" % (step_bytes / 1e9)}
+        step, step_bytes, tokens_per_step, scaling, cfg, _cleanup = build_batch64(bk, par, ctx, mode, rank, world, total_steps, args.mode)
     elif args.workload == "prefill":
         # one prompt of `--ctx` tokens (default here 8192) through all layers in blocks of 512 tokens:
         # per block and layer one bulk append and one batched causal attention (bk_prefill_step)
@@ -305,56 +499,8 @@ def run_other_workload(args):
                            f"per block and layer a bulk append and a batched causal attention over the quantized cache",
                "useful_tflop_per_step": flops / 1e12}
     elif args.workload == "splitctx":
-        import torch
-        n_total = 262144
-        chunks = par.split_context(n_total - total_steps, world)
-        b, e = chunks[rank]
-        owner = par.tail_owner(chunks)
-        cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=(e - b) + total_steps, rope_positions=n_total)
-        k, v = synth_chunk(rng, 8192, channels)
-        dk, dv = ctx.to_device(k), ctx.to_device(v)
-        for il in range(N_LAYERS):
-            p = b
-            while p < e:
-                n = min(8192, e - p)
-                cache.append_device(il, dk.ptr, dv.ptr, n_tokens=n, pos=p)
-                p += n
-        ctx.synchronize()
-        d_q = ctx.to_device(rng.standard_normal((N_LAYERS, NH, HD), dtype=np.float32))
-        dev = torch.device("cuda", local)
-        part = torch.zeros((NH, HD + 2), dtype=torch.float32, device=dev)
-        out = torch.zeros((NH, HD), dtype=torch.float32, device=dev)
-        gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
-        pos_now = [n_total - total_steps]
-        lib_stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
-        split = par.ContextSplit(cache, dist, rank, world) if (world > 1 and args.exchange == "p2p") else None
-
-        def step(_s):
-            for il in range(N_LAYERS):
-                if split is not None:  # one launch per rank and layer: append (tail owner), scan, exchange, merge
-                    own = rank == owner
-                    split.step_device(il, d_q.offset(il * NH * HD * 4), dk.ptr if own else None, dv.ptr if own else None,
-                                      out.data_ptr(), q_pos=pos_now[0])
-                    continue
-                if rank == owner:
-                    cache.append_device(il, dk.ptr, dv.ptr, n_tokens=1, pos=pos_now[0])
-                if world == 1:
-                    cache.decode_device(il, d_q.offset(il * NH * HD * 4), out.data_ptr(), q_pos=[pos_now[0]])
-                elif split is not None:
-                    split.attend_device(il, d_q.offset(il * NH * HD * 4), out.data_ptr(), q_pos=pos_now[0])
-                else:
-                    cache.decode_device(il, d_q.offset(il * NH * HD * 4), part.data_ptr(), q_pos=[pos_now[0]], partial=True)
-                    with torch.cuda.stream(lib_stream):     # NCCL orders itself against the library's stream:
-                        dist.all_gather_into_tensor(gathered.view(-1), part.view(-1))   # no host sync per layer
-                    ctx.check(ctx.lib.bk_lse_merge(ctx.h, world, NH, HD, gathered.data_ptr(), out.data_ptr()))
-            pos_now[0] += 1
-        step_bytes = N_LAYERS * (attn_bytes(mode, n_total) + append_bytes(mode))
-        tokens_per_step, scaling = 1, "strong"
-        cfg = {"workload": f"splitctx: 1 sequence, context {n_total}, {N_LAYERS} layers, {args.mode}; contiguous context "
-                           f"chunks over {world} GPU(s); per layer the (acc, m, l) partials are exchanged "
-                           + ("through peer memory inside the merge kernel (bk_decode_attn_split)" if split is not None
-                              else "by one NCCL all-gather, then bk_lse_merge"),
-               "l2": "%.2f GB of cache per step over all GPUs" % (step_bytes / 1e9)}
+        step, step_bytes, tokens_per_step, scaling, cfg, _cleanup = build_splitctx(bk, par, ctx, mode, rank, world, local, dist,
+                                                                                   total_steps, args.mode, args.exchange)
     elif args.workload == "pq2":
         # The four PQ2_0 projections of a full-attention layer, one token: wq [12288 x 5120] (q | gate),
         # wk and wv [1024 x 5120], wo [5120 x 6144]; 16 layers with their own weights (446 MB, larger than L2).
@@ -477,9 +623,10 @@ def run_other_workload(args):
         if args.workload == "pq2":
             line["roofline"]["note"] = ("pq2_matvec_kernel, every launch of the step: payload bytes (the algorithmic "
                                         "bytes: each weight byte once) over the step's device time")
-            # dram__bytes_read.sum + dram__bytes_write.sum of one layer's two launches (19.55 + 8.41 MB, writes 0),
-            # profiles/pq2_matvec_attn_projections_ncu.md, times the layers of a step
+            # not measured by this run: dram__bytes_read.sum + dram__bytes_write.sum of one layer's two launches
+            # (19.55 + 8.41 MB, writes 0) from an ncu capture, times the layers of a step
             line["roofline"]["traffic"] = N_LAYERS * 27.96e6   # per GPU, like `achieved`
+            line["roofline"]["traffic_source"] = "ncu capture of one layer (copied constant)"
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -506,6 +653,8 @@ def main():
     ap.add_argument("--mode", default="planar4")
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sharded", dest="sharded", action="store_false",
+                    help="skip the batch64 / splitctx passes that follow the headline pass")
     ap.add_argument("--chunk", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=16, help="full-attention layers (16 = qwen35; fewer only to keep a profiler capture small)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
@@ -525,8 +674,7 @@ def main():
         return run_other_workload(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
-    bk = importlib.import_module("ternary-bonsai-inference_b200")
-    mode = bk.parse_mode(args.mode)
+    mode = Mode(args.mode)                # (the reference arm runs without the CUDA library)
     total_steps = args.steps + args.warmup
     n0 = args.ctx - total_steps           # the context reaches args.ctx at the last step
     assert n0 > 0
@@ -546,6 +694,8 @@ def main():
         run_reference(args, mode, make_chunks)
         return
 
+    bk = importlib.import_module("ternary-bonsai-inference_b200")
+    mode = bk.parse_mode(args.mode)
     rank, world, local, dist = dist_setup(args.gpus)
     ctx = bk.Context(local)
     cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=args.ctx)
@@ -620,10 +770,12 @@ def main():
         device_step(s, evs[i])
     ctx.synchronize()
     dec_ms = [a.elapsed_ms(b) for step in evs for (a, b) in step]
-    dec_ms_avg = float(np.mean(dec_ms))
+    dec_ms_isolated = float(np.mean(dec_ms))       # each launch between its own pair of events (no overlap with its neighbours)
     clocks = sampler.stop() if rank == 0 else None
     peak, peak_kind = measured_peak()
     alg = attn_bytes(mode, args.ctx - args.steps // 2)
+    # the kernel's average launch duration over the timed region: the step is nothing but these launches
+    dec_ms_avg = ms_total / max(launches, 1)
     achieved = alg / (dec_ms_avg * 1e-3) / 1e9
 
     # ---- e2e: the same steps through the host-buffer entry point ---------------------------------
@@ -655,6 +807,12 @@ def main():
     e2e_tok_s = world * args.steps / e2e_s
     checksum = float(np.abs(hout.array).sum())
 
+    # ---- the configurations that shard one job over the GPUs (16 layers, planar cache) --------------
+    sharded = None
+    if args.sharded and mode.kind == "planar" and N_LAYERS == 16:
+        cache.close()
+        sharded = run_sharded(bk, ctx, mode, args.mode, rank, world, local, dist)
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -677,10 +835,20 @@ def main():
         else:
             ts = [cpu_layer_step(ref, q_all[s, 0], k_new[s], v_new[s], n0 + s, threads) for s in range(3)]
         t_layer = float(np.mean(ts[1:]))
+        # the reference's own loop is single-threaded (src/forward.rs:297): one thread over a 1/8 slice of the
+        # context (attention is linear in it), scaled back
+        n_slice = max(n0 // 8, 1)
+        t0 = time.perf_counter()
+        ref.attend(0, q_all[0, 0][:, :HD] if layer_form else q_all[0, 0], n_slice - 1, n_slice, threads=1)
+        t_one = (time.perf_counter() - t0) * (n0 / n_slice)
         cpu = {"value": 1.0 / (t_layer * N_LAYERS), "unit": "tokens/s", "cores": min(threads, NH), "kind": "port",
                "sample": f"1 of {N_LAYERS} layers at context {n0} (append + attention, 2 timed steps after 1 warm-up), "
                          f"time x{N_LAYERS}; q-heads spread over {min(threads, NH)} host threads",
-               "ms_per_layer": t_layer * 1e3}
+               "ms_per_layer": t_layer * 1e3,
+               "single_thread": {"value": 1.0 / (t_one * N_LAYERS), "unit": "tokens/s", "cores": 1,
+                                 "ms_per_layer": t_one * 1e3,
+                                 "sample": f"attention of 1 layer over the first {n_slice} of {n0} positions on one thread, "
+                                           f"time x{n0 / n_slice:.0f} x{N_LAYERS}"}}
 
     tok_s = world * 1e3 / ms_step
     step_bytes = N_LAYERS * (attn_bytes(mode, args.ctx - args.steps // 2) + append_bytes(mode))
@@ -688,7 +856,9 @@ def main():
         "metric": "quantized-KV decode attention tokens/s at 128K ctx",
         "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": workload_config(args, mode),
+        "dtype": ("f16 tensor-core operands (centroid table and q as f16, q and V weights hi+lo), f32 accumulate and softmax"
+                  if mode.kind != "f32" and args.ctx >= 2048 else "f32"),
+        "data": "synthetic", "config": workload_config(args, mode),
         "effective_gbs": world * step_bytes / (ms_step * 1e-3) / 1e9,
         "gpu_launches": launches,
         "e2e": {"value": e2e_tok_s, "unit": "tokens/s",
@@ -700,13 +870,17 @@ def main():
         "roofline": {"bound": "hbm", "kernel": decode_kernel_name(args.mode, args.ctx),
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}",
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this
-                     # workload, from the ncu captures summarised in profiles/decode_p4_mma_ctx131072_ncu.md
-                     # and profiles/decode_f16_mma_ctx32768_ncu.md (mean of the two captured launches)
-                     "traffic": {("planar4", 131072): 143.4e6, ("f16", 32768): 138.3e6}.get((args.mode, args.ctx)),
+                     # not measured by this run: dram__bytes_read.sum + dram__bytes_write.sum of one launch of this
+                     # kernel at this workload, copied from an ncu capture (mean of the captured launches)
+                     "traffic": {("planar4", 131072): 142.5e6, ("f16", 32768): 138.3e6}.get((args.mode, args.ctx)),
+                     "traffic_source": "ncu capture of one layer of this workload (copied constant, see the profile summaries)",
                      "algorithmic_bytes_per_launch": alg, "avg_launch_ms": dec_ms_avg,
+                     "avg_launch_ms_source": "timed region / launches (the step consists of these launches only, "
+                                             "overlapped by programmatic dependent launch)",
+                     "isolated_launch_ms": dec_ms_isolated,
+                     "frac_isolated": alg / (dec_ms_isolated * 1e-3) / 1e9 / peak,
                      "frac_of_8TBs_nominal": achieved / 8000.0},
-        "cpu_baseline": cpu, "clocks": clocks,
+        "cpu_baseline": cpu, "clocks": clocks, "sharded": sharded,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:

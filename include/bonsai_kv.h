@@ -197,15 +197,18 @@ BK_API bk_status bk_decode_attn_partial(bk_cache *cache, int32_t layer, int32_t 
                                         const int32_t *seq_ids, const int32_t *n_pos,
                                         const int32_t *q_pos, const float *q_dev,
                                         float *part_dev);
-/* No counterpart in the reference.  Same result as bk_decode_attn for callers that must not
- * allocate once they are running (a serving loop that gave all of HBM to the caches at start-up
- * and forbids later cudaMalloc because it synchronises the device and can fail on a fragmented
- * heap; a thread or callback in which the CUDA allocator must not be entered).  The split-K
- * scratch is a fixed array inside the library (about 4.3 MB per GPU, held until the process
- * exits) instead of allocated memory, and the call uses no allocator of any kind.  Limits: at
- * most 64 sequences and 512 (sequence, kv head, chunk) work items per call, else
- * BK_ERR_INVALID.  Every call on a device shares the array: calls that overlap on the GPU race,
- * so serialise them.  The first call on a device resolves the array's address; make it during
+/* No counterpart in the reference.  bk_decode_attn for callers that must not allocate once they
+ * are running (a serving loop that gave all of HBM to the caches at start-up and forbids later
+ * cudaMalloc because it synchronises the device and can fail on a fragmented heap; a thread or
+ * callback in which the CUDA allocator must not be entered).  The split-K scratch is a fixed
+ * array inside the library (about 4.3 MB per GPU, held until the process exits) instead of
+ * allocated memory, and a call that succeeds touches no allocator of any kind (a call that
+ * fails builds its error text on the host heap).  Limits: at most 64 sequences per call, else
+ * BK_ERR_INVALID; the scratch holds 512 (sequence, kv head, chunk) work items, and a request
+ * that would need more is cut into coarser chunks instead of being rejected, so the result
+ * equals bk_decode_attn's within the parity tolerance (1e-3), not bit for bit.  Every call on
+ * a device shares the array: calls that overlap on the GPU race, so serialise them.  The first
+ * call on a device resolves the array's address (thread-safe, once per device); make it during
  * set-up, outside any stream capture. */
 BK_API bk_status bk_decode_attn_noalloc(bk_cache *cache, int32_t layer, int32_t n_seqs,
                                         const int32_t *seq_ids, const int32_t *n_pos,

@@ -20,18 +20,23 @@ namespace bk {
 // codebook: the centroids are only 2^bits distinct values, so a good alpha makes all of them
 // round almost exactly and the tensor-core path loses nothing to the f16 table.
 static float best_lut_alpha(const float *book, int n) {
-    float best_a = 1.0f, best_e = 1e30f;
+    // What reaches the output is the ABSOLUTE error of a centroid (times a row norm), and with a softmax
+    // peaked on a few rows nothing averages it out: minimise the largest absolute error, the largest
+    // relative one breaking ties.  (4 bit: 5.7e-6 on centroids up to 0.17; 3 bit: 7e-7.)
+    float best_a = 1.0f, best_abs = 1e30f, best_rel = 1e30f;
     for (int i = 0; i < 65536; i++) {  // (one binade covers every alignment of the f16 grid)
         const float al = 1.0f + (float)i / 65536.0f;
-        float worst = 0.f;
+        float worst_abs = 0.f, worst_rel = 0.f;
         for (int k = 0; k < n; k++) {
             const float c = book[k];
             if (c == 0.f) continue;
             const float r = __half2float(__float2half_rn(c * al)) / al;
-            worst = std::max(worst, fabsf(r - c) / fabsf(c));
+            worst_abs = std::max(worst_abs, fabsf(r - c));
+            worst_rel = std::max(worst_rel, fabsf(r - c) / fabsf(c));
         }
-        if (worst < best_e) {
-            best_e = worst;
+        if (worst_abs < best_abs || (worst_abs == best_abs && worst_rel < best_rel)) {
+            best_abs = worst_abs;
+            best_rel = worst_rel;
             best_a = al;
         }
     }
@@ -216,8 +221,16 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
     const size_t cnt_bytes = (size_t)kCtrTotal * sizeof(unsigned);
     if ((e = cudaMalloc(&ctx->d_counters, cnt_bytes)) != cudaSuccess) return bail(e, "cudaMalloc counters");
     if ((e = cudaMemset(ctx->d_counters, 0, cnt_bytes)) != cudaSuccess) return bail(e, "clear counters");
-    if ((e = cudaMalloc(&ctx->d_err, sizeof(int))) != cudaSuccess) return bail(e, "cudaMalloc error flag");
-    if ((e = cudaMemset(ctx->d_err, 0, sizeof(int))) != cudaSuccess) return bail(e, "clear error flag");
+    {
+        void *herr = nullptr, *derr = nullptr;
+        if ((e = cudaHostAlloc(&herr, sizeof(int), cudaHostAllocMapped)) != cudaSuccess) return bail(e, "cudaHostAlloc error word");
+        ctx->h_err = static_cast<volatile int *>(herr);
+        *ctx->h_err = 0;
+        if ((e = cudaHostGetDevicePointer(&derr, herr, 0)) != cudaSuccess) return bail(e, "cudaHostGetDevicePointer error word");
+        ctx->d_err = static_cast<int *>(derr);
+        const char *e7 = getenv("BONSAI_KV_XCH_POLLS");
+        if (e7 && atoi(e7) > 0) ctx->xch_polls = atoi(e7);
+    }
     *out = ctx;
     return BK_OK;
 }
@@ -231,7 +244,7 @@ void bk_ctx_destroy(bk_ctx *ctx) {
     if (ctx->d_codebooks) cudaFree(ctx->d_codebooks);
     if (ctx->d_partials) cudaFree(ctx->d_partials);
     if (ctx->d_counters) cudaFree(ctx->d_counters);
-    if (ctx->d_err) cudaFree(ctx->d_err);
+    if (ctx->h_err) cudaFreeHost(const_cast<int *>(ctx->h_err));
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->d_stage) cudaFree(ctx->d_stage);
     if (ctx->d_layer) cudaFree(ctx->d_layer);
@@ -246,16 +259,32 @@ void bk_ctx_destroy(bk_ctx *ctx) {
 
 const char *bk_last_error(const bk_ctx *ctx) { return ctx ? ctx->err.c_str() : g_err.c_str(); }
 
-bk_status bk_synchronize(bk_ctx *ctx) {
-    if (!ctx) return fail(nullptr, BK_ERR_INVALID, "bk_synchronize: ctx is null");
+}  // extern "C"
+
+namespace bk {
+bk_status sync_and_check(bk_ctx *ctx) {
     BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    int flag = 0;
-    BK_CUDA(ctx, cudaMemcpy(&flag, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost));
+    const int flag = ctx->h_err ? *ctx->h_err : 0;
     if (flag) {
-        cudaMemset(ctx->d_err, 0, sizeof(int));
-        return fail(ctx, BK_ERR_CUDA, "a decode kernel gave up waiting for its shared-memory copies; results are invalid");
+        *ctx->h_err = 0;
+        // a kernel that gave up may have left arrival counters behind: start the next launch from zero
+        cudaMemsetAsync(ctx->d_counters, 0, sizeof(unsigned) * kCtrTotal, ctx->stream);
+        ctx->ctr_dirty[0] = ctx->ctr_dirty[1] = 0;
+        static const char *const what[] = {"", "a tile copy did not arrive", "no room for the tile ring", "the context-split exchange (a peer never sent its rows) or a split-K copy did not arrive",
+                                           "a tensor-memory operation of the prefill kernel did not complete", "a weight tile of the PQ2_0 matvec did not arrive",
+                                           "the CTAs of a kv head did not all arrive for the split-K combine"};
+        return fail(ctx, BK_ERR_CUDA, std::string("a kernel gave up a bounded wait (code ") + std::to_string(flag) + ": " +
+                                          (flag > 0 && flag < 7 ? what[flag] : "unknown") + "); results of the calls since the last check are invalid");
     }
     return BK_OK;
+}
+}  // namespace bk
+
+extern "C" {
+
+bk_status bk_synchronize(bk_ctx *ctx) {
+    if (!ctx) return fail(nullptr, BK_ERR_INVALID, "bk_synchronize: ctx is null");
+    return sync_and_check(ctx);
 }
 
 void *bk_ctx_stream(bk_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
@@ -471,7 +500,10 @@ static bk_status cache_copy(bk_cache *c, int layer, int seq, int pos0, int n_pos
     if (v_rows) BK_CUDA(ctx, cp(v_rows, c->v_rows(layer, seq) + r0 * c->v_row_bytes, nr * c->v_row_bytes));
     if (k_norms && c->d_kn) BK_CUDA(ctx, cp(k_norms, c->k_norms(layer, seq) + r0, nr * 4));
     if (v_norms && c->d_vn) BK_CUDA(ctx, cp(v_norms, c->v_norms(layer, seq) + r0, nr * 4));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     return BK_OK;
 }
 
@@ -553,7 +585,10 @@ bk_status bk_append_host(bk_cache *c, int32_t layer, int32_t seq, int32_t rope_p
     st = bk_append(c, layer, seq, rope_pos, n_tokens, (const float *)ctx->d_stage,
                    (const float *)((char *)ctx->d_stage + per));
     if (st != BK_OK) return st;
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     return BK_OK;
 }
 
@@ -646,6 +681,7 @@ void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out
     a.xch_world = a.xch_rank = 0;
     a.xch_seqno = 0;
     a.xch_err = ctx->d_err;
+    a.xch_spin = ctx->xch_polls;
     a.dyn = a.dist = 0;
     a.counters_other = nullptr;
     a.other_n = 0;
@@ -888,7 +924,10 @@ bk_status bk_attn_step_host(bk_cache *c, int32_t layer, int32_t seq, int32_t pos
     float *h_out = (float *)(h + qb + 2 * kb);
     st = bk_attn_step(c, layer, seq, pos, (const float *)d, (const float *)(d + qb), (const float *)(d + qb + kb), h_out);
     if (st != BK_OK) return st;
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out_host, h_out, qb);
     return BK_OK;
 }
@@ -1072,7 +1111,10 @@ bk_status bk_attn_layer_step_host(bk_cache *c, int32_t layer, int32_t seq, int32
     st = bk_attn_layer_step(c, layer, seq, pos, (const float *)d, (const float *)(d + qfb), (const float *)(d + qfb + kb),
                             (const float *)(d + qfb + 2 * kb), (const float *)(d + qfb + 2 * kb + wb), eps, h_out);
     if (st != BK_OK) return st;
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out_host, h_out, ob);
     return BK_OK;
 }
@@ -1096,7 +1138,10 @@ bk_status bk_rms_norm_rows(bk_ctx *ctx, int32_t n_rows, int32_t row_len, const f
     const NormSeg s1{nullptr, 0, nullptr, nullptr, 0};
     if ((st = launch_rms_norm_rows(ctx, s0, s1, row_len, eps)) != BK_OK) return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + xb + wb, d + xb + wb, xb, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out_host, h + xb + wb, xb);
     return BK_OK;
 }
@@ -1185,7 +1230,10 @@ bk_status bk_pq2_matvec_host(bk_ctx *ctx, const void *payload_dev, size_t payloa
     // y is written straight into the pinned staging buffer by the kernel
     if ((st = pq2_run(ctx, (const uint8_t *)payload_dev, ne0, base_row, n_rows, (const float *)d, n_tok, (float *)(h + xpad))) != BK_OK)
         return st;
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(y_host, h + xpad, yb);
     return BK_OK;
 }
@@ -1229,7 +1277,10 @@ bk_status bk_attn_oneshot_host(bk_ctx *ctx, const float *q_host, const float *k_
     m.item_start[1] = m.n_items;
     if ((st = launch_decode(ctx, a, m)) != BK_OK) return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + qb + 2 * kvb, a.out, qb, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out_host, h + qb + 2 * kvb, qb);
     return BK_OK;
 }
@@ -1290,7 +1341,10 @@ bk_status bk_kvq_quantize(bk_ctx *ctx, int32_t hd, int32_t bits, int32_t n_vec, 
         return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + op, d + op, pb, cudaMemcpyDeviceToHost, ctx->stream));
     BK_CUDA(ctx, cudaMemcpyAsync(h + on, d + on, nb, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(packed, h + op, pb);
     memcpy(norms, h + on, nb);
     return BK_OK;
@@ -1312,7 +1366,10 @@ bk_status bk_kvq_dequantize(bk_ctx *ctx, int32_t hd, int32_t bits, int32_t n_vec
     if ((st = launch_dequantize(ctx, bits, n_vec, (const uint8_t *)(d + op), (const float *)(d + on), (float *)(d + ox))) != BK_OK)
         return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + ox, d + ox, xb, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out, h + ox, xb);
     return BK_OK;
 }
@@ -1330,7 +1387,10 @@ bk_status bk_kvq_rotate(bk_ctx *ctx, int32_t hd, int32_t n_vec, int32_t inverse,
     BK_CUDA(ctx, cudaMemcpyAsync(d + ox, h + ox, xb, cudaMemcpyHostToDevice, ctx->stream));
     if ((st = launch_rotate(ctx, n_vec, inverse, (const float *)(d + ox), (float *)(d + oo))) != BK_OK) return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + oo, d + oo, xb, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out, h + oo, xb);
     return BK_OK;
 }
@@ -1353,7 +1413,10 @@ bk_status bk_kvq_dot_rotated(bk_ctx *ctx, int32_t hd, int32_t bits, int32_t n_ve
                                  (const float *)(d + on), (float *)(d + oo))) != BK_OK)
         return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + oo, d + oo, nb, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out, h + oo, nb);
     return BK_OK;
 }
@@ -1380,7 +1443,10 @@ bk_status bk_rope_imrope(bk_ctx *ctx, int32_t n_heads, int32_t hd, float *heads,
     if ((st = launch_rope(ctx, n_heads, hd, (float *)(d + oh), (const float2 *)(d + orow), n_dims, (const int *)(d + ob))) != BK_OK)
         return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + oh, d + oh, hb, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(heads, h + oh, hb);
     return BK_OK;
 }
@@ -1399,7 +1465,10 @@ bk_status bk_f32_to_half(bk_ctx *ctx, size_t n, const float *in, uint16_t *out) 
     BK_CUDA(ctx, cudaMemcpyAsync(d + oi, h + oi, n * 4, cudaMemcpyHostToDevice, ctx->stream));
     if ((st = launch_f32_to_half(ctx, n, (const float *)(d + oi), (uint16_t *)(d + oo))) != BK_OK) return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + oo, d + oo, n * 2, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out, h + oo, n * 2);
     return BK_OK;
 }
@@ -1418,7 +1487,10 @@ bk_status bk_half_to_f32(bk_ctx *ctx, size_t n, const uint16_t *in, float *out) 
     BK_CUDA(ctx, cudaMemcpyAsync(d + oi, h + oi, n * 2, cudaMemcpyHostToDevice, ctx->stream));
     if ((st = launch_half_to_f32(ctx, n, (const uint16_t *)(d + oi), (float *)(d + oo))) != BK_OK) return st;
     BK_CUDA(ctx, cudaMemcpyAsync(h + oo, d + oo, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     memcpy(out, h + oo, n * 4);
     return BK_OK;
 }
@@ -1443,7 +1515,10 @@ bk_status bk_dev_free(bk_ctx *ctx, void *dev) {
     if (!dev) return BK_OK;
     bk_status st = bind(ctx);
     if (st != BK_OK) return st;
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     BK_CUDA(ctx, cudaFree(dev));
     return BK_OK;
 }
@@ -1460,7 +1535,10 @@ bk_status bk_host_alloc_pinned(bk_ctx *ctx, size_t bytes, void **out) {
 bk_status bk_host_free_pinned(bk_ctx *ctx, void *host) {
     if (!ctx) return fail(nullptr, BK_ERR_INVALID, "bk_host_free_pinned: ctx is null");
     if (!host) return BK_OK;
-    BK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    {
+        const bk_status st_sync = sync_and_check(ctx);
+        if (st_sync != BK_OK) return st_sync;
+    }
     BK_CUDA(ctx, cudaFreeHost(host));
     return BK_OK;
 }

@@ -72,7 +72,7 @@ __device__ __forceinline__ bool combine_slice(const DecodeArgs &a, int slot, int
         while (cnt.load(cuda::memory_order_acquire) < (unsigned)n_chunks) {
             if (++polls > kDistSpin) {  // never expected: leave a mark, write nothing
                 ok = 0;
-                if (err_flag) atomicExch(err_flag, 6);
+                raise_error(err_flag, 6);
                 break;
             }
         }
@@ -279,7 +279,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
                 int polls = 0;
                 while (!mbar_try_wait(bar, parity)) {
                     if (++polls > kWaitPolls) {  // never expected; leave a mark and go on rather than hang
-                        if (tid == 0 && fs.err_flag) atomicExch(fs.err_flag, 3);
+                        if (tid == 0) raise_error(fs.err_flag, 3);
                         break;
                     }
                 }
@@ -465,7 +465,6 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
         // ---- context split: send this kv head's rows to every rank, wait for everybody's, merge ----
         __shared__ int s_ok;
         constexpr int kStride = kHd + 2;
-        constexpr int kXchSpin = 1 << 20;  // polls of one arrival word before giving up (order of a second)
         const int world = a.xch_world, rank = a.xch_rank, n_rows = a.n_head, row0 = kv * NREP;
         const unsigned seqno = a.xch_seqno, par = seqno & 1u;
         const size_t slot_f = (size_t)n_rows * kStride, data_b = 2 * (size_t)world * slot_f * sizeof(float);
@@ -489,9 +488,9 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
             cuda::atomic_ref<unsigned, cuda::thread_scope_system> g(*mine);
             int polls = 0;
             while (g.load(cuda::memory_order_acquire) != seqno) {
-                if (++polls > kXchSpin) {  // never expected; leave a mark and go on rather than hang
+                if (++polls > a.xch_spin) {  // never expected; leave a mark and go on rather than hang
                     s_ok = 0;
-                    if (a.xch_err) atomicExch(a.xch_err, 3);
+                    raise_error(a.xch_err, 3);
                     break;
                 }
                 __nanosleep(64);

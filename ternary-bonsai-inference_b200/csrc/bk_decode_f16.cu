@@ -65,7 +65,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     const uint32_t ring_end = base + smem_bytes;
     const int n_stages = ring_end > ring0 ? min((int)((ring_end - ring0) / (uint32_t)(kFW * kStageBytes)), kMaxStages) : 0;
     if (n_stages < 1) {  // never expected (the host checks the size): report, do not run
-        if (tid == 0) atomicExch(err_flag, 2);
+        if (tid == 0) raise_error(err_flag, 2);
         return;
     }
     const uint32_t bar0 = base + (uint32_t)offsetof(Other, bar) + (uint32_t)(warp * kMaxStages) * 8u;
@@ -106,7 +106,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
         int polls = 0;
         while (!mbar_try_wait(bar, parity)) {
             if (++polls > kWaitPolls) {  // never expected; leave a mark and go on rather than hang
-                if (lane == 0) atomicExch(err_flag, 1);
+                if (lane == 0) raise_error(err_flag, 1);
                 break;
             }
         }

@@ -146,7 +146,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     const uint32_t n_a = (a_hi > a_lo ? a_hi - a_lo : 0u) / stage_bytes, n_b = (b_hi > b_lo ? b_hi - b_lo : 0u) / stage_bytes;
     const int n_stages = min((int)((n_a + n_b) / kMW), kMaxStages);
     if (n_stages < 1 || b_lo > b_hi) {  // the table's alignment left no room for the ring: report, do not run
-        if (tid == 0) atomicExch(err_flag, 2);
+        if (tid == 0) raise_error(err_flag, 2);
         asm volatile("griddepcontrol.wait;\n" ::: "memory");  // keep the stream's kernel order intact
         return;
     }
@@ -211,7 +211,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
         int polls = 0;
         while (!mbar_try_wait(bar, parity)) {
             if (++polls > kWaitPolls) {  // never expected; leave a mark and go on rather than hang
-                if (lane == 0) atomicExch(err_flag, 1);
+                if (lane == 0) raise_error(err_flag, 1);
                 break;
             }
         }

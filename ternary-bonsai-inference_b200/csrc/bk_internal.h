@@ -81,7 +81,11 @@ struct bk_ctx {
     unsigned *d_counters = nullptr;
     int ctr_set = 0;               // which of the two tensor-core counter sets the next launch counts in
     int ctr_dirty[2] = {0, 0};     // entries of each set that a launch has left non-zero
-    int *d_err = nullptr;          // set by a kernel whose bounded wait ran out; read by bk_synchronize
+    // Set by a kernel whose bounded wait ran out (the code says which wait).  The word lives in pinned host
+    // memory that the device writes directly, so every host-side wait for the stream can look at it for free.
+    int *d_err = nullptr;          // device view
+    volatile int *h_err = nullptr; // host view of the same word
+    int xch_polls = 1 << 20;       // polls of one arrival word of the context-split exchange before giving up (BONSAI_KV_XCH_POLLS)
     int n_sms = 148;
     std::vector<std::shared_ptr<bk::RopeTable>> ropes;
     // token descriptors of bk_append_batch: a ring of pinned/device slots, one event per slot
@@ -119,6 +123,18 @@ struct bk_cache {
     }
 };
 
+#ifdef __CUDACC__
+namespace bk {
+// Raise the context's error word from a kernel (plain store: the word may live in host memory).
+__device__ __forceinline__ void raise_error(int *flag, int code) {
+    if (flag) {
+        *reinterpret_cast<volatile int *>(flag) = code;
+        __threadfence_system();
+    }
+}
+}  // namespace bk
+#endif
+
 struct bk_event {
     cudaEvent_t ev = nullptr;
     int device = 0;
@@ -135,6 +151,9 @@ bk_status cuda_fail(bk_ctx *ctx, cudaError_t e, const char *what);
     } while (0)
 
 bk_status ensure_stage(bk_ctx *ctx, size_t bytes);
+// Wait for the context's stream, then look at the error word the kernels raise when a bounded wait runs
+// out: BK_ERR_CUDA (and the word and the split-K counters cleared) if one did.
+bk_status sync_and_check(bk_ctx *ctx);
 
 // ---- kernel launchers (bk_append.cu, bk_decode.cu, bk_kvq.cu) --------------
 
@@ -207,6 +226,7 @@ struct DecodeArgs {
     int xch_world, xch_rank;
     unsigned xch_seqno;
     int *xch_err;
+    int xch_spin;  // polls of one arrival word before the exchange gives up
     // Set by launch_decode_group for the tensor-core kernels:
     //   dyn   the warps of a (sequence, kv head) draw their tiles from one shared pool (a counter in
     //         the scratch) instead of a fixed share, so that a CTA that starts late takes less

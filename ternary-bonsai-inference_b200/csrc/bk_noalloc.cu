@@ -12,8 +12,10 @@
 //
 // What it costs: every GPU that loads this library reserves kStaticItems partial results
 // (about 4.3 MB) plus 1024 counters for as long as the process lives, whether or not the entry
-// point is ever called.  One call handles at most 64 sequences and at most kStaticItems
-// (sequence, kv head, chunk) work items; larger requests are rejected, not split.
+// point is ever called.  One call handles at most 64 sequences (more are rejected, not split); the
+// work of a call is cut into at most kStaticItems (sequence, kv head, chunk) items, with coarser
+// chunks than bk_decode_attn would use if need be, so the two agree within the parity tolerance
+// rather than bit for bit.
 //
 // All calls on a device share the one array.  It keeps whatever the previous call left in it;
 // the only part that must start from zero, the arrival counters, is cleared at the start of
@@ -21,8 +23,11 @@
 // mixed with nothing else - the normal entry points use their own per-context scratch) race on
 // the array and give wrong results: serialise them.
 //
-// The first call on each device looks up the array's device address (cudaGetSymbolAddress).
-// Make that first call during set-up, outside any stream capture.
+// The first call on each device looks up the array's device address (cudaGetSymbolAddress), once,
+// under std::call_once.  Make that first call during set-up, outside any stream capture.  A call
+// that succeeds enters no allocator; a failing call builds its message as a std::string.
+#include <mutex>
+
 #include "bk_internal.h"
 
 namespace bk {
@@ -39,21 +44,22 @@ static __device__ __align__(256) float g_static_partials[(size_t)kStaticItems * 
 static __device__ __align__(256) unsigned g_static_counters[kStaticCounters];
 
 struct DeviceScratch {
+    std::once_flag once;
     float *partials = nullptr;
     unsigned *counters = nullptr;
-    bool ready = false;
+    cudaError_t err = cudaSuccess;
 };
 DeviceScratch g_scratch[64];
 
-// Once per device, with that device current.
+// Once per device, with that device current (the caller has bound it).
 bk_status static_scratch(bk_ctx *ctx, DeviceScratch **out) {
     if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "bk_decode_attn_noalloc: device index above 63");
     DeviceScratch &s = g_scratch[ctx->device];
-    if (!s.ready) {
-        BK_CUDA(ctx, cudaGetSymbolAddress((void **)&s.partials, g_static_partials));
-        BK_CUDA(ctx, cudaGetSymbolAddress((void **)&s.counters, g_static_counters));
-        s.ready = true;
-    }
+    std::call_once(s.once, [&s]() {
+        s.err = cudaGetSymbolAddress((void **)&s.partials, g_static_partials);
+        if (s.err == cudaSuccess) s.err = cudaGetSymbolAddress((void **)&s.counters, g_static_counters);
+    });
+    if (s.err != cudaSuccess) return cuda_fail(ctx, s.err, "cudaGetSymbolAddress(static split-K scratch)");
     *out = &s;
     return BK_OK;
 }
@@ -74,8 +80,7 @@ extern "C" bk_status bk_decode_attn_noalloc(bk_cache *c, int32_t layer, int32_t 
     if (n_seqs == 0) return BK_OK;
     if (n_seqs > kStaticSeqs)
         return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_noalloc: at most 64 sequences per call (the fixed scratch holds no more)");
-    if ((int64_t)n_seqs * c->cfg.n_kv > kStaticItems)
-        return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_noalloc: sequences x kv heads exceeds the 512 work items of the fixed scratch");
+    static_assert(kStaticSeqs * 8 <= kStaticItems, "64 sequences x 8 kv heads always fit the fixed scratch");
     if (!q_dev || !out_dev) return fail(ctx, BK_ERR_INVALID, "bk_decode_attn_noalloc: null q/out");
     bk_status st = bind_device(ctx);
     if (st != BK_OK) return st;

@@ -19,6 +19,9 @@
 #include <math_constants.h>
 
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "bk_internal.h"
 
@@ -31,13 +34,18 @@ struct bk_mailbox {
     bool opened[bk::kMaxWorld] = {};
     float *part = nullptr;              // staging for the local partial rows
     uint8_t **d_peer = nullptr;         // device copy of peer[]
+    unsigned char handle[BK_IPC_HANDLE_BYTES] = {};  // what bk_mailbox_create handed out for `local`
 };
 
 namespace bk {
 
 namespace {
 
-constexpr int kSpinLimit = 1 << 20;  // polls of one arrival word before giving up (order of a second)
+// Mailboxes of this process: ranks that live in one process (threads, or a test that plays several
+// ranks) cannot open each other's IPC handles - CUDA refuses a handle in the process that made it - so
+// bk_mailbox_open_peers looks a handle up here first and uses the allocation directly.
+std::mutex g_boxes_mu;
+std::vector<bk_mailbox *> g_boxes;
 
 __host__ __device__ inline size_t slot_floats(int n_rows, int hd) { return (size_t)n_rows * (hd + 2); }
 __host__ __device__ inline size_t data_bytes(int world, int n_rows, int hd) {
@@ -49,7 +57,7 @@ __host__ __device__ inline size_t mailbox_bytes(int world, int n_rows, int hd) {
 
 __global__ void __launch_bounds__(256) exchange_merge_kernel(uint8_t *const *peer, int world, int rank, int n_rows,
                                                              int hd, const float *part, unsigned seqno, float *out,
-                                                             int *err_flag) {
+                                                             int *err_flag, int spin_limit) {
     const int row = blockIdx.x, tid = threadIdx.x, stride = hd + 2;
     const unsigned par = seqno & 1u;
     const size_t slot = slot_floats(n_rows, hd);
@@ -77,9 +85,9 @@ __global__ void __launch_bounds__(256) exchange_merge_kernel(uint8_t *const *pee
         cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
         int polls = 0;
         while (f.load(cuda::memory_order_acquire) != seqno) {
-            if (++polls > kSpinLimit) {
+            if (++polls > spin_limit) {
                 s_ok = 0;
-                atomicExch(err_flag, 3);
+                raise_error(err_flag, 3);
                 break;
             }
             __nanosleep(64);
@@ -147,6 +155,11 @@ bk_status bk_mailbox_create(bk_ctx *ctx, int32_t world, int32_t rank, int32_t n_
         bk_mailbox_destroy(m);
         return cuda_fail(ctx, e, "bk_mailbox_create");
     }
+    memcpy(m->handle, ipc_handle_out, BK_IPC_HANDLE_BYTES);
+    {
+        std::lock_guard<std::mutex> lock(g_boxes_mu);
+        g_boxes.push_back(m);
+    }
     *out = m;
     return BK_OK;
 }
@@ -171,7 +184,13 @@ bk_status bk_mailbox_open_peers(bk_mailbox *m, const void *handles) {
         cudaGetLastError();
     }
     for (int r = 0; r < m->world; r++) {
-        if (r == m->rank || m->opened[r]) continue;
+        if (r == m->rank || m->opened[r] || m->peer[r]) continue;
+        {   // a rank of this very process: use its allocation as it is
+            std::lock_guard<std::mutex> lock(g_boxes_mu);
+            for (bk_mailbox *o : g_boxes)
+                if (o != m && memcmp(o->handle, &h[r], BK_IPC_HANDLE_BYTES) == 0) m->peer[r] = o->local;
+        }
+        if (m->peer[r]) continue;
         void *p = nullptr;
         BK_CUDA(ctx, cudaIpcOpenMemHandle(&p, h[r], cudaIpcMemLazyEnablePeerAccess));
         m->peer[r] = static_cast<uint8_t *>(p);
@@ -183,6 +202,14 @@ bk_status bk_mailbox_open_peers(bk_mailbox *m, const void *handles) {
 
 void bk_mailbox_destroy(bk_mailbox *m) {
     if (!m) return;
+    {
+        std::lock_guard<std::mutex> lock(g_boxes_mu);
+        for (size_t i = 0; i < g_boxes.size(); i++)
+            if (g_boxes[i] == m) {
+                g_boxes.erase(g_boxes.begin() + (long)i);
+                break;
+            }
+    }
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     for (int r = 0; r < m->world; r++)
@@ -211,7 +238,7 @@ bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t 
     bk_status st = bk_decode_attn_partial(c, layer, 1, &seq, &n_pos, &q_pos, q_dev, m->part);
     if (st != BK_OK) return st;
     exchange_merge_kernel<<<m->n_rows, 256, 0, ctx->stream>>>(m->d_peer, m->world, m->rank, m->n_rows, m->hd, m->part,
-                                                              seqno, out_dev, ctx->d_err);
+                                                              seqno, out_dev, ctx->d_err, ctx->xch_polls);
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     return BK_OK;

@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
             int polls = 0;
             while (!mbar_try_wait(sbase + 8u * st, (phase >> sl) & 1u)) {
                 if (++polls > kWaitPolls) {  // never expected: leave a mark rather than hang
-                    if (lane == 0) atomicExch(a.err_flag, 5);
+                    if (lane == 0) raise_error(a.err_flag, 5);
                     break;
                 }
             }

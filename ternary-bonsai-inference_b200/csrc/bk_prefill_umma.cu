@@ -276,7 +276,7 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
         int polls = 0;
         while (!mbar_try_wait(bar, parity)) {
             if (++polls > kWaitPolls) {  // never expected; leave a mark and go on rather than hang
-                if (lane == 0) atomicExch(pa.err_flag, 4);
+                if (lane == 0) raise_error(pa.err_flag, 4);
                 break;
             }
         }

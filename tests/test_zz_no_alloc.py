@@ -4,9 +4,9 @@ The no-alloc entry point exists for hosts that may not allocate once they are se
 HBM already belongs to the caches; a later cudaMalloc would synchronise the device or fail on a
 fragmented heap) or that call from a thread where the CUDA allocator must not be entered.  It
 keeps its split-K scratch in a fixed array inside the library.  This file checks, through the C
-ABI, that it returns what the ordinary entry point returns, on two calls in a row (the second
-call finds the array as the first left it), and that it rejects requests beyond its stated
-limits.  It is named to be collected last and runs on its own as well as after the other tests.
+ABI, that it returns what the ordinary entry point returns AND what the CPU oracle computes, on two
+calls in a row (the second call finds the array as the first left it), and that it rejects requests
+beyond its stated limits.  It is named to be collected last and runs on its own as well as after the other tests.
 """
 import ctypes as C
 
@@ -25,17 +25,23 @@ def _decode(cache, fn, q_dev, out_dev, n_seqs):
 
 
 @pytest.mark.parametrize("tag", ["planar4", "f16"])
-def test_noalloc_matches_regular_entry_point_twice(bk, gpu_ctx, tag):
+def test_noalloc_matches_regular_entry_point_twice(bk, gpu_ctx, oracle, tag):
+    from oracle_lib import MODE_F16, MODE_PLANAR
     rng = np.random.default_rng(5)
     lens = [5000, 300, 0, 2048]           # both kernels, many chunks, an empty sequence
     cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_seqs=len(lens), n_ctx=max(lens))
+    refs = []
     for s, n in enumerate(lens):
+        ref = oracle.cache(MODE_PLANAR, 4, True) if tag == "planar4" else oracle.cache(MODE_F16)
+        refs.append(ref)
         if n:
             k = rng.standard_normal((n, NKV, HD)).astype(np.float32)
             v = rng.standard_normal((n, NKV, HD)).astype(np.float32)
             k[:, :, [3, 77, 190]] *= np.float32(20.0)
             v[:, :, [3, 77, 190]] *= np.float32(20.0)
             cache.append(0, k, v, seq=s)
+            for p in range(n):
+                ref.append(0, k[p], v[p], p)
     lib = gpu_ctx.lib
     out_a, out_b = gpu_ctx.alloc(len(lens) * NH * HD * 4), gpu_ctx.alloc(len(lens) * NH * HD * 4)
     for call in range(2):                 # two calls in a row through the new entry point
@@ -46,6 +52,11 @@ def test_noalloc_matches_regular_entry_point_twice(bk, gpu_ctx, tag):
         err = np.max(np.abs(got.astype(np.float64) - want))
         assert err <= ABS_TOL and err / max(np.max(np.abs(want)), 1e-30) <= REL_TOL, (tag, call, err)
         assert np.all(got[2] == 0.0)
+        for s, n in enumerate(lens):          # third column: the CPU oracle
+            if n:
+                cpu = refs[s].attend(0, q[s], n - 1, n, threads=8).astype(np.float64)
+                e2 = np.max(np.abs(got[s] - cpu))
+                assert e2 <= ABS_TOL and e2 / max(np.max(np.abs(cpu)), 1e-30) <= REL_TOL, (tag, call, s, e2)
         q_dev.free()
     cache.close()
 
