@@ -761,7 +761,7 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
         ctx->ctr_set = 1 - set;
     }
     // every CTA holds a whole SM, so a launch of at most n_sms items is resident all at once
-    a2.dist = (ctx->dist_combine && items <= ctx->n_sms && !a.xch_peer) ? 1 : 0;
+    a2.dist = (ctx->dist_combine && items <= ctx->n_sms) ? 1 : 0;
     return a.k_kind == ROW_F16 ? launch_decode_f16_mma(ctx, a2, m, ctx->qsplit)
                                : launch_decode_p4_mma(ctx, a2, m, ctx->lut_alpha[a.bits], ctx->qsplit);
 }

@@ -52,6 +52,95 @@ struct FinishSmem {
     int *err_flag = nullptr;
 };
 
+// The exchange step of the context split, for coordinates d0 .. d0 + dn - 1 (dn a multiple of 8) of the n_rep
+// q heads of kv head `kv`: send this rank's values to slot [rank] of every rank's mailbox (plain peer stores;
+// the CTA that holds coordinate 0 also sends the heads' m and l), publish them octet by octet with a
+// system-scope release of the call's sequence number, wait (bounded) for the same octets - and octet 0, for
+// m and l - of every rank in this rank's own mailbox, and write the log-sum-exp merge to a.out.
+// A mailbox is [2 parities][world][n_head][hd + 2] floats followed by [2][world][kXchFlags] arrival words,
+// word kv * 32 + (coordinate / 8).  The octet grid does not depend on how a rank has cut its work, so ranks
+// whose launches have different shapes (or that send from the stand-alone exchange kernel) understand each
+// other.  vals: [n_rep][dn] in shared memory, relative to s_M (exp2 domain), not normalised.  Every thread of
+// the CTA must call; on a time-out the output is zeros and the context's error word is raised.
+__device__ __forceinline__ void exchange_slice(const DecodeArgs &a, int n_rep, int slot, int kv, int d0, int dn,
+                                               const float *vals, const float *s_M, const float *s_L, int *s_ok) {
+    constexpr int kStride = kHd + 2;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int world = a.xch_world, rank = a.xch_rank, n_rows = a.n_head, row0 = kv * n_rep;
+    const unsigned seqno = a.xch_seqno, par = seqno & 1u;
+    const size_t slot_f = (size_t)n_rows * kStride, data_b = 2 * (size_t)world * slot_f * sizeof(float);
+    for (int r = 0; r < world; r++) {
+        float *dst = reinterpret_cast<float *>(a.xch_peer[r]) + ((size_t)par * world + rank) * slot_f + (size_t)row0 * kStride;
+        for (int i = tid; i < n_rep * dn; i += nt) {
+            const int rr = i / dn, d = i - rr * dn;
+            dst[rr * kStride + d0 + d] = vals[i];
+        }
+        if (d0 == 0 && tid < n_rep) {
+            dst[tid * kStride + kHd] = s_M[tid] * 0.6931471805599453f;  // log2 -> ln
+            dst[tid * kStride + kHd + 1] = s_L[tid];
+        }
+    }
+    if (tid == 0) *s_ok = 1;
+    // The barrier orders every thread's stores before the release stores below, which are cumulative: whoever
+    // acquires an arrival word sees the rows.  No thread needs a system-wide fence of its own.
+    __syncthreads();
+    const int n_oct = dn >> 3, oct0 = d0 >> 3, per = n_oct + 1;
+    for (int x = tid; x < world * per; x += nt) {
+        const int r = x / per, j = x - r * per;
+        if (j < n_oct) {
+            unsigned *flag = reinterpret_cast<unsigned *>(a.xch_peer[r] + data_b) + ((size_t)par * world + rank) * kXchFlags + kv * 32 + oct0 + j;
+            cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
+            f.store(seqno, cuda::memory_order_release);
+        }
+        if (j < n_oct || oct0 != 0) {  // ... and wait for the same octet (j == n_oct: octet 0, which carries m and l) of rank r
+            const int oct = j < n_oct ? oct0 + j : 0;
+            unsigned *mine = reinterpret_cast<unsigned *>(a.xch_peer[rank] + data_b) + ((size_t)par * world + r) * kXchFlags + kv * 32 + oct;
+            cuda::atomic_ref<unsigned, cuda::thread_scope_system> g2(*mine);
+            int polls = 0;
+            while (g2.load(cuda::memory_order_acquire) != seqno) {
+                if (++polls > a.xch_spin) {  // the peer never sent: leave a mark and go on rather than hang
+                    *s_ok = 0;
+                    raise_error(a.xch_err, 3);
+                    break;
+                }
+                if (polls > 2048) __nanosleep(64);  // the first microseconds without a pause: the ranks run in lock step
+            }
+        }
+    }
+    __syncthreads();
+    const float *mbox = reinterpret_cast<const float *>(a.xch_peer[rank]) + (size_t)par * world * slot_f + (size_t)row0 * kStride;
+    const bool ok = *s_ok != 0;
+    for (int i = tid; i < n_rep * dn; i += nt) {
+        const int rr = i / dn, d = d0 + (i - rr * dn);
+        // every rank's (m, l, value) first, all loads independent of one another: one trip to the mailbox
+        float m[kMaxWorld], l[kMaxWorld], x[kMaxWorld];
+#pragma unroll
+        for (int r = 0; r < kMaxWorld; r++) {
+            m[r] = -CUDART_INF_F;
+            l[r] = x[r] = 0.f;
+            if (r < world) {
+                const float *p = mbox + (size_t)r * slot_f + (size_t)rr * kStride;
+                m[r] = __ldcv(p + kHd);
+                l[r] = __ldcv(p + kHd + 1);
+                x[r] = __ldcv(p + d);
+            }
+        }
+        float Mx = -CUDART_INF_F;
+#pragma unroll
+        for (int r = 0; r < kMaxWorld; r++)
+            if (l[r] > 0.f) Mx = fmaxf(Mx, m[r]);
+        float Ls = 0.f, sum = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxWorld; r++)
+            if (l[r] > 0.f) {
+                const float f = expf(m[r] - Mx);
+                Ls = fmaf(l[r], f, Ls);
+                sum = fmaf(x[r], f, sum);
+            }
+        a.out[((size_t)slot * a.n_head + row0 + rr) * kHd + d] = (ok && Ls > 0.f) ? sum / Ls : 0.f;
+    }
+}
+
 // The slice form of the split-K combine.  When every CTA of a (sequence, kv head) is resident at
 // the same time (the launcher sets DecodeArgs::dist only then), nobody leaves after publishing:
 // each CTA waits (bounded) until all n_chunks triples are in the scratch and then combines ONE
@@ -81,7 +170,12 @@ __device__ __forceinline__ bool combine_slice(const DecodeArgs &a, int slot, int
     __syncthreads();
     BK_STAMP(7);
     if (!*s_flag) return false;
-    const int D4 = (kHd / 4 + n_chunks - 1) / n_chunks;  // 16-byte columns per head in a slice
+    int D4 = (kHd / 4 + n_chunks - 1) / n_chunks;  // 16-byte columns per head in a slice
+    if (a.xch_peer) {  // context split: slices on the mailbox's octet grid, and of a size that divides the row
+        int D8 = 8;
+        while (D8 * n_chunks < kHd) D8 <<= 1;
+        D4 = D8 >> 2;
+    }
     const int D = 4 * D4, n_slices = (kHd + D - 1) / D;
     if (my_chunk >= n_slices) return true;
     const int d0 = my_chunk * D, d4 = min(D4, (kHd - d0) >> 2), dn = 4 * d4;
@@ -166,23 +260,33 @@ __device__ __forceinline__ bool combine_slice(const DecodeArgs &a, int slot, int
         res[tid] = t;
     }
     __syncthreads();
+    float o = 0.f;
+    const int r_o = tid / dn, d_o = tid - r_o * dn;
     if (tid < NREP * dn) {
-        const int r = tid / dn, d = tid - r * dn;
-        float o = res[tid];
+        o = res[tid];
         if (v_planar) {  // undo the Givens rotation: coordinate d0 + d and its partner (src/forward.rs:349)
-            const int pr = (d0 + d) >> 1;
+            const int pr = (d0 + d_o) >> 1;
             const float c = givens[2 * pr], sn = givens[2 * pr + 1];
             float o0, o1;
-            givens_inv(res[r * dn + (d & ~1)], res[r * dn + (d | 1)], c, sn, o0, o1);
-            o = (d & 1) ? o1 : o0;
+            givens_inv(res[r_o * dn + (d_o & ~1)], res[r_o * dn + (d_o | 1)], c, sn, o0, o1);
+            o = (d_o & 1) ? o1 : o0;
         }
+    }
+    if (a.xch_peer) {  // context split: this slice goes to every rank and is merged with theirs
+        float *snd = res + NREP * dn;
+        if (tid < NREP * dn) snd[tid] = o;
+        __syncthreads();
+        exchange_slice(a, NREP, slot, kv, d0, dn, snd, s_M, s_L, s_flag);
+        return true;
+    }
+    if (tid < NREP * dn) {
         if (a.partial) {
-            a.out[((size_t)slot * a.n_head + (size_t)kv * NREP + r) * kPartStride + d0 + d] = o;
+            a.out[((size_t)slot * a.n_head + (size_t)kv * NREP + r_o) * kPartStride + d0 + d_o] = o;
         } else {
-            const float Ls = s_L[r];
+            const float Ls = s_L[r_o];
             o = Ls > 0.f ? o / Ls : 0.f;
             if (gate) o *= 1.0f / (1.0f + expf(-gv));
-            a.out[((size_t)slot * a.n_head + (size_t)kv * NREP + r) * kHd + d0 + d] = o;
+            a.out[((size_t)slot * a.n_head + (size_t)kv * NREP + r_o) * kHd + d0 + d_o] = o;
         }
     }
     if (a.partial && my_chunk == 0 && tid < NREP) {
@@ -464,60 +568,7 @@ __device__ __forceinline__ void finish_item(const DecodeArgs &a, int slot, int s
     if (a.xch_peer) {
         // ---- context split: send this kv head's rows to every rank, wait for everybody's, merge ----
         __shared__ int s_ok;
-        constexpr int kStride = kHd + 2;
-        const int world = a.xch_world, rank = a.xch_rank, n_rows = a.n_head, row0 = kv * NREP;
-        const unsigned seqno = a.xch_seqno, par = seqno & 1u;
-        const size_t slot_f = (size_t)n_rows * kStride, data_b = 2 * (size_t)world * slot_f * sizeof(float);
-        for (int r = 0; r < world; r++) {
-            float *dst = reinterpret_cast<float *>(a.xch_peer[r]) + ((size_t)par * world + rank) * slot_f + (size_t)row0 * kStride;
-            for (int i = tid0; i < NREP * kStride; i += nt) {
-                const int rr = i / kStride, c = i - rr * kStride;
-                dst[i] = c < kHd ? s_acc[rr * kHd + c] : (c == kHd ? s_M[rr] * 0.6931471805599453f : s_L[rr]);
-            }
-        }
-        if (tid == 0) s_ok = 1;
-        __threadfence_system();
-        __syncthreads();
-        if (tid < world * NREP) {
-            const int r = tid / NREP, rr = tid - r * NREP;
-            unsigned *flag = reinterpret_cast<unsigned *>(a.xch_peer[r] + data_b) + ((size_t)par * world + rank) * n_rows + row0 + rr;
-            cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
-            f.store(seqno, cuda::memory_order_release);
-            // ... and wait for row rr of rank r in this rank's own mailbox
-            unsigned *mine = reinterpret_cast<unsigned *>(a.xch_peer[rank] + data_b) + ((size_t)par * world + r) * n_rows + row0 + rr;
-            cuda::atomic_ref<unsigned, cuda::thread_scope_system> g(*mine);
-            int polls = 0;
-            while (g.load(cuda::memory_order_acquire) != seqno) {
-                if (++polls > a.xch_spin) {  // never expected; leave a mark and go on rather than hang
-                    s_ok = 0;
-                    raise_error(a.xch_err, 3);
-                    break;
-                }
-                __nanosleep(64);
-            }
-        }
-        __syncthreads();
-        const float *mbox = reinterpret_cast<const float *>(a.xch_peer[rank]) + (size_t)par * world * slot_f + (size_t)row0 * kStride;
-        float *out = a.out + ((size_t)slot * a.n_head + row0) * kHd;
-        if (act) {
-            for (int rr = 0; rr < NREP; rr++) {
-                float Mx = -CUDART_INF_F;
-                for (int r = 0; r < world; r++) {
-                    const volatile float *p = mbox + (size_t)r * slot_f + (size_t)rr * kStride;
-                    if (p[kHd + 1] > 0.f) Mx = fmaxf(Mx, p[kHd]);
-                }
-                float Ls = 0.f, sum = 0.f;
-                for (int r = 0; r < world; r++) {
-                    const volatile float *p = mbox + (size_t)r * slot_f + (size_t)rr * kStride;
-                    if (p[kHd + 1] > 0.f) {
-                        const float f = expf(p[kHd] - Mx);
-                        Ls = fmaf(p[kHd + 1], f, Ls);
-                        sum = fmaf(p[tid], f, sum);
-                    }
-                }
-                out[rr * kHd + tid] = (s_ok && Ls > 0.f) ? sum / Ls : 0.f;
-            }
-        }
+        exchange_slice(a, NREP, slot, kv, 0, kHd, s_acc, s_M, s_L, &s_ok);
     } else if (a.partial) {
         float *out = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP) * kPartStride;
         for (int i = tid0; i < NREP * kHd; i += nt) {

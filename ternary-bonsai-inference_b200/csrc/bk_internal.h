@@ -22,6 +22,7 @@ constexpr int kPartStride = kHd + 2;   // floats per partial result handed to ca
 constexpr int kScratchStride = kHd + 4; // floats per partial in the split-K scratch (16-byte aligned rows)
 constexpr int kMmaMinPos = 2048;       // shorter sequences take the generic f32 decode kernel
 constexpr int kMaxWorld = 8;            // ranks a context-split mailbox can connect
+constexpr int kXchFlags = 512;          // arrival words per (parity, rank) of a mailbox: kv head * 32 + coordinate octet
 // The arrival counters of the split-K scratch, one per (sequence in the launch, kv head) pair i (i < 512),
 // in three sets of kCtrSet: set 0 for the generic kernel, whose last arriver puts its counter back to zero;
 // sets 1 and 2 for the tensor-core kernels, which alternate between them from launch to launch: a launch

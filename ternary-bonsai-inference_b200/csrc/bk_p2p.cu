@@ -23,6 +23,7 @@
 #include <mutex>
 #include <vector>
 
+#include "bk_decode_common.cuh"
 #include "bk_internal.h"
 
 struct bk_mailbox {
@@ -52,67 +53,27 @@ __host__ __device__ inline size_t data_bytes(int world, int n_rows, int hd) {
     return 2 * (size_t)world * slot_floats(n_rows, hd) * sizeof(float);
 }
 __host__ __device__ inline size_t mailbox_bytes(int world, int n_rows, int hd) {
-    return data_bytes(world, n_rows, hd) + 2 * (size_t)world * n_rows * sizeof(unsigned);
+    return data_bytes(world, n_rows, hd) + 2 * (size_t)world * kXchFlags * sizeof(unsigned);
 }
 
-__global__ void __launch_bounds__(256) exchange_merge_kernel(uint8_t *const *peer, int world, int rank, int n_rows,
-                                                             int hd, const float *part, unsigned seqno, float *out,
-                                                             int *err_flag, int spin_limit) {
-    const int row = blockIdx.x, tid = threadIdx.x, stride = hd + 2;
-    const unsigned par = seqno & 1u;
-    const size_t slot = slot_floats(n_rows, hd);
-    // ---- send: this rank's row into slot [rank] of every mailbox (its own included) ----------
-    const float *src = part + (size_t)row * stride;
-    for (int r = 0; r < world; r++) {
-        float *dst = reinterpret_cast<float *>(peer[r]) + ((size_t)par * world + rank) * slot + (size_t)row * stride;
-        for (int i = tid; i < stride; i += blockDim.x) dst[i] = src[i];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < world) {
-        unsigned *flag = reinterpret_cast<unsigned *>(peer[tid] + data_bytes(world, n_rows, hd)) +
-                         ((size_t)par * world + rank) * n_rows + row;
-        cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
-        f.store(seqno, cuda::memory_order_release);
-    }
-    // ---- wait for row `row` of every rank (bounded), then merge ------------------------------
+// The exchange on its own, for a rank whose rows were produced by another launch (or that has no rows: l = 0):
+// one CTA per kv head sends that head's rows of `part` ([n_rows][hd + 2]: acc, m in natural-log units, l) and
+// merges what arrives, in the protocol of exchange_slice().
+__global__ void __launch_bounds__(256) exchange_merge_kernel(DecodeArgs a, int n_rep, const float *part) {
+    __shared__ float s_M[kMaxRep], s_L[kMaxRep];
     __shared__ int s_ok;
-    if (tid == 0) s_ok = 1;
-    __syncthreads();
-    if (tid < world) {
-        unsigned *flag = reinterpret_cast<unsigned *>(peer[rank] + data_bytes(world, n_rows, hd)) +
-                         ((size_t)par * world + tid) * n_rows + row;
-        cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
-        int polls = 0;
-        while (f.load(cuda::memory_order_acquire) != seqno) {
-            if (++polls > spin_limit) {
-                s_ok = 0;
-                raise_error(err_flag, 3);
-                break;
-            }
-            __nanosleep(64);
-        }
+    extern __shared__ float s_vals[];  // [n_rep][hd]
+    const int kv = blockIdx.x, tid = threadIdx.x, stride = kHd + 2;
+    for (int i = tid; i < n_rep * kHd; i += blockDim.x) {
+        const int rr = i / kHd, d = i - rr * kHd;
+        s_vals[i] = part[(size_t)(kv * n_rep + rr) * stride + d];
+    }
+    if (tid < n_rep) {
+        s_M[tid] = part[(size_t)(kv * n_rep + tid) * stride + kHd] * 1.4426950408889634f;  // exchange_slice sends m * ln 2
+        s_L[tid] = part[(size_t)(kv * n_rep + tid) * stride + kHd + 1];
     }
     __syncthreads();
-    const float *mine = reinterpret_cast<const float *>(peer[rank]) + (size_t)par * world * slot + (size_t)row * stride;
-    float M = -CUDART_INF_F;
-    for (int r = 0; r < world; r++) {
-        const volatile float *p = mine + (size_t)r * slot;
-        if (p[hd + 1] > 0.f) M = fmaxf(M, p[hd]);
-    }
-    float Ls = 0.f;
-    for (int r = 0; r < world; r++) {
-        const volatile float *p = mine + (size_t)r * slot;
-        if (p[hd + 1] > 0.f) Ls += p[hd + 1] * expf(p[hd] - M);
-    }
-    for (int d = tid; d < hd; d += blockDim.x) {
-        float sum = 0.f;
-        for (int r = 0; r < world; r++) {
-            const volatile float *p = mine + (size_t)r * slot;
-            if (p[hd + 1] > 0.f) sum = fmaf(p[d], expf(p[hd] - M), sum);
-        }
-        out[(size_t)row * hd + d] = (s_ok && Ls > 0.f) ? sum / Ls : 0.f;
-    }
+    exchange_slice(a, n_rep, 0, kv, 0, kHd, s_vals, s_M, s_L, &s_ok);
 }
 
 }  // namespace
@@ -237,8 +198,15 @@ bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t 
         return decode_with_exchange(c, layer, seq, n_pos, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, seqno);
     bk_status st = bk_decode_attn_partial(c, layer, 1, &seq, &n_pos, &q_pos, q_dev, m->part);
     if (st != BK_OK) return st;
-    exchange_merge_kernel<<<m->n_rows, 256, 0, ctx->stream>>>(m->d_peer, m->world, m->rank, m->n_rows, m->hd, m->part,
-                                                              seqno, out_dev, ctx->d_err, ctx->xch_polls);
+    DecodeArgs xa;
+    fill_decode_args(c, layer, 0, &xa);
+    xa.out = out_dev;
+    xa.xch_peer = m->d_peer;
+    xa.xch_world = m->world;
+    xa.xch_rank = m->rank;
+    xa.xch_seqno = seqno;
+    const int n_rep = c->cfg.n_head / c->cfg.n_kv;
+    exchange_merge_kernel<<<c->cfg.n_kv, 256, (size_t)n_rep * kHd * sizeof(float), ctx->stream>>>(xa, n_rep, m->part);
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     return BK_OK;
