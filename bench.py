@@ -356,6 +356,37 @@ def build_splitctx(bk, par, ctx, mode, rank, world, local, dist, total_steps, mo
     return step, step_bytes, 1, "strong", cfg, cleanup
 
 
+def append_sweep(bk, ctx, mode, rng, channels, max_tokens=4096):
+    """Append throughput for 1, 2, 4, ... tokens per call (one call per layer, 16 layers per measurement):
+    the fused rope + quantize + store kernel alone, device-resident K/V, CUDA events, median of the repeats."""
+    cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=max_tokens * 2)
+    k, v = synth_chunk(rng, max_tokens, channels)
+    dk, dv = ctx.to_device(k), ctx.to_device(v)
+    table = []
+    n = 1
+    while n <= max_tokens:
+        reps = max(4, min(64, 8192 // n))
+        ts = []
+        for r in range(reps + 2):
+            cache.reset()
+            e0, e1 = ctx.event(), ctx.event()
+            e0.record()
+            for il in range(N_LAYERS):
+                cache.append_device(il, dk.ptr, dv.ptr, n_tokens=n, pos=0)
+            e1.record()
+            ctx.synchronize()
+            if r >= 2:
+                ts.append(e0.elapsed_ms(e1))
+        t = float(np.median(ts)) * 1e-3
+        table.append({"tokens_per_call": n, "tokens_per_s": n / t, "gb_per_s": N_LAYERS * append_bytes(mode, n) / t / 1e9,
+                      "us_per_call_all_layers": t * 1e6})
+        n *= 2
+    cache.close()
+    dk.free()
+    dv.free()
+    return table
+
+
 def timed_steps(ctx, dist, local, step, steps, warmup):
     """Device time of `steps` steps after `warmup`: CUDA events on the library's stream, barriers on both
     sides, max over the ranks.  Returns ms per step."""
@@ -555,28 +586,7 @@ def run_other_workload(args):
                                        "sample": "the four tensors of one layer through the oracle's scalar row dot, time x 16"}
             return out
     else:  # appendsweep
-        cache = bk.AttnCache(ctx, mode, n_layers=N_LAYERS, n_seqs=1, n_ctx=4096 * 2)
-        k, v = synth_chunk(rng, 4096, channels)
-        dk, dv = ctx.to_device(k), ctx.to_device(v)
-        table = []
-        n = 1
-        while n <= 4096:
-            reps = max(4, min(64, 8192 // n))
-            ts = []
-            for r in range(reps + 2):
-                cache.reset()
-                e0, e1 = ctx.event(), ctx.event()
-                e0.record()
-                for il in range(N_LAYERS):
-                    cache.append_device(il, dk.ptr, dv.ptr, n_tokens=n, pos=0)
-                e1.record()
-                ctx.synchronize()
-                if r >= 2:
-                    ts.append(e0.elapsed_ms(e1))
-            t = float(np.median(ts)) * 1e-3
-            table.append({"tokens_per_call": n, "tokens_per_s": n / t, "gb_per_s": N_LAYERS * append_bytes(mode, n) / t / 1e9,
-                          "us_per_call_all_layers": t * 1e6})
-            n *= 2
+        table = append_sweep(bk, ctx, mode, rng, channels)
         if rank == 0:
             line.update({"metric": "KV append throughput (fused rope+quantize+store)", "value": table[-1]["tokens_per_s"],
                          "ms_per_step": table[-1]["us_per_call_all_layers"] / 1e3, "scaling": "weak",
@@ -808,10 +818,13 @@ def main():
     checksum = float(np.abs(hout.array).sum())
 
     # ---- the configurations that shard one job over the GPUs (16 layers, planar cache) --------------
-    sharded = None
+    sharded, sweep = None, None
     if args.sharded and mode.kind == "planar" and N_LAYERS == 16:
         cache.close()
         sharded = run_sharded(bk, ctx, mode, args.mode, rank, world, local, dist)
+        if rank == 0 and world == 1:   # the append kernel on its own, 1 .. 4096 tokens per call
+            r2 = np.random.default_rng(99)
+            sweep = append_sweep(bk, ctx, mode, r2, r2.choice(HD, size=3, replace=False))
 
     if rank != 0:
         if dist is not None:
@@ -880,7 +893,7 @@ def main():
                      "isolated_launch_ms": dec_ms_isolated,
                      "frac_isolated": alg / (dec_ms_isolated * 1e-3) / 1e9 / peak,
                      "frac_of_8TBs_nominal": achieved / 8000.0},
-        "cpu_baseline": cpu, "clocks": clocks, "sharded": sharded,
+        "cpu_baseline": cpu, "clocks": clocks, "sharded": sharded, "append_sweep": sweep,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:

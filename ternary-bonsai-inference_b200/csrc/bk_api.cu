@@ -205,7 +205,7 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
         ctx->prefill_umma = !(e3 && std::string(e3) == "mma");  // tcgen05 kernel unless BONSAI_KV_PREFILL=mma
         ctx->qsplit = !(e2 && e2[0] == '0');  // on unless BONSAI_KV_QSPLIT=0
         const char *e5 = getenv("BONSAI_KV_DYN"), *e6 = getenv("BONSAI_KV_DIST");
-        ctx->dyn_tiles = e5 ? atoi(e5) : 1;
+        ctx->dyn_tiles = e5 ? atoi(e5) : 0;
         ctx->dist_combine = !(e6 && e6[0] == '0');
     }
     if ((e = cudaMalloc(&ctx->d_givens, sizeof(ctx->h_givens))) != cudaSuccess) return bail(e, "cudaMalloc givens");

@@ -8,8 +8,8 @@
 //      the (cos, sin) row of the token's position from the host-built rope table;
 //   2. planar rows: one warp adds the 256 squares of all 32 vectors, a vector per lane, each lane
 //      in order (the reference's f32 sum is sequential, so each chain is; 32 run side by side);
-//   3. the warps scale, Givens-rotate, find the nearest centroid (binary search + one neighbour
-//      check, same index as the reference's linear scan) and write `bits` bytes per lane;
+//   3. the warps scale, Givens-rotate, find the nearest centroid (a cell table or a binary search, then
+//      one neighbour check: the same index as the reference's linear scan) and write `bits` bytes per lane;
 //      f32/f16 rows leave as 128-bit stores.
 // Traffic per token is the algorithmic minimum: 2*n_kv*1 KiB in, rows + norms out.
 #include "bk_device.cuh"
@@ -38,6 +38,24 @@ __device__ __forceinline__ void store_planar_row(const float *sx, int lane, floa
         givens_fwd(a, b, givens[2 * i], givens[2 * i + 1], r0, r1);
         packed |= (uint64_t)nearest_centroid_fast<BITS>(r0, sbook) << (BITS * (2 * pr));
         packed |= (uint64_t)nearest_centroid_fast<BITS>(r1, sbook) << (BITS * (2 * pr + 1));
+    }
+    store_group8<BITS>(row, lane, packed);
+}
+
+// The same with the two-read centroid search (codebooks of up to 16 centroids).
+template <int BITS>
+__device__ __forceinline__ void store_planar_row_cell(const float *sx, int lane, float n, const float *givens,
+                                                      const float *sbook, const float4 *b4, const uint8_t *cells, uint8_t *row) {
+    const float inv = (n > 1e-12f) ? __fdiv_rn(1.0f, n) : 0.0f;
+    uint64_t packed = 0;
+#pragma unroll
+    for (int pr = 0; pr < 4; pr++) {
+        const int i = lane * 4 + pr;  // pair index: coordinates 2i, 2i+1
+        const float a = __fmul_rn(sx[2 * i], inv), b = __fmul_rn(sx[2 * i + 1], inv);
+        float r0, r1;
+        givens_fwd(a, b, givens[2 * i], givens[2 * i + 1], r0, r1);
+        packed |= (uint64_t)nearest_centroid_cell<BITS>(r0, sbook, b4, cells) << (BITS * (2 * pr));
+        packed |= (uint64_t)nearest_centroid_cell<BITS>(r1, sbook, b4, cells) << (BITS * (2 * pr + 1));
     }
     store_group8<BITS>(row, lane, packed);
 }
@@ -73,6 +91,8 @@ __global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
     float *sbook = smem + kVecs * kVecPad;  // centroids
     float *sgiv = sbook + 256;              // Givens table
     float *snorm = sgiv + kHd;              // the 32 norms
+    [[maybe_unused]] float4 *b4 = reinterpret_cast<float4 *>(snorm + 32);   // centroid neighbourhoods of the two-read search
+    [[maybe_unused]] uint8_t *cells = reinterpret_cast<uint8_t *>(b4 + 16); // its 512 cells
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kv = a.n_kv, per_tok = 2 * n_kv;
     const int n_vec = a.n_tokens * per_tok, v0 = blockIdx.x * kVecs;
@@ -81,6 +101,10 @@ __global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
     if (BITS > 0) {
         for (int i = threadIdx.x; i < (1 << BITS); i += kThreads) sbook[i] = a.book[i];
         for (int i = threadIdx.x; i < kHd; i += kThreads) sgiv[i] = a.givens[i];
+        if constexpr (BITS >= 1 && BITS <= 4) {
+            __syncthreads();
+            build_cell_tables(sbook, 1 << BITS, b4, cells);
+        }
     }
     // k and v may come from the previous kernel in the stream: with programmatic dependent launch
     // only the table copies above run ahead of it.  Nothing after this kernel depends on more
@@ -185,11 +209,13 @@ __global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
             if constexpr (BITS > 0) {
                 const float n = snorm[lv];
                 if (lane == 0) (is_v ? a.v_norms : a.k_norms)[r] = n;
-                store_planar_row<BITS>(sx, lane, n, sgiv, sbook, row);
+                if constexpr (BITS <= 4) store_planar_row_cell<BITS>(sx, lane, n, sgiv, sbook, b4, cells, row);
+                else store_planar_row<BITS>(sx, lane, n, sgiv, sbook, row);
             }
         }
     }
 }
+
 
 }  // namespace
 
@@ -199,7 +225,7 @@ bk_status launch_append(bk_ctx *ctx, const AppendArgs &a) {
     const size_t n_vec = (size_t)a.n_tokens * 2 * a.n_kv;
     const bool bulk = n_vec > (size_t)8 * 2 * ctx->n_sms;  // more than two small CTAs per SM: go for throughput
     const int vecs = bulk ? 32 : 8;
-    const size_t smem = (size_t)(vecs * kVecPad + 256 + kHd + vecs) * sizeof(float);
+    const size_t smem = (size_t)(vecs * kVecPad + 256 + kHd + 32) * sizeof(float) + 16 * sizeof(float4) + 512;
     const unsigned grid = (unsigned)((n_vec + vecs - 1) / vecs);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);

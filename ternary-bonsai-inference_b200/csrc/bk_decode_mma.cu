@@ -36,9 +36,10 @@
 //
 // Work split.  A launch has about one CTA (8 warps) per SM; a CTA owns a contiguous chunk of one
 // (sequence, kv head) - contiguous chunks stream measurably faster than interleaved ones - and
-// its warps draw the chunk's tiles one at a time from a counter in shared memory, the next draw
-// always made while the current tile is computed.  So the two warps that first store the new
-// token's rows (the fused append, in the CTA of the last chunk) simply take fewer tiles.
+// its warps take the chunk's tiles in fixed shares (the result then does not depend on timing);
+// in the CTA of the last chunk the two warps that first store the new token's rows (the fused
+// append) join after a head start of the others.  BONSAI_KV_DYN=1 lets the warps draw tiles from
+// a counter in shared memory instead (same speed on an idle GPU, results vary in the last bits).
 // Partials and the split-K combine are shared with the other decode kernels.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -259,15 +260,24 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             q_reg[u] = i < NREP * kHd ? __ldg(q + (size_t)(i >> 8) * a.q_stride + (i & 255)) : 0.f;
         }
     }
-    // ---- fill the ring: warp w starts with tiles w, w + 8, ... of the chunk
+    // Fixed shares (the default: the result then does not depend on timing).  Warp w takes tiles w, w + 8, ...;
+    // in the appending CTA warps 0 and 1 start late (they store the new rows first), so there the other six
+    // warps share the first kHeadStart rounds among themselves.
+    constexpr int kHeadStart = 4;
+    auto fixed_tile = [&](int i) -> int {
+        if (!appender) return warp + kMW * i;
+        if (warp < 2) return (kMW - 2) * kHeadStart + kMW * i + warp;
+        return i < kHeadStart ? (kMW - 2) * i + (warp - 2) : (kMW - 2) * kHeadStart + kMW * (i - kHeadStart) + warp;
+    };
+    // ---- fill the ring
     int in_stage[kMaxStages];  // which tile each stage holds, -1 = none
 #pragma unroll
     for (int st = 0; st < kMaxStages; st++) {
-        const int lt = warp + st * kMW;
+        const int lt = dyn ? warp + st * kMW : fixed_tile(st);
         in_stage[st] = (st < n_stages && lt < n_pool) ? lt : -1;
         if (in_stage[st] >= 0) issue_tile(lt, st);
     }
-    int i_next = n_stages;  // fixed shares (dyn off): the warp's next tile is warp + 8 i_next
+    int i_next = n_stages;
     // ---- q: per-head RMSNorm (layer form), rope, Givens rotation, scale, split into f16 hi/lo, written in the
     // MMA's B-fragment layout and then fetched by every lane into registers.  The scratch for this is the
     // unused upper half of the table's 256-byte slots (the table itself fills only the lower halves):
@@ -629,7 +639,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                     if (nu < n_pool) draw();  // the draw after this one
                     else nu = -1;
                 } else {
-                    nu = warp + kMW * i_next++;
+                    nu = fixed_tile(i_next++);
                     if (nu >= n_pool) nu = -1;
                 }
                 if (nu >= 0) issue_tile(nu, st);

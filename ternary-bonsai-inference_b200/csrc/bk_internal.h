@@ -67,7 +67,7 @@ struct bk_ctx {
     bool prefill_umma = true;              // batched attention on tcgen05; BONSAI_KV_PREFILL=mma picks the mma.sync kernel
     bool force_generic = false;            // BONSAI_KV_GENERIC=1: never take the tensor-core path
     bool qsplit = true;                    // q as f16 hi + lo in the tensor-core path (BONSAI_KV_QSPLIT=0: hi only)
-    int dyn_tiles = 1; bool dist_combine = true;  // BONSAI_KV_DYN=0 / BONSAI_KV_DIST=0 switch them off
+    int dyn_tiles = 0; bool dist_combine = true;  // BONSAI_KV_DYN=0 / BONSAI_KV_DIST=0 switch them off
     // staging for the *_host entry points (grown on demand)
     void *h_stage = nullptr;
     size_t h_stage_bytes = 0;
@@ -229,8 +229,8 @@ struct DecodeArgs {
     int *xch_err;
     int xch_spin;  // polls of one arrival word before the exchange gives up
     // Set by launch_decode_group for the tensor-core kernels:
-    //   dyn   the warps of a (sequence, kv head) draw their tiles from one shared pool (a counter in
-    //         the scratch) instead of a fixed share, so that a CTA that starts late takes less
+    //   dyn   bit 0: the warps of a CTA draw their tiles from a counter in shared memory instead of taking
+    //         fixed shares (off by default: with it the last bits of a result depend on timing)
     //   dist  every CTA of the launch is resident at once (items <= SMs): the split-K combine is
     //         done in slices by all CTAs of a kv head instead of by the last one to arrive
     //   counters_other / other_n  the counter set the next launch will count in, and how many of its

@@ -14,9 +14,15 @@ __global__ void quantize_kernel(int n_vec, const float *x, const float *givens, 
                                 uint8_t *packed, float *norms) {
     __shared__ __align__(16) float sx[4][kHd];
     __shared__ float sbook[256];
+    __shared__ float4 b4[16];       // tables of the two-read centroid search (codebooks of up to 16 centroids)
+    __shared__ uint8_t cells[512];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int vec = blockIdx.x * 4 + warp;
     for (int i = threadIdx.x; i < (1 << BITS); i += blockDim.x) sbook[i] = book[i];
+    if constexpr (BITS <= 4) {
+        __syncthreads();
+        build_cell_tables(sbook, 1 << BITS, b4, cells);
+    }
     if (vec < n_vec) {
         const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)vec * kHd);
         reinterpret_cast<float4 *>(sx[warp])[lane] = src[lane];
@@ -36,8 +42,13 @@ __global__ void quantize_kernel(int n_vec, const float *x, const float *givens, 
         float r0, r1;
         givens_fwd(__fmul_rn(sx[warp][2 * i], inv), __fmul_rn(sx[warp][2 * i + 1], inv), givens[2 * i],
                    givens[2 * i + 1], r0, r1);
-        word |= (uint64_t)nearest_centroid_fast<BITS>(r0, sbook) << (BITS * (2 * pr));
-        word |= (uint64_t)nearest_centroid_fast<BITS>(r1, sbook) << (BITS * (2 * pr + 1));
+        if constexpr (BITS <= 4) {  // the search the bulk append uses
+            word |= (uint64_t)nearest_centroid_cell<BITS>(r0, sbook, b4, cells) << (BITS * (2 * pr));
+            word |= (uint64_t)nearest_centroid_cell<BITS>(r1, sbook, b4, cells) << (BITS * (2 * pr + 1));
+        } else {
+            word |= (uint64_t)nearest_centroid_fast<BITS>(r0, sbook) << (BITS * (2 * pr));
+            word |= (uint64_t)nearest_centroid_fast<BITS>(r1, sbook) << (BITS * (2 * pr + 1));
+        }
     }
     store_group8<BITS>(packed + (size_t)vec * 32 * BITS, lane, word);
 }

@@ -195,7 +195,7 @@ def test_config5_context_262144_and_chunk_merges(bk, gpu_ctx, oracle):
         gpu_ctx.check(gpu_ctx.lib.bk_lse_merge(gpu_ctx.h, parts, NH, HD, dparts.ptr, dout.ptr))
         merged = dout.download((NH, HD), np.float32)
         err2, rel2 = close(merged, got.astype(np.float64))
-        assert err2 <= 2e-4 and rel2 <= 3e-4, (parts, err2, rel2)
+        assert err2 <= 2e-4 and rel2 <= 5e-4, (parts, err2, rel2)   # two GPU results, each about 1e-4 from the oracle
         err3, rel3 = close(merged, want.astype(np.float64))
         assert err3 <= 1e-3 and rel3 <= 1e-3, (parts, err3, rel3)
     cache.close()
