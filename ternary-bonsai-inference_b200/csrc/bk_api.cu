@@ -708,8 +708,9 @@ bk_status check_decode_entry(const bk_cache *c, int layer, int slot, const int32
 
 // One launch for up to kMaxSeqsPerLaunch sequences of one class.  Chunk length: generic kernel
 // about 4 CTAs per SM over the whole launch, at least 64 positions each; tensor-core kernel one
-// CTA per SM, chunks in units of 128 positions (8 warps x 16-position tiles); never more than
-// max_items work items (the capacity of the split-K scratch behind a.partials).
+// CTA per SM in one wave (chunks in units of 128 positions), or whole sequences when there are
+// at least as many (sequence, kv head) pairs as SMs; never more than max_items work items (the
+// capacity of the split-K scratch behind a.partials).
 bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntry *list, int nb, bool use_mma,
                               int max_items) {
     const int n_kv = a.n_kv;
@@ -717,29 +718,48 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
         return fail(ctx, BK_ERR_INVALID, "decode: more (sequence, kv head) pairs than the split-K scratch holds");
     DecodeMeta m{};
     m.n_seqs = nb;
+    // Longest first: the hardware hands CTAs out in index order, so a launch of more items than SMs then
+    // ends with its short items (slot[] keeps every sequence's place in the caller's arrays).
+    int order[kMaxSeqsPerLaunch];
+    for (int i = 0; i < nb; i++) order[i] = i;
+    std::stable_sort(order, order + nb, [&](int x, int y) { return list[x].np > list[y].np; });
     int64_t total = 0;
+    int max_np = 0;
     for (int i = 0; i < nb; i++) {
-        m.slot[i] = list[i].slot;
-        m.seq_id[i] = list[i].seq;
-        m.n_pos[i] = list[i].np;
-        m.q_pos[i] = list[i].qp;
-        total += list[i].np;
+        const DecodeEntry &e = list[order[i]];
+        m.slot[i] = e.slot;
+        m.seq_id[i] = e.seq;
+        m.n_pos[i] = e.np;
+        m.q_pos[i] = e.qp;
+        total += e.np;
+        max_np = std::max(max_np, e.np);
     }
     const int64_t gran = use_mma ? 128 : 64;
-    // A launch that already has at least half as many (sequence, kv head) pairs as SMs cannot be
-    // one balanced wave; it is cut into about four waves of equal-sized items instead and the
-    // hardware's in-order CTA dispatch evens out the ragged lengths.
-    const bool many = use_mma && (int64_t)nb * n_kv * 2 > ctx->n_sms;
-    int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * ((use_mma && !many) ? 1 : 4) / n_kv);
-    target_items = std::min<int64_t>(target_items, std::max<int64_t>(1, max_items / n_kv));
-    int64_t L = (total + target_items - 1) / target_items;
-    L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
-    for (;;) {
+    auto items_for = [&](int64_t len) {
         int64_t items = 0;
-        for (int i = 0; i < nb; i++) items += (int64_t)n_kv * ((m.n_pos[i] + L - 1) / L);
-        if (items <= max_items) break;
-        L *= 2;
+        for (int i = 0; i < nb; i++) items += (int64_t)n_kv * ((m.n_pos[i] + len - 1) / len);
+        return items;
+    };
+    int64_t L;
+    if (use_mma && (int64_t)nb * n_kv >= ctx->n_sms) {
+        // At least one (sequence, kv head) pair per SM: no split at all.  Every CTA scans a whole sequence
+        // and writes its output itself: no partials, no combine, and the SMs pick up the next pair as they
+        // finish (longest first).
+        L = ((int64_t)max_np + gran - 1) / gran * gran;
+    } else if (use_mma) {
+        // Fewer pairs than SMs: one wave.  The balanced chunk length, grown until the items fit the SMs, so
+        // that all CTAs are resident together (which the slice form of the split-K combine needs) and no
+        // second, nearly empty wave doubles the launch.
+        const int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms / n_kv);
+        L = (total + target_items - 1) / target_items;
+        L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
+        while (items_for(L) > ctx->n_sms && L < max_np) L += gran;
+    } else {
+        const int64_t target_items = std::max<int64_t>(1, (int64_t)ctx->n_sms * 4 / n_kv);  // about four CTAs per SM
+        L = (total + target_items - 1) / target_items;
+        L = std::max<int64_t>(gran, (L + gran - 1) / gran * gran);
     }
+    while (items_for(L) > max_items) L *= 2;
     m.chunk_len = (int)L;
     int items = 0;
     for (int i = 0; i < nb; i++) {

@@ -194,8 +194,6 @@ __device__ __forceinline__ bool combine_slice(const DecodeArgs &a, int slot, int
                                        : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     const float *gate = (a.gate && !a.partial) ? a.gate + ((size_t)slot * a.n_head + (size_t)kv * NREP) * a.gate_stride + d0 : nullptr;
-    float gv = 0.f;
-    if (gate && tid < NREP * dn) gv = __ldg(gate + (size_t)(tid / dn) * a.gate_stride + (tid % dn));
     if (warp < NREP) {  // one warp per head: global max, every chunk's factor, the merged l
         const int r = warp;
         constexpr int kPer = kFactorCap / 32;
@@ -253,17 +251,18 @@ __device__ __forceinline__ bool combine_slice(const DecodeArgs &a, int slot, int
     }
     __syncthreads();
     float *res = red + (size_t)4 * n_grp * n_col;  // [NREP][dn], fixed summation order over the groups
-    if (tid < NREP * dn) {
-        const int r = tid / dn, d = tid - r * dn;
+    const int n_out = NREP * dn, nthr = (int)blockDim.x;  // (up to 768 outputs for a slice of half a row: loop)
+    for (int i = tid; i < n_out; i += nthr) {
+        const int r = i / dn, d = i - r * dn;
         float t = 0.f;
         for (int g2 = 0; g2 < n_grp; g2++) t += red[((size_t)g2 * n_col + r * d4 + (d >> 2)) * 4 + (d & 3)];
-        res[tid] = t;
+        res[i] = t;
     }
     __syncthreads();
-    float o = 0.f;
-    const int r_o = tid / dn, d_o = tid - r_o * dn;
-    if (tid < NREP * dn) {
-        o = res[tid];
+    float *snd = res + n_out;  // context split: what this slice sends
+    for (int i = tid; i < n_out; i += nthr) {
+        const int r_o = i / dn, d_o = i - r_o * dn;
+        float o = res[i];
         if (v_planar) {  // undo the Givens rotation: coordinate d0 + d and its partner (src/forward.rs:349)
             const int pr = (d0 + d_o) >> 1;
             const float c = givens[2 * pr], sn = givens[2 * pr + 1];
@@ -271,23 +270,22 @@ __device__ __forceinline__ bool combine_slice(const DecodeArgs &a, int slot, int
             givens_inv(res[r_o * dn + (d_o & ~1)], res[r_o * dn + (d_o | 1)], c, sn, o0, o1);
             o = (d_o & 1) ? o1 : o0;
         }
-    }
-    if (a.xch_peer) {  // context split: this slice goes to every rank and is merged with theirs
-        float *snd = res + NREP * dn;
-        if (tid < NREP * dn) snd[tid] = o;
-        __syncthreads();
-        exchange_slice(a, NREP, slot, kv, d0, dn, snd, s_M, s_L, s_flag);
-        return true;
-    }
-    if (tid < NREP * dn) {
-        if (a.partial) {
+        if (a.xch_peer) {
+            snd[i] = o;
+        } else if (a.partial) {
             a.out[((size_t)slot * a.n_head + (size_t)kv * NREP + r_o) * kPartStride + d0 + d_o] = o;
         } else {
             const float Ls = s_L[r_o];
             o = Ls > 0.f ? o / Ls : 0.f;
-            if (gate) o *= 1.0f / (1.0f + expf(-gv));
+            // src/forward.rs:379-382 with src/kernels.rs:162: out *= 1 / (1 + exp(-gate))
+            if (gate) o *= 1.0f / (1.0f + expf(-__ldg(gate + (size_t)r_o * a.gate_stride + d_o)));
             a.out[((size_t)slot * a.n_head + (size_t)kv * NREP + r_o) * kHd + d0 + d_o] = o;
         }
+    }
+    if (a.xch_peer) {  // context split: this slice goes to every rank and is merged with theirs
+        __syncthreads();
+        exchange_slice(a, NREP, slot, kv, d0, dn, snd, s_M, s_L, s_flag);
+        return true;
     }
     if (a.partial && my_chunk == 0 && tid < NREP) {
         float *po = a.out + ((size_t)slot * a.n_head + (size_t)kv * NREP + tid) * kPartStride;
