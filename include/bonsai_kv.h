@@ -18,6 +18,19 @@
  *    the call is asynchronous on the context's stream.  Pointers named *_host
  *    are host pointers and the call returns after the result is in host memory.
  *  - The caller owns q/k/v/out buffers; the library owns caches and tables.
+ *  - Kernels of one context overlap at their edges: a kernel begins its set-up
+ *    while the one before it on the stream is finishing, and reads what earlier
+ *    calls produced (q, k, v, the cache) only after that kernel has completed.
+ *    Weights are read during the set-up: the norm weights given to
+ *    bk_attn_layer_step and the payloads given to bk_pq2_matvec* must be
+ *    complete in device memory before the PRECEDING call on the context is
+ *    issued, and must not be rewritten while calls are in flight (upload them
+ *    once with bk_memcpy_h2d + bk_synchronize).
+ *  - Every wait inside a kernel is bounded.  A wait that runs out (a peer of the
+ *    context split never sent its rows) sets an error word; every call that
+ *    blocks the host (bk_synchronize, the *_host forms, downloads, snapshots,
+ *    bk_event_elapsed_ms) then returns BK_ERR_CUDA with the reason, the step
+ *    in flight is void, and the context stays usable.
  *  - Layouts follow the reference: token-major [pos][kv_head][...].
  */
 #ifndef BONSAI_KV_H
@@ -43,7 +56,7 @@ typedef struct bk_event bk_event;
 typedef enum bk_status {
     BK_OK = 0,
     BK_ERR_INVALID = 1,     /* bad argument (null pointer, size mismatch, bits outside 1..8) */
-    BK_ERR_CUDA = 2,        /* a CUDA runtime call failed; text in bk_last_error */
+    BK_ERR_CUDA = 2,        /* a CUDA runtime call failed or a kernel gave up a bounded wait; text in bk_last_error */
     BK_ERR_OOM = 3,         /* device or host allocation failed */
     BK_ERR_RANGE = 4,       /* position beyond the allocated context (src/gdev.rs:907-912) */
     BK_ERR_UNSUPPORTED = 5  /* geometry this build has no kernel for (src/gdev.rs:274-282) */

@@ -1624,6 +1624,8 @@ bk_status bk_event_elapsed_ms(bk_ctx *ctx, bk_event *start, bk_event *stop, floa
     if (st != BK_OK) return st;
     BK_CUDA(ctx, cudaEventSynchronize(stop->ev));
     BK_CUDA(ctx, cudaEventElapsedTime(ms, start->ev, stop->ev));
+    // a time between two events is worthless if a kernel between them gave up a wait: report it here too
+    if (ctx->h_err && *ctx->h_err) return sync_and_check(ctx);
     return BK_OK;
 }
 

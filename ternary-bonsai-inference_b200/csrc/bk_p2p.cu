@@ -3,18 +3,23 @@
 // single-device); it is the exchange step of "one long sequence, context chunks per GPU".
 //
 // Every rank owns a mailbox (one cudaMalloc, shared with the other ranks' processes through CUDA
-// IPC): two parities x world slots of n_rows x (hd + 2) floats, and two parities x world x n_rows
-// arrival words.  bk_decode_attn_split scans the local chunk into (acc, m, l) rows and then
-// launches ONE kernel of n_rows CTAs: CTA h stores row h into slot [rank] of every rank's
-// mailbox with plain peer stores, publishes it with a system-scope release of the call's sequence
-// number, waits (bounded) until the arrival words of all ranks for row h carry that number, and
-// merges the world rows into out[h].  The transfer is 24.8 KB per rank and layer, so what
-// matters is latency: one launch, no host synchronisation, no collective-library call.
+// IPC; ranks of one process find each other's mailbox in a process-local registry): two parities x
+// world slots of n_rows x (hd + 2) floats, and two parities x world x kXchFlags arrival words.
+// The exchange runs slice by slice (exchange_slice() in bk_decode_common.cuh): whoever holds
+// dims [d0, d0 + dn) of a kv head's rows, merged over the rank's own chunks, stores them into slot
+// [rank] of every rank's mailbox with plain peer stores, publishes each octet of dims with a
+// system-scope release of the call's sequence number in the octet's own arrival word, waits
+// (bounded) until the same words of all ranks carry that number, and merges the world's values.
+// In the one-launch form the holders are the CTAs of the decode launch itself, each with its slice of
+// the split-K combine; exchange_merge_kernel below is the stand-alone form (one CTA per kv head, all
+// dims) for a rank whose decode ran as a separate launch or whose chunk is empty.  The transfer is
+// 24.8 KB per rank and layer, so what matters is latency: no host synchronisation, no
+// collective-library call.
 //
 // The only cross-GPU dependency is between kernels on DIFFERENT GPUs; every wait gives up after
-// kSpinLimit polls and flags the error instead of hanging.  Slots alternate with the parity of
-// the sequence number, so a rank that runs ahead by one call never overwrites rows still being
-// merged.  No TMA and no multicast is used on peer memory.
+// a bounded number of polls and raises the context's error word instead of hanging.  Slots alternate
+// with the parity of the sequence number, so a rank that runs ahead by one call never overwrites rows
+// still being merged.  No TMA and no multicast is used on peer memory.
 #include <cuda/atomic>
 #include <math_constants.h>
 
