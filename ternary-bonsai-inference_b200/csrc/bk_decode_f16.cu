@@ -1,6 +1,6 @@
-// Decode attention over an f16 cache (K and V rows of 256 halfs): tensor-core path.
+// Decode attention over an f16 or an f32 cache (K and V rows of 256 halfs or floats): tensor-core path.
 //
-// The stored halfs are MMA operands as they are, so the kernel is the 4-bit one without its
+// f16: the stored halfs are MMA operands as they are, so the kernel is the 4-bit one without its
 // lookup table: per warp a ring of shared-memory stages, each one tile of 16 positions of one kv
 // head (K 8 KiB + V 8 KiB), filled by the TMA engine as eight tiled copies of 16 rows x 128 bytes
 // (a 3-D tensor map over [position][kv head][512 B]; four column slabs per row because the
@@ -13,7 +13,17 @@
 // weights (p * 2^14) are each split into f16 hi + lo parts when QSPLIT is set, so both products
 // carry about 22 bits; the softmax runs in f32 in the exp2 domain.  Six of the eight MMA columns
 // are real heads (the GQA group).
-// The CPU path this replaces is src/forward.rs:318-343 (f16 rows widened, f32 dot, f64 softmax sum).
+//
+// f32 (EB = 4): the same contraction with every stored float split on the fly into f16 hi + lo
+// (x = hi + lo to about 22 bits; |x| up to 65504, which activations never approach), three MMAs
+// per fragment (hi.hi, lo.hi, hi.lo).  A row is 1 KiB = eight slabs, a tile of 16 positions 16 KiB
+// for K and as much for V, so a CTA has six warps with one K and one V buffer each (192 KiB), each
+// buffer with its own mbarrier and refilled as soon as its half of the tile is done; a row costs
+// a quarter of the instructions per byte of the 4-bit kernel, so six warps keep up with HBM.
+// Fragments are read with plain 8-byte (K: two adjacent coordinates of a row) and 4-byte (V: one
+// coordinate of two adjacent rows) loads, conflict-free under the 128-byte swizzle.
+// The CPU path this replaces is src/forward.rs:318-343 (f16 rows widened, f32 dot, f64 softmax sum)
+// and src/forward.rs:344-375 (f32 rows).
 //
 // Work split, partials and the last-arriver combine are shared with the other decode kernels.
 #include <cuda.h>
@@ -26,14 +36,21 @@ namespace bk {
 
 namespace {
 
-constexpr int kFW = 12;                  // warps per CTA
-constexpr int kFT = kFW * 32;
+constexpr int kMaxFW = 12;               // warps per CTA: 12 (f16), 8 of which 6 scan (f32)
 constexpr int kTile = 16;                // positions per warp tile (the MMA's M)
 constexpr int kSlabBytes = kTile * 128;  // 16 rows x 128 B, 128B-swizzled
-constexpr int kSlabs = 4;                // 512-byte rows = 4 slabs
-constexpr int kHalfStage = kSlabs * kSlabBytes;  // one K or V tile: 8 KiB
-constexpr int kStageBytes = 2 * kHalfStage;      // 16 KiB
 constexpr int kMaxStages = 2;
+template <int EB> struct Rows {          // EB: bytes per stored element
+    static constexpr int kFW = EB == 2 ? 12 : 8;             // warps in the CTA
+    static constexpr int kScanW = EB == 2 ? 12 : 6;          // of which this many scan (f32: six buffers of 32 KiB fit)
+    static constexpr int kFT = kFW * 32;
+    static constexpr int kSlabs = EB * 2;                    // 512- or 1024-byte rows = 4 or 8 slabs
+    static constexpr int kHalfStage = kSlabs * kSlabBytes;   // one K or V tile: 8 or 16 KiB
+    static constexpr int kStageBytes = 2 * kHalfStage;       // 16 or 32 KiB
+    // f16: up to two stages per warp, one barrier per stage.  f32: one stage per warp, its K and V halves
+    // with a barrier each (bar[warp][0], bar[warp][1]).
+    static constexpr bool kSplitHalves = EB == 4;
+};
 constexpr int kHeadStride = 276;         // floats per head in the warp-merge area (bank-conflict free)
 constexpr float kWScale = 16384.0f;      // 2^14: V weights are stored as f16 in (0, 2^14]
 
@@ -43,17 +60,30 @@ struct Other {
     float new_row[2][kHd];               // the newest token's k and v of this kv head (fused append)
     float2 rope_row[kHd / 2];            // (cos, sin) of the q position
     float qw[kHd];                       // q RMSNorm weight (layer form of the step)
-    float m_w[kFW][8], l_w[kFW][8];
+    float m_w[kMaxFW][8], l_w[kMaxFW][8];
     float M[8], L[8];
     int last;
-    unsigned long long bar[kFW][kMaxStages];
+    unsigned long long bar[kMaxFW][kMaxStages];
     unsigned long long fin_bar[2];       // the split-K combine's two streaming rounds
 };
 
-template <int NREP, bool QSPLIT>
-__global__ void __launch_bounds__(kFT, 1)
+// f32 -> f16 hi + lo for two values at once: hi = rn(x), lo = rn(x - hi).
+__device__ __forceinline__ void split_pair(float x0, float x1, uint32_t &hi, uint32_t &lo) {
+    const __half2 h = __floats2half2_rn(x0, x1);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
+    hi = *reinterpret_cast<const uint32_t *>(&h);
+    lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+
+template <int EB, int NREP, bool QSPLIT>
+__global__ void __launch_bounds__(Rows<EB>::kFT, 1)
 decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *err_flag,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+    constexpr int kFW = Rows<EB>::kFW, kFT = Rows<EB>::kFT, kSlabs = Rows<EB>::kSlabs, kScanW = Rows<EB>::kScanW;
+    constexpr int kHalfStage = Rows<EB>::kHalfStage, kStageBytes = Rows<EB>::kStageBytes;
+    constexpr bool kSplit = Rows<EB>::kSplitHalves;
+    constexpr int kRowB = 256 * EB;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -63,7 +93,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     Other &o = *reinterpret_cast<Other *>(smem_raw);
     const uint32_t ring0 = (base + (uint32_t)sizeof(Other) + 1023u) & ~1023u;
     const uint32_t ring_end = base + smem_bytes;
-    const int n_stages = ring_end > ring0 ? min((int)((ring_end - ring0) / (uint32_t)(kFW * kStageBytes)), kMaxStages) : 0;
+    const int n_stages = ring_end > ring0 ? min((int)((ring_end - ring0) / (uint32_t)(kScanW * kStageBytes)), kSplit ? 1 : kMaxStages) : 0;
     if (n_stages < 1) {  // never expected (the host checks the size): report, do not run
         if (tid == 0) raise_error(err_flag, 2);
         return;
@@ -99,6 +129,16 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
                 tma_tile_x(dst + sl * kSlabBytes, &tm_k, sl * 128, kv, pos, bar);
                 tma_tile_x(dst + kHalfStage + sl * kSlabBytes, &tm_v, sl * 128, kv, pos, bar);
             }
+        }
+    };
+    // f32: one half (0 = K, 1 = V) of the warp's single stage, on that half's own barrier
+    auto issue_half = [&](int tile, int half) {
+        if (lane == 0) {
+            const uint32_t bar = bar0 + (uint32_t)half * 8u, dst = stage_of(0) + (uint32_t)(half * kHalfStage);
+            mbar_expect_tx(bar, kHalfStage);
+            const int pos = gpos0 + tile * kTile;
+#pragma unroll
+            for (int sl = 0; sl < kSlabs; sl++) tma_tile_x(dst + sl * kSlabBytes, half ? &tm_v : &tm_k, sl * 128, kv, pos, bar);
         }
     };
     auto wait_tile = [&](int st, uint32_t parity) {
@@ -165,21 +205,33 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
                 }
                 __syncwarp();
             }
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-                w[i] = (uint32_t)f32_to_half_ref(sx[lane * 8 + 2 * i]) | ((uint32_t)f32_to_half_ref(sx[lane * 8 + 2 * i + 1]) << 16);
             const size_t row = seq_rows + (size_t)(n_pos - 1) * a.n_kv + kv;
-            uint8_t *dst = (warp == 0 ? a.k_rows_w : a.v_rows_w) + row * 512;
-            reinterpret_cast<uint4 *>(dst)[lane] = make_uint4(w[0], w[1], w[2], w[3]);
+            uint8_t *dst = (warp == 0 ? a.k_rows_w : a.v_rows_w) + row * kRowB;
+            if constexpr (EB == 2) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    w[i] = (uint32_t)f32_to_half_ref(sx[lane * 8 + 2 * i]) | ((uint32_t)f32_to_half_ref(sx[lane * 8 + 2 * i + 1]) << 16);
+                reinterpret_cast<uint4 *>(dst)[lane] = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {  // f32 rows are stored as they are (src/forward.rs:279-285)
+                reinterpret_cast<float4 *>(dst)[lane] = reinterpret_cast<const float4 *>(sx)[lane];
+                reinterpret_cast<float4 *>(dst)[lane + 32] = reinterpret_cast<const float4 *>(sx)[lane + 32];
+            }
             __threadfence();
             asm volatile("fence.proxy.async;\n" ::: "memory");  // generic-proxy stores before the TMA reads below
         }
         __syncthreads();
     }
     // fill the ring now so that the copies fly during the rest of the set-up
-    for (int st = 0; st < n_stages; st++)
-        if (warp + st * kFW < n_tiles) issue_tile(warp + st * kFW, st);
+    if constexpr (kSplit) {
+        if (warp < kScanW && warp < n_tiles) {
+            issue_half(warp, 0);
+            issue_half(warp, 1);
+        }
+    } else {
+        for (int st = 0; st < n_stages; st++)
+            if (warp + st * kFW < n_tiles) issue_tile(warp + st * kFW, st);
+    }
 
     // ---- q: rope, scale, split into f16 hi/lo, laid out as B fragments ---------------------
     {
@@ -262,37 +314,71 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     const uint32_t k_row_off = (uint32_t)((lane & 7) + ((lane >> 3) & 1) * 8) * 128u, k_csel = (uint32_t)(lane >> 4);
     const uint32_t v_row_off = (uint32_t)((lane & 7) + (lane >> 4) * 8) * 128u, v_csel = (uint32_t)((lane >> 3) & 1);
 
-    auto compute_tile = [&](int tile, uint32_t st_addr) {
+    // Ragged last tile of the sequence: the rows past its end hold whatever the cache has there, possibly
+    // non-finite values, and 0 * Inf would poison the accumulators.  Zero them (one K or V tile at addr).
+    auto zero_tail = [&](uint32_t addr, int valid) {
+        for (int i = lane; i < kSlabs * kTile * 8; i += 32) {
+            const int slab = i >> 7, r = (i >> 3) & 15, c = i & 7;
+            if (r >= valid)
+                asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(addr + (uint32_t)(slab * kSlabBytes + r * 128 + c * 16)), "r"(0u) : "memory");
+        }
+        __syncwarp();
+    };
+    // ---- scores^T = K . Q^T for the tile at k_addr, then the online softmax: leaves the V weights (B fragments)
+    uint32_t b0 = 0, b1 = 0, b0l = 0, b1l = 0;
+    auto compute_scores = [&](int tile, uint32_t k_addr) {
         const int pb = p0 + tile * kTile;
-        if (pb + kTile > p1) {
-            // Ragged last tile of the sequence: the rows past its end hold whatever the cache has
-            // there, possibly non-finite halfs, and 0 * Inf would poison the accumulators.  Zero them.
-            const int valid = p1 - pb;
-            for (int i = lane; i < 2 * kSlabs * kTile * 8; i += 32) {
-                const int slab = i >> 7, r = (i >> 3) & 15, c = i & 7;
-                if (r >= valid)
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(st_addr + (uint32_t)(slab * kSlabBytes + r * 128 + c * 16)), "r"(0u) : "memory");
-            }
-            __syncwarp();
-        }
-        // ---- scores^T = K . Q^T; four independent accumulator chains --------------------------
-        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
-        float sc2[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-            const uint32_t addr = st_addr + (uint32_t)((ks >> 2) * kSlabBytes) + k_row_off + ((((uint32_t)(2 * (ks & 3)) + k_csel) ^ key) << 4);
-            uint32_t a0, a1, a2, a3, qx, qy;
-            ldmatrix_x4(addr, a0, a1, a2, a3);
-            q_frag(qh_addr, ks, qx, qy);
-            mma16816((ks & 1) ? sb : sa, a0, a1, a2, a3, qx, qy);
-            if (QSPLIT) {
-                q_frag(ql_addr, ks, qx, qy);
-                mma16816((ks & 1) ? sd : sc2, a0, a1, a2, a3, qx, qy);
-            }
-        }
+        if (pb + kTile > p1) zero_tail(k_addr, p1 - pb);
         float sc[4];
+        if constexpr (EB == 2) {
+            // four independent accumulator chains
+            float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+            float sc2[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < 4; i++) sc[i] = (sa[i] + sb[i]) + (sc2[i] + sd[i]);
+            for (int ks = 0; ks < 16; ks++) {
+                const uint32_t addr = k_addr + (uint32_t)((ks >> 2) * kSlabBytes) + k_row_off + ((((uint32_t)(2 * (ks & 3)) + k_csel) ^ key) << 4);
+                uint32_t a0, a1, a2, a3, qx, qy;
+                ldmatrix_x4(addr, a0, a1, a2, a3);
+                q_frag(qh_addr, ks, qx, qy);
+                mma16816((ks & 1) ? sb : sa, a0, a1, a2, a3, qx, qy);
+                if (QSPLIT) {
+                    q_frag(ql_addr, ks, qx, qy);
+                    mma16816((ks & 1) ? sd : sc2, a0, a1, a2, a3, qx, qy);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) sc[i] = (sa[i] + sb[i]) + (sc2[i] + sd[i]);
+        } else {
+            // k-step ks: coordinates 16 ks .. + 15 = 64 bytes of slab ks / 2.  Lane (g, t) reads the pairs
+            // (2t, 2t + 1) and (2t + 8, 2t + 9) of rows g and g + 8: 8-byte loads at chunk (4 (ks & 1) + t / 2
+            // (+ 2)) ^ g, half t & 1.  Three chains: hi.hi, lo.hi, hi.lo.
+            float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t row_g = k_addr + (uint32_t)(g * 128) + (uint32_t)((t & 1) * 8);
+#pragma unroll
+            for (int ks = 0; ks < 16; ks++) {
+                const uint32_t slab = row_g + (uint32_t)((ks >> 1) * kSlabBytes);
+                const uint32_t c0 = (((uint32_t)(4 * (ks & 1) + (t >> 1))) ^ (uint32_t)g) << 4, c1 = (((uint32_t)(4 * (ks & 1) + 2 + (t >> 1))) ^ (uint32_t)g) << 4;
+                float2 x0, x1, x2, x3;
+                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(x0.x), "=f"(x0.y) : "r"(slab + c0));
+                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(x1.x), "=f"(x1.y) : "r"(slab + 8 * 128 + c0));
+                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(x2.x), "=f"(x2.y) : "r"(slab + c1));
+                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(x3.x), "=f"(x3.y) : "r"(slab + 8 * 128 + c1));
+                uint32_t h0, h1, h2, h3, l0_, l1_, l2_, l3_, qx, qy;
+                split_pair(x0.x, x0.y, h0, l0_);
+                split_pair(x1.x, x1.y, h1, l1_);
+                split_pair(x2.x, x2.y, h2, l2_);
+                split_pair(x3.x, x3.y, h3, l3_);
+                q_frag(qh_addr, ks, qx, qy);
+                mma16816(sa, h0, h1, h2, h3, qx, qy);
+                mma16816(sb, l0_, l1_, l2_, l3_, qx, qy);
+                if (QSPLIT) {
+                    q_frag(ql_addr, ks, qx, qy);
+                    mma16816(sc2, h0, h1, h2, h3, qx, qy);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) sc[i] = (sa[i] + sc2[i]) + sb[i];
+        }
         // ---- online softmax in the exp2 domain ------------------------------------------------
         const bool ok0 = pb + g < p1, ok1 = pb + g + 8 < p1;
         const float t00 = ok0 ? sc[0] : -CUDART_INF_F, t01 = ok0 ? sc[1] : -CUDART_INF_F;
@@ -325,36 +411,88 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
         l1 += e01 + e11;
         const float w00 = e00 * kWScale, w01 = e01 * kWScale, w10 = e10 * kWScale, w11 = e11 * kWScale;
         const __half2 pl = __floats2half2_rn(w00, w01), ph = __floats2half2_rn(w10, w11);
-        const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
-        const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
+        b0 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
+        b1 = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
         // The weights get a low part as well: V rows are raw activations, and with a peaked softmax
         // over rows of very different size a single f16 weight (11 bits) would show in the output.
-        uint32_t b0l = 0, b1l = 0;
         if (QSPLIT) {
             const float2 fl = __half22float2(pl), fh = __half22float2(ph);
             const __half2 ql = __floats2half2_rn(w00 - fl.x, w01 - fl.y), qh = __floats2half2_rn(w10 - fh.x, w11 - fh.y);
             b0l = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ql));
             b1l = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&qh));
         }
-        // ---- out^T += V^T . W : MMA j covers coordinates 16j + g (c0, c1) and 16j + g + 8 (c2, c3)
-        const uint32_t v_tile = st_addr + kHalfStage;
+    };
+    // ---- out^T += V^T . W for the tile at v_tile: MMA j covers coordinates 16j + g (c0, c1) and 16j + g + 8 (c2, c3)
+    auto compute_out = [&](int tile, uint32_t v_tile) {
+        const int pb = p0 + tile * kTile;
+        if (pb + kTile > p1) zero_tail(v_tile, p1 - pb);
+        if constexpr (EB == 2) {
 #pragma unroll
-        for (int j = 0; j < 16; j++) {
-            const uint32_t addr = v_tile + (uint32_t)((j >> 2) * kSlabBytes) + v_row_off + ((((uint32_t)(2 * (j & 3)) + v_csel) ^ key) << 4);
-            uint32_t a0, a1, a2, a3;
-            ldmatrix_x4_trans(addr, a0, a1, a2, a3);
-            mma16816(acc[j], a0, a1, a2, a3, b0, b1);
-            if (QSPLIT) mma16816(acc[j], a0, a1, a2, a3, b0l, b1l);
+            for (int j = 0; j < 16; j++) {
+                const uint32_t addr = v_tile + (uint32_t)((j >> 2) * kSlabBytes) + v_row_off + ((((uint32_t)(2 * (j & 3)) + v_csel) ^ key) << 4);
+                uint32_t a0, a1, a2, a3;
+                ldmatrix_x4_trans(addr, a0, a1, a2, a3);
+                mma16816(acc[j], a0, a1, a2, a3, b0, b1);
+                if (QSPLIT) mma16816(acc[j], a0, a1, a2, a3, b0l, b1l);
+            }
+        } else {
+            // Block j: coordinates 16 j .. + 15 = 64 bytes of slab j / 2.  Lane (g, t) reads coordinate g (and
+            // g + 8) of position rows 2t, 2t + 1, 2t + 8, 2t + 9: 4-byte loads at chunk (4 (j & 1) + g / 4 (+ 2)) ^
+            // (row & 7), word g & 3 (rows r and r + 8 share the swizzle).
+            const uint32_t ra = (uint32_t)(2 * t), rb = (uint32_t)(2 * t + 1);
+            const uint32_t wsel = (uint32_t)((g & 3) * 4);
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const uint32_t slab = v_tile + (uint32_t)((j >> 1) * kSlabBytes) + wsel;
+                const uint32_t cl = (uint32_t)(4 * (j & 1) + (g >> 2)), ch = cl + 2;
+                const uint32_t a_lo = slab + ra * 128 + ((cl ^ ra) << 4), b_lo = slab + rb * 128 + ((cl ^ rb) << 4);
+                const uint32_t a_hi = slab + ra * 128 + ((ch ^ ra) << 4), b_hi = slab + rb * 128 + ((ch ^ rb) << 4);
+                float v00, v01, v10, v11, v20, v21, v30, v31;
+                asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v00) : "r"(a_lo));              // dim g,     pos 2t
+                asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v01) : "r"(b_lo));              // dim g,     pos 2t + 1
+                asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v10) : "r"(a_hi));              // dim g + 8, pos 2t
+                asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v11) : "r"(b_hi));              // dim g + 8, pos 2t + 1
+                asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v20) : "r"(a_lo + 8 * 128));    // dim g,     pos 2t + 8
+                asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v21) : "r"(b_lo + 8 * 128));    // dim g,     pos 2t + 9
+                asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v30) : "r"(a_hi + 8 * 128));    // dim g + 8, pos 2t + 8
+                asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v31) : "r"(b_hi + 8 * 128));    // dim g + 8, pos 2t + 9
+                uint32_t h0, h1, h2, h3, l0_, l1_, l2_, l3_;
+                split_pair(v00, v01, h0, l0_);
+                split_pair(v10, v11, h1, l1_);
+                split_pair(v20, v21, h2, l2_);
+                split_pair(v30, v31, h3, l3_);
+                mma16816(acc[j], h0, h1, h2, h3, b0, b1);
+                mma16816(acc[j], l0_, l1_, l2_, l3_, b0, b1);
+                if (QSPLIT) mma16816(acc[j], h0, h1, h2, h3, b0l, b1l);
+            }
         }
     };
 
-    // ---- scan: the warp's tiles are warp, warp + kFW, ...; tile i lives in stage i % n_stages ---
-    {
+    // ---- scan: the warp's tiles are warp, warp + kScanW, ...
+    if constexpr (kSplit) {
+        // one K and one V buffer per warp; each is refilled with the next tile's half as soon as it is consumed
+        uint32_t parity = 0;
+        if (warp < kScanW)
+            for (int tile = warp; tile < n_tiles; tile += kScanW) {
+                const uint32_t st_addr = stage_of(0);
+                wait_tile(0, parity);
+                compute_scores(tile, st_addr);
+                __syncwarp();
+                if (tile + kScanW < n_tiles) issue_half(tile + kScanW, 0);
+                wait_tile(1, parity);
+                compute_out(tile, st_addr + kHalfStage);
+                __syncwarp();
+                if (tile + kScanW < n_tiles) issue_half(tile + kScanW, 1);
+                parity ^= 1u;
+            }
+    } else {
+        // tile i lives in stage i % n_stages
         int st = 0;
         uint32_t parity = 0;
         for (int tile = warp; tile < n_tiles; tile += kFW) {
             wait_tile(st, parity);
-            compute_tile(tile, stage_of(st));
+            compute_scores(tile, stage_of(st));
+            compute_out(tile, stage_of(st) + kHalfStage);
             __syncwarp();  // every lane has read the stage: lane 0 may refill it
             if (tile + n_stages * kFW < n_tiles) issue_tile(tile + n_stages * kFW, st);
             if (++st == n_stages) { st = 0; parity ^= 1u; }
@@ -431,29 +569,30 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     finish_item<NREP, true>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, false, nullptr, fs);
 }
 
-template <int NREP, bool QSPLIT>
+template <int EB, int NREP, bool QSPLIT>
 bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m) {
+    constexpr int kScanW = Rows<EB>::kScanW, kFW = Rows<EB>::kFW, kStageBytes = Rows<EB>::kStageBytes;
     static size_t smem_for[64] = {};
     const int dev = ctx->device;
-    if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (f16 mma): device index above 63");
+    if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (row mma): device index above 63");
     if (smem_for[dev] == 0) {
         cudaFuncAttributes fa;
-        BK_CUDA(ctx, cudaFuncGetAttributes(&fa, decode_f16_mma_kernel<NREP, QSPLIT>));
+        BK_CUDA(ctx, cudaFuncGetAttributes(&fa, decode_f16_mma_kernel<EB, NREP, QSPLIT>));
         int optin = 0;
         BK_CUDA(ctx, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
         const size_t dyn = (size_t)optin - fa.sharedSizeBytes;
-        // bookkeeping + alignment slack + one stage per warp, and the merge area must fit the ring
-        const size_t need = sizeof(Other) + 1024 + (size_t)kFW * kStageBytes;
-        static_assert((size_t)kFW * kStageBytes >= (size_t)kFW * 6 * kHeadStride * 4, "merge area does not fit the ring");
-        if (dyn < need) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (f16 mma): not enough shared memory per block on this device");
-        BK_CUDA(ctx, cudaFuncSetAttribute(decode_f16_mma_kernel<NREP, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        // bookkeeping + alignment slack + one stage per scanning warp, and the merge area must fit the ring
+        const size_t need = sizeof(Other) + 1024 + (size_t)kScanW * kStageBytes;
+        static_assert((size_t)kScanW * kStageBytes >= (size_t)kFW * 6 * kHeadStride * 4, "merge area does not fit the ring");
+        if (dyn < need) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (row mma): not enough shared memory per block on this device");
+        BK_CUDA(ctx, cudaFuncSetAttribute(decode_f16_mma_kernel<EB, NREP, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
         smem_for[dev] = dyn;
     }
     const size_t smem = smem_for[dev];
-    if (!a.h_tmap_k || !a.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "decode (f16 mma): the cache has no tensor maps");
+    if (!a.h_tmap_k || !a.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "decode (row mma): the cache has no tensor maps");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)m.n_items);
-    cfg.blockDim = dim3(kFT);
+    cfg.blockDim = dim3(Rows<EB>::kFT);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -461,7 +600,7 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    BK_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_f16_mma_kernel<NREP, QSPLIT>, a, m, (uint32_t)smem, ctx->d_err,
+    BK_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_f16_mma_kernel<EB, NREP, QSPLIT>, a, m, (uint32_t)smem, ctx->d_err,
                                     *static_cast<const CUtensorMap *>(a.h_tmap_k),
                                     *static_cast<const CUtensorMap *>(a.h_tmap_v)));
     ctx->launches++;
@@ -473,22 +612,25 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m) {
 
 bool decode_f16_mma_supported(const DecodeArgs &a) {
     const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
-    return a.h_tmap_k && a.h_tmap_v && a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 &&
-           a.v_row_bytes == 512 && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
+    const bool f16 = a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 && a.v_row_bytes == 512;
+    const bool f32 = a.k_kind == ROW_F32 && a.v_kind == ROW_F32 && a.k_row_bytes == 1024 && a.v_row_bytes == 1024;
+    return a.h_tmap_k && a.h_tmap_v && (f16 || f32) && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
 bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, bool qsplit) {
     if (m.n_items <= 0) return BK_OK;
     const int n_rep = a.n_head / a.n_kv;
-#define BK_F16_CASE(R)                                                          \
-    case R:                                                                     \
-        return qsplit ? launch_one<R, true>(ctx, a, m) : launch_one<R, false>(ctx, a, m);
+    const bool f32 = a.k_kind == ROW_F32;
+#define BK_F16_CASE(R)                                                                                              \
+    case R:                                                                                                         \
+        if (f32) return qsplit ? launch_one<4, R, true>(ctx, a, m) : launch_one<4, R, false>(ctx, a, m);            \
+        return qsplit ? launch_one<2, R, true>(ctx, a, m) : launch_one<2, R, false>(ctx, a, m);
     switch (n_rep) {
         BK_F16_CASE(1)
         BK_F16_CASE(2)
         BK_F16_CASE(4)
         BK_F16_CASE(6)
-        default: return fail(ctx, BK_ERR_UNSUPPORTED, "decode (f16 mma): n_head/n_kv must be 1, 2, 4 or 6");
+        default: return fail(ctx, BK_ERR_UNSUPPORTED, "decode (row mma): n_head/n_kv must be 1, 2, 4 or 6");
     }
 #undef BK_F16_CASE
 }
