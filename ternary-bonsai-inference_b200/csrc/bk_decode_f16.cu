@@ -40,17 +40,23 @@ constexpr int kMaxFW = 12;               // warps per CTA: 12 (f16), 8 of which 
 constexpr int kTile = 16;                // positions per warp tile (the MMA's M)
 constexpr int kSlabBytes = kTile * 128;  // 16 rows x 128 B, 128B-swizzled
 constexpr int kMaxStages = 2;
-template <int EB> struct Rows {          // EB: bytes per stored element
-    static constexpr int kFW = EB == 2 ? 12 : 8;             // warps in the CTA
-    static constexpr int kScanW = EB == 2 ? 12 : 6;          // of which this many scan (f32: six buffers of 32 KiB fit)
+// KB / VB: bytes per stored K / V element (2 = f16, 4 = f32); KB = 0: K rows in the 4-bit planar format
+// (128 bytes of indices + a norm, src/kvquant.rs:397-412) beside f32 V rows, the reference's K-only mode.
+template <int KB, int VB> struct Rows {
+    static constexpr bool kPlanarK = KB == 0;
+    // f16 + f16: up to two stages per warp, one barrier per stage.  Otherwise: one stage per warp, its K and V
+    // halves with a barrier each (bar[warp][0], bar[warp][1]).
+    static constexpr bool kSplitHalves = !(KB == 2 && VB == 2);
+    static constexpr int kFW = kSplitHalves ? 8 : 12;        // warps in the CTA
+    static constexpr int kScanW = kSplitHalves ? 6 : 12;     // of which this many scan (six buffers of 32 KiB fit)
     static constexpr int kFT = kFW * 32;
-    static constexpr int kSlabs = EB * 2;                    // 512- or 1024-byte rows = 4 or 8 slabs
-    static constexpr int kHalfStage = kSlabs * kSlabBytes;   // one K or V tile: 8 or 16 KiB
-    static constexpr int kStageBytes = 2 * kHalfStage;       // 16 or 32 KiB
-    // f16: up to two stages per warp, one barrier per stage.  f32: one stage per warp, its K and V halves
-    // with a barrier each (bar[warp][0], bar[warp][1]).
-    static constexpr bool kSplitHalves = EB == 4;
+    static constexpr int kSlabsK = kPlanarK ? 1 : KB * 2;    // 128-byte column slabs per row: 4 (f16), 8 (f32), 1 (planar)
+    static constexpr int kSlabsV = VB * 2;
+    static constexpr int kHalfK = kPlanarK ? 3072 : kSlabsK * kSlabBytes;  // planar: the tile, then its norms (1 KiB slot)
+    static constexpr int kHalfV = kSlabsV * kSlabBytes;
+    static constexpr int kStageBytes = kHalfK + kHalfV;
 };
+constexpr uint32_t kLutBytes = 65536;    // planar K: 256 entries x 256 B, one word per lane (as in the 4-bit kernel)
 constexpr int kHeadStride = 276;         // floats per head in the warp-merge area (bank-conflict free)
 constexpr float kWScale = 16384.0f;      // 2^14: V weights are stored as f16 in (0, 2^14]
 
@@ -60,6 +66,8 @@ struct Other {
     float new_row[2][kHd];               // the newest token's k and v of this kv head (fused append)
     float2 rope_row[kHd / 2];            // (cos, sin) of the q position
     float qw[kHd];                       // q RMSNorm weight (layer form of the step)
+    float givens[kHd];                   // planar K: (cos, sin) pairs
+    float book[16];                      // planar K: unscaled centroids (fused append)
     float m_w[kMaxFW][8], l_w[kMaxFW][8];
     float M[8], L[8];
     int last;
@@ -76,14 +84,25 @@ __device__ __forceinline__ void split_pair(float x0, float x1, uint32_t &hi, uin
     lo = *reinterpret_cast<const uint32_t *>(&l);
 }
 
-template <int EB, int NREP, bool QSPLIT>
-__global__ void __launch_bounds__(Rows<EB>::kFT, 1)
-decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *err_flag,
+// Table lookup of packed byte K (0..3) of word x in a table that starts anywhere: the byte moves to bits 8..15
+// and is added to the lane's base address (table + 4 * lane).
+template <int K>
+__device__ __forceinline__ uint32_t lutx(uint32_t x, uint32_t lane_base) {
+    uint32_t off, v;
+    asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(off) : "r"(x), "r"(0u), "n"(0x4404 | (K << 4)));
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(off + lane_base));
+    return v;
+}
+
+template <int KB, int VB, int NREP, bool QSPLIT>
+__global__ void __launch_bounds__(Rows<KB, VB>::kFT, 1)
+decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t smem_bytes, int *err_flag,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
-    constexpr int kFW = Rows<EB>::kFW, kFT = Rows<EB>::kFT, kSlabs = Rows<EB>::kSlabs, kScanW = Rows<EB>::kScanW;
-    constexpr int kHalfStage = Rows<EB>::kHalfStage, kStageBytes = Rows<EB>::kStageBytes;
-    constexpr bool kSplit = Rows<EB>::kSplitHalves;
-    constexpr int kRowB = 256 * EB;
+    using R = Rows<KB, VB>;
+    constexpr int kFW = R::kFW, kFT = R::kFT, kSlabsK = R::kSlabsK, kSlabsV = R::kSlabsV, kScanW = R::kScanW;
+    constexpr int kHalfK = R::kHalfK, kHalfV = R::kHalfV, kStageBytes = R::kStageBytes;
+    constexpr bool kSplit = R::kSplitHalves, kPlanarK = R::kPlanarK;
+    constexpr int kRowK = kPlanarK ? 128 : 256 * KB, kRowV = 256 * VB;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -91,7 +110,10 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     // ---- shared-memory layout: bookkeeping first, then the ring on a 1 KiB boundary ----------
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem_raw);
     Other &o = *reinterpret_cast<Other *>(smem_raw);
-    const uint32_t ring0 = (base + (uint32_t)sizeof(Other) + 1023u) & ~1023u;
+    // planar K: the lookup table follows the bookkeeping block (256-byte aligned), the ring follows the table
+    const uint32_t lut_addr = (base + (uint32_t)sizeof(Other) + 255u) & ~255u;
+    const uint32_t ring0 = ((kPlanarK ? lut_addr + kLutBytes : base + (uint32_t)sizeof(Other)) + 1023u) & ~1023u;
+    [[maybe_unused]] const uint32_t lane_base = lut_addr + (uint32_t)(lane << 2);
     const uint32_t ring_end = base + smem_bytes;
     const int n_stages = ring_end > ring0 ? min((int)((ring_end - ring0) / (uint32_t)(kScanW * kStageBytes)), kSplit ? 1 : kMaxStages) : 0;
     if (n_stages < 1) {  // never expected (the host checks the size): report, do not run
@@ -119,26 +141,38 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     const int gpos0 = a.layer_pos0 + meta.seq_id[s] * a.n_ctx + p0;  // position index in the tensor map
 
     auto stage_of = [&](int st) -> uint32_t { return ring0 + (uint32_t)(warp * n_stages + st) * kStageBytes; };
-    auto issue_tile = [&](int tile, int st) {
+    auto issue_tile = [&](int tile, int st) {  // f16 + f16: a whole stage on one barrier
         if (lane == 0) {
             const uint32_t bar = bar0 + (uint32_t)st * 8u, dst = stage_of(st);
             mbar_expect_tx(bar, kStageBytes);
             const int pos = gpos0 + tile * kTile;
 #pragma unroll
-            for (int sl = 0; sl < kSlabs; sl++) {
-                tma_tile_x(dst + sl * kSlabBytes, &tm_k, sl * 128, kv, pos, bar);
-                tma_tile_x(dst + kHalfStage + sl * kSlabBytes, &tm_v, sl * 128, kv, pos, bar);
-            }
+            for (int sl = 0; sl < kSlabsK; sl++) tma_tile_x(dst + sl * kSlabBytes, &tm_k, sl * 128, kv, pos, bar);
+#pragma unroll
+            for (int sl = 0; sl < kSlabsV; sl++) tma_tile_x(dst + kHalfK + sl * kSlabBytes, &tm_v, sl * 128, kv, pos, bar);
         }
     };
-    // f32: one half (0 = K, 1 = V) of the warp's single stage, on that half's own barrier
+    // split form: one half (0 = K, 1 = V) of the warp's single stage, on that half's own barrier
+    const uint32_t nb_k = (uint32_t)(kTile * 4 * a.n_kv);  // planar K: the norms of 16 positions, every kv head
     auto issue_half = [&](int tile, int half) {
         if (lane == 0) {
-            const uint32_t bar = bar0 + (uint32_t)half * 8u, dst = stage_of(0) + (uint32_t)(half * kHalfStage);
-            mbar_expect_tx(bar, kHalfStage);
+            const uint32_t bar = bar0 + (uint32_t)half * 8u, dst = stage_of(0) + (uint32_t)(half * kHalfK);
             const int pos = gpos0 + tile * kTile;
+            if (half == 0) {
+                if constexpr (kPlanarK) {
+                    mbar_expect_tx(bar, kSlabBytes + nb_k);
+                    tma_tile_x(dst, &tm_k, 0, kv, pos, bar);
+                    tma_bulk(dst + kSlabBytes, a.k_norms + seq_rows + (size_t)(p0 + tile * kTile) * a.n_kv, nb_k, bar);
+                } else {
+                    mbar_expect_tx(bar, kHalfK);
 #pragma unroll
-            for (int sl = 0; sl < kSlabs; sl++) tma_tile_x(dst + sl * kSlabBytes, half ? &tm_v : &tm_k, sl * 128, kv, pos, bar);
+                    for (int sl = 0; sl < kSlabsK; sl++) tma_tile_x(dst + sl * kSlabBytes, &tm_k, sl * 128, kv, pos, bar);
+                }
+            } else {
+                mbar_expect_tx(bar, kHalfV);
+#pragma unroll
+                for (int sl = 0; sl < kSlabsV; sl++) tma_tile_x(dst + sl * kSlabBytes, &tm_v, sl * 128, kv, pos, bar);
+            }
         }
     };
     auto wait_tile = [&](int st, uint32_t parity) {
@@ -161,6 +195,17 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     }
     if (a.q_norm_w)
         for (int i = tid; i < kHd; i += kFT) o.qw[i] = a.q_norm_w[i];
+    if constexpr (kPlanarK) {
+        for (int i = tid; i < kHd; i += kFT) o.givens[i] = a.givens[i];
+        if (tid < 16) o.book[tid] = a.book[tid];
+        // the lookup table: entry e -> half2(alpha * c[low nibble], alpha * c[high nibble]), one copy per lane
+        uint8_t *lut_ptr = smem_raw + (lut_addr - base);
+        const float c_lo = a.book[lane & 15] * lut_alpha;
+        for (int e = warp; e < 256; e += kFW) {
+            const float lo = __shfl_sync(0xffffffffu, c_lo, e & 15), hi = __shfl_sync(0xffffffffu, c_lo, (e >> 4) & 15);
+            *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + lane * 4) = __floats2half2_rn(lo, hi);
+        }
+    }
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     // the counter set of the next launch: whatever the launch before the previous one left there goes now
     if (blockIdx.x == 0 && a.counters_other)
@@ -206,16 +251,33 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
                 __syncwarp();
             }
             const size_t row = seq_rows + (size_t)(n_pos - 1) * a.n_kv + kv;
-            uint8_t *dst = (warp == 0 ? a.k_rows_w : a.v_rows_w) + row * kRowB;
-            if constexpr (EB == 2) {
+            uint8_t *dst = warp == 0 ? a.k_rows_w + row * kRowK : a.v_rows_w + row * kRowV;
+            const int eb = warp == 0 ? KB : VB;
+            if (eb == 2) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; i++)
                     w[i] = (uint32_t)f32_to_half_ref(sx[lane * 8 + 2 * i]) | ((uint32_t)f32_to_half_ref(sx[lane * 8 + 2 * i + 1]) << 16);
                 reinterpret_cast<uint4 *>(dst)[lane] = make_uint4(w[0], w[1], w[2], w[3]);
-            } else {  // f32 rows are stored as they are (src/forward.rs:279-285)
+            } else if (eb == 4) {  // f32 rows are stored as they are (src/forward.rs:279-285)
                 reinterpret_cast<float4 *>(dst)[lane] = reinterpret_cast<const float4 *>(sx)[lane];
                 reinterpret_cast<float4 *>(dst)[lane + 32] = reinterpret_cast<const float4 *>(sx)[lane + 32];
+            } else {  // planar K row: norm, unit vector, Givens rotation, nearest centroid, pack (src/kvquant.rs:397-412)
+                float n = 0.f;
+                if (lane == 0) n = serial_norm(sx, kHd);
+                n = __shfl_sync(0xffffffffu, n, 0);
+                const float inv = (n > 1e-12f) ? __fdiv_rn(1.0f, n) : 0.0f;
+                uint64_t packed = 0;
+#pragma unroll
+                for (int pr = 0; pr < 4; pr++) {
+                    const int i = lane * 4 + pr;  // pair index: coordinates 2i, 2i+1
+                    float r0, r1;
+                    givens_fwd(__fmul_rn(sx[2 * i], inv), __fmul_rn(sx[2 * i + 1], inv), o.givens[2 * i], o.givens[2 * i + 1], r0, r1);
+                    packed |= (uint64_t)nearest_centroid_fast<4>(r0, o.book) << (4 * (2 * pr));
+                    packed |= (uint64_t)nearest_centroid_fast<4>(r1, o.book) << (4 * (2 * pr + 1));
+                }
+                store_group8<4>(dst, lane, packed);
+                if (lane == 0) a.k_norms_w[row] = n;
             }
             __threadfence();
             asm volatile("fence.proxy.async;\n" ::: "memory");  // generic-proxy stores before the TMA reads below
@@ -272,16 +334,30 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
         // 1/sqrt(hd) * log2(e): the scores come out in the exp2 domain.
         // k-step ks covers coordinates 16 ks .. 16 ks + 15; lane (g, t) holds head g's values at
         // 16 ks + 2t, +1 (b0) and 16 ks + 2t + 8, +9 (b1).
-        const float qscale = rsqrtf((float)kHd) * 1.4426950408889634f;
+        // Planar K: q is Givens-rotated into the stored rows' basis (src/forward.rs:304), the table's alpha is
+        // undone in the scale, and k-step ks = c*8 + w*2 + bp covers coordinates (2t+c)*32 + w*8 + bp*4 + 0..3
+        // (the order in which the packed bytes of a row come out of the table).
+        const float qscale = rsqrtf((float)kHd) * 1.4426950408889634f / (kPlanarK ? lut_alpha : 1.0f);
         for (int i = tid; i < 16 * 32; i += kFT) {
             const int ks = i >> 5, ln = i & 31, gg = ln >> 2, tt = ln & 3;
-            const int d0 = 16 * ks + 2 * tt;
             float x[4] = {0.f, 0.f, 0.f, 0.f};
-            if (gg < NREP) {
-                x[0] = sq[gg * kHd + d0] * qscale;
-                x[1] = sq[gg * kHd + d0 + 1] * qscale;
-                x[2] = sq[gg * kHd + d0 + 8] * qscale;
-                x[3] = sq[gg * kHd + d0 + 9] * qscale;
+            if constexpr (kPlanarK) {
+                const int c = ks >> 3, w = (ks >> 1) & 3, bp = ks & 1;
+                const int d0 = (2 * tt + c) * 32 + w * 8 + bp * 4;
+                if (gg < NREP) {
+                    givens_fwd(sq[gg * kHd + d0], sq[gg * kHd + d0 + 1], o.givens[d0], o.givens[d0 + 1], x[0], x[1]);
+                    givens_fwd(sq[gg * kHd + d0 + 2], sq[gg * kHd + d0 + 3], o.givens[d0 + 2], o.givens[d0 + 3], x[2], x[3]);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) x[e] *= qscale;
+                }
+            } else {
+                const int d0 = 16 * ks + 2 * tt;
+                if (gg < NREP) {
+                    x[0] = sq[gg * kHd + d0] * qscale;
+                    x[1] = sq[gg * kHd + d0 + 1] * qscale;
+                    x[2] = sq[gg * kHd + d0 + 8] * qscale;
+                    x[3] = sq[gg * kHd + d0 + 9] * qscale;
+                }
             }
             __half h[4], l[4];
 #pragma unroll
@@ -316,8 +392,8 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
 
     // Ragged last tile of the sequence: the rows past its end hold whatever the cache has there, possibly
     // non-finite values, and 0 * Inf would poison the accumulators.  Zero them (one K or V tile at addr).
-    auto zero_tail = [&](uint32_t addr, int valid) {
-        for (int i = lane; i < kSlabs * kTile * 8; i += 32) {
+    auto zero_tail = [&](uint32_t addr, int valid, int n_slabs) {
+        for (int i = lane; i < n_slabs * kTile * 8; i += 32) {
             const int slab = i >> 7, r = (i >> 3) & 15, c = i & 7;
             if (r >= valid)
                 asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(addr + (uint32_t)(slab * kSlabBytes + r * 128 + c * 16)), "r"(0u) : "memory");
@@ -328,9 +404,54 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     uint32_t b0 = 0, b1 = 0, b0l = 0, b1l = 0;
     auto compute_scores = [&](int tile, uint32_t k_addr) {
         const int pb = p0 + tile * kTile;
-        if (pb + kTile > p1) zero_tail(k_addr, p1 - pb);
+        if (pb + kTile > p1) zero_tail(k_addr, p1 - pb, kSlabsK);
         float sc[4];
-        if constexpr (EB == 2) {
+        if constexpr (kPlanarK) {
+            // the 4-bit kernel's K product for one row block: rows g and g + 8, chunks 2t and 2t + 1 (swizzled),
+            // every packed byte one table lookup = two adjacent coordinates; four chains
+            float S[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.f;
+            const uint32_t k_row = k_addr + (uint32_t)(g * 128);
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const uint32_t koff = (uint32_t)(((2 * t + c) ^ g) << 4);
+                const uint4 rk_g = lds128(k_row + koff), rk_h = lds128(k_row + 8 * 128 + koff);
+                const uint32_t kg[4] = {rk_g.x, rk_g.y, rk_g.z, rk_g.w}, kh[4] = {rk_h.x, rk_h.y, rk_h.z, rk_h.w};
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const int ks = c * 8 + w * 2;
+                    uint32_t qx, qy;
+                    {
+                        const uint32_t a0 = lutx<0>(kg[w], lane_base), a1 = lutx<0>(kh[w], lane_base);
+                        const uint32_t a2 = lutx<1>(kg[w], lane_base), a3 = lutx<1>(kh[w], lane_base);
+                        q_frag(qh_addr, ks, qx, qy);
+                        mma16816(S[c], a0, a1, a2, a3, qx, qy);
+                        if (QSPLIT) {
+                            q_frag(ql_addr, ks, qx, qy);
+                            mma16816(S[2 + c], a0, a1, a2, a3, qx, qy);
+                        }
+                    }
+                    {
+                        const uint32_t a0 = lutx<2>(kg[w], lane_base), a1 = lutx<2>(kh[w], lane_base);
+                        const uint32_t a2 = lutx<3>(kg[w], lane_base), a3 = lutx<3>(kh[w], lane_base);
+                        q_frag(qh_addr, ks + 1, qx, qy);
+                        mma16816(S[2 + c], a0, a1, a2, a3, qx, qy);
+                        if (QSPLIT) {
+                            q_frag(ql_addr, ks + 1, qx, qy);
+                            mma16816(S[c], a0, a1, a2, a3, qx, qy);
+                        }
+                    }
+                }
+            }
+            // the stored rows are unit vectors: their norms scale the scores (src/forward.rs:306)
+            float kn0, kn1;
+            const uint32_t na = k_addr + (uint32_t)kSlabBytes + (uint32_t)((g * a.n_kv + kv) * 4);
+            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(kn0) : "r"(na));
+            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(kn1) : "r"(na + (uint32_t)(8 * a.n_kv * 4)));
+#pragma unroll
+            for (int i = 0; i < 4; i++) sc[i] = ((S[0][i] + S[1][i]) + (S[2][i] + S[3][i])) * ((i >> 1) ? kn1 : kn0);
+        } else if constexpr (KB == 2) {
             // four independent accumulator chains
             float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
             float sc2[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
@@ -425,8 +546,8 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     // ---- out^T += V^T . W for the tile at v_tile: MMA j covers coordinates 16j + g (c0, c1) and 16j + g + 8 (c2, c3)
     auto compute_out = [&](int tile, uint32_t v_tile) {
         const int pb = p0 + tile * kTile;
-        if (pb + kTile > p1) zero_tail(v_tile, p1 - pb);
-        if constexpr (EB == 2) {
+        if (pb + kTile > p1) zero_tail(v_tile, p1 - pb, kSlabsV);
+        if constexpr (VB == 2) {
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 const uint32_t addr = v_tile + (uint32_t)((j >> 2) * kSlabBytes) + v_row_off + ((((uint32_t)(2 * (j & 3)) + v_csel) ^ key) << 4);
@@ -480,7 +601,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
                 __syncwarp();
                 if (tile + kScanW < n_tiles) issue_half(tile + kScanW, 0);
                 wait_tile(1, parity);
-                compute_out(tile, st_addr + kHalfStage);
+                compute_out(tile, st_addr + kHalfK);
                 __syncwarp();
                 if (tile + kScanW < n_tiles) issue_half(tile + kScanW, 1);
                 parity ^= 1u;
@@ -492,7 +613,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
         for (int tile = warp; tile < n_tiles; tile += kFW) {
             wait_tile(st, parity);
             compute_scores(tile, stage_of(st));
-            compute_out(tile, stage_of(st) + kHalfStage);
+            compute_out(tile, stage_of(st) + kHalfK);
             __syncwarp();  // every lane has read the stage: lane 0 may refill it
             if (tile + n_stages * kFW < n_tiles) issue_tile(tile + n_stages * kFW, st);
             if (++st == n_stages) { st = 0; parity ^= 1u; }
@@ -569,30 +690,32 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, uint32_t smem_bytes, int *e
     finish_item<NREP, true>(a, meta.slot[s], s, kv, item, n_chunks, first_item, s_acc, o.M, o.L, &o.last, false, nullptr, fs);
 }
 
-template <int EB, int NREP, bool QSPLIT>
-bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m) {
-    constexpr int kScanW = Rows<EB>::kScanW, kFW = Rows<EB>::kFW, kStageBytes = Rows<EB>::kStageBytes;
+template <int KB, int VB, int NREP, bool QSPLIT>
+bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float lut_alpha) {
+    using R = Rows<KB, VB>;
+    constexpr int kScanW = R::kScanW, kFW = R::kFW, kStageBytes = R::kStageBytes;
+    auto *kernel = decode_f16_mma_kernel<KB, VB, NREP, QSPLIT>;
     static size_t smem_for[64] = {};
     const int dev = ctx->device;
     if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (row mma): device index above 63");
     if (smem_for[dev] == 0) {
         cudaFuncAttributes fa;
-        BK_CUDA(ctx, cudaFuncGetAttributes(&fa, decode_f16_mma_kernel<EB, NREP, QSPLIT>));
+        BK_CUDA(ctx, cudaFuncGetAttributes(&fa, kernel));
         int optin = 0;
         BK_CUDA(ctx, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
         const size_t dyn = (size_t)optin - fa.sharedSizeBytes;
-        // bookkeeping + alignment slack + one stage per scanning warp, and the merge area must fit the ring
-        const size_t need = sizeof(Other) + 1024 + (size_t)kScanW * kStageBytes;
+        // bookkeeping + (planar K) the table + alignment slack + one stage per scanning warp; the merge area must fit the ring
+        const size_t need = sizeof(Other) + (R::kPlanarK ? kLutBytes + 256 : 0) + 1024 + (size_t)kScanW * kStageBytes;
         static_assert((size_t)kScanW * kStageBytes >= (size_t)kFW * 6 * kHeadStride * 4, "merge area does not fit the ring");
         if (dyn < need) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (row mma): not enough shared memory per block on this device");
-        BK_CUDA(ctx, cudaFuncSetAttribute(decode_f16_mma_kernel<EB, NREP, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        BK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
         smem_for[dev] = dyn;
     }
     const size_t smem = smem_for[dev];
     if (!a.h_tmap_k || !a.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "decode (row mma): the cache has no tensor maps");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)m.n_items);
-    cfg.blockDim = dim3(Rows<EB>::kFT);
+    cfg.blockDim = dim3(R::kFT);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -600,7 +723,7 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    BK_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_f16_mma_kernel<EB, NREP, QSPLIT>, a, m, (uint32_t)smem, ctx->d_err,
+    BK_CUDA(ctx, cudaLaunchKernelEx(&cfg, kernel, a, m, lut_alpha, (uint32_t)smem, ctx->d_err,
                                     *static_cast<const CUtensorMap *>(a.h_tmap_k),
                                     *static_cast<const CUtensorMap *>(a.h_tmap_v)));
     ctx->launches++;
@@ -608,23 +731,30 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m) {
     return BK_OK;
 }
 
+bool rows_f16(const DecodeArgs &a) { return a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 && a.v_row_bytes == 512; }
+bool rows_f32(const DecodeArgs &a) { return a.k_kind == ROW_F32 && a.v_kind == ROW_F32 && a.k_row_bytes == 1024 && a.v_row_bytes == 1024; }
+// K-only planar, 4 bit: the norms of a tile travel as a 16-byte aligned bulk copy (n_ctx * n_kv a multiple of 4) into a 1 KiB slot
+bool rows_p4_f32(const DecodeArgs &a) {
+    return a.k_kind == ROW_PLANAR && a.bits == 4 && a.v_kind == ROW_F32 && a.k_row_bytes == 128 && a.v_row_bytes == 1024 &&
+           a.seq_stride_rows % 4 == 0 && a.n_kv <= 16;
+}
+
 }  // namespace
 
 bool decode_f16_mma_supported(const DecodeArgs &a) {
     const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
-    const bool f16 = a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 && a.v_row_bytes == 512;
-    const bool f32 = a.k_kind == ROW_F32 && a.v_kind == ROW_F32 && a.k_row_bytes == 1024 && a.v_row_bytes == 1024;
-    return a.h_tmap_k && a.h_tmap_v && (f16 || f32) && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
+    return a.h_tmap_k && a.h_tmap_v && (rows_f16(a) || rows_f32(a) || rows_p4_f32(a)) && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
-bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, bool qsplit) {
+bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float lut_alpha, bool qsplit) {
     if (m.n_items <= 0) return BK_OK;
     const int n_rep = a.n_head / a.n_kv;
-    const bool f32 = a.k_kind == ROW_F32;
-#define BK_F16_CASE(R)                                                                                              \
-    case R:                                                                                                         \
-        if (f32) return qsplit ? launch_one<4, R, true>(ctx, a, m) : launch_one<4, R, false>(ctx, a, m);            \
-        return qsplit ? launch_one<2, R, true>(ctx, a, m) : launch_one<2, R, false>(ctx, a, m);
+    const int kind = rows_f16(a) ? 0 : rows_f32(a) ? 1 : 2;
+#define BK_F16_CASE(R)                                                                                                            \
+    case R:                                                                                                                       \
+        if (kind == 2) return qsplit ? launch_one<0, 4, R, true>(ctx, a, m, lut_alpha) : launch_one<0, 4, R, false>(ctx, a, m, lut_alpha); \
+        if (kind == 1) return qsplit ? launch_one<4, 4, R, true>(ctx, a, m, 1.0f) : launch_one<4, 4, R, false>(ctx, a, m, 1.0f);  \
+        return qsplit ? launch_one<2, 2, R, true>(ctx, a, m, 1.0f) : launch_one<2, 2, R, false>(ctx, a, m, 1.0f);
     switch (n_rep) {
         BK_F16_CASE(1)
         BK_F16_CASE(2)

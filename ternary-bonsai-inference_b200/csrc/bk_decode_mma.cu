@@ -772,11 +772,11 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
 
 }  // namespace
 
-// Tensor maps over the K and V rows of a cache whose rows are row_bytes long (128 for 4-bit planar,
-// 96 for 3-bit, 512 for f16): dims (row_bytes, n_kv, positions of all layers and sequences), box
+// Tensor maps over the K and V rows of a cache whose rows are k_row_bytes / v_row_bytes long (128 for
+// 4-bit planar, 96 for 3-bit, 512 for f16, 1024 for f32): dims (row_bytes, n_kv, positions of all layers and sequences), box
 // (128 bytes or the whole row, 1, box_rows positions), 128-byte swizzle where rows allow it.
 // Built once per cache.
-bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, size_t row_bytes, int n_kv,
+bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, size_t k_row_bytes, size_t v_row_bytes, int n_kv,
                                 size_t total_pos, int box_rows, void *out_k, void *out_v) {
     static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -794,18 +794,20 @@ bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_r
         encode_fn.store(encode);
     }
     if (total_pos >= (size_t)1 << 31) return fail(ctx, BK_ERR_UNSUPPORTED, "cache has more than 2^31 positions");
-    // rows of a multiple of 128 bytes travel as 128-byte swizzled slabs; shorter rows (96 bytes: 3 bit)
-    // as whole dense rows without a swizzle
-    const bool swizzled = row_bytes % 128 == 0;
-    if (!swizzled && (row_bytes % 16 != 0 || row_bytes > 256))
-        return fail(ctx, BK_ERR_UNSUPPORTED, "tensor maps need rows of a multiple of 16 bytes");
-    const cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)n_kv, (cuuint64_t)total_pos};
-    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)row_bytes * n_kv};
-    const cuuint32_t box[3] = {swizzled ? 128u : (cuuint32_t)row_bytes, 1, (cuuint32_t)box_rows};
-    const cuuint32_t estr[3] = {1, 1, 1};
     const void *ptrs[2] = {k_rows, v_rows};
+    const size_t row_bytes_of[2] = {k_row_bytes, v_row_bytes};
     void *outs[2] = {out_k, out_v};
     for (int i = 0; i < 2; i++) {
+        const size_t row_bytes = row_bytes_of[i];
+        // rows of a multiple of 128 bytes travel as 128-byte swizzled slabs; shorter rows (96 bytes: 3 bit)
+        // as whole dense rows without a swizzle
+        const bool swizzled = row_bytes % 128 == 0;
+        if (!swizzled && (row_bytes % 16 != 0 || row_bytes > 256))
+            return fail(ctx, BK_ERR_UNSUPPORTED, "tensor maps need rows of a multiple of 16 bytes");
+        const cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)n_kv, (cuuint64_t)total_pos};
+        const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)row_bytes * n_kv};
+        const cuuint32_t box[3] = {swizzled ? 128u : (cuuint32_t)row_bytes, 1, (cuuint32_t)box_rows};
+        const cuuint32_t estr[3] = {1, 1, 1};
         const CUresult r = encode(static_cast<CUtensorMap *>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
                                   const_cast<void *>(ptrs[i]), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                   swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

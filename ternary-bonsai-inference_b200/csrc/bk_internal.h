@@ -262,10 +262,10 @@ bk_status decode_with_exchange(bk_cache *c, int layer, int seq, int n_pos, int q
 bool decode_p4_mma_supported(const DecodeArgs &a);
 bool decode_f16_mma_supported(const DecodeArgs &a);
 inline bool decode_mma_supported(const DecodeArgs &a) { return decode_p4_mma_supported(a) || decode_f16_mma_supported(a); }
-bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, size_t row_bytes, int n_kv,
+bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, size_t k_row_bytes, size_t v_row_bytes, int n_kv,
                                 size_t total_pos, int box_rows, void *out_k, void *out_v);
 bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
-bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, bool qsplit);
+bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float lut_alpha, bool qsplit);
 // RMSNorm over rows (bk_layer.cu): up to two row groups per launch, each with its own source
 // stride, weight and contiguous destination.
 struct NormSeg {
