@@ -1,4 +1,5 @@
-// Decode attention over an f16 or an f32 cache (K and V rows of 256 halfs or floats): tensor-core path.
+// Decode attention over an f16 or an f32 cache (K and V rows of 256 halfs or floats), or 4/3-bit K rows beside
+// f32 V rows: tensor-core path.
 //
 // f16: the stored halfs are MMA operands as they are, so the kernel is the 4-bit one without its
 // lookup table: per warp a ring of shared-memory stages, each one tile of 16 positions of one kv
@@ -22,7 +23,12 @@
 // a quarter of the instructions per byte of the 4-bit kernel, so six warps keep up with HBM.
 // Fragments are read with plain 8-byte (K: two adjacent coordinates of a row) and 4-byte (V: one
 // coordinate of two adjacent rows) loads, conflict-free under the 128-byte swizzle.
-// The CPU path this replaces is src/forward.rs:318-343 (f16 rows widened, f32 dot, f64 softmax sum)
+// K-only planar (KB = -4, -3): the reference's mixed mode, quantized K beside f32 V (src/kvquant.rs:515-543
+// with the trailing 'k'; src/gdev.rs:706-717, 770-779).  The K product is the 4-bit kernel's for one row
+// block: a 256-entry table of half2(c[lo nibble], c[hi nibble]) per lane (here behind the bookkeeping
+// block, its index added to the lane's base), one lookup per packed byte, q Givens-rotated into the rows'
+// basis, the row norms (which travel with the K tile) on the scores; the V product is the f32 one.
+// The CPU path this replaces is src/forward.rs:297-343 (planar and f16 rows, f32 dot, f64 softmax sum)
 // and src/forward.rs:344-375 (f32 rows).
 //
 // Work split, partials and the last-arriver combine are shared with the other decode kernels.
@@ -40,10 +46,12 @@ constexpr int kMaxFW = 12;               // warps per CTA: 12 (f16), 8 of which 
 constexpr int kTile = 16;                // positions per warp tile (the MMA's M)
 constexpr int kSlabBytes = kTile * 128;  // 16 rows x 128 B, 128B-swizzled
 constexpr int kMaxStages = 2;
-// KB / VB: bytes per stored K / V element (2 = f16, 4 = f32); KB = 0: K rows in the 4-bit planar format
-// (128 bytes of indices + a norm, src/kvquant.rs:397-412) beside f32 V rows, the reference's K-only mode.
+// KB / VB: bytes per stored K / V element (2 = f16, 4 = f32); KB = -4 or -3: K rows in the 4- or 3-bit planar
+// format (128 or 96 bytes of indices + a norm, src/kvquant.rs:397-412) beside f32 V rows, the reference's
+// K-only mode.
 template <int KB, int VB> struct Rows {
-    static constexpr bool kPlanarK = KB == 0;
+    static constexpr bool kPlanarK = KB < 0;
+    static constexpr int kBits = kPlanarK ? -KB : 0;
     // f16 + f16: up to two stages per warp, one barrier per stage.  Otherwise: one stage per warp, its K and V
     // halves with a barrier each (bar[warp][0], bar[warp][1]).
     static constexpr bool kSplitHalves = !(KB == 2 && VB == 2);
@@ -84,6 +92,20 @@ __device__ __forceinline__ void split_pair(float x0, float x1, uint32_t &hi, uin
     lo = *reinterpret_cast<const uint32_t *>(&l);
 }
 
+// Eight 3-bit indices in the low 24 bits of y -> eight nibbles.
+__device__ __forceinline__ uint32_t expand24(uint32_t y) {
+    y &= 0x00ffffffu;
+    y += (y & 0x00fff000u) * 15u;   // upper four indices up by 4 bits
+    y += (y & 0x0fc00fc0u) * 3u;    // upper two of every four up by 2
+    y += (y & 0x38383838u);         // upper one of every two up by 1
+    return y;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
 // Table lookup of packed byte K (0..3) of word x in a table that starts anywhere: the byte moves to bits 8..15
 // and is added to the lane's base address (table + 4 * lane).
 template <int K>
@@ -102,7 +124,8 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
     constexpr int kFW = R::kFW, kFT = R::kFT, kSlabsK = R::kSlabsK, kSlabsV = R::kSlabsV, kScanW = R::kScanW;
     constexpr int kHalfK = R::kHalfK, kHalfV = R::kHalfV, kStageBytes = R::kStageBytes;
     constexpr bool kSplit = R::kSplitHalves, kPlanarK = R::kPlanarK;
-    constexpr int kRowK = kPlanarK ? 128 : 256 * KB, kRowV = 256 * VB;
+    constexpr int kBits = R::kBits, kRowK = kPlanarK ? 32 * kBits : 256 * KB, kRowV = 256 * VB;
+    [[maybe_unused]] constexpr int kKTile = kTile * kRowK;  // planar K: bytes of a tile (2048 or 1536)
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -160,7 +183,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
             const int pos = gpos0 + tile * kTile;
             if (half == 0) {
                 if constexpr (kPlanarK) {
-                    mbar_expect_tx(bar, kSlabBytes + nb_k);
+                    mbar_expect_tx(bar, kKTile + nb_k);
                     tma_tile_x(dst, &tm_k, 0, kv, pos, bar);
                     tma_bulk(dst + kSlabBytes, a.k_norms + seq_rows + (size_t)(p0 + tile * kTile) * a.n_kv, nb_k, bar);
                 } else {
@@ -197,12 +220,13 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
         for (int i = tid; i < kHd; i += kFT) o.qw[i] = a.q_norm_w[i];
     if constexpr (kPlanarK) {
         for (int i = tid; i < kHd; i += kFT) o.givens[i] = a.givens[i];
-        if (tid < 16) o.book[tid] = a.book[tid];
+        constexpr int kIdxMask = (1 << (kPlanarK ? kBits : 1)) - 1;
+        if (tid < 16) o.book[tid] = tid <= kIdxMask ? a.book[tid] : 0.f;
         // the lookup table: entry e -> half2(alpha * c[low nibble], alpha * c[high nibble]), one copy per lane
         uint8_t *lut_ptr = smem_raw + (lut_addr - base);
-        const float c_lo = a.book[lane & 15] * lut_alpha;
+        const float c_lo = a.book[lane & kIdxMask] * lut_alpha;
         for (int e = warp; e < 256; e += kFW) {
-            const float lo = __shfl_sync(0xffffffffu, c_lo, e & 15), hi = __shfl_sync(0xffffffffu, c_lo, (e >> 4) & 15);
+            const float lo = __shfl_sync(0xffffffffu, c_lo, e & kIdxMask), hi = __shfl_sync(0xffffffffu, c_lo, (e >> 4) & kIdxMask);
             *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + lane * 4) = __floats2half2_rn(lo, hi);
         }
     }
@@ -273,10 +297,11 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
                     const int i = lane * 4 + pr;  // pair index: coordinates 2i, 2i+1
                     float r0, r1;
                     givens_fwd(__fmul_rn(sx[2 * i], inv), __fmul_rn(sx[2 * i + 1], inv), o.givens[2 * i], o.givens[2 * i + 1], r0, r1);
-                    packed |= (uint64_t)nearest_centroid_fast<4>(r0, o.book) << (4 * (2 * pr));
-                    packed |= (uint64_t)nearest_centroid_fast<4>(r1, o.book) << (4 * (2 * pr + 1));
+                    constexpr int kB = kPlanarK ? kBits : 4;
+                    packed |= (uint64_t)nearest_centroid_fast<kB>(r0, o.book) << (kB * (2 * pr));
+                    packed |= (uint64_t)nearest_centroid_fast<kB>(r1, o.book) << (kB * (2 * pr + 1));
                 }
-                store_group8<4>(dst, lane, packed);
+                store_group8<(kPlanarK ? kBits : 4)>(dst, lane, packed);
                 if (lane == 0) a.k_norms_w[row] = n;
             }
             __threadfence();
@@ -404,7 +429,8 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
     uint32_t b0 = 0, b1 = 0, b0l = 0, b1l = 0;
     auto compute_scores = [&](int tile, uint32_t k_addr) {
         const int pb = p0 + tile * kTile;
-        if (pb + kTile > p1) zero_tail(k_addr, p1 - pb, kSlabsK);
+        if constexpr (!kPlanarK)  // (planar rows past the end are finite whatever their bytes; their scores are masked below)
+            if (pb + kTile > p1) zero_tail(k_addr, p1 - pb, kSlabsK);
         float sc[4];
         if constexpr (kPlanarK) {
             // the 4-bit kernel's K product for one row block: rows g and g + 8, chunks 2t and 2t + 1 (swizzled),
@@ -412,12 +438,40 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
             float S[4][4];
 #pragma unroll
             for (int i = 0; i < 4; i++) S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.f;
-            const uint32_t k_row = k_addr + (uint32_t)(g * 128);
+            const uint32_t k_row = k_addr + (uint32_t)(g * kRowK);
+            // 3 bit: coordinates 64 t .. 64 t + 63 of a row are 24 bytes (the tile is dense and unswizzled), read once
+            // as three 8-byte words and widened to words of eight nibbles: [row g / g + 8][c][w]
+            [[maybe_unused]] uint32_t k3[2][2][4];
+            if constexpr (kBits == 3) {
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++) {
+                    const uint32_t addr = k_row + (uint32_t)(8 * hh * kRowK) + 24 * t;
+                    const uint2 u01 = lds64(addr), u23 = lds64(addr + 8), u45 = lds64(addr + 16);
+                    k3[hh][0][0] = expand24(u01.x);
+                    k3[hh][0][1] = expand24(__funnelshift_r(u01.x, u01.y, 24));
+                    k3[hh][0][2] = expand24(__funnelshift_r(u01.y, u23.x, 16));
+                    k3[hh][0][3] = expand24(u23.x >> 8);
+                    k3[hh][1][0] = expand24(u23.y);
+                    k3[hh][1][1] = expand24(__funnelshift_r(u23.y, u45.x, 24));
+                    k3[hh][1][2] = expand24(__funnelshift_r(u45.x, u45.y, 16));
+                    k3[hh][1][3] = expand24(u45.y >> 8);
+                }
+            }
 #pragma unroll
             for (int c = 0; c < 2; c++) {
-                const uint32_t koff = (uint32_t)(((2 * t + c) ^ g) << 4);
-                const uint4 rk_g = lds128(k_row + koff), rk_h = lds128(k_row + 8 * 128 + koff);
-                const uint32_t kg[4] = {rk_g.x, rk_g.y, rk_g.z, rk_g.w}, kh[4] = {rk_h.x, rk_h.y, rk_h.z, rk_h.w};
+                uint32_t kg[4], kh[4];
+                if constexpr (kBits == 3) {
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        kg[w] = k3[0][c][w];
+                        kh[w] = k3[1][c][w];
+                    }
+                } else {
+                    const uint32_t koff = (uint32_t)(((2 * t + c) ^ g) << 4);
+                    const uint4 rk_g = lds128(k_row + koff), rk_h = lds128(k_row + 8 * 128 + koff);
+                    kg[0] = rk_g.x; kg[1] = rk_g.y; kg[2] = rk_g.z; kg[3] = rk_g.w;
+                    kh[0] = rk_h.x; kh[1] = rk_h.y; kh[2] = rk_h.z; kh[3] = rk_h.w;
+                }
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
                     const int ks = c * 8 + w * 2;
@@ -446,7 +500,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
             }
             // the stored rows are unit vectors: their norms scale the scores (src/forward.rs:306)
             float kn0, kn1;
-            const uint32_t na = k_addr + (uint32_t)kSlabBytes + (uint32_t)((g * a.n_kv + kv) * 4);
+            const uint32_t na = k_addr + (uint32_t)kSlabBytes + (uint32_t)((g * a.n_kv + kv) * 4);  // the norms sit behind the tile's 2 KiB slot
             asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(kn0) : "r"(na));
             asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(kn1) : "r"(na + (uint32_t)(8 * a.n_kv * 4)));
 #pragma unroll
@@ -733,26 +787,27 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
 
 bool rows_f16(const DecodeArgs &a) { return a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 && a.v_row_bytes == 512; }
 bool rows_f32(const DecodeArgs &a) { return a.k_kind == ROW_F32 && a.v_kind == ROW_F32 && a.k_row_bytes == 1024 && a.v_row_bytes == 1024; }
-// K-only planar, 4 bit: the norms of a tile travel as a 16-byte aligned bulk copy (n_ctx * n_kv a multiple of 4) into a 1 KiB slot
-bool rows_p4_f32(const DecodeArgs &a) {
-    return a.k_kind == ROW_PLANAR && a.bits == 4 && a.v_kind == ROW_F32 && a.k_row_bytes == 128 && a.v_row_bytes == 1024 &&
-           a.seq_stride_rows % 4 == 0 && a.n_kv <= 16;
+// K-only planar, 4 or 3 bit: the norms of a tile travel as a 16-byte aligned bulk copy (n_ctx * n_kv a multiple of 4) into a 1 KiB slot
+bool rows_pq_f32(const DecodeArgs &a) {
+    return a.k_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3) && a.v_kind == ROW_F32 && a.k_row_bytes == (size_t)(32 * a.bits) &&
+           a.v_row_bytes == 1024 && a.seq_stride_rows % 4 == 0 && a.n_kv <= 16;
 }
 
 }  // namespace
 
 bool decode_f16_mma_supported(const DecodeArgs &a) {
     const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
-    return a.h_tmap_k && a.h_tmap_v && (rows_f16(a) || rows_f32(a) || rows_p4_f32(a)) && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
+    return a.h_tmap_k && a.h_tmap_v && (rows_f16(a) || rows_f32(a) || rows_pq_f32(a)) && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
 bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float lut_alpha, bool qsplit) {
     if (m.n_items <= 0) return BK_OK;
     const int n_rep = a.n_head / a.n_kv;
-    const int kind = rows_f16(a) ? 0 : rows_f32(a) ? 1 : 2;
+    const int kind = rows_f16(a) ? 0 : rows_f32(a) ? 1 : a.bits == 4 ? 2 : 3;
 #define BK_F16_CASE(R)                                                                                                            \
     case R:                                                                                                                       \
-        if (kind == 2) return qsplit ? launch_one<0, 4, R, true>(ctx, a, m, lut_alpha) : launch_one<0, 4, R, false>(ctx, a, m, lut_alpha); \
+        if (kind == 2) return qsplit ? launch_one<-4, 4, R, true>(ctx, a, m, lut_alpha) : launch_one<-4, 4, R, false>(ctx, a, m, lut_alpha); \
+        if (kind == 3) return qsplit ? launch_one<-3, 4, R, true>(ctx, a, m, lut_alpha) : launch_one<-3, 4, R, false>(ctx, a, m, lut_alpha); \
         if (kind == 1) return qsplit ? launch_one<4, 4, R, true>(ctx, a, m, 1.0f) : launch_one<4, 4, R, false>(ctx, a, m, 1.0f);  \
         return qsplit ? launch_one<2, 2, R, true>(ctx, a, m, 1.0f) : launch_one<2, 2, R, false>(ctx, a, m, 1.0f);
     switch (n_rep) {
