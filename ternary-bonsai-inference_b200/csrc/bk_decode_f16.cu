@@ -28,6 +28,10 @@
 // block: a 256-entry table of half2(c[lo nibble], c[hi nibble]) per lane (here behind the bookkeeping
 // block, its index added to the lane's base), one lookup per packed byte, q Givens-rotated into the rows'
 // basis, the row norms (which travel with the K tile) on the scores; the V product is the f32 one.
+// Unlike the 4-bit kernel this one also carries what the rounding of the centroids to f16 left over (a second
+// half2 in the upper half of each table slot, one more load and one more MMA per fragment): V rows here are
+// raw activations, several times larger than dequantized ones, and the 11-bit table alone showed as 2e-3 in
+// the output at short contexts; with the remainders the result is within ~1e-5 of the f32 CPU path.
 // The CPU path this replaces is src/forward.rs:297-343 (planar and f16 rows, f32 dot, f64 softmax sum)
 // and src/forward.rs:344-375 (f32 rows).
 //
@@ -107,13 +111,14 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 }
 
 // Table lookup of packed byte K (0..3) of word x in a table that starts anywhere: the byte moves to bits 8..15
-// and is added to the lane's base address (table + 4 * lane).
+// and is added to the lane's base address (table + 4 * lane); the entry's rounding remainder (the slot's upper
+// half) comes with it.
 template <int K>
-__device__ __forceinline__ uint32_t lutx(uint32_t x, uint32_t lane_base) {
-    uint32_t off, v;
+__device__ __forceinline__ void lutx2(uint32_t x, uint32_t lane_base, uint32_t &v, uint32_t &rem) {
+    uint32_t off;
     asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(off) : "r"(x), "r"(0u), "n"(0x4404 | (K << 4)));
     asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(off + lane_base));
-    return v;
+    asm volatile("ld.shared.b32 %0, [%1+128];\n" : "=r"(rem) : "r"(off + lane_base));
 }
 
 template <int KB, int VB, int NREP, bool QSPLIT>
@@ -227,7 +232,12 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
         const float c_lo = a.book[lane & kIdxMask] * lut_alpha;
         for (int e = warp; e < 256; e += kFW) {
             const float lo = __shfl_sync(0xffffffffu, c_lo, e & kIdxMask), hi = __shfl_sync(0xffffffffu, c_lo, (e >> 4) & kIdxMask);
-            *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + lane * 4) = __floats2half2_rn(lo, hi);
+            const __half2 hv = __floats2half2_rn(lo, hi);
+            const float2 hf = __half22float2(hv);
+            *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + lane * 4) = hv;
+            // the upper half of the slot: what the rounding to f16 left over (the V rows of this mode are raw
+            // activations, so the scores need more than the table's 11 bits; see compute_scores)
+            *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + 128 + lane * 4) = __floats2half2_rn(lo - hf.x, hi - hf.y);
         }
     }
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
@@ -475,26 +485,29 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
                     const int ks = c * 8 + w * 2;
-                    uint32_t qx, qy;
-                    {
-                        const uint32_t a0 = lutx<0>(kg[w], lane_base), a1 = lutx<0>(kh[w], lane_base);
-                        const uint32_t a2 = lutx<1>(kg[w], lane_base), a3 = lutx<1>(kh[w], lane_base);
-                        q_frag(qh_addr, ks, qx, qy);
-                        mma16816(S[c], a0, a1, a2, a3, qx, qy);
-                        if (QSPLIT) {
-                            q_frag(ql_addr, ks, qx, qy);
-                            mma16816(S[2 + c], a0, a1, a2, a3, qx, qy);
-                        }
-                    }
-                    {
-                        const uint32_t a0 = lutx<2>(kg[w], lane_base), a1 = lutx<2>(kh[w], lane_base);
-                        const uint32_t a2 = lutx<3>(kg[w], lane_base), a3 = lutx<3>(kh[w], lane_base);
-                        q_frag(qh_addr, ks + 1, qx, qy);
+                    uint32_t qx, qy, a0, a1, a2, a3, r0, r1, r2, r3;
+                    // centroid = table value + remainder, q = hi + lo: value.hi, remainder.hi, value.lo
+                    lutx2<0>(kg[w], lane_base, a0, r0);
+                    lutx2<0>(kh[w], lane_base, a1, r1);
+                    lutx2<1>(kg[w], lane_base, a2, r2);
+                    lutx2<1>(kh[w], lane_base, a3, r3);
+                    q_frag(qh_addr, ks, qx, qy);
+                    mma16816(S[c], a0, a1, a2, a3, qx, qy);
+                    mma16816(S[2 + c], r0, r1, r2, r3, qx, qy);
+                    if (QSPLIT) {
+                        q_frag(ql_addr, ks, qx, qy);
                         mma16816(S[2 + c], a0, a1, a2, a3, qx, qy);
-                        if (QSPLIT) {
-                            q_frag(ql_addr, ks + 1, qx, qy);
-                            mma16816(S[c], a0, a1, a2, a3, qx, qy);
-                        }
+                    }
+                    lutx2<2>(kg[w], lane_base, a0, r0);
+                    lutx2<2>(kh[w], lane_base, a1, r1);
+                    lutx2<3>(kg[w], lane_base, a2, r2);
+                    lutx2<3>(kh[w], lane_base, a3, r3);
+                    q_frag(qh_addr, ks + 1, qx, qy);
+                    mma16816(S[2 + c], a0, a1, a2, a3, qx, qy);
+                    mma16816(S[c], r0, r1, r2, r3, qx, qy);
+                    if (QSPLIT) {
+                        q_frag(ql_addr, ks + 1, qx, qy);
+                        mma16816(S[c], a0, a1, a2, a3, qx, qy);
                     }
                 }
             }

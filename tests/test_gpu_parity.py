@@ -628,6 +628,106 @@ def test_fused_step_on_long_f16_cache(bk, gpu_ctx, oracle):
     cache.close()
 
 
+ROW_KERNEL_MODES = [("f32", MODE_F32, 0, False), ("planar4k", MODE_PLANAR, 4, False), ("planar3k", MODE_PLANAR, 3, False)]
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq", ROW_KERNEL_MODES)
+@pytest.mark.parametrize("env", [{"BONSAI_KV_GENERIC": "1"}, {}])
+def test_f32_and_k_only_kernel_variants(bk, oracle, monkeypatch, env, tag, mode, bits, vq):
+    """f32 caches and K-only 4/3-bit caches have the same two decode kernels behind one entry point (the
+    tensor-core row kernel from 2048 positions on).  Lengths hit ragged tiles, single chunks, many chunks
+    and a mixed batch."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    ctx = bk.Context(0)
+    for lens in ([2047], [2048], [2049], [2063, 2064, 2065], [5000], [21000, 3, 2500]):
+        got, want = run_both(bk, ctx, oracle, tag, mode, bits, vq, lens, seed=sum(lens) + bits)
+        assert_close(got, want, f"{tag} {env} {lens}")
+    ctx.close()
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq", ROW_KERNEL_MODES)
+def test_f32_and_k_only_tensor_core_path_other_group_sizes(bk, gpu_ctx, oracle, tag, mode, bits, vq):
+    rng = np.random.default_rng(79 + bits)
+    n = 2500
+    for n_head, n_kv in ((4, 4), (8, 4), (8, 2), (16, 2)):
+        k = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
+        v = rng.standard_normal((n, n_kv, HD)).astype(np.float32)
+        q = rng.standard_normal((n_head, HD)).astype(np.float32)
+        cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=n, n_head=n_head, n_kv=n_kv)
+        cache.append(0, k, v)
+        ref = oracle.cache(mode, bits, vq, n_head=n_head, n_kv=n_kv)
+        for p in range(n):
+            ref.append(0, k[p], v[p], p)
+        want = ref.attend(0, q, n - 1, n, threads=8)
+        got = cache.attend(0, q)[0]
+        assert_close(got, want, f"{tag} {n_head}/{n_kv}")
+        cache.close()
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq", ROW_KERNEL_MODES)
+def test_f32_rows_past_the_end_do_not_leak_in(bk, gpu_ctx, oracle, tag, mode, bits, vq):
+    """The row kernel copies whole 16-position tiles; rows past n_pos may hold anything, including
+    infinities and NaNs in f32 rows, and must not reach the result."""
+    rng = np.random.default_rng(6 + bits)
+    n, extra = 2500 + 7, 9
+    k, v = synth_kv(rng, n + extra)
+    k[n:] = np.float32(np.inf)
+    v[n:] = np.float32(np.nan)
+    q = rng.standard_normal((NH, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=n + extra)
+    cache.append(0, k, v)
+    ref = oracle.cache(mode, bits, vq)
+    for p in range(n):
+        ref.append(0, k[p], v[p], p)
+    want = ref.attend(0, q, n - 1, n, threads=8)
+    got = cache.attend(0, q[None], n_pos=[n], q_pos=[n - 1])[0]
+    assert np.all(np.isfinite(got))
+    assert_close(got, want)
+    cache.close()
+
+
+@pytest.mark.parametrize("tag,mode,bits,vq", ROW_KERNEL_MODES)
+def test_fused_step_on_long_f32_and_k_only_caches(bk, gpu_ctx, oracle, tag, mode, bits, vq):
+    """On long f32 and K-only caches the attention step is one launch too; stored rows stay bit-exact."""
+    rng = np.random.default_rng(44 + bits)
+    n0, steps = 2600, 12
+    k, v = synth_kv(rng, n0 + steps)
+    q = rng.standard_normal((steps, NH, HD)).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=n0 + steps)
+    ref = oracle.cache(mode, bits, vq)
+    cache.append(0, k[:n0], v[:n0])
+    for p in range(n0):
+        ref.append(0, k[p], v[p], p)
+    for t in range(steps):
+        launches = gpu_ctx.launch_count
+        got = bk.full_attention_step(cache, 0, q[t], k[n0 + t], v[n0 + t], n0 + t)
+        assert gpu_ctx.launch_count - launches == 1
+        want = ref.step(0, q[t], k[n0 + t], v[n0 + t], n0 + t, threads=8)
+        assert_close(got, want, f"{tag} step {t}")
+    compare_dumps(cache.dump_kv(0, pos0=n0 - 3), {key: val[n0 - 3:] for key, val in ref.dump(0).items()})
+    cache.close()
+
+
+def test_f32_tensor_core_path_precision(bk, gpu_ctx, oracle):
+    """The f32 row kernel splits every stored float into f16 hi + lo: with x20 outlier channels and a peaked
+    softmax its result still agrees with the f32 CPU path to 2e-5 (the bar of the path is 1e-3)."""
+    rng = np.random.default_rng(91)
+    n = 3000
+    k, v = synth_kv(rng, n)
+    q = (rng.standard_normal((NH, HD)) * 3).astype(np.float32)
+    cache = bk.AttnCache(gpu_ctx, bk.parse_mode("f32"), n_layers=1, n_ctx=n)
+    cache.append(0, k, v)
+    ref = oracle.cache(MODE_F32, 0, False)
+    for p in range(n):
+        ref.append(0, k[p], v[p], p)
+    want = ref.attend(0, q, n - 1, n, threads=8)
+    got = cache.attend(0, q)[0]
+    err = float(np.max(np.abs(got - want))) / float(np.max(np.abs(want)))
+    assert err <= 2e-5, err
+    cache.close()
+
+
 @pytest.mark.parametrize("bits", range(1, 9))
 def test_nearest_centroid_search_equals_the_reference_scan(bk, gpu_ctx, oracle, bits):
     """The kernels find the nearest centroid by binary search plus one neighbour check; the
