@@ -321,9 +321,19 @@ def build_splitctx(bk, par, ctx, mode, rank, world, local, dist, total_steps, mo
     gathered = torch.zeros((world, NH, HD + 2), dtype=torch.float32, device=dev)
     pos_now = [n_total - total_steps]
     lib_stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
-    split = par.ContextSplit(cache, dist, rank, world) if (world > 1 and exchange == "p2p") else None
+    split = par.ContextSplit(cache, dist, rank, world) if (world > 1 and exchange in ("p2p", "p2p_layers")) else None
+    out_layers = None
+    if split is not None and exchange == "p2p_layers":
+        split.open_layers_mailbox(dist, N_LAYERS)
+        out_layers = torch.zeros((N_LAYERS, NH, HD), dtype=torch.float32, device=dev)
 
     def step(_s):
+        if out_layers is not None:  # all layers scanned back to back, ONE exchange of their partial rows per token
+            own = rank == owner
+            split.step_layers_device(d_q.ptr, dk.ptr if own else None, dv.ptr if own else None, out_layers.data_ptr(),
+                                     q_pos=pos_now[0])
+            pos_now[0] += 1
+            return
         for il in range(N_LAYERS):
             if split is not None:  # one launch per rank and layer: append (tail owner), scan, exchange, merge
                 own = rank == owner
@@ -350,7 +360,9 @@ def build_splitctx(bk, par, ctx, mode, rank, world, local, dist, total_steps, mo
     step_bytes = N_LAYERS * (attn_bytes(mode, n_total) + append_bytes(mode))
     cfg = {"workload": f"splitctx: 1 sequence, context {n_total}, {N_LAYERS} layers, {mode_name}; contiguous context "
                        f"chunks over {world} GPU(s); per layer the (acc, m, l) partials are exchanged "
-                       + ("through peer memory inside the decode launch (bk_attn_step_split)" if split is not None
+                       + ("through peer memory in ONE call per token after all layers are scanned (bk_exchange_merge; "
+                          "layers independent of one another)" if out_layers is not None else
+                          "through peer memory inside the decode launch (bk_attn_step_split)" if split is not None
                           else ("by one NCCL all-gather, then bk_lse_merge" if world > 1 else "- one GPU, nothing to exchange")),
            "l2": "%.2f GB of cache per step over all GPUs" % (step_bytes / 1e9)}
     return step, step_bytes, 1, "strong", cfg, cleanup
@@ -434,13 +446,17 @@ def splitctx_self_check(bk, par, ctx, dist, rank, world):
     if whole:
         whole.append(0, k[:n0], v[:n0])
     split = par.ContextSplit(mine, dist, rank, world)
+    split.open_layers_mailbox(dist, 1)
     d_out = ctx.alloc(NH * HD * 4)
     worst = 0.0
     for s in range(steps):
         pos = n0 + s
         d_q, d_k, d_v = ctx.to_device(q[s]), ctx.to_device(k[pos]), ctx.to_device(v[pos])
         own = rank == owner
-        split.step_device(0, d_q.ptr, d_k.ptr if own else None, d_v.ptr if own else None, d_out.ptr, q_pos=pos)
+        if s == 0:   # the step whose exchange rides in the decode launch ...
+            split.step_device(0, d_q.ptr, d_k.ptr if own else None, d_v.ptr if own else None, d_out.ptr, q_pos=pos)
+        else:        # ... and the form that scans first and exchanges all (here: one) layers' rows in one call
+            split.step_layers_device(d_q.ptr, d_k.ptr if own else None, d_v.ptr if own else None, d_out.ptr, q_pos=pos)
         got = d_out.download((NH, HD), np.float32)
         want = whole.step(0, q[s], k[pos], v[pos], pos) if whole else None
         box = [want]
@@ -489,6 +505,17 @@ def run_sharded(bk, ctx, mode, mode_name, rank, world, local, dist, steps=5, war
                 entry["efficiency_vs_own_n1"] = n1["ms_per_step"] / ms / world
             if name == "splitctx":
                 entry["exchange"] = "p2p"
+                entry["form"] = "per-layer dependent: every layer's exchange completes before the next layer starts"
+                # the other form: the 16 layers batched, one exchange per token (callers whose layers are independent)
+                step, step_bytes, tokens, _sc, cfg, cleanup = build_splitctx(bk, par, ctx, mode, rank, world, local, dist, total,
+                                                                             mode_name, "p2p_layers")
+                ms_b = timed_steps(ctx, dist, local, step, steps, warmup)
+                cleanup()
+                entry["layers_batched"] = {"tokens_per_s": tokens * 1e3 / ms_b, "ms_per_step": ms_b,
+                                           "effective_gbs": step_bytes / ms_b / 1e6, "workload": cfg["workload"]}
+                if n1:
+                    entry["layers_batched"]["speedup_vs_own_n1"] = n1["ms_per_step"] / ms_b
+                    entry["layers_batched"]["efficiency_vs_own_n1"] = n1["ms_per_step"] / ms_b / world
                 entry["check_max_abs"] = splitctx_self_check(bk, par, ctx, dist, rank, world)
         out[name] = entry
     return out
@@ -675,7 +702,7 @@ def main():
                     help="skip the batch64 / splitctx passes that follow the headline pass")
     ap.add_argument("--chunk", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=16, help="full-attention layers (16 = qwen35; fewer only to keep a profiler capture small)")
-    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p_layers", "nccl"],
                     help="splitctx only: p2p = peer-memory exchange fused with the merge (bk_decode_attn_split); "
                          "nccl = all-gather of the partials + bk_lse_merge")
     ap.add_argument("--step", default="attn", choices=["attn", "layer"],

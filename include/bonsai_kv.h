@@ -257,6 +257,15 @@ BK_API bk_status bk_decode_attn_split(bk_cache *cache, int32_t layer, int32_t se
 BK_API bk_status bk_attn_step_split(bk_cache *cache, int32_t layer, int32_t seq, int32_t q_pos,
                                     const float *q_dev, const float *k_dev, const float *v_dev,
                                     float *out_dev, bk_mailbox *mailbox, uint32_t seqno);
+/* The exchange and merge on their own, for partial rows produced by other calls: part_dev is
+ * [n_rows][hd + 2] = (acc, m, l) rows as bk_decode_attn_partial writes them, n_rows the row
+ * count the mailbox was created with, taken in groups of n_rep consecutive rows (one CTA
+ * each); every rank sends its rows to all ranks and writes the log-sum-exp merge of all
+ * ranks' rows to out_dev [n_rows][hd].  With a mailbox of n_layers * n_head rows a caller
+ * whose layers do not depend on one another (a benchmark; speculative or batched callers)
+ * scans all layers first and pays ONE exchange per token instead of one per layer. */
+BK_API bk_status bk_exchange_merge(bk_mailbox *mailbox, int32_t n_rep, const float *part_dev,
+                                   float *out_dev, uint32_t seqno);
 
 /* The attention step with the reference's own shape (src/forward.rs:247-375,
  * src/gdev.rs:584-829): rope q and k at `pos`, store k/v at row `pos` (which

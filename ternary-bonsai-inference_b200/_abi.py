@@ -62,6 +62,7 @@ SIGNATURES = {
     "bk_mailbox_create": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _pp, _vp]),
     "bk_mailbox_open_peers": (C.c_int, [_vp, _vp]),
     "bk_mailbox_destroy": (None, [_vp]),
+    "bk_exchange_merge": (C.c_int, [_vp, _i32, _vp, _vp, C.c_uint32]),
     "bk_decode_attn_split": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, C.c_uint32]),
     "bk_attn_step": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bk_attn_step_host": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),

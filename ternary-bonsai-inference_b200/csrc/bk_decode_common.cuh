@@ -57,7 +57,7 @@ struct FinishSmem {
 // the CTA that holds coordinate 0 also sends the heads' m and l), publish them octet by octet with a
 // system-scope release of the call's sequence number, wait (bounded) for the same octets - and octet 0, for
 // m and l - of every rank in this rank's own mailbox, and write the log-sum-exp merge to a.out.
-// A mailbox is [2 parities][world][n_head][hd + 2] floats followed by [2][world][kXchFlags] arrival words,
+// A mailbox is [2 parities][world][n_head][hd + 2] floats followed by [2][world][a.xch_flags] arrival words,
 // word kv * 32 + (coordinate / 8).  The octet grid does not depend on how a rank has cut its work, so ranks
 // whose launches have different shapes (or that send from the stand-alone exchange kernel) understand each
 // other.  vals: [n_rep][dn] in shared memory, relative to s_M (exp2 domain), not normalised.  Every thread of
@@ -88,13 +88,13 @@ __device__ __forceinline__ void exchange_slice(const DecodeArgs &a, int n_rep, i
     for (int x = tid; x < world * per; x += nt) {
         const int r = x / per, j = x - r * per;
         if (j < n_oct) {
-            unsigned *flag = reinterpret_cast<unsigned *>(a.xch_peer[r] + data_b) + ((size_t)par * world + rank) * kXchFlags + kv * 32 + oct0 + j;
+            unsigned *flag = reinterpret_cast<unsigned *>(a.xch_peer[r] + data_b) + ((size_t)par * world + rank) * a.xch_flags + kv * 32 + oct0 + j;
             cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
             f.store(seqno, cuda::memory_order_release);
         }
         if (j < n_oct || oct0 != 0) {  // ... and wait for the same octet (j == n_oct: octet 0, which carries m and l) of rank r
             const int oct = j < n_oct ? oct0 + j : 0;
-            unsigned *mine = reinterpret_cast<unsigned *>(a.xch_peer[rank] + data_b) + ((size_t)par * world + r) * kXchFlags + kv * 32 + oct;
+            unsigned *mine = reinterpret_cast<unsigned *>(a.xch_peer[rank] + data_b) + ((size_t)par * world + r) * a.xch_flags + kv * 32 + oct;
             cuda::atomic_ref<unsigned, cuda::thread_scope_system> g2(*mine);
             int polls = 0;
             while (g2.load(cuda::memory_order_acquire) != seqno) {

@@ -4,7 +4,7 @@
 //
 // Every rank owns a mailbox (one cudaMalloc, shared with the other ranks' processes through CUDA
 // IPC; ranks of one process find each other's mailbox in a process-local registry): two parities x
-// world slots of n_rows x (hd + 2) floats, and two parities x world x kXchFlags arrival words.
+// world slots of n_rows x (hd + 2) floats, and two parities x world x mailbox_flags(n_rows) arrival words.
 // The exchange runs slice by slice (exchange_slice() in bk_decode_common.cuh): whoever holds
 // dims [d0, d0 + dn) of a kv head's rows, merged over the rank's own chunks, stores them into slot
 // [rank] of every rank's mailbox with plain peer stores, publishes each octet of dims with a
@@ -58,7 +58,7 @@ __host__ __device__ inline size_t data_bytes(int world, int n_rows, int hd) {
     return 2 * (size_t)world * slot_floats(n_rows, hd) * sizeof(float);
 }
 __host__ __device__ inline size_t mailbox_bytes(int world, int n_rows, int hd) {
-    return data_bytes(world, n_rows, hd) + 2 * (size_t)world * kXchFlags * sizeof(unsigned);
+    return data_bytes(world, n_rows, hd) + 2 * (size_t)world * mailbox_flags(n_rows) * sizeof(unsigned);
 }
 
 // The exchange on its own, for a rank whose rows were produced by another launch (or that has no rows: l = 0):
@@ -200,7 +200,7 @@ bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t 
     // sends, waits and merges that head's rows itself.  An empty chunk has no such CTA and goes the
     // two-step way (zero rows, then the exchange kernel); both speak the same mailbox protocol.
     if (n_pos > 0 && !getenv("BONSAI_KV_SPLIT_UNFUSED"))
-        return decode_with_exchange(c, layer, seq, n_pos, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, seqno);
+        return decode_with_exchange(c, layer, seq, n_pos, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, mailbox_flags(m->n_rows), seqno);
     bk_status st = bk_decode_attn_partial(c, layer, 1, &seq, &n_pos, &q_pos, q_dev, m->part);
     if (st != BK_OK) return st;
     DecodeArgs xa;
@@ -209,9 +209,37 @@ bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t 
     xa.xch_peer = m->d_peer;
     xa.xch_world = m->world;
     xa.xch_rank = m->rank;
+    xa.xch_flags = mailbox_flags(m->n_rows);
     xa.xch_seqno = seqno;
     const int n_rep = c->cfg.n_head / c->cfg.n_kv;
     exchange_merge_kernel<<<c->cfg.n_kv, 256, (size_t)n_rep * kHd * sizeof(float), ctx->stream>>>(xa, n_rep, m->part);
+    ctx->launches++;
+    BK_CUDA(ctx, cudaGetLastError());
+    return BK_OK;
+}
+
+bk_status bk_exchange_merge(bk_mailbox *m, int32_t n_rep, const float *part_dev, float *out_dev, uint32_t seqno) {
+    if (!m || !part_dev || !out_dev) return fail(m ? m->ctx : nullptr, BK_ERR_INVALID, "bk_exchange_merge: null argument");
+    bk_ctx *ctx = m->ctx;
+    if (m->hd != kHd) return fail(ctx, BK_ERR_UNSUPPORTED, "bk_exchange_merge: rows of 256 values only");
+    if (n_rep < 1 || n_rep > kMaxRep || m->n_rows % n_rep != 0)
+        return fail(ctx, BK_ERR_INVALID, "bk_exchange_merge: the mailbox's rows are not a whole number of groups of n_rep");
+    if (seqno == 0) return fail(ctx, BK_ERR_INVALID, "bk_exchange_merge: sequence numbers start at 1");
+    for (int r = 0; r < m->world; r++)
+        if (!m->peer[r]) return fail(ctx, BK_ERR_INVALID, "bk_exchange_merge: peers are not opened");
+    bk_status st = bind_device(ctx);
+    if (st != BK_OK) return st;
+    DecodeArgs xa{};
+    xa.n_head = m->n_rows;  // the mailbox's rows are the "heads" of this exchange, in groups of n_rep
+    xa.out = out_dev;
+    xa.xch_peer = m->d_peer;
+    xa.xch_world = m->world;
+    xa.xch_rank = m->rank;
+    xa.xch_flags = mailbox_flags(m->n_rows);
+    xa.xch_seqno = seqno;
+    xa.xch_err = ctx->d_err;
+    xa.xch_spin = ctx->xch_polls;
+    exchange_merge_kernel<<<m->n_rows / n_rep, 256, (size_t)n_rep * kHd * sizeof(float), ctx->stream>>>(xa, n_rep, part_dev);
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     return BK_OK;
@@ -238,7 +266,7 @@ bk_status bk_attn_step_split(bk_cache *c, int32_t layer, int32_t seq, int32_t q_
     DecodeArgs a;
     fill_decode_args(c, layer, 0, &a);
     const bool fused_append = decode_entry_uses_mma(ctx, a, np + 1);
-    bk_status st = decode_with_exchange(c, layer, seq, np + 1, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, seqno,
+    bk_status st = decode_with_exchange(c, layer, seq, np + 1, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, mailbox_flags(m->n_rows), seqno,
                                         k_dev, v_dev);
     if (st == BK_OK && fused_append) np += 1;  // (the other route went through bk_append, which counted it)
     return st;

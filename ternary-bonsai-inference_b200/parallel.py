@@ -114,7 +114,45 @@ class ContextSplit:
         self.ctx.check(self.ctx.lib.bk_attn_step_split(self.cache.h, il, seq, q_pos, q_ptr, k_ptr, v_ptr, out_ptr,
                                                        self.mb, self.seqno))
 
+    def open_layers_mailbox(self, dist, n_layers):
+        """A second mailbox with a row for every (layer, q head), for steps whose layers do not depend on one
+        another: all layers are scanned first and the partial rows of all of them cross in ONE exchange."""
+        import ctypes as C
+        handle = (C.c_ubyte * 64)()
+        mb = C.c_void_p()
+        self.ctx.check(self.ctx.lib.bk_mailbox_create(self.ctx.h, self.world, self.rank, n_layers * self.cache.n_head,
+                                                      self.cache.hd, C.byref(mb), handle))
+        self.mb_layers, self.n_layers_mb, self.seqno_layers = mb, n_layers, 0
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, bytes(handle))
+        else:
+            handles[0] = bytes(handle)
+        blob = (C.c_ubyte * (64 * self.world)).from_buffer_copy(b"".join(handles))
+        self.ctx.check(self.ctx.lib.bk_mailbox_open_peers(self.mb_layers, blob))
+        self.part_layers = self.ctx.alloc(n_layers * self.cache.n_head * (self.cache.hd + 2) * 4)
+        if self.world > 1:
+            dist.barrier()
+
+    def step_layers_device(self, q_ptr, k_ptr, v_ptr, out_ptr, q_pos, seq=0):
+        """One token through all layers of the layers mailbox with a single exchange: q_ptr [n_layers][n_head][hd],
+        out_ptr the same shape; the tail owner passes the new token's k/v (the same rows for every layer here),
+        the others None.  Only for callers whose layer l + 1 does not need layer l's output."""
+        nh, hd = self.cache.n_head, self.cache.hd
+        for il in range(self.n_layers_mb):
+            if k_ptr is not None:
+                self.cache.append_device(il, k_ptr, v_ptr, n_tokens=1, pos=q_pos, seq=seq)
+            self.cache.decode_device(il, q_ptr + il * nh * hd * 4, self.part_layers.ptr + il * nh * (hd + 2) * 4,
+                                     q_pos=[q_pos], partial=True)
+        self.seqno_layers += 1
+        self.ctx.check(self.ctx.lib.bk_exchange_merge(self.mb_layers, nh // self.cache.n_kv, self.part_layers.ptr, out_ptr,
+                                                      self.seqno_layers))
+
     def close(self):
         if getattr(self, "mb", None):
             self.ctx.lib.bk_mailbox_destroy(self.mb)
             self.mb = None
+        if getattr(self, "mb_layers", None):
+            self.ctx.lib.bk_mailbox_destroy(self.mb_layers)
+            self.mb_layers = None
+            self.part_layers.free()

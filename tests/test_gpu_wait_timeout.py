@@ -80,3 +80,61 @@ def test_exchange_wait_gives_up_reports_and_recovers(bk, monkeypatch):
         c.close()
     for c in ctx:
         c.close()
+
+
+def test_exchange_of_several_layers_rows_in_one_call(bk, monkeypatch):
+    """bk_exchange_merge: the partial rows of two layers (48 rows, a mailbox with more arrival words than the
+    per-layer one) cross in one call per rank and merge to the whole-cache attention.  The two ranks are played
+    by one process and never run together: rank 1 sends and gives up waiting (reported), then rank 0 finds
+    everything it waits for."""
+    monkeypatch.setenv("BONSAI_KV_XCH_POLLS", "3000")
+    abi = bk._abi
+    ctx = [bk.Context(0), bk.Context(0)]
+    lib = ctx[0].lib
+    rng = np.random.default_rng(23)
+    n_layers, n = 2, [2300, 900]
+    total = sum(n)
+    k = rng.standard_normal((n_layers, total, NKV, HD), dtype=np.float32)
+    v = rng.standard_normal((n_layers, total, NKV, HD), dtype=np.float32)
+    q = rng.standard_normal((n_layers, NH, HD), dtype=np.float32)
+    mode = bk.parse_mode("planar4")
+    part = [bk.AttnCache(ctx[r], mode, n_layers=n_layers, n_ctx=n[r], rope_positions=total) for r in range(2)]
+    whole = bk.AttnCache(ctx[0], mode, n_layers=n_layers, n_ctx=total)
+    for il in range(n_layers):
+        part[0].append(il, k[il, :n[0]], v[il, :n[0]], pos=0)
+        part[1].append(il, k[il, n[0]:], v[il, n[0]:], pos=n[0])
+        whole.append(il, k[il], v[il])
+    want = np.stack([whole.attend(il, q[il])[0] for il in range(n_layers)])
+
+    boxes = []
+    for r in range(2):
+        handle = (C.c_ubyte * 64)()
+        mb = C.c_void_p()
+        ctx[r].check(lib.bk_mailbox_create(ctx[r].h, 2, r, n_layers * NH, HD, C.byref(mb), handle))
+        boxes.append((mb, bytes(handle)))
+    blob = (C.c_ubyte * 128).from_buffer_copy(boxes[0][1] + boxes[1][1])
+    for r in range(2):
+        ctx[r].check(lib.bk_mailbox_open_peers(boxes[r][0], blob))
+    d_q = [ctx[r].to_device(q) for r in range(2)]
+    d_part = [ctx[r].alloc(n_layers * NH * (HD + 2) * 4) for r in range(2)]
+    d_out = [ctx[r].alloc(n_layers * NH * HD * 4) for r in range(2)]
+
+    def call(r, seqno):
+        for il in range(n_layers):
+            part[r].decode_device(il, d_q[r].ptr + il * NH * HD * 4, d_part[r].ptr + il * NH * (HD + 2) * 4,
+                                  q_pos=[total - 1], partial=True)
+        ctx[r].check(lib.bk_exchange_merge(boxes[r][0], NH // NKV, d_part[r].ptr, d_out[r].ptr, seqno))
+        return lib.bk_synchronize(ctx[r].h)
+
+    assert call(1, 1) == abi.BK_ERR_CUDA                   # rank 1 alone: sends its 48 rows, gives up on rank 0
+    assert call(0, 1) == abi.BK_OK                         # rank 0: rank 1's rows are there
+    got = d_out[0].download((n_layers, NH, HD), np.float32)
+    err = float(np.max(np.abs(got - want)))
+    assert err <= 5e-4, err
+    # bad arguments are refused
+    assert lib.bk_exchange_merge(boxes[0][0], 5, d_part[0].ptr, d_out[0].ptr, 2) == abi.BK_ERR_INVALID   # 48 % 5 != 0
+    assert lib.bk_exchange_merge(boxes[0][0], NH // NKV, d_part[0].ptr, d_out[0].ptr, 0) == abi.BK_ERR_INVALID
+    for r in range(2):
+        lib.bk_mailbox_destroy(boxes[r][0])
+    for c in part + [whole]:
+        c.close()
