@@ -422,10 +422,10 @@ bk_status bk_cache_create(bk_ctx *ctx, const bk_cache_config *cfg, bk_cache **ou
         return st;
     }
     c->n_pos.assign((size_t)cfg->n_layers * cfg->n_seqs, 0);
-    // tiles of 16 positions: f16, f32, and 4- or 3-bit K beside f32 V; tiles of 32: K and V both 4 or 3 bit
+    // tiles of 16 positions: f16, f32, and 4- or 3-bit K beside f32 V; tiles of 32: K and V both 4, 3 or 2 bit
     const bool row_tiles = (k_kind == ROW_F16 && v_kind == ROW_F16) || (k_kind == ROW_F32 && v_kind == ROW_F32) ||
                            (k_kind == ROW_PLANAR && (bits == 4 || bits == 3) && v_kind == ROW_F32);
-    if ((k_kind == ROW_PLANAR && v_kind == ROW_PLANAR && (bits == 4 || bits == 3)) || row_tiles) {
+    if ((k_kind == ROW_PLANAR && v_kind == ROW_PLANAR && (bits == 4 || bits == 3 || bits == 2)) || row_tiles) {
         st = make_tile_tensor_maps(ctx, c->d_k, c->d_v, c->k_row_bytes, c->v_row_bytes, cfg->n_kv,
                                    (size_t)cfg->n_layers * cfg->n_seqs * cfg->n_ctx, row_tiles ? 16 : 32, c->tmap_k, c->tmap_v);
         if (st != BK_OK) {

@@ -1,4 +1,4 @@
-// Decode attention over a 4-bit (or 3-bit) planar cache (K and V both quantized): the bandwidth path.
+// Decode attention over a 4-bit (or 3-bit, or 2-bit) planar cache (K and V both quantized): the bandwidth path.
 //
 // A 4-bit row carries 11.6 multiply-adds per byte once six q heads share it, more than the
 // FP32 pipes of an SM can retire at HBM speed, and a non-uniform Lloyd-Max codebook needs a
@@ -60,8 +60,9 @@ constexpr uint32_t kLutBytes = 65536;   // 256 entries x 256 B (128 B used: one 
 constexpr int kHeadStride = 276;        // floats per head in the warp-merge area (bank-conflict free)
 constexpr float kWScale = 16384.0f;     // 2^14: V weights are stored as f16 in (0, 2^14]
 constexpr int kMaxStages = 4;
-// Per index width (4 or 3 bits): a row is 32 * BITS bytes, a tile 32 dense rows (4-bit tiles land
-// with the 128-byte swizzle, 3-bit tiles plain), a stage = K tile, V tile, K norms, V norms (the
+// Per index width (4, 3 or 2 bits): a row is 32 * BITS bytes, a tile 32 dense rows (4-bit tiles land
+// with the 128-byte swizzle, 2-bit tiles with the 64-byte one, 3-bit tiles plain; 3- and 2-bit indices are
+// widened to nibbles before the table lookups), a stage = K tile, V tile, K norms, V norms (the
 // norms of every kv head travel: 32 positions x n_kv floats, padded to 512 or 1024 bytes).
 template <int BITS> struct Width {
     static constexpr int kRowBytes = 32 * BITS;
@@ -70,8 +71,12 @@ template <int BITS> struct Width {
 // Which shared-memory row holds the MMA's position row g.  4 bit: g itself (the swizzle spreads
 // the banks).  3 bit: rows are 96 bytes apart and unswizzled; this order makes both the K reads
 // (row g, 8 bytes at 24 t) and the V reads (rows 2t, 2t+1, 4 bytes at 12 g) spread over the banks.
+// 2 bit: rows are 64 bytes apart and land with the 64-byte swizzle (16-byte chunk ^= (row >> 1) & 3); this order
+// gives the K reads (row g, chunk t) two rows of different parity per quarter warp and the V reads (rows 2t,
+// 2t + 1, 8 bytes at 8 g) four rows with different (row & 1, row & 4): both conflict-free.
 template <int BITS> __device__ __forceinline__ int row_of(int g) {
     if constexpr (BITS == 3) return (g < 4) ? g : (g ^ 1);  // 0 1 2 3 5 4 7 6
+    else if constexpr (BITS == 2) return ((0x65742130u >> (4 * g)) & 7);  // 0 3 1 2 4 7 5 6
     else return g;
 }
 // Eight 3-bit indices in the low 24 bits of y -> eight nibbles.
@@ -80,6 +85,14 @@ __device__ __forceinline__ uint32_t expand24(uint32_t y) {
     y += (y & 0x00fff000u) * 15u;   // upper four indices up by 4 bits
     y += (y & 0x0fc00fc0u) * 3u;    // upper two of every four up by 2
     y += (y & 0x38383838u);         // upper one of every two up by 1
+    return y;
+}
+// Eight 2-bit indices in the low 16 bits of y -> eight nibbles.
+__device__ __forceinline__ uint32_t expand16(uint32_t y) {
+    y &= 0x0000ffffu;
+    y = (y | (y << 8)) & 0x00ff00ffu;
+    y = (y | (y << 4)) & 0x0f0f0f0fu;
+    y = (y | (y << 2)) & 0x33333333u;
     return y;
 }
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
@@ -440,7 +453,25 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             for (int i = 0; i < 4; i++) S[m][i][0] = S[m][i][1] = S[m][i][2] = S[m][i][3] = 0.f;
         // 3 bit: coordinates 64 t .. 64 t + 63 of a row are 24 bytes, read once as three 8-byte words and
         // widened group by group to words of eight nibbles: [m][row g / g + 8][c][w]
-        uint32_t k3[BITS == 3 ? 2 : 1][2][2][4];
+        uint32_t k3[BITS != 4 ? 2 : 1][2][2][4];
+        if constexpr (BITS == 2) {
+            // 2 bit: coordinates 64 t .. 64 t + 63 of a row are one 16-byte chunk (swizzled), four words of sixteen indices
+#pragma unroll
+            for (int m = 0; m < 2; m++)
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++) {
+                    const uint32_t row = (uint32_t)(16 * m + 8 * hh + row_of<BITS>(g));
+                    const uint4 u = lds128(st_addr + row * kRowBytes + ((((uint32_t)t) ^ ((row >> 1) & 3u)) << 4));
+                    k3[m][hh][0][0] = expand16(u.x);
+                    k3[m][hh][0][1] = expand16(u.x >> 16);
+                    k3[m][hh][0][2] = expand16(u.y);
+                    k3[m][hh][0][3] = expand16(u.y >> 16);
+                    k3[m][hh][1][0] = expand16(u.z);
+                    k3[m][hh][1][1] = expand16(u.z >> 16);
+                    k3[m][hh][1][2] = expand16(u.w);
+                    k3[m][hh][1][3] = expand16(u.w >> 16);
+                }
+        }
         if constexpr (BITS == 3) {
 #pragma unroll
             for (int m = 0; m < 2; m++)
@@ -566,6 +597,18 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                 x1[0] = rv1.x; x1[1] = rv1.y; x1[2] = rv1.z; x1[3] = rv1.w;
                 x2[0] = rv2.x; x2[1] = rv2.y; x2[2] = rv2.z; x2[3] = rv2.w;
                 x3[0] = rv3.x; x3[1] = rv3.y; x3[2] = rv3.z; x3[3] = rv3.w;
+            } else if constexpr (BITS == 2) {  // 8 bytes per row (chunk g / 2, swizzled, half g & 1), widened
+                auto load_v = [&](uint32_t row, uint32_t (&out)[4]) {
+                    const uint2 u = lds64(v_blk + row * kRowBytes + (((uint32_t)(g >> 1) ^ ((row >> 1) & 3u)) << 4) + (uint32_t)((g & 1) * 8));
+                    out[0] = expand16(u.x);
+                    out[1] = expand16(u.x >> 16);
+                    out[2] = expand16(u.y);
+                    out[3] = expand16(u.y >> 16);
+                };
+                load_v(r0, x0);
+                load_v(r1, x1);
+                load_v(r0 + 8, x2);
+                load_v(r1 + 8, x3);
             } else {  // 12 bytes per row: three 4-byte reads, widened
                 auto load_v = [&](uint32_t addr, uint32_t (&out)[4]) {
                     const uint32_t u0 = lds32(addr), u1 = lds32(addr + 4), u2 = lds32(addr + 8);
@@ -799,9 +842,9 @@ bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_r
     void *outs[2] = {out_k, out_v};
     for (int i = 0; i < 2; i++) {
         const size_t row_bytes = row_bytes_of[i];
-        // rows of a multiple of 128 bytes travel as 128-byte swizzled slabs; shorter rows (96 bytes: 3 bit)
-        // as whole dense rows without a swizzle
-        const bool swizzled = row_bytes % 128 == 0;
+        // rows of a multiple of 128 bytes travel as 128-byte swizzled slabs; 64-byte rows (2 bit) whole, with the
+        // 64-byte swizzle; other short rows (96 bytes: 3 bit) as whole dense rows without a swizzle
+        const bool swizzled = row_bytes % 128 == 0, swizzled64 = row_bytes == 64;
         if (!swizzled && (row_bytes % 16 != 0 || row_bytes > 256))
             return fail(ctx, BK_ERR_UNSUPPORTED, "tensor maps need rows of a multiple of 16 bytes");
         const cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)n_kv, (cuuint64_t)total_pos};
@@ -810,7 +853,7 @@ bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_r
         const cuuint32_t estr[3] = {1, 1, 1};
         const CUresult r = encode(static_cast<CUtensorMap *>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
                                   const_cast<void *>(ptrs[i]), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                  swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : swizzled64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(ctx, BK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
     }
@@ -822,7 +865,7 @@ bool decode_p4_mma_supported(const DecodeArgs &a) {
     // the norms of a tile travel as a 16-byte aligned bulk copy: n_ctx * n_kv must be a multiple of 4;
     // the in-lane rope needs both coordinates of a pair in one lane (n_rot = 64) or exactly 1 or 2 lanes apart
     const bool rope_ok = a.no_rope || a.n_rot == 0 || a.n_rot == 64 || a.n_rot == 128 || a.n_rot == 256;
-    return a.h_tmap_k && a.h_tmap_v && (a.seq_stride_rows % 4 == 0) && a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3) &&
+    return a.h_tmap_k && a.h_tmap_v && (a.seq_stride_rows % 4 == 0) && a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3 || a.bits == 2) &&
            a.n_kv <= 8 && rope_ok && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
@@ -832,6 +875,7 @@ bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMet
 #define BK_MMA_CASE(R)                                                                                     \
     case R:                                                                                                \
         if (a.bits == 3) return qsplit ? launch_one<3, R, true>(ctx, a, m, alpha) : launch_one<3, R, false>(ctx, a, m, alpha); \
+        if (a.bits == 2) return qsplit ? launch_one<2, R, true>(ctx, a, m, alpha) : launch_one<2, R, false>(ctx, a, m, alpha); \
         return qsplit ? launch_one<4, R, true>(ctx, a, m, alpha) : launch_one<4, R, false>(ctx, a, m, alpha);
     switch (n_rep) {
         BK_MMA_CASE(1)

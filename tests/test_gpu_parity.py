@@ -628,7 +628,8 @@ def test_fused_step_on_long_f16_cache(bk, gpu_ctx, oracle):
     cache.close()
 
 
-ROW_KERNEL_MODES = [("f32", MODE_F32, 0, False), ("planar4k", MODE_PLANAR, 4, False), ("planar3k", MODE_PLANAR, 3, False)]
+ROW_KERNEL_MODES = [("f32", MODE_F32, 0, False), ("planar4k", MODE_PLANAR, 4, False), ("planar3k", MODE_PLANAR, 3, False),
+                    ("planar2", MODE_PLANAR, 2, True)]   # (planar2: the 4-bit kernel with 2-bit rows widened to nibbles)
 
 
 @pytest.mark.parametrize("tag,mode,bits,vq", ROW_KERNEL_MODES)
@@ -802,7 +803,8 @@ def test_layer_step_golden(bk, gpu_ctx, layer_golden, tag):
                                                  ("planar4", MODE_PLANAR, 4, True, 300), ("f32", MODE_F32, 0, False, 500),
                                                  ("planar3", MODE_PLANAR, 3, True, 2600), ("planar4k", MODE_PLANAR, 4, False, 700),
                                                  ("planar4k", MODE_PLANAR, 4, False, 2600), ("f32", MODE_F32, 0, False, 2600),
-                                                 ("planar4k", MODE_PLANAR, 4, False, 2331), ("planar3k", MODE_PLANAR, 3, False, 2600)])
+                                                 ("planar4k", MODE_PLANAR, 4, False, 2331), ("planar3k", MODE_PLANAR, 3, False, 2600),
+                                                 ("planar2", MODE_PLANAR, 2, True, 2600)])
 def test_layer_step_on_a_filled_cache(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0):
     """Layer steps after a prefill, on caches that take the tensor-core path (one launch per
     step) and on ones that do not: gated outputs within the bar, stored rows bit-exact."""
@@ -819,7 +821,7 @@ def test_layer_step_on_a_filled_cache(bk, gpu_ctx, oracle, tag, mode, bits, vq, 
     cache.append(0, k, v)
     for p in range(n0):
         ref.append(0, k[p], v[p], p)
-    one_launch = n0 >= 2048 and tag in ("planar4", "planar3", "f16", "f32", "planar4k", "planar3k")
+    one_launch = n0 >= 2048 and tag in ("planar4", "planar3", "f16", "f32", "planar4k", "planar3k", "planar2")
     for t in range(steps):
         launches = gpu_ctx.launch_count
         got = bk.full_attention_layer_core(cache, 0, qfull[t], kraw[t], vraw[t], qw, kw, 1e-6, n0 + t)
