@@ -1,4 +1,4 @@
-// Batched (prefill) attention over a 4-bit or 3-bit planar cache, or an f16 cache, on the
+// Batched (prefill) attention over a 4-, 3- or 2-bit planar cache, or an f16 cache, on the
 // 5th-generation tensor cores: the same work split, operands and arithmetic as bk_prefill.cu
 // (which documents them and stays as the mma.sync form), with both contractions issued as
 // tcgen05.mma and the accumulators in tensor memory.
@@ -67,6 +67,13 @@ __device__ __forceinline__ uint32_t expand24u(uint32_t y) {
     y += (y & 0x00fff000u) * 15u;
     y += (y & 0x0fc00fc0u) * 3u;
     y += (y & 0x38383838u);
+    return y;
+}
+__device__ __forceinline__ uint32_t expand16u(uint32_t y) {  // eight 2-bit indices -> eight nibbles
+    y &= 0x0000ffffu;
+    y = (y | (y << 8)) & 0x00ff00ffu;
+    y = (y | (y << 4)) & 0x0f0f0f0fu;
+    y = (y | (y << 2)) & 0x33333333u;
     return y;
 }
 // 32 coordinates (four words of eight nibbles) -> 32 halfs as four 16-byte chunks of a tile row.
@@ -257,6 +264,10 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             const uint32_t *k3 = reinterpret_cast<const uint32_t *>(kr) + 3 * my_c, *v3 = reinterpret_cast<const uint32_t *>(vr) + 3 * my_c;
             pk[0] = __ldg(k3); pk[1] = __ldg(k3 + 1); pk[2] = __ldg(k3 + 2); pk[3] = 0;
             pv[0] = __ldg(v3); pv[1] = __ldg(v3 + 1); pv[2] = __ldg(v3 + 2); pv[3] = 0;
+        } else {  // 2 bit: 32 coordinates are 8 bytes
+            const uint2 x = __ldg(reinterpret_cast<const uint2 *>(kr) + my_c), y = __ldg(reinterpret_cast<const uint2 *>(vr) + my_c);
+            pk[0] = x.x; pk[1] = x.y; pk[2] = pk[3] = 0;
+            pv[0] = y.x; pv[1] = y.y; pv[2] = pv[3] = 0;
         }
         if (tid < 2 * kTK) {
             const int p2 = min(c0 + tile * kTK + (tid & (kTK - 1)), a.n_ctx - 1);
@@ -270,6 +281,12 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             w[1] = expand24u(__funnelshift_r(u0, u1, 24));
             w[2] = expand24u(__funnelshift_r(u1, u2, 16));
             w[3] = expand24u(u2 >> 8);
+        } else if constexpr (BITS == 2) {  // sixteen indices per word -> two words of eight nibbles
+            const uint32_t u0 = w[0], u1 = w[1];
+            w[0] = expand16u(u0);
+            w[1] = expand16u(u0 >> 16);
+            w[2] = expand16u(u1);
+            w[3] = expand16u(u1 >> 16);
         }
     };
     auto wait_bar = [&](uint32_t bar, uint32_t parity) {
@@ -547,7 +564,7 @@ bk_status launch_umma_one(bk_ctx *ctx, const PrefillUArgs &pa) {
 
 bool prefill_umma_supported(const DecodeArgs &a) {
     const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
-    const bool planar = a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3);
+    const bool planar = a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3 || a.bits == 2);
     const bool f16 = a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 && a.v_row_bytes == 512;
     return (planar || f16) && a.h_tmap_k && a.h_tmap_v && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
@@ -583,6 +600,7 @@ bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos
 #define BK_PU_CASE(R)                                                                            \
     case R:                                                                                      \
         if (a.k_kind == ROW_F16) return launch_umma_one<16, R>(ctx, pa);                         \
+        if (a.bits == 2) return launch_umma_one<2, R>(ctx, pa);                                  \
         return a.bits == 3 ? launch_umma_one<3, R>(ctx, pa) : launch_umma_one<4, R>(ctx, pa);
     switch (n_rep) {
         BK_PU_CASE(1)
