@@ -19,6 +19,61 @@ namespace bk {
 // Scale alpha in [1, 2) that minimises the worst relative error of f16(alpha * c) / alpha over a
 // codebook: the centroids are only 2^bits distinct values, so a good alpha makes all of them
 // round almost exactly and the tensor-core path loses nothing to the f16 table.
+// Host side of nearest_centroid_thr() (bk_device.cuh): the 512 (count, threshold) cells of one ascending
+// codebook of n <= 16 centroids.  Everything is computed with the kernels' own single-precision operations
+// (this file is built without floating-point contraction).  Returns false if a cell would hold two thresholds.
+static bool build_threshold_cells(const float *book, int n, uint2 *tab) {
+    auto key = [](float f) -> int64_t {  // floats in ascending order as integers
+        int32_t b;
+        memcpy(&b, &f, 4);
+        return b >= 0 ? (int64_t)b : -(int64_t)(b & 0x7fffffff);
+    };
+    auto unkey = [](int64_t k) -> float {
+        const int32_t b = k >= 0 ? (int32_t)k : (int32_t)((uint32_t)(-k) | 0x80000000u);
+        float f;
+        memcpy(&f, &b, 4);
+        return f;
+    };
+    auto cell_of = [](float v) -> int {
+        volatile float t = v + 0.25f;
+        volatile float u = t * 1024.0f;
+        const int c = (int)floorf(u);
+        return c < 0 ? 0 : (c > 511 ? 511 : c);
+    };
+    float thr[16];
+    int thr_cell[16];
+    for (int i = 0; i + 1 < n; i++) {
+        const float c0 = book[i], c1 = book[i + 1];
+        auto beats = [&](float v) {  // does the scan move from centroid i to i + 1 at v?
+            volatile float d0 = v - c0, d1 = v - c1;
+            return fabsf(d1) < fabsf(d0);
+        };
+        int64_t lo = key(c0), hi = key(c1);  // beats(c0) is false, beats(c1) is true
+        if (beats(c0) || !beats(c1)) return false;
+        while (hi - lo > 1) {
+            const int64_t mid = lo + (hi - lo) / 2;
+            if (beats(unkey(mid))) hi = mid;
+            else lo = mid;
+        }
+        thr[i] = unkey(hi);
+        thr_cell[i] = cell_of(thr[i]);
+        if (i > 0 && thr_cell[i] <= thr_cell[i - 1]) return false;  // two thresholds in one cell (or out of order)
+    }
+    const float inf = INFINITY;
+    for (int k = 0; k < 512; k++) {
+        uint32_t below = 0;
+        float mine = inf;
+        for (int i = 0; i + 1 < n; i++) {
+            if (thr_cell[i] < k) below++;
+            else if (thr_cell[i] == k) mine = thr[i];
+        }
+        uint32_t bits;
+        memcpy(&bits, &mine, 4);
+        tab[k] = make_uint2(below, bits);
+    }
+    return true;
+}
+
 static float best_lut_alpha(const float *book, int n) {
     // What reaches the output is the ABSOLUTE error of a centroid (times a row norm), and with a softmax
     // peaked on a few rows nothing averages it out: minimise the largest absolute error, the largest
@@ -209,6 +264,18 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
         ctx->dist_combine = !(e6 && e6[0] == '0');
     }
     if ((e = cudaMalloc(&ctx->d_givens, sizeof(ctx->h_givens))) != cudaSuccess) return bail(e, "cudaMalloc givens");
+    {   // the threshold cells of the widths 1..4 (the append kernel's nearest-centroid search)
+        std::vector<uint2> tabs(4 * 512);
+        for (int b = 1; b <= 4; b++)
+            if (!build_threshold_cells(ctx->h_codebooks + (b - 1) * kBookStride, 1 << b, tabs.data() + (b - 1) * 512)) {
+                fail(nullptr, BK_ERR_UNSUPPORTED, "codebook thresholds do not fit the cell table");
+                bk_ctx_destroy(ctx);
+                return BK_ERR_UNSUPPORTED;
+            }
+        if ((e = cudaMalloc(&ctx->d_cell_tabs, tabs.size() * sizeof(uint2))) != cudaSuccess) return bail(e, "cudaMalloc cell tables");
+        if ((e = cudaMemcpy(ctx->d_cell_tabs, tabs.data(), tabs.size() * sizeof(uint2), cudaMemcpyHostToDevice)) != cudaSuccess)
+            return bail(e, "cudaMemcpy cell tables");
+    }
     if ((e = cudaMalloc(&ctx->d_codebooks, sizeof(ctx->h_codebooks))) != cudaSuccess)
         return bail(e, "cudaMalloc codebooks");
     if ((e = cudaMemcpy(ctx->d_givens, ctx->h_givens, sizeof(ctx->h_givens), cudaMemcpyHostToDevice)) != cudaSuccess)
@@ -242,6 +309,7 @@ void bk_ctx_destroy(bk_ctx *ctx) {
     ctx->ropes.clear();
     if (ctx->d_givens) cudaFree(ctx->d_givens);
     if (ctx->d_codebooks) cudaFree(ctx->d_codebooks);
+    if (ctx->d_cell_tabs) cudaFree(ctx->d_cell_tabs);
     if (ctx->d_partials) cudaFree(ctx->d_partials);
     if (ctx->d_counters) cudaFree(ctx->d_counters);
     if (ctx->h_err) cudaFreeHost(const_cast<int *>(ctx->h_err));
@@ -530,6 +598,7 @@ static AppendArgs base_append_args(const bk_cache *c, const float *k, const floa
     a.rope = c->rope->d;
     a.givens = c->ctx->d_givens;
     a.book = c->cfg.mode.kind == BK_MODE_PLANAR ? c->ctx->d_codebooks + (c->cfg.mode.bits - 1) * kBookStride : nullptr;
+    a.cell_tab = (c->cfg.mode.kind == BK_MODE_PLANAR && c->cfg.mode.bits <= 4) ? c->ctx->d_cell_tabs + (c->cfg.mode.bits - 1) * 512 : nullptr;
     a.seq_stride_rows = (size_t)c->cfg.n_ctx * c->cfg.n_kv;
     a.n_kv = c->cfg.n_kv;
     a.n_rot = c->cfg.n_rot;

@@ -8,10 +8,13 @@
 //      the (cos, sin) row of the token's position from the host-built rope table;
 //   2. planar rows: one warp adds the 256 squares of all 32 vectors, a vector per lane, each lane
 //      in order (the reference's f32 sum is sequential, so each chain is; 32 run side by side);
-//   3. the warps scale, Givens-rotate, find the nearest centroid (a cell table or a binary search, then
-//      one neighbour check: the same index as the reference's linear scan) and write `bits` bytes per lane;
+//   3. the warps scale, Givens-rotate, find the nearest centroid (one read of a host-built cell table of the
+//      decision thresholds, or a binary search and a neighbour check: the same index as the reference's
+//      linear scan) and write `bits` bytes per lane;
 //      f32/f16 rows leave as 128-bit stores.
 // Traffic per token is the algorithmic minimum: 2*n_kv*1 KiB in, rows + norms out.
+#include <atomic>
+
 #include "bk_device.cuh"
 #include "bk_internal.h"
 
@@ -24,40 +27,65 @@ constexpr int kVecPad = kHd + 4;  // floats per staged vector; +4 keeps float4 a
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 
+// Eight consecutive coordinates of a staged vector for every lane without bank conflicts: two 128-bit reads
+// in the staging layout (coordinates 4 l .. 4 l + 3 and 128 + 4 l .. + 3), then lanes 2m and 2m + 1 swap
+// one of them: the even lane ends with group m (coordinates 8 m .. 8 m + 7), the odd one with group 16 + m.
+// (Reading 8 consecutive floats per lane directly puts eight lanes on every bank.)  Returns the group.
+__device__ __forceinline__ int load_group_of_8(const float *sx, int lane, float (&x)[8]) {
+    const float4 a = reinterpret_cast<const float4 *>(sx)[lane], b = reinterpret_cast<const float4 *>(sx)[lane + 32];
+    const bool odd = lane & 1;
+    const float4 send = odd ? a : b;
+    float4 recv;
+    recv.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
+    recv.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
+    recv.z = __shfl_xor_sync(0xffffffffu, send.z, 1);
+    recv.w = __shfl_xor_sync(0xffffffffu, send.w, 1);
+    const float4 lo = odd ? recv : a, hi = odd ? b : recv;
+    x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+    x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+    return odd ? 16 + (lane >> 1) : (lane >> 1);
+}
+
 // Rotate, quantize and pack the 8 coordinates of one lane; `n` is the vector's norm.
 template <int BITS>
 __device__ __forceinline__ void store_planar_row(const float *sx, int lane, float n, const float *givens,
                                                  const float *sbook, uint8_t *row) {
     const float inv = (n > 1e-12f) ? __fdiv_rn(1.0f, n) : 0.0f;
+    float x[8];
+    const int group = load_group_of_8(sx, lane, x);
+    const float4 g0 = reinterpret_cast<const float4 *>(givens)[2 * group], g1 = reinterpret_cast<const float4 *>(givens)[2 * group + 1];
+    const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
     uint64_t packed = 0;
 #pragma unroll
     for (int pr = 0; pr < 4; pr++) {
-        const int i = lane * 4 + pr;  // pair index: coordinates 2i, 2i+1
-        const float a = __fmul_rn(sx[2 * i], inv), b = __fmul_rn(sx[2 * i + 1], inv);
+        const float a = __fmul_rn(x[2 * pr], inv), b = __fmul_rn(x[2 * pr + 1], inv);
         float r0, r1;
-        givens_fwd(a, b, givens[2 * i], givens[2 * i + 1], r0, r1);
+        givens_fwd(a, b, gv[2 * pr], gv[2 * pr + 1], r0, r1);
         packed |= (uint64_t)nearest_centroid_fast<BITS>(r0, sbook) << (BITS * (2 * pr));
         packed |= (uint64_t)nearest_centroid_fast<BITS>(r1, sbook) << (BITS * (2 * pr + 1));
     }
-    store_group8<BITS>(row, lane, packed);
+    store_group8<BITS>(row, group, packed);
 }
 
-// The same with the two-read centroid search (codebooks of up to 16 centroids).
+// The same with the one-read centroid search (codebooks of up to 16 centroids; bk_device.cuh).
 template <int BITS>
-__device__ __forceinline__ void store_planar_row_cell(const float *sx, int lane, float n, const float *givens,
-                                                      const float *sbook, const float4 *b4, const uint8_t *cells, uint8_t *row) {
+__device__ __forceinline__ void store_planar_row_thr(const float *sx, int lane, float n, const float *givens,
+                                                     const float *sbook, const uint2 *tab, uint8_t *row) {
     const float inv = (n > 1e-12f) ? __fdiv_rn(1.0f, n) : 0.0f;
-    uint64_t packed = 0;
+    float x[8];
+    const int group = load_group_of_8(sx, lane, x);  // coordinates 8 group .. 8 group + 7
+    const float4 g0 = reinterpret_cast<const float4 *>(givens)[2 * group], g1 = reinterpret_cast<const float4 *>(givens)[2 * group + 1];
+    const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    uint32_t packed = 0;  // 8 indices of at most 4 bits
 #pragma unroll
     for (int pr = 0; pr < 4; pr++) {
-        const int i = lane * 4 + pr;  // pair index: coordinates 2i, 2i+1
-        const float a = __fmul_rn(sx[2 * i], inv), b = __fmul_rn(sx[2 * i + 1], inv);
+        const float a = __fmul_rn(x[2 * pr], inv), b = __fmul_rn(x[2 * pr + 1], inv);
         float r0, r1;
-        givens_fwd(a, b, givens[2 * i], givens[2 * i + 1], r0, r1);
-        packed |= (uint64_t)nearest_centroid_cell<BITS>(r0, sbook, b4, cells) << (BITS * (2 * pr));
-        packed |= (uint64_t)nearest_centroid_cell<BITS>(r1, sbook, b4, cells) << (BITS * (2 * pr + 1));
+        givens_fwd(a, b, gv[2 * pr], gv[2 * pr + 1], r0, r1);
+        packed |= nearest_centroid_thr<BITS>(r0, sbook, tab) << (BITS * (2 * pr));
+        packed |= nearest_centroid_thr<BITS>(r1, sbook, tab) << (BITS * (2 * pr + 1));
     }
-    store_group8<BITS>(row, lane, packed);
+    store_group8<BITS>(row, group, (uint64_t)packed);
 }
 
 __device__ __forceinline__ void store_f32_row(const float *sx, int lane, uint8_t *row) {
@@ -68,14 +96,16 @@ __device__ __forceinline__ void store_f32_row(const float *sx, int lane, uint8_t
 }
 
 __device__ __forceinline__ void store_f16_row(const float *sx, int lane, uint8_t *row) {
+    float x[8];
+    const int group = load_group_of_8(sx, lane, x);
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const uint32_t lo = f32_to_half_ref(sx[lane * 8 + 2 * i]);
-        const uint32_t hi = f32_to_half_ref(sx[lane * 8 + 2 * i + 1]);
+        const uint32_t lo = f32_to_half_ref(x[2 * i]);
+        const uint32_t hi = f32_to_half_ref(x[2 * i + 1]);
         w[i] = lo | (hi << 16);
     }
-    reinterpret_cast<uint4 *>(row)[lane] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4 *>(row)[group] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // A CTA takes 32 consecutive vectors of the launch (vector = token * 2*n_kv + j; j < n_kv: K head
@@ -86,25 +116,25 @@ __device__ __forceinline__ void store_f16_row(const float *sx, int lane, uint8_t
 // kVecs = 32 for bulk calls (throughput: every lane of the norm pass works), 8 for small calls
 // (latency: one vector per warp).
 template <int BITS, int kVecs>
-__global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
+__global__ void __launch_bounds__(kThreads, kVecs == 32 ? 5 : 4) append_kernel(AppendArgs a) {
     extern __shared__ __align__(16) float smem[];
     float *sbook = smem + kVecs * kVecPad;  // centroids
     float *sgiv = sbook + 256;              // Givens table
     float *snorm = sgiv + kHd;              // the 32 norms
-    [[maybe_unused]] float4 *b4 = reinterpret_cast<float4 *>(snorm + 32);   // centroid neighbourhoods of the two-read search
-    [[maybe_unused]] uint8_t *cells = reinterpret_cast<uint8_t *>(b4 + 16); // its 512 cells
+    [[maybe_unused]] uint2 *tab = reinterpret_cast<uint2 *>(snorm + 32);    // the 512 cells of the one-read centroid search
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kv = a.n_kv, per_tok = 2 * n_kv;
     const int n_vec = a.n_tokens * per_tok, v0 = blockIdx.x * kVecs;
+    // vector -> (token, K|V head): a shift and a mask when 2 * n_kv is a power of two (it is for qwen35)
+    const int tok_shift = (per_tok & (per_tok - 1)) == 0 ? __ffs(per_tok) - 1 : -1;
+    auto tok_of = [&](int vec) { return tok_shift >= 0 ? vec >> tok_shift : vec / per_tok; };
     const bool planar = a.k_kind == ROW_PLANAR || a.v_kind == ROW_PLANAR;
 
     if (BITS > 0) {
         for (int i = threadIdx.x; i < (1 << BITS); i += kThreads) sbook[i] = a.book[i];
         for (int i = threadIdx.x; i < kHd; i += kThreads) sgiv[i] = a.givens[i];
-        if constexpr (BITS >= 1 && BITS <= 4) {
-            __syncthreads();
-            build_cell_tables(sbook, 1 << BITS, b4, cells);
-        }
+        if constexpr (BITS >= 1 && BITS <= 4)  // built once per context on the host
+            for (int i = threadIdx.x; i < 256; i += kThreads) reinterpret_cast<uint4 *>(tab)[i] = __ldg(reinterpret_cast<const uint4 *>(a.cell_tab) + i);
     }
     // k and v may come from the previous kernel in the stream: with programmatic dependent launch
     // only the table copies above run ahead of it.  Nothing after this kernel depends on more
@@ -124,7 +154,7 @@ __global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
         ra[u] = rb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         rcs[u] = make_float2(1.f, 0.f);
         if (vec < n_vec) {
-            const int tok = vec / per_tok, j = vec - tok * per_tok;
+            const int tok = tok_of(vec), j = vec - tok * per_tok;
             const bool is_v = j >= n_kv;
             const int kv = is_v ? j - n_kv : j;
             const float4 *src4 = reinterpret_cast<const float4 *>((is_v ? a.v : a.k) + ((size_t)tok * n_kv + kv) * kHd);
@@ -143,7 +173,7 @@ __global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
         float *sx = smem + lv * kVecPad;
         reinterpret_cast<float4 *>(sx)[lane] = ra[u];
         reinterpret_cast<float4 *>(sx)[lane + 32] = rb[u];
-        const bool is_v = (vec % per_tok) >= n_kv;
+        const bool is_v = (vec - tok_of(vec) * per_tok) >= n_kv;
         if (!is_v) {
             __syncwarp();
             if (half <= 32) {
@@ -154,7 +184,7 @@ __global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
                     sx[lane + half] = x1;
                 }
             } else {  // wider rotations: entries beyond the prefetched 32 come straight from the table
-                const int tok = vec / per_tok, pos = a.desc ? a.desc[tok].z : a.pos0 + tok;
+                const int tok = tok_of(vec), pos = a.desc ? a.desc[tok].z : a.pos0 + tok;
                 const float2 *cs = a.rope + (size_t)pos * half;
                 for (int p = lane; p < half; p += 32) {
                     float x0 = sx[p], x1 = sx[p + half];
@@ -185,7 +215,7 @@ __global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
     for (int lv = warp; lv < kVecs; lv += kWarps) {
         const int vec = v0 + lv;
         if (vec >= n_vec) break;
-        const int tok = vec / per_tok, j = vec - tok * per_tok;
+        const int tok = tok_of(vec), j = vec - tok * per_tok;
         const bool is_v = j >= n_kv;
         const int kv = is_v ? j - n_kv : j;
         size_t seq_rows = 0;
@@ -209,7 +239,7 @@ __global__ void __launch_bounds__(kThreads) append_kernel(AppendArgs a) {
             if constexpr (BITS > 0) {
                 const float n = snorm[lv];
                 if (lane == 0) (is_v ? a.v_norms : a.k_norms)[r] = n;
-                if constexpr (BITS <= 4) store_planar_row_cell<BITS>(sx, lane, n, sgiv, sbook, b4, cells, row);
+                if constexpr (BITS <= 4) store_planar_row_thr<BITS>(sx, lane, n, sgiv, sbook, tab, row);
                 else store_planar_row<BITS>(sx, lane, n, sgiv, sbook, row);
             }
         }
@@ -225,7 +255,7 @@ bk_status launch_append(bk_ctx *ctx, const AppendArgs &a) {
     const size_t n_vec = (size_t)a.n_tokens * 2 * a.n_kv;
     const bool bulk = n_vec > (size_t)8 * 2 * ctx->n_sms;  // more than two small CTAs per SM: go for throughput
     const int vecs = bulk ? 32 : 8;
-    const size_t smem = (size_t)(vecs * kVecPad + 256 + kHd + 32) * sizeof(float) + 16 * sizeof(float4) + 512;
+    const size_t smem = (size_t)(vecs * kVecPad + 256 + kHd + 32) * sizeof(float) + 512 * sizeof(uint2);
     const unsigned grid = (unsigned)((n_vec + vecs - 1) / vecs);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -239,11 +269,18 @@ bk_status launch_append(bk_ctx *ctx, const AppendArgs &a) {
     cfg.numAttrs = 1;
     cudaError_t err = cudaSuccess;
     const bool planar = a.k_kind == ROW_PLANAR || a.v_kind == ROW_PLANAR;
+    // The bulk kernel wants five CTAs of 39 KiB per SM: ask for the largest shared-memory carve-out (once per
+    // kernel and process; a hint, so its result is not checked).
+    auto launch_bulk = [&](auto *kernel) {
+        static std::atomic<bool> hinted{false};
+        if (!hinted.exchange(true)) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        return cudaLaunchKernelEx(&cfg, kernel, a);
+    };
     if (!planar) {
-        err = bulk ? cudaLaunchKernelEx(&cfg, append_kernel<0, 32>, a) : cudaLaunchKernelEx(&cfg, append_kernel<0, 8>, a);
+        err = bulk ? launch_bulk(append_kernel<0, 32>) : cudaLaunchKernelEx(&cfg, append_kernel<0, 8>, a);
     } else {
         const bool ok = dispatch_bits(a.bits, [&]<int B>() {
-            err = bulk ? cudaLaunchKernelEx(&cfg, append_kernel<B, 32>, a) : cudaLaunchKernelEx(&cfg, append_kernel<B, 8>, a);
+            err = bulk ? launch_bulk(append_kernel<B, 32>) : cudaLaunchKernelEx(&cfg, append_kernel<B, 8>, a);
         });
         if (!ok) return fail(ctx, BK_ERR_INVALID, "append: bits must be 1..8");
     }

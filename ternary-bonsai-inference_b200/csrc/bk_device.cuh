@@ -90,49 +90,20 @@ __device__ __forceinline__ uint32_t nearest_centroid_fast(float v, const float *
     return (uint32_t)((d1 < d0) ? hi : lo);
 }
 
-// The same index once more, for codebooks of up to 16 centroids, with two shared-memory reads instead of
-// six: the value picks one of 512 cells of width 2^-10 over [-0.25, 0.25) (clamped), the cell names the last
-// centroid at or below its lower edge (a cell is narrower than any gap between centroids, so the last
-// centroid <= v is that one or a neighbour), and one 16-byte read brings that centroid with its left and
-// right neighbours.  cells[512] and b4[16] = (c[i-1], c[i], c[i+1], c[i+2]) with -inf / +inf beyond the ends
-// are built per CTA by build_cell_tables().  Non-finite v takes the scan.
+// The same index once more, for codebooks of up to 16 centroids, from ONE 8-byte read.  Along the ascending codebook the scan's answer is the number of
+// thresholds T_i <= v, where T_i is the smallest float for which centroid i + 1 beats centroid i in the scan's
+// own arithmetic (|v - c_{i+1}| < |v - c_i|, both differences rounded to f32; the predicate is monotone in v
+// because f32 subtraction is).  The host finds every T_i by bisection over the floats, with the same rounded
+// operations, and lays them out in 512 cells of width 2^-10 over [-0.25, 0.25) (clamped): cell k holds how many
+// thresholds lie in lower cells and the one threshold inside it (+inf if none; the host checks that no cell
+// holds two).  tab[cell] = (count, threshold bits).  Non-finite and huge v take the scan.
 template <int BITS>
-__device__ __forceinline__ uint32_t nearest_centroid_cell(float v, const float *book, const float4 *b4, const uint8_t *cells) {
+__device__ __forceinline__ uint32_t nearest_centroid_thr(float v, const float *book, const uint2 *tab) {
     static_assert(BITS <= 4, "the cell table covers codebooks of up to 16 centroids");
     if (!(fabsf(v) < 4.0f)) return nearest_centroid(v, book, 1 << BITS);
     const int cell = min(max(__float2int_rd(__fmul_rn(__fadd_rn(v, 0.25f), 1024.0f)), 0), 511);
-    int lo = cells[cell];
-    const float4 c = b4[lo];  // c.y = book[lo]
-    float c_lo = c.y, c_hi = c.z;
-    if (c.z <= v) {  // the right neighbour is at or below v too: it is the last one (cells are narrower than gaps)
-        lo += 1;
-        c_lo = c.z;
-        c_hi = c.w;
-    } else if (c.y > v) {  // v lies below the cell's centroid (rounding of the cell index, or v below book[0])
-        lo -= 1;
-        c_lo = c.x;
-        c_hi = c.y;
-    }
-    // lo may be -1 (c_lo = -inf: its distance is inf, the right one wins) or the last index (c_hi = +inf)
-    const float d0 = fabsf(__fsub_rn(v, c_lo)), d1 = fabsf(__fsub_rn(v, c_hi));
-    return (uint32_t)((d1 < d0) ? lo + 1 : lo);
-}
-// Fills the tables of nearest_centroid_cell() from an ascending codebook of n <= 16 centroids (all threads of
-// the CTA call; the caller synchronises afterwards).
-__device__ __forceinline__ void build_cell_tables(const float *book, int n, float4 *b4, uint8_t *cells) {
-    const float inf = __int_as_float(0x7f800000);
-    for (int i = threadIdx.x; i < 16; i += blockDim.x) {
-        const float cm = (i >= 1 && i - 1 < n) ? book[i - 1] : -inf, c0 = i < n ? book[i] : inf;
-        const float c1 = i + 1 < n ? book[i + 1] : inf, c2 = i + 2 < n ? book[i + 2] : inf;
-        b4[i] = make_float4(cm, c0, c1, c2);
-    }
-    for (int cell = threadIdx.x; cell < 512; cell += blockDim.x) {
-        const float edge = __fsub_rn(__fmul_rn((float)cell, 1.0f / 1024.0f), 0.25f);  // exact
-        int last = 0;
-        for (int i = 1; i < n; i++)
-            if (book[i] <= edge) last = i;
-        cells[cell] = (uint8_t)last;
-    }
+    const uint2 e = tab[cell];
+    return e.x + (v >= __uint_as_float(e.y) ? 1u : 0u);
 }
 
 // src/kvquant.rs:398: sequential f32 sum of squares then sqrt; 256 dependent adds by design.

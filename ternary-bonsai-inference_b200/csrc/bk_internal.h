@@ -62,6 +62,7 @@ struct bk_ctx {
     uint64_t launches = 0;
     float *d_givens = nullptr;     // 128 (cos, sin) pairs
     float *d_codebooks = nullptr;  // 8 books, book of width b at (b-1)*kBookStride
+    uint2 *d_cell_tabs = nullptr;  // widths 1..4: 512 (index, threshold) cells each, table of width b at (b-1)*512 (bk_device.cuh)
     float h_givens[bk::kHd];
     float h_codebooks[bk::kMaxBits * bk::kBookStride];
     float lut_alpha[bk::kMaxBits + 1] = {};  // per width: scale applied to centroids before f16 rounding
@@ -166,6 +167,7 @@ struct AppendArgs {
     const float2 *rope;        // [rope_n_pos][n_rot/2]
     const float *givens;
     const float *book;         // codebook of this width (null unless planar)
+    const uint2 *cell_tab;     // widths 1..4: the 512 cells of nearest_centroid_thr() (null otherwise)
     const int4 *desc;          // per token (seq, row, rope_pos, 0); nullptr = contiguous single sequence
     size_t seq_stride_rows;    // rows (pos*n_kv units) between sequences of one layer
     int n_tokens, n_kv, n_rot, bits;

@@ -10,19 +10,16 @@ namespace {
 
 // PlanarQuant::quantize, src/kvquant.rs:397-412.  One warp per vector.
 template <int BITS>
-__global__ void quantize_kernel(int n_vec, const float *x, const float *givens, const float *book,
+__global__ void quantize_kernel(int n_vec, const float *x, const float *givens, const float *book, const uint2 *cell_tab,
                                 uint8_t *packed, float *norms) {
     __shared__ __align__(16) float sx[4][kHd];
     __shared__ float sbook[256];
-    __shared__ float4 b4[16];       // tables of the two-read centroid search (codebooks of up to 16 centroids)
-    __shared__ uint8_t cells[512];
+    __shared__ __align__(16) uint2 tab[BITS <= 4 ? 512 : 1];  // the cells of the one-read centroid search (up to 16 centroids)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int vec = blockIdx.x * 4 + warp;
     for (int i = threadIdx.x; i < (1 << BITS); i += blockDim.x) sbook[i] = book[i];
-    if constexpr (BITS <= 4) {
-        __syncthreads();
-        build_cell_tables(sbook, 1 << BITS, b4, cells);
-    }
+    if constexpr (BITS <= 4)
+        for (int i = threadIdx.x; i < 512; i += blockDim.x) tab[i] = cell_tab[i];
     if (vec < n_vec) {
         const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)vec * kHd);
         reinterpret_cast<float4 *>(sx[warp])[lane] = src[lane];
@@ -43,8 +40,8 @@ __global__ void quantize_kernel(int n_vec, const float *x, const float *givens, 
         givens_fwd(__fmul_rn(sx[warp][2 * i], inv), __fmul_rn(sx[warp][2 * i + 1], inv), givens[2 * i],
                    givens[2 * i + 1], r0, r1);
         if constexpr (BITS <= 4) {  // the search the bulk append uses
-            word |= (uint64_t)nearest_centroid_cell<BITS>(r0, sbook, b4, cells) << (BITS * (2 * pr));
-            word |= (uint64_t)nearest_centroid_cell<BITS>(r1, sbook, b4, cells) << (BITS * (2 * pr + 1));
+            word |= (uint64_t)nearest_centroid_thr<BITS>(r0, sbook, tab) << (BITS * (2 * pr));
+            word |= (uint64_t)nearest_centroid_thr<BITS>(r1, sbook, tab) << (BITS * (2 * pr + 1));
         } else {
             word |= (uint64_t)nearest_centroid_fast<BITS>(r0, sbook) << (BITS * (2 * pr));
             word |= (uint64_t)nearest_centroid_fast<BITS>(r1, sbook) << (BITS * (2 * pr + 1));
@@ -136,7 +133,8 @@ bk_status launch_quantize(bk_ctx *ctx, int bits, int n_vec, const float *x, uint
     if (n_vec <= 0) return BK_OK;
     const float *book = ctx->d_codebooks + (bits - 1) * kBookStride;
     if (!dispatch_bits(bits, [&]<int B>() {
-            quantize_kernel<B><<<(n_vec + 3) / 4, 128, 0, ctx->stream>>>(n_vec, x, ctx->d_givens, book, packed, norms);
+            quantize_kernel<B><<<(n_vec + 3) / 4, 128, 0, ctx->stream>>>(n_vec, x, ctx->d_givens, book,
+                                                                         B <= 4 ? ctx->d_cell_tabs + (B - 1) * 512 : nullptr, packed, norms);
         }))
         return fail(ctx, BK_ERR_INVALID, "bits must be 1..8");
     BK_LAUNCH_DONE(ctx);
