@@ -1,4 +1,4 @@
-// Batched (prefill) attention over a 4-, 3- or 2-bit planar cache, or an f16 cache, on the
+// Batched (prefill) attention over a 4-, 3- or 2-bit planar cache, or an f16 or f32 cache, on the
 // 5th-generation tensor cores: the same work split, operands and arithmetic as bk_prefill.cu
 // (which documents them and stays as the mma.sync form), with both contractions issued as
 // tcgen05.mma and the accumulators in tensor memory.
@@ -19,6 +19,8 @@
 //      into 256 tensor-memory columns and commits.
 // f16 caches (BITS = 16) skip the dequantization: the TMA engine drops their rows, which are the
 // operands as stored, into two shared-memory stages through the cache's swizzled tensor maps.
+// f32 caches (BITS = 32) take the place of the dequantization with a split of every float into f16 hi + lo
+// (both K parts side by side as for 4 bit, both V parts as for 4 bit).
 // Every mbarrier wait is bounded (a time-out raises the context's error flag and the kernel runs
 // on to its end, where the tensor memory is always released).  The packed rows of the next tile
 // are fetched into registers (f16: into the other stage) while the current one is computed.
@@ -119,8 +121,12 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
     // two shared-memory stages in the swizzled layout and nothing is dequantized (no table, no norms,
     // no Givens rotation); everything else is the same kernel.
     constexpr bool kF16 = BITS == 16;
-    constexpr int kRowBytes = kF16 ? 512 : 32 * BITS;
-    constexpr bool kLoTiles = BITS == 4;  // see bk_prefill.cu: a 4-bit f16 table is only good to 1e-4
+    // BITS = 32 stands for an f32 cache: its rows are split into f16 hi + lo on their way into the operand tiles
+    // (the lo tiles are the ones the 4-bit rows use for their rounding remainders); like f16 rows they are
+    // neither rotated nor normalised.
+    constexpr bool kF32 = BITS == 32, kRaw = kF16 || kF32;
+    constexpr int kRowBytes = kF16 ? 512 : kF32 ? 1024 : 32 * BITS;
+    constexpr bool kLoTiles = BITS == 4 || kF32;  // see bk_prefill.cu: a 4-bit f16 table is only good to 1e-4
     // The K operand holds k_hi in rows 0-31 of every slab and, for 4 bit, k_lo in rows 32-63: one MMA
     // with N = 64 then yields q_hi k_hi and q_hi k_lo side by side (q is re-read from shared memory
     // once instead of twice, and that read is what an N = 32 MMA waits for).
@@ -140,12 +146,12 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
     // ---- tables, barriers, tensor memory ----------------------------------------------------
     for (int i = tid; i < kHd; i += kUT) ss.givens[i] = a.givens[i];
     if (tid < 16) {
-        const float c = kF16 ? 0.f : a.book[tid & ((1 << (kF16 ? 4 : BITS)) - 1)] * pa.lut_alpha;
+        const float c = kRaw ? 0.f : a.book[tid & ((1 << (kRaw ? 4 : BITS)) - 1)] * pa.lut_alpha;
         const __half h = __float2half_rn(c);
         ss.table[tid] = h;
         ss.table_lo[tid] = __float2half_rn(c - __half2float(h));
     }
-    if (kF16 && tid < kTK) {  // no norms: ||k|| = 1, log2 ||v|| = 0
+    if (kRaw && tid < kTK) {  // no norms: ||k|| = 1, log2 ||v|| = 0
         ss.kn[tid] = 1.f;
         ss.lv[tid] = 0.f;
     }
@@ -222,7 +228,7 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
                 float o0 = 0.f, o1 = 0.f;
                 if (real) {
                     const int d = 8 * lane + 2 * p;
-                    if constexpr (kF16) {
+                    if constexpr (kRaw) {
                         o0 = stage[pad(d)];
                         o1 = stage[pad(d + 1)];
                     } else {
@@ -251,8 +257,42 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
     const size_t seq_rows = (size_t)pa.seq * a.seq_stride_rows;
     uint32_t pk[4], pv[4];
     float pn = 0.f;
+    // f32: the thread's 128 bytes of a K row or of a V row (one buffer: K of this tile until it is split, then
+    // V of this tile, then K of the next one)
+    [[maybe_unused]] float4 pf[kF32 ? 8 : 1];
+    [[maybe_unused]] auto fetch_f32 = [&](int tile, bool v_side) {
+        const int pos = min(c0 + tile * kTK + my_row, a.n_ctx - 1);
+        const size_t row = seq_rows + (size_t)pos * a.n_kv + kv;
+        const float4 *src = reinterpret_cast<const float4 *>((v_side ? a.v_rows : a.k_rows) + row * kRowBytes) + 8 * my_c;
+#pragma unroll
+        for (int i = 0; i < (kF32 ? 8 : 1); i++) pf[i] = __ldg(src + i);
+    };
+    // f32: split the buffer into f16 hi + lo and store both as four 16-byte chunks of a tile row; rows at or past
+    // `end` are stored as zeros (they may hold anything, and 0 * Inf would poison the accumulators)
+    [[maybe_unused]] auto split_store_f32 = [&](uint8_t *tile_hi, uint8_t *tile_lo, int rows, int row_hi, int row_lo, bool live) {
+#pragma unroll
+        for (int j = 0; j < (kF32 ? 4 : 0); j++) {
+            const float x[8] = {pf[2 * j].x, pf[2 * j].y, pf[2 * j].z, pf[2 * j].w, pf[2 * j + 1].x, pf[2 * j + 1].y, pf[2 * j + 1].z, pf[2 * j + 1].w};
+            uint32_t h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float x0 = live ? x[2 * e] : 0.f, x1 = live ? x[2 * e + 1] : 0.f;
+                const __half2 hv = __floats2half2_rn(x0, x1);
+                const float2 hf = __half22float2(hv);
+                const __half2 lv = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
+                h[e] = *reinterpret_cast<const uint32_t *>(&hv);
+                l[e] = *reinterpret_cast<const uint32_t *>(&lv);
+            }
+            *reinterpret_cast<uint4 *>(tile_hi + sw_off(rows, row_hi, 4 * my_c + j)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4 *>(tile_lo + sw_off(rows, row_lo, 4 * my_c + j)) = make_uint4(l[0], l[1], l[2], l[3]);
+        }
+    };
     auto fetch = [&](int tile) {
         if constexpr (kF16) return;
+        if constexpr (kF32) {
+            fetch_f32(tile, false);
+            return;
+        }
         const int pos = min(c0 + tile * kTK + my_row, a.n_ctx - 1);
         const size_t row = seq_rows + (size_t)pos * a.n_kv + kv;
         const uint8_t *kr = a.k_rows + row * kRowBytes, *vr = a.v_rows + row * kRowBytes;
@@ -346,10 +386,15 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             __syncthreads();
         } else {
             // ---- 1. dequantize K (the previous tile's products are complete: bar_o was awaited) --------
-            widen(pk);
-            dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, 4 * my_c);
-            if (tid < kTK) ss.kn[tid] = pn;
-            else if (tid < 2 * kTK) ss.lv[tid - kTK] = fast_log2(fmaxf(pn, 1e-30f));
+            if constexpr (kF32) {
+                split_store_f32(sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, c0 + tile * kTK + my_row < c1);
+                fetch_f32(tile, true);  // this tile's V rows travel while the S products are issued
+            } else {
+                widen(pk);
+                dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, 4 * my_c);
+                if (tid < kTK) ss.kn[tid] = pn;
+                else if (tid < 2 * kTK) ss.lv[tid - kTK] = fast_log2(fmaxf(pn, 1e-30f));
+            }
             fence_smem_to_async_proxy();
             __syncthreads();
         }
@@ -370,7 +415,11 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             umma_commit(bar_s);
         }
         __syncwarp();
-        if constexpr (!kF16) {
+        if constexpr (kF32) {
+            split_store_f32(sm + oVhi, sm + oVlo, kTK, my_row, my_row, c0 + tile * kTK + my_row < c1);
+            if (tile + 1 < n_tiles) fetch(tile + 1);
+            fence_smem_to_async_proxy();
+        } else if constexpr (!kF16) {
             widen(pv);
             dequant_store_shfl<kLoTiles>(pv, tab, sm + oVhi, sm + oVlo, kTK, my_row, my_row, 4 * my_c);
             if (tile + 1 < n_tiles) fetch(tile + 1);
@@ -483,7 +532,7 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             for (int j = 0; j < 32; j += 2) {
                 const int d = 32 * b + j;
                 float o0 = __uint_as_float(o[j]) * mul, o1 = __uint_as_float(o[j + 1]) * mul;
-                if (whole && !kF16) {
+                if (whole && !kRaw) {
                     float r0, r1;
                     givens_inv(o0, o1, ss.givens[d], ss.givens[d + 1], r0, r1);
                     o0 = r0;
@@ -552,7 +601,7 @@ bk_status launch_umma_one(bk_ctx *ctx, const PrefillUArgs &pa) {
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     if (pa.n_chunks > 1) {
-        prefill_umma_merge_kernel<<<pa.n_tokens * pa.d.n_head, 128, 0, ctx->stream>>>(pa.scratch, BITS == 16 ? nullptr : pa.d.givens,
+        prefill_umma_merge_kernel<<<pa.n_tokens * pa.d.n_head, 128, 0, ctx->stream>>>(pa.scratch, (BITS == 16 || BITS == 32) ? nullptr : pa.d.givens,
                                                                                       pa.n_chunks, pa.d.out);
         ctx->launches++;
         BK_CUDA(ctx, cudaGetLastError());
@@ -566,7 +615,8 @@ bool prefill_umma_supported(const DecodeArgs &a) {
     const int n_rep = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
     const bool planar = a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3 || a.bits == 2);
     const bool f16 = a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 && a.v_row_bytes == 512;
-    return (planar || f16) && a.h_tmap_k && a.h_tmap_v && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
+    const bool f32 = a.k_kind == ROW_F32 && a.v_kind == ROW_F32 && a.k_row_bytes == 1024 && a.v_row_bytes == 1024;
+    return (planar || f16 || f32) && a.h_tmap_k && a.h_tmap_v && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
 bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha) {
@@ -600,6 +650,7 @@ bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos
 #define BK_PU_CASE(R)                                                                            \
     case R:                                                                                      \
         if (a.k_kind == ROW_F16) return launch_umma_one<16, R>(ctx, pa);                         \
+        if (a.k_kind == ROW_F32) return launch_umma_one<32, R>(ctx, pa);                         \
         if (a.bits == 2) return launch_umma_one<2, R>(ctx, pa);                                  \
         return a.bits == 3 ? launch_umma_one<3, R>(ctx, pa) : launch_umma_one<4, R>(ctx, pa);
     switch (n_rep) {
