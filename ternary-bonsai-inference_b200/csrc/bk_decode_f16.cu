@@ -39,6 +39,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "bk_decode_common.cuh"
 #include "bk_mma_common.cuh"
 
@@ -146,6 +148,7 @@ decode_f16_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t s
     const int n_stages = ring_end > ring0 ? min((int)((ring_end - ring0) / (uint32_t)(kScanW * kStageBytes)), kSplit ? 1 : kMaxStages) : 0;
     if (n_stages < 1) {  // never expected (the host checks the size): report, do not run
         if (tid == 0) raise_error(err_flag, 2);
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");  // keep the stream's kernel order intact
         return;
     }
     const uint32_t bar0 = base + (uint32_t)offsetof(Other, bar) + (uint32_t)(warp * kMaxStages) * 8u;
@@ -762,10 +765,10 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
     using R = Rows<KB, VB>;
     constexpr int kScanW = R::kScanW, kFW = R::kFW, kStageBytes = R::kStageBytes;
     auto *kernel = decode_f16_mma_kernel<KB, VB, NREP, QSPLIT>;
-    static size_t smem_for[64] = {};
+    static std::atomic<size_t> smem_for[64] = {};  // per device; racing first calls compute the same value
     const int dev = ctx->device;
     if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (row mma): device index above 63");
-    if (smem_for[dev] == 0) {
+    if (smem_for[dev].load() == 0) {
         cudaFuncAttributes fa;
         BK_CUDA(ctx, cudaFuncGetAttributes(&fa, kernel));
         int optin = 0;
@@ -776,9 +779,9 @@ bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, floa
         static_assert((size_t)kScanW * kStageBytes >= (size_t)kFW * 6 * kHeadStride * 4, "merge area does not fit the ring");
         if (dyn < need) return fail(ctx, BK_ERR_UNSUPPORTED, "decode (row mma): not enough shared memory per block on this device");
         BK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-        smem_for[dev] = dyn;
+        smem_for[dev].store(dyn);
     }
-    const size_t smem = smem_for[dev];
+    const size_t smem = smem_for[dev].load();
     if (!a.h_tmap_k || !a.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "decode (row mma): the cache has no tensor maps");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)m.n_items);

@@ -25,6 +25,7 @@
 //     memory, where the four digit sums are joined.
 // The result differs from the reference's scalar path by the summation order across blocks and
 // the 2^-25 (block max|x|) grid of X, less than its own AVX2 path does (src/kernels.rs:652-660).
+#include <atomic>
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
@@ -264,10 +265,12 @@ __global__ void __launch_bounds__(kPqGroupThreads * kPqMaxGroups) pq2_matvec_ker
 
 template <int NT>
 bk_status launch_nt(bk_ctx *ctx, const Pq2Args &a, int grid, size_t smem) {
-    static int opted_in_device = -1;  // the opt-in is per device and costs a driver call: once is enough
-    if (opted_in_device != ctx->device) {
+    static std::atomic<bool> opted_in[64] = {};  // the opt-in is per device and costs a driver call: once per device is enough
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "pq2 matvec: device index above 63");
+    if (!opted_in[dev].load()) {
         BK_CUDA(ctx, cudaFuncSetAttribute(pq2_matvec_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        opted_in_device = ctx->device;
+        opted_in[dev].store(true);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);

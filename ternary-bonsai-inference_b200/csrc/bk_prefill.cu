@@ -25,6 +25,7 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "bk_device.cuh"
 #include "bk_internal.h"
@@ -430,12 +431,12 @@ __global__ void __launch_bounds__(128) prefill_merge_kernel(const float *scratch
 
 template <int BITS, int NREP>
 bk_status launch_prefill_one(bk_ctx *ctx, const PrefillArgs &pa) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};  // per device; racing first calls set the same attribute
     const int dev = ctx->device;
     if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "prefill: device index above 63");
-    if (!configured[dev]) {
+    if (!configured[dev].load()) {
         BK_CUDA(ctx, cudaFuncSetAttribute(prefill_mma_kernel<BITS, NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefillSmem));
-        configured[dev] = true;
+        configured[dev].store(true);
     }
     const int grid = pa.n_blocks * pa.d.n_kv * pa.n_chunks;
     prefill_mma_kernel<BITS, NREP><<<grid, kPT, kPrefillSmem, ctx->stream>>>(pa);

@@ -28,6 +28,7 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "bk_device.cuh"
 #include "bk_internal.h"
@@ -587,12 +588,12 @@ __global__ void __launch_bounds__(128) prefill_umma_merge_kernel(const float *sc
 
 template <int BITS, int NREP>
 bk_status launch_umma_one(bk_ctx *ctx, const PrefillUArgs &pa) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};  // per device; racing first calls set the same attribute
     const int dev = ctx->device;
     if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "prefill: device index above 63");
-    if (!configured[dev]) {
+    if (!configured[dev].load()) {
         BK_CUDA(ctx, cudaFuncSetAttribute(prefill_umma_kernel<BITS, NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmem));
-        configured[dev] = true;
+        configured[dev].store(true);
     }
     const int grid = pa.n_blocks * pa.d.n_kv * pa.n_chunks;
     if (!pa.d.h_tmap_k || !pa.d.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "prefill: the cache has no tensor maps");
