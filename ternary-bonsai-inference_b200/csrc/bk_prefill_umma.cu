@@ -108,7 +108,7 @@ struct PrefillUArgs {
     int *err_flag;
 };
 
-template <int BITS, int NREP>
+template <int BITS, int NREP, bool VF32 = false>
 __global__ void __launch_bounds__(kUT, 1)
 prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -126,8 +126,15 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
     // (the lo tiles are the ones the 4-bit rows use for their rounding remainders); like f16 rows they are
     // neither rotated nor normalised.
     constexpr bool kF32 = BITS == 32, kRaw = kF16 || kF32;
-    constexpr int kRowBytes = kF16 ? 512 : kF32 ? 1024 : 32 * BITS;
-    constexpr bool kLoTiles = BITS == 4 || kF32;  // see bk_prefill.cu: a 4-bit f16 table is only good to 1e-4
+    // VF32: the reference's K-only mode, planar K rows (BITS = 4 or 3) beside f32 V rows: the K side of the planar
+    // kernel, the V side of the f32 one; q is rotated into the K rows' basis, the output is not rotated back.
+    static_assert(!VF32 || BITS == 4 || BITS == 3, "VF32 goes with 4- or 3-bit K rows");
+    constexpr bool kVRows32 = kF32 || VF32;   // V rows are floats
+    constexpr bool kVPlanar = !kRaw && !VF32; // V rows are planar: a norm per row, the output is rotated back
+    constexpr int kRowBytes = kF16 ? 512 : kF32 ? 1024 : 32 * BITS;  // (K rows; f32 V rows are 1024 bytes)
+    // lo tiles: the rounding remainders of the 4-bit table (see bk_prefill.cu: it is only good to 1e-4), the lo parts
+    // of f32 rows; beside raw V rows (several times larger than dequantized ones) the 3-bit table carries them too
+    constexpr bool kLoTiles = BITS == 4 || kF32 || VF32;
     // The K operand holds k_hi in rows 0-31 of every slab and, for 4 bit, k_lo in rows 32-63: one MMA
     // with N = 64 then yields q_hi k_hi and q_hi k_lo side by side (q is re-read from shared memory
     // once instead of twice, and that read is what an N = 32 MMA waits for).
@@ -260,19 +267,19 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
     float pn = 0.f;
     // f32: the thread's 128 bytes of a K row or of a V row (one buffer: K of this tile until it is split, then
     // V of this tile, then K of the next one)
-    [[maybe_unused]] float4 pf[kF32 ? 8 : 1];
+    [[maybe_unused]] float4 pf[kVRows32 ? 8 : 1];
     [[maybe_unused]] auto fetch_f32 = [&](int tile, bool v_side) {
         const int pos = min(c0 + tile * kTK + my_row, a.n_ctx - 1);
         const size_t row = seq_rows + (size_t)pos * a.n_kv + kv;
-        const float4 *src = reinterpret_cast<const float4 *>((v_side ? a.v_rows : a.k_rows) + row * kRowBytes) + 8 * my_c;
+        const float4 *src = reinterpret_cast<const float4 *>((v_side ? a.v_rows : a.k_rows) + row * 1024) + 8 * my_c;
 #pragma unroll
-        for (int i = 0; i < (kF32 ? 8 : 1); i++) pf[i] = __ldg(src + i);
+        for (int i = 0; i < (kVRows32 ? 8 : 1); i++) pf[i] = __ldg(src + i);
     };
     // f32: split the buffer into f16 hi + lo and store both as four 16-byte chunks of a tile row; rows at or past
     // `end` are stored as zeros (they may hold anything, and 0 * Inf would poison the accumulators)
     [[maybe_unused]] auto split_store_f32 = [&](uint8_t *tile_hi, uint8_t *tile_lo, int rows, int row_hi, int row_lo, bool live) {
 #pragma unroll
-        for (int j = 0; j < (kF32 ? 4 : 0); j++) {
+        for (int j = 0; j < (kVRows32 ? 4 : 0); j++) {
             const float x[8] = {pf[2 * j].x, pf[2 * j].y, pf[2 * j].z, pf[2 * j].w, pf[2 * j + 1].x, pf[2 * j + 1].y, pf[2 * j + 1].z, pf[2 * j + 1].w};
             uint32_t h[4], l[4];
 #pragma unroll
@@ -297,7 +304,15 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
         const int pos = min(c0 + tile * kTK + my_row, a.n_ctx - 1);
         const size_t row = seq_rows + (size_t)pos * a.n_kv + kv;
         const uint8_t *kr = a.k_rows + row * kRowBytes, *vr = a.v_rows + row * kRowBytes;
-        if constexpr (BITS == 4) {
+        if constexpr (VF32) {  // only the K row is packed (vr is not used: the V row is fetched as floats below)
+            if constexpr (BITS == 4) {
+                const uint4 x = __ldg(reinterpret_cast<const uint4 *>(kr) + my_c);
+                pk[0] = x.x; pk[1] = x.y; pk[2] = x.z; pk[3] = x.w;
+            } else {
+                const uint32_t *k3 = reinterpret_cast<const uint32_t *>(kr) + 3 * my_c;
+                pk[0] = __ldg(k3); pk[1] = __ldg(k3 + 1); pk[2] = __ldg(k3 + 2); pk[3] = 0;
+            }
+        } else if constexpr (BITS == 4) {
             const uint4 x = __ldg(reinterpret_cast<const uint4 *>(kr) + my_c), y = __ldg(reinterpret_cast<const uint4 *>(vr) + my_c);
             pk[0] = x.x; pk[1] = x.y; pk[2] = x.z; pk[3] = x.w;
             pv[0] = y.x; pv[1] = y.y; pv[2] = y.z; pv[3] = y.w;
@@ -310,10 +325,11 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             pk[0] = x.x; pk[1] = x.y; pk[2] = pk[3] = 0;
             pv[0] = y.x; pv[1] = y.y; pv[2] = pv[3] = 0;
         }
-        if (tid < 2 * kTK) {
+        if (tid < (VF32 ? kTK : 2 * kTK)) {
             const int p2 = min(c0 + tile * kTK + (tid & (kTK - 1)), a.n_ctx - 1);
             pn = __ldg((tid < kTK ? a.k_norms : a.v_norms) + seq_rows + (size_t)p2 * a.n_kv + kv);
         }
+        if constexpr (VF32) fetch_f32(tile, true);
     };
     auto widen = [&](uint32_t (&w)[4]) {
         if constexpr (BITS == 3) {
@@ -394,7 +410,7 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
                 widen(pk);
                 dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, 4 * my_c);
                 if (tid < kTK) ss.kn[tid] = pn;
-                else if (tid < 2 * kTK) ss.lv[tid - kTK] = fast_log2(fmaxf(pn, 1e-30f));
+                else if (tid < 2 * kTK) ss.lv[tid - kTK] = VF32 ? 0.f : fast_log2(fmaxf(pn, 1e-30f));
             }
             fence_smem_to_async_proxy();
             __syncthreads();
@@ -416,7 +432,7 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             umma_commit(bar_s);
         }
         __syncwarp();
-        if constexpr (kF32) {
+        if constexpr (kVRows32) {
             split_store_f32(sm + oVhi, sm + oVlo, kTK, my_row, my_row, c0 + tile * kTK + my_row < c1);
             if (tile + 1 < n_tiles) fetch(tile + 1);
             fence_smem_to_async_proxy();
@@ -518,7 +534,7 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
     if (warp < 4) {  // every lane takes part in the warp-collective tensor-memory loads, rows past the block only skip the stores
         const bool real = my_q < n_rows;
         const size_t out_row = real ? (size_t)(tok0 + my_q / NREP) * a.n_head + kv * NREP + my_q % NREP : 0;
-        const float unscale = 1.0f / (kPScale * pa.lut_alpha);
+        const float unscale = 1.0f / (kPScale * (kVPlanar ? pa.lut_alpha : 1.0f));  // (raw V rows carry no table scale)
         const bool whole = pa.n_chunks == 1;
         const float mul = whole ? (lsum > 0.f ? unscale / lsum : 0.f) : unscale;
         float *dst = whole ? a.out + out_row * kHd : pa.scratch + (out_row * pa.n_chunks + chunk) * (kHd + 2);
@@ -533,7 +549,7 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             for (int j = 0; j < 32; j += 2) {
                 const int d = 32 * b + j;
                 float o0 = __uint_as_float(o[j]) * mul, o1 = __uint_as_float(o[j + 1]) * mul;
-                if (whole && !kRaw) {
+                if (whole && kVPlanar) {
                     float r0, r1;
                     givens_inv(o0, o1, ss.givens[d], ss.givens[d + 1], r0, r1);
                     o0 = r0;
@@ -586,23 +602,23 @@ __global__ void __launch_bounds__(128) prefill_umma_merge_kernel(const float *sc
     *reinterpret_cast<float2 *>(out + row * kHd + 2 * pr) = make_float2(o0, o1);
 }
 
-template <int BITS, int NREP>
+template <int BITS, int NREP, bool VF32 = false>
 bk_status launch_umma_one(bk_ctx *ctx, const PrefillUArgs &pa) {
     static std::atomic<bool> configured[64] = {};  // per device; racing first calls set the same attribute
     const int dev = ctx->device;
     if (dev < 0 || dev >= 64) return fail(ctx, BK_ERR_UNSUPPORTED, "prefill: device index above 63");
     if (!configured[dev].load()) {
-        BK_CUDA(ctx, cudaFuncSetAttribute(prefill_umma_kernel<BITS, NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmem));
+        BK_CUDA(ctx, cudaFuncSetAttribute(prefill_umma_kernel<BITS, NREP, VF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmem));
         configured[dev].store(true);
     }
     const int grid = pa.n_blocks * pa.d.n_kv * pa.n_chunks;
     if (!pa.d.h_tmap_k || !pa.d.h_tmap_v) return fail(ctx, BK_ERR_INVALID, "prefill: the cache has no tensor maps");
-    prefill_umma_kernel<BITS, NREP><<<grid, kUT, kUmmaSmem, ctx->stream>>>(pa, *static_cast<const CUtensorMap *>(pa.d.h_tmap_k),
+    prefill_umma_kernel<BITS, NREP, VF32><<<grid, kUT, kUmmaSmem, ctx->stream>>>(pa, *static_cast<const CUtensorMap *>(pa.d.h_tmap_k),
                                                                           *static_cast<const CUtensorMap *>(pa.d.h_tmap_v));
     ctx->launches++;
     BK_CUDA(ctx, cudaGetLastError());
     if (pa.n_chunks > 1) {
-        prefill_umma_merge_kernel<<<pa.n_tokens * pa.d.n_head, 128, 0, ctx->stream>>>(pa.scratch, (BITS == 16 || BITS == 32) ? nullptr : pa.d.givens,
+        prefill_umma_merge_kernel<<<pa.n_tokens * pa.d.n_head, 128, 0, ctx->stream>>>(pa.scratch, (BITS == 16 || BITS == 32 || VF32) ? nullptr : pa.d.givens,
                                                                                       pa.n_chunks, pa.d.out);
         ctx->launches++;
         BK_CUDA(ctx, cudaGetLastError());
@@ -617,7 +633,8 @@ bool prefill_umma_supported(const DecodeArgs &a) {
     const bool planar = a.k_kind == ROW_PLANAR && a.v_kind == ROW_PLANAR && (a.bits == 4 || a.bits == 3 || a.bits == 2);
     const bool f16 = a.k_kind == ROW_F16 && a.v_kind == ROW_F16 && a.k_row_bytes == 512 && a.v_row_bytes == 512;
     const bool f32 = a.k_kind == ROW_F32 && a.v_kind == ROW_F32 && a.k_row_bytes == 1024 && a.v_row_bytes == 1024;
-    return (planar || f16 || f32) && a.h_tmap_k && a.h_tmap_v && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
+    const bool k_only = a.k_kind == ROW_PLANAR && a.v_kind == ROW_F32 && (a.bits == 4 || a.bits == 3) && a.v_row_bytes == 1024;
+    return (planar || f16 || f32 || k_only) && a.h_tmap_k && a.h_tmap_v && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
 bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos0, int n_tokens, float alpha) {
@@ -652,6 +669,7 @@ bk_status launch_prefill_umma(bk_ctx *ctx, const DecodeArgs &a, int seq, int pos
     case R:                                                                                      \
         if (a.k_kind == ROW_F16) return launch_umma_one<16, R>(ctx, pa);                         \
         if (a.k_kind == ROW_F32) return launch_umma_one<32, R>(ctx, pa);                         \
+        if (a.v_kind == ROW_F32) return a.bits == 3 ? launch_umma_one<3, R, true>(ctx, pa) : launch_umma_one<4, R, true>(ctx, pa); \
         if (a.bits == 2) return launch_umma_one<2, R>(ctx, pa);                                  \
         return a.bits == 3 ? launch_umma_one<3, R>(ctx, pa) : launch_umma_one<4, R>(ctx, pa);
     switch (n_rep) {

@@ -942,7 +942,8 @@ def prefill_both(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0, n_tok, seed, n_he
     return got, want
 
 
-@pytest.mark.parametrize("tag,mode,bits,vq", [MODES[2], MODES[3], MODES[1], MODES[8], MODES[0], ("planar2", MODE_PLANAR, 2, True)])
+@pytest.mark.parametrize("tag,mode,bits,vq", [MODES[2], MODES[3], MODES[1], MODES[8], MODES[0], ("planar2", MODE_PLANAR, 2, True),
+                                              MODES[4], ("planar3k", MODE_PLANAR, 3, False)])
 @pytest.mark.parametrize("n0,n_tok", [(0, 45), (300, 50), (3000, 100), (37, 3), (0, 1)])
 def test_prefill_attention_equals_token_by_token(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0, n_tok):
     """planar4 / planar3 / f16 take the batched tensor-core kernel (from 4 tokens on), the other
