@@ -21,6 +21,8 @@
 // operands as stored, into two shared-memory stages through the cache's swizzled tensor maps.
 // f32 caches (BITS = 32) take the place of the dequantization with a split of every float into f16 hi + lo
 // (both K parts side by side as for 4 bit, both V parts as for 4 bit).
+// For packed and f32 caches the K rows of tile t + 1 are dequantized right after the O products of tile t are
+// issued (the K tile is free once S of tile t is complete), so that step runs under the tensor cores' work.
 // Every mbarrier wait is bounded (a time-out raises the context's error flag and the kernel runs
 // on to its end, where the tensor memory is always released).  The packed rows of the next tile
 // are fetched into registers (f16: into the other stage) while the current one is computed.
@@ -378,10 +380,29 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
                 tma_tile_x(dstv + sl * kKVSlab + hf * 2048, &tm_v, sl * 128, kv, gpos + 16 * hf, bar);
             }
     };
+    // Packed (or f32) caches: K of tile t + 1 is dequantized right after the O products of tile t are issued, so
+    // that it runs under them (the K tile is free once S of tile t is complete, which the softmax has waited for);
+    // the norms of the tile travel with it.
+    [[maybe_unused]] auto dequant_k = [&](int tile) {
+        if constexpr (kF32) {
+            split_store_f32(sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, c0 + tile * kTK + my_row < c1);
+            fetch_f32(tile, true);  // this tile's V rows travel while the S products are issued
+        } else if constexpr (!kF16) {
+            widen(pk);
+            dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, 4 * my_c);
+            if (tid < kTK) ss.kn[tid] = pn;
+            else if (tid < 2 * kTK) ss.lv[tid - kTK] = VF32 ? 0.f : fast_log2(fmaxf(pn, 1e-30f));
+        }
+        fence_smem_to_async_proxy();
+    };
     if constexpr (kF16) {
         if (tid == 0 && n_tiles > 0) issue_tma(0, 0);
     } else {
-        if (n_tiles > 0) fetch(0);
+        if (n_tiles > 0) {
+            fetch(0);
+            dequant_k(0);
+        }
+        __syncthreads();
     }
     for (int tile = 0; tile < n_tiles; tile++) {
         const uint32_t parity = (uint32_t)tile & 1u;
@@ -401,20 +422,7 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             }
             fence_smem_to_async_proxy();
             __syncthreads();
-        } else {
-            // ---- 1. dequantize K (the previous tile's products are complete: bar_o was awaited) --------
-            if constexpr (kF32) {
-                split_store_f32(sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, c0 + tile * kTK + my_row < c1);
-                fetch_f32(tile, true);  // this tile's V rows travel while the S products are issued
-            } else {
-                widen(pk);
-                dequant_store_shfl<kLoTiles>(pk, tab, sm + oKhi, sm + oKhi, kKRows, my_row, my_row + 32, 4 * my_c);
-                if (tid < kTK) ss.kn[tid] = pn;
-                else if (tid < 2 * kTK) ss.lv[tid - kTK] = VF32 ? 0.f : fast_log2(fmaxf(pn, 1e-30f));
-            }
-            fence_smem_to_async_proxy();
-            __syncthreads();
-        }
+        }  // (packed and f32 caches: K of this tile was dequantized at the end of the previous iteration)
 
         // ---- 2. S = Q . K^T, and V is dequantized while it runs ---------------------------------------
         if (tid == 0) {
@@ -432,6 +440,14 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             umma_commit(bar_s);
         }
         __syncwarp();
+        if constexpr (!kF16) {
+            // the previous tile's O products read the V tiles and the P buffers and write O: they must be complete
+            // before V is overwritten here and before the softmax below rescales O or rewrites P
+            if (tile > 0) {
+                wait_bar(bar_o, (uint32_t)(tile - 1) & 1u);
+                tc_fence_after_sync();
+            }
+        }
         if constexpr (kVRows32) {
             split_store_f32(sm + oVhi, sm + oVlo, kTK, my_row, my_row, c0 + tile * kTK + my_row < c1);
             if (tile + 1 < n_tiles) fetch(tile + 1);
@@ -526,8 +542,19 @@ prefill_umma_kernel(PrefillUArgs pa, const __grid_constant__ CUtensorMap tm_k, c
             umma_commit(bar_o);
         }
         __syncwarp();
-        wait_bar(bar_o, parity);  // everybody: the tiles and the P buffers may be overwritten, O may be rescaled
-        tc_fence_after_sync();
+        if constexpr (kF16) {
+            wait_bar(bar_o, parity);  // everybody: the tiles and the P buffers may be overwritten, O may be rescaled
+            tc_fence_after_sync();
+        } else {
+            if (tile + 1 < n_tiles) dequant_k(tile + 1);  // under the O products just issued
+            __syncthreads();
+        }
+    }
+    if constexpr (!kF16) {
+        if (n_tiles > 0) {  // the last tile's O products
+            wait_bar(bar_o, (uint32_t)(n_tiles - 1) & 1u);
+            tc_fence_after_sync();
+        }
     }
 
     // ---- epilogue: thread = query row ------------------------------------------------------------------
