@@ -297,6 +297,8 @@ bk_status bk_ctx_create(int device, bk_ctx **out) {
         ctx->d_err = static_cast<int *>(derr);
         const char *e7 = getenv("BONSAI_KV_XCH_POLLS");
         if (e7 && atoi(e7) > 0) ctx->xch_polls = atoi(e7);
+        const char *e8 = getenv("BONSAI_KV_MMA_MIN");
+        if (e8 && atoi(e8) > 0) ctx->mma_min_rows = atoi(e8);
     }
     *out = ctx;
     return BK_OK;
@@ -860,11 +862,15 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
 }
 
 bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos) {
-    // Long sequences of 4-bit planar caches go to the tensor-core kernel, short ones to the
-    // generic f32 kernel.  Below kMmaMinPos positions a sequence cannot fill the machine anyway,
-    // and the f16 lookup table of the tensor-core path (relative error ~1e-4 per centroid) is
-    // only averaged out over many positions, so short contexts keep the exact f32 arithmetic.
-    return !ctx->force_generic && decode_mma_supported(a) && n_pos >= kMmaMinPos;
+    // Long sequences of 4-, 3- and 2-bit planar caches go to the tensor-core kernel, short ones to the
+    // generic f32 kernel: below kMmaMinPos positions the f16 lookup table of that path (relative error ~1e-4 per
+    // centroid) is not averaged out over enough positions, so short contexts keep the exact f32 arithmetic.
+    // f16, f32 and K-only caches take the row kernel from kRowMinPos rows on: it carries about 22 bits at any
+    // length and (append fused in, one launch) is faster than the generic kernel even at 256 rows.
+    if (ctx->force_generic || !decode_mma_supported(a)) return false;
+    // the row kernel (f16, f32, K-only) computes with about 22 bits whatever the length; only speed decides there
+    if (decode_f16_mma_supported(a)) return n_pos >= (ctx->mma_min_rows > 0 ? ctx->mma_min_rows : kRowMinPos);
+    return n_pos >= kMmaMinPos;
 }
 
 }  // namespace bk

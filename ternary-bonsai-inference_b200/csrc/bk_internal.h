@@ -20,7 +20,8 @@ constexpr int kMaxItems = 4096;        // split-K work items one decode launch m
 constexpr int kMaxRep = 8;             // q heads per kv head the scratch is sized for
 constexpr int kPartStride = kHd + 2;   // floats per partial result handed to callers: acc[hd], m, l
 constexpr int kScratchStride = kHd + 4; // floats per partial in the split-K scratch (16-byte aligned rows)
-constexpr int kMmaMinPos = 2048;       // shorter sequences take the generic f32 decode kernel
+constexpr int kMmaMinPos = 2048;       // 4-, 3- and 2-bit caches: shorter sequences take the generic f32 decode kernel
+constexpr int kRowMinPos = 128;        // f16, f32 and K-only caches: the same for the row kernel (speed only: it is exact to ~1e-5 at any length)
 constexpr int kMaxWorld = 8;            // ranks a context-split mailbox can connect
 constexpr int kXchFlags = 512;          // arrival words per (parity, rank) of a mailbox, at least: kv head * 32 + coordinate octet
 __host__ __device__ inline int mailbox_flags(int n_rows) { return n_rows * 32 > kXchFlags ? n_rows * 32 : kXchFlags; }
@@ -69,6 +70,7 @@ struct bk_ctx {
     bool prefill_umma = true;              // batched attention on tcgen05; BONSAI_KV_PREFILL=mma picks the mma.sync kernel
     bool force_generic = false;            // BONSAI_KV_GENERIC=1: never take the tensor-core path
     bool qsplit = true;                    // q as f16 hi + lo in the tensor-core path (BONSAI_KV_QSPLIT=0: hi only)
+    int mma_min_rows = 0;                  // BONSAI_KV_MMA_MIN: rows from which the row kernel (f16, f32, K-only) is taken; 0 = built-in
     int dyn_tiles = 0; bool dist_combine = true;  // BONSAI_KV_DYN=0 / BONSAI_KV_DIST=0 switch them off
     // staging for the *_host entry points (grown on demand)
     void *h_stage = nullptr;

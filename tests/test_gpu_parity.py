@@ -562,7 +562,7 @@ def test_f16_kernel_variants(bk, oracle, monkeypatch, env):
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     ctx = bk.Context(0)
-    for lens in ([17], [2047], [2048], [2049], [2063, 2064, 2065], [5000], [40000, 3, 2500]):
+    for lens in ([17], [127], [128], [129], [143, 144, 145], [1000], [2047], [2048], [2049], [2063, 2064, 2065], [5000], [40000, 3, 2500]):
         got, want = run_both(bk, ctx, oracle, "f16", MODE_F16, 0, False, lens, seed=sum(lens))
         assert_close(got, want, f"{env} {lens}")
     ctx.close()
@@ -641,7 +641,7 @@ def test_f32_and_k_only_kernel_variants(bk, oracle, monkeypatch, env, tag, mode,
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     ctx = bk.Context(0)
-    for lens in ([2047], [2048], [2049], [2063, 2064, 2065], [5000], [21000, 3, 2500]):
+    for lens in ([127], [128], [129], [143, 144, 145], [1000], [2047], [2048], [2049], [2063, 2064, 2065], [5000], [21000, 3, 2500]):
         got, want = run_both(bk, ctx, oracle, tag, mode, bits, vq, lens, seed=sum(lens) + bits)
         assert_close(got, want, f"{tag} {env} {lens}")
     ctx.close()
@@ -688,11 +688,15 @@ def test_f32_rows_past_the_end_do_not_leak_in(bk, gpu_ctx, oracle, tag, mode, bi
     cache.close()
 
 
+@pytest.mark.parametrize("n0", [2600, 131])
 @pytest.mark.parametrize("tag,mode,bits,vq", ROW_KERNEL_MODES)
-def test_fused_step_on_long_f32_and_k_only_caches(bk, gpu_ctx, oracle, tag, mode, bits, vq):
-    """On long f32 and K-only caches the attention step is one launch too; stored rows stay bit-exact."""
+def test_fused_step_on_long_f32_and_k_only_caches(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0):
+    """On f32 and K-only caches (from 128 rows on; 2-bit ones from 2048) the attention step is one launch too;
+    stored rows stay bit-exact."""
+    if tag == "planar2" and n0 < 2048:
+        pytest.skip("2-bit caches take the tensor-core kernel from 2048 rows on")
     rng = np.random.default_rng(44 + bits)
-    n0, steps = 2600, 12
+    steps = 12
     k, v = synth_kv(rng, n0 + steps)
     q = rng.standard_normal((steps, NH, HD)).astype(np.float32)
     cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=n0 + steps)
@@ -821,7 +825,8 @@ def test_layer_step_on_a_filled_cache(bk, gpu_ctx, oracle, tag, mode, bits, vq, 
     cache.append(0, k, v)
     for p in range(n0):
         ref.append(0, k[p], v[p], p)
-    one_launch = n0 >= 2048 and tag in ("planar4", "planar3", "f16", "f32", "planar4k", "planar3k", "planar2")
+    # 4-, 3- and 2-bit caches take the tensor-core kernel (append fused in) from 2048 rows on, the others from 128
+    one_launch = (n0 >= 2048 and tag in ("planar4", "planar3", "planar2")) or (n0 >= 128 and tag in ("f16", "f32", "planar4k", "planar3k"))
     for t in range(steps):
         launches = gpu_ctx.launch_count
         got = bk.full_attention_layer_core(cache, 0, qfull[t], kraw[t], vraw[t], qw, kw, 1e-6, n0 + t)
