@@ -756,7 +756,6 @@ void fill_decode_args(const bk_cache *c, int layer, int partial, DecodeArgs *out
     a.xch_seqno = 0;
     a.xch_err = ctx->d_err;
     a.xch_spin = ctx->xch_polls;
-    a.xch_flags = kXchFlags;
     a.dyn = a.dist = 0;
     a.counters_other = nullptr;
     a.other_n = 0;
@@ -915,7 +914,7 @@ static bk_status decode_impl(bk_cache *c, int32_t layer, int32_t n_seqs, const i
 
 namespace bk {
 bk_status decode_with_exchange(bk_cache *c, int layer, int seq, int n_pos, int q_pos, const float *q_dev, float *out_dev,
-                               uint8_t *const *d_peer, int world, int rank, int xch_flags, unsigned seqno, const float *new_k,
+                               uint8_t *const *d_peer, int world, int rank, unsigned seqno, const float *new_k,
                                const float *new_v) {
     bk_ctx *ctx = c->ctx;
     bk_status st = bind(ctx);
@@ -935,7 +934,6 @@ bk_status decode_with_exchange(bk_cache *c, int layer, int seq, int n_pos, int q
     a.xch_peer = d_peer;
     a.xch_world = world;
     a.xch_rank = rank;
-    a.xch_flags = xch_flags;
     a.xch_seqno = seqno;
     DecodeEntry e;
     if ((st = check_decode_entry(c, layer, 0, &seq, &n_pos, &q_pos, "bk_decode_attn_split", &e)) != BK_OK) return st;

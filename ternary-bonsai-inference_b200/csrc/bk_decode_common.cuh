@@ -52,93 +52,89 @@ struct FinishSmem {
     int *err_flag = nullptr;
 };
 
-// The exchange step of the context split, for coordinates d0 .. d0 + dn - 1 (dn a multiple of 8) of the n_rep
-// q heads of kv head `kv`: send this rank's values to slot [rank] of every rank's mailbox (plain peer stores;
-// the CTA that holds coordinate 0 also sends the heads' m and l), publish them octet by octet with a
-// system-scope release of the call's sequence number, wait (bounded) for the same octets - and octet 0, for
-// m and l - of every rank in this rank's own mailbox, and write the log-sum-exp merge to a.out.
-// A mailbox is [2 parities][world][n_head][hd + 2] floats followed by [2][world][a.xch_flags] arrival words,
-// word kv * 32 + (coordinate / 8).  The octet grid does not depend on how a rank has cut its work, so ranks
-// whose launches have different shapes (or that send from the stand-alone exchange kernel) understand each
-// other.  vals: [n_rep][dn] in shared memory, relative to s_M (exp2 domain), not normalised.  Every thread of
-// the CTA must call; on a time-out the output is zeros and the context's error word is raised.
+// Context split over the GPUs of one node: dims [d0, d0 + dn) of the (acc, m, l) rows of the n_rep q heads of
+// kv head `kv`: send this rank's values to slot [rank] of every rank's mailbox, wait (bounded) for the same
+// values of every rank in this rank's own mailbox, and write the log-sum-exp merge to a.out.
+// A mailbox is [2 parities][world][n_head][hd + 2] eight-byte words (value bits, sequence number).  A word is
+// stored with one 8-byte store, which arrives whole, so it validates itself: the receiver reads it until its
+// second half is the call's sequence number.  Nothing else is needed - no arrival flags, no fence between data
+// and flag, one trip over the link instead of three.  The CTA that holds coordinate 0 also sends the heads' m
+// and l.  The word grid does not depend on how a rank has cut its work, so ranks whose launches have different
+// shapes (or that send from the stand-alone exchange kernel) understand each other.  Slots alternate with the
+// parity of the sequence number: a rank can be at most one call ahead of another (it needs the other's rows to
+// finish a call), so a word is never overwritten before it was read.  vals: [n_rep][dn] in shared memory,
+// relative to s_M (exp2 domain), not normalised.  Every thread of the CTA must call; on a time-out the
+// affected outputs are zeros and the context's error word is raised.
 __device__ __forceinline__ void exchange_slice(const DecodeArgs &a, int n_rep, int slot, int kv, int d0, int dn,
                                                const float *vals, const float *s_M, const float *s_L, int *s_ok) {
     constexpr int kStride = kHd + 2;
     const int tid = threadIdx.x, nt = blockDim.x;
     const int world = a.xch_world, rank = a.xch_rank, n_rows = a.n_head, row0 = kv * n_rep;
     const unsigned seqno = a.xch_seqno, par = seqno & 1u;
-    const size_t slot_f = (size_t)n_rows * kStride, data_b = 2 * (size_t)world * slot_f * sizeof(float);
+    const size_t slot_w = (size_t)n_rows * kStride;
+    (void)s_ok;
+    BK_STAMP(10);
     for (int r = 0; r < world; r++) {
-        float *dst = reinterpret_cast<float *>(a.xch_peer[r]) + ((size_t)par * world + rank) * slot_f + (size_t)row0 * kStride;
+        uint2 *dst = reinterpret_cast<uint2 *>(a.xch_peer[r]) + ((size_t)par * world + rank) * slot_w + (size_t)row0 * kStride;
         for (int i = tid; i < n_rep * dn; i += nt) {
             const int rr = i / dn, d = i - rr * dn;
-            dst[rr * kStride + d0 + d] = vals[i];
+            dst[rr * kStride + d0 + d] = make_uint2(__float_as_uint(vals[i]), seqno);
         }
         if (d0 == 0 && tid < n_rep) {
-            dst[tid * kStride + kHd] = s_M[tid] * 0.6931471805599453f;  // log2 -> ln
-            dst[tid * kStride + kHd + 1] = s_L[tid];
+            dst[tid * kStride + kHd] = make_uint2(__float_as_uint(s_M[tid] * 0.6931471805599453f), seqno);  // log2 -> ln
+            dst[tid * kStride + kHd + 1] = make_uint2(__float_as_uint(s_L[tid]), seqno);
         }
     }
-    if (tid == 0) *s_ok = 1;
-    // The barrier orders every thread's stores before the release stores below, which are cumulative: whoever
-    // acquires an arrival word sees the rows.  No thread needs a system-wide fence of its own.
-    __syncthreads();
-    const int n_oct = dn >> 3, oct0 = d0 >> 3, per = n_oct + 1;
-    for (int x = tid; x < world * per; x += nt) {
-        const int r = x / per, j = x - r * per;
-        if (j < n_oct) {
-            unsigned *flag = reinterpret_cast<unsigned *>(a.xch_peer[r] + data_b) + ((size_t)par * world + rank) * a.xch_flags + kv * 32 + oct0 + j;
-            cuda::atomic_ref<unsigned, cuda::thread_scope_system> f(*flag);
-            f.store(seqno, cuda::memory_order_release);
-        }
-        if (j < n_oct || oct0 != 0) {  // ... and wait for the same octet (j == n_oct: octet 0, which carries m and l) of rank r
-            const int oct = j < n_oct ? oct0 + j : 0;
-            unsigned *mine = reinterpret_cast<unsigned *>(a.xch_peer[rank] + data_b) + ((size_t)par * world + r) * a.xch_flags + kv * 32 + oct;
-            cuda::atomic_ref<unsigned, cuda::thread_scope_system> g2(*mine);
-            int polls = 0;
-            while (g2.load(cuda::memory_order_acquire) != seqno) {
-                if (++polls > a.xch_spin) {  // the peer never sent: leave a mark and go on rather than hang
-                    *s_ok = 0;
+    const uint2 *mbox = reinterpret_cast<const uint2 *>(a.xch_peer[rank]) + (size_t)par * world * slot_w + (size_t)row0 * kStride;
+    bool first = true;
+    for (int i = tid; i < n_rep * dn; i += nt) {
+        const int rr = i / dn, d = d0 + (i - rr * dn);
+        // every rank's (m, l, value): all loads of a round are issued together; words that have not arrived yet
+        // are read again
+        uint2 wm[kMaxWorld], wl[kMaxWorld], wx[kMaxWorld];
+        unsigned pending = (world >= 32) ? 0xffffffffu : ((1u << world) - 1u);
+        int polls = 0;
+        bool ok = true;
+        while (pending) {
+#pragma unroll
+            for (int r = 0; r < kMaxWorld; r++)
+                if (pending >> r & 1u) {
+                    const uint2 *p = mbox + (size_t)r * slot_w + (size_t)rr * kStride;
+                    wm[r] = __ldcv(p + kHd);
+                    wl[r] = __ldcv(p + kHd + 1);
+                    wx[r] = __ldcv(p + d);
+                }
+#pragma unroll
+            for (int r = 0; r < kMaxWorld; r++)
+                if ((pending >> r & 1u) && wm[r].y == seqno && wl[r].y == seqno && wx[r].y == seqno) pending &= ~(1u << r);
+            if (pending) {
+                if (++polls > a.xch_spin) {  // a peer never sent: leave a mark and go on rather than hang
+                    ok = false;
                     raise_error(a.xch_err, 3);
                     break;
                 }
                 if (polls > 2048) __nanosleep(64);  // the first microseconds without a pause: the ranks run in lock step
             }
         }
-    }
-    __syncthreads();
-    const float *mbox = reinterpret_cast<const float *>(a.xch_peer[rank]) + (size_t)par * world * slot_f + (size_t)row0 * kStride;
-    const bool ok = *s_ok != 0;
-    for (int i = tid; i < n_rep * dn; i += nt) {
-        const int rr = i / dn, d = d0 + (i - rr * dn);
-        // every rank's (m, l, value) first, all loads independent of one another: one trip to the mailbox
-        float m[kMaxWorld], l[kMaxWorld], x[kMaxWorld];
-#pragma unroll
-        for (int r = 0; r < kMaxWorld; r++) {
-            m[r] = -CUDART_INF_F;
-            l[r] = x[r] = 0.f;
-            if (r < world) {
-                const float *p = mbox + (size_t)r * slot_f + (size_t)rr * kStride;
-                m[r] = __ldcv(p + kHd);
-                l[r] = __ldcv(p + kHd + 1);
-                x[r] = __ldcv(p + d);
-            }
+        if (first) {
+            BK_STAMP(11);
+            first = false;
         }
         float Mx = -CUDART_INF_F;
 #pragma unroll
         for (int r = 0; r < kMaxWorld; r++)
-            if (l[r] > 0.f) Mx = fmaxf(Mx, m[r]);
+            if (r < world && ok && __uint_as_float(wl[r].x) > 0.f) Mx = fmaxf(Mx, __uint_as_float(wm[r].x));
         float Ls = 0.f, sum = 0.f;
 #pragma unroll
         for (int r = 0; r < kMaxWorld; r++)
-            if (l[r] > 0.f) {
-                const float f = expf(m[r] - Mx);
-                Ls = fmaf(l[r], f, Ls);
-                sum = fmaf(x[r], f, sum);
+            if (r < world && ok && __uint_as_float(wl[r].x) > 0.f) {
+                const float f = expf(__uint_as_float(wm[r].x) - Mx);
+                Ls = fmaf(__uint_as_float(wl[r].x), f, Ls);
+                sum = fmaf(__uint_as_float(wx[r].x), f, sum);
             }
         a.out[((size_t)slot * a.n_head + row0 + rr) * kHd + d] = (ok && Ls > 0.f) ? sum / Ls : 0.f;
     }
+    BK_STAMP(12);
 }
 
 // The slice form of the split-K combine.  When every CTA of a (sequence, kv head) is resident at

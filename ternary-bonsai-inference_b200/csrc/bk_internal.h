@@ -23,8 +23,6 @@ constexpr int kScratchStride = kHd + 4; // floats per partial in the split-K scr
 constexpr int kMmaMinPos = 2048;       // 4-, 3- and 2-bit caches: shorter sequences take the generic f32 decode kernel
 constexpr int kRowMinPos = 128;        // f16, f32 and K-only caches: the same for the row kernel (speed only: it is exact to ~1e-5 at any length)
 constexpr int kMaxWorld = 8;            // ranks a context-split mailbox can connect
-constexpr int kXchFlags = 512;          // arrival words per (parity, rank) of a mailbox, at least: kv head * 32 + coordinate octet
-__host__ __device__ inline int mailbox_flags(int n_rows) { return n_rows * 32 > kXchFlags ? n_rows * 32 : kXchFlags; }
 // The arrival counters of the split-K scratch, one per (sequence in the launch, kv head) pair i (i < 512),
 // in three sets of kCtrSet: set 0 for the generic kernel, whose last arriver puts its counter back to zero;
 // sets 1 and 2 for the tensor-core kernels, which alternate between them from launch to launch: a launch
@@ -233,7 +231,6 @@ struct DecodeArgs {
     unsigned xch_seqno;
     int *xch_err;
     int xch_spin;  // polls of one arrival word before the exchange gives up
-    int xch_flags; // arrival words per (parity, rank) of the mailbox
     // Set by launch_decode_group for the tensor-core kernels:
     //   dyn   bit 0: the warps of a CTA draw their tiles from a counter in shared memory instead of taking
     //         fixed shares (off by default: with it the last bits of a result depend on timing)
@@ -261,7 +258,7 @@ bk_status bind_device(bk_ctx *ctx);
 // One sequence's decode attention whose finishing CTAs exchange and merge their rows through the
 // ranks' mailboxes (bk_api.cu; used by bk_decode_attn_split).
 bk_status decode_with_exchange(bk_cache *c, int layer, int seq, int n_pos, int q_pos, const float *q_dev, float *out_dev,
-                               uint8_t *const *d_peer, int world, int rank, int xch_flags, unsigned seqno,
+                               uint8_t *const *d_peer, int world, int rank, unsigned seqno,
                                const float *new_k = nullptr, const float *new_v = nullptr);
 // Tensor-core paths: 4-bit planar K and V (bk_decode_mma.cu) and f16 K and V (bk_decode_f16.cu).
 // Chunks must be multiples of 16 positions.

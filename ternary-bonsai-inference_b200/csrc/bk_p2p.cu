@@ -4,21 +4,21 @@
 //
 // Every rank owns a mailbox (one cudaMalloc, shared with the other ranks' processes through CUDA
 // IPC; ranks of one process find each other's mailbox in a process-local registry): two parities x
-// world slots of n_rows x (hd + 2) floats, and two parities x world x mailbox_flags(n_rows) arrival words.
-// The exchange runs slice by slice (exchange_slice() in bk_decode_common.cuh): whoever holds
-// dims [d0, d0 + dn) of a kv head's rows, merged over the rank's own chunks, stores them into slot
-// [rank] of every rank's mailbox with plain peer stores, publishes each octet of dims with a
-// system-scope release of the call's sequence number in the octet's own arrival word, waits
-// (bounded) until the same words of all ranks carry that number, and merges the world's values.
+// world slots of n_rows x (hd + 2) eight-byte words, each a value and the sequence number of the call
+// that wrote it.  The exchange runs slice by slice (exchange_slice() in bk_decode_common.cuh): whoever
+// holds dims [d0, d0 + dn) of a kv head's rows, merged over the rank's own chunks, stores them as such
+// words into slot [rank] of every rank's mailbox with plain 8-byte peer stores (which arrive whole, so a
+// word whose second half is the call's sequence number is valid: no flags, no fences), reads the same
+// words of all ranks from its own mailbox until they carry that number (bounded), and merges them.
 // In the one-launch form the holders are the CTAs of the decode launch itself, each with its slice of
 // the split-K combine; exchange_merge_kernel below is the stand-alone form (one CTA per kv head, all
-// dims) for a rank whose decode ran as a separate launch or whose chunk is empty.  The transfer is
-// 24.8 KB per rank and layer, so what matters is latency: no host synchronisation, no
-// collective-library call.
+// dims) for a rank whose decode ran as a separate launch or whose chunk is empty, and for
+// bk_exchange_merge.  The transfer is 50 KB per rank and layer, so what matters is latency: no host
+// synchronisation, no collective-library call, one trip over the link.
 //
 // The only cross-GPU dependency is between kernels on DIFFERENT GPUs; every wait gives up after
 // a bounded number of polls and raises the context's error word instead of hanging.  Slots alternate
-// with the parity of the sequence number, so a rank that runs ahead by one call never overwrites rows
+// with the parity of the sequence number, so a rank that runs ahead by one call never overwrites words
 // still being merged.  No TMA and no multicast is used on peer memory.
 #include <cuda/atomic>
 #include <math_constants.h>
@@ -54,11 +54,9 @@ std::mutex g_boxes_mu;
 std::vector<bk_mailbox *> g_boxes;
 
 __host__ __device__ inline size_t slot_floats(int n_rows, int hd) { return (size_t)n_rows * (hd + 2); }
-__host__ __device__ inline size_t data_bytes(int world, int n_rows, int hd) {
-    return 2 * (size_t)world * slot_floats(n_rows, hd) * sizeof(float);
-}
+// two parities x world slots of eight-byte (value, sequence number) words
 __host__ __device__ inline size_t mailbox_bytes(int world, int n_rows, int hd) {
-    return data_bytes(world, n_rows, hd) + 2 * (size_t)world * mailbox_flags(n_rows) * sizeof(unsigned);
+    return 2 * (size_t)world * slot_floats(n_rows, hd) * sizeof(uint2);
 }
 
 // The exchange on its own, for a rank whose rows were produced by another launch (or that has no rows: l = 0):
@@ -200,7 +198,7 @@ bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t 
     // sends, waits and merges that head's rows itself.  An empty chunk has no such CTA and goes the
     // two-step way (zero rows, then the exchange kernel); both speak the same mailbox protocol.
     if (n_pos > 0 && !getenv("BONSAI_KV_SPLIT_UNFUSED"))
-        return decode_with_exchange(c, layer, seq, n_pos, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, mailbox_flags(m->n_rows), seqno);
+        return decode_with_exchange(c, layer, seq, n_pos, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, seqno);
     bk_status st = bk_decode_attn_partial(c, layer, 1, &seq, &n_pos, &q_pos, q_dev, m->part);
     if (st != BK_OK) return st;
     DecodeArgs xa;
@@ -209,7 +207,6 @@ bk_status bk_decode_attn_split(bk_cache *c, int32_t layer, int32_t seq, int32_t 
     xa.xch_peer = m->d_peer;
     xa.xch_world = m->world;
     xa.xch_rank = m->rank;
-    xa.xch_flags = mailbox_flags(m->n_rows);
     xa.xch_seqno = seqno;
     const int n_rep = c->cfg.n_head / c->cfg.n_kv;
     exchange_merge_kernel<<<c->cfg.n_kv, 256, (size_t)n_rep * kHd * sizeof(float), ctx->stream>>>(xa, n_rep, m->part);
@@ -235,7 +232,6 @@ bk_status bk_exchange_merge(bk_mailbox *m, int32_t n_rep, const float *part_dev,
     xa.xch_peer = m->d_peer;
     xa.xch_world = m->world;
     xa.xch_rank = m->rank;
-    xa.xch_flags = mailbox_flags(m->n_rows);
     xa.xch_seqno = seqno;
     xa.xch_err = ctx->d_err;
     xa.xch_spin = ctx->xch_polls;
@@ -266,7 +262,7 @@ bk_status bk_attn_step_split(bk_cache *c, int32_t layer, int32_t seq, int32_t q_
     DecodeArgs a;
     fill_decode_args(c, layer, 0, &a);
     const bool fused_append = decode_entry_uses_mma(ctx, a, np + 1);
-    bk_status st = decode_with_exchange(c, layer, seq, np + 1, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, mailbox_flags(m->n_rows), seqno,
+    bk_status st = decode_with_exchange(c, layer, seq, np + 1, q_pos, q_dev, out_dev, m->d_peer, m->world, m->rank, seqno,
                                         k_dev, v_dev);
     if (st == BK_OK && fused_append) np += 1;  // (the other route went through bk_append, which counted it)
     return st;
