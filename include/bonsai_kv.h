@@ -368,6 +368,13 @@ BK_API size_t bk_kvq_packed_len(int32_t hd, int32_t bits);
 BK_API bk_status bk_kvq_codebook(int32_t hd, int32_t bits, float *out_host);
 /* givens_table(d) (src/kvquant.rs:131-145): ceil(hd/2) (cos, sin) pairs. */
 BK_API bk_status bk_kvq_givens(int32_t hd, float *out_host);
+/* No counterpart in the reference: the table behind the bulk append's nearest-centroid search for head
+ * dimension 256 and widths 1..4, for checking that search against the reference's scan
+ * (src/kvquant.rs:357-370) without a GPU.  512 cells of width 2^-10 over [-0.25, 0.25): out_host[2k] = how
+ * many decision thresholds lie in cells below k, out_host[2k + 1] = the bits of the one threshold inside
+ * cell k (+inf if none).  nearest(v) = out[2k] + (v >= threshold) with k = clamp(floor((v + 0.25) * 1024)),
+ * all in f32.  Host only. */
+BK_API bk_status bk_kvq_threshold_cells(int32_t bits, uint32_t *out_host);
 /* PlanarQuant::quantize (src/kvquant.rs:397-412) for n_vec vectors of hd floats. */
 BK_API bk_status bk_kvq_quantize(bk_ctx *ctx, int32_t hd, int32_t bits, int32_t n_vec,
                                  const float *x_host, uint8_t *packed_host, float *norms_host);

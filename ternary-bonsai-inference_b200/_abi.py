@@ -84,6 +84,7 @@ SIGNATURES = {
     "bk_kvq_packed_len": (_sz, [_i32, _i32]),
     "bk_kvq_codebook": (C.c_int, [_i32, _i32, _vp]),
     "bk_kvq_givens": (C.c_int, [_i32, _vp]),
+    "bk_kvq_threshold_cells": (C.c_int, [_i32, _vp]),
     "bk_kvq_quantize": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "bk_kvq_dequantize": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "bk_kvq_rotate": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp]),

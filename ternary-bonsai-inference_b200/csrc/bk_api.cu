@@ -1397,6 +1397,16 @@ bk_status bk_kvq_codebook(int32_t hd, int32_t bits, float *out) {
     return BK_OK;
 }
 
+bk_status bk_kvq_threshold_cells(int32_t bits, uint32_t *out) {
+    if (!out || bits < 1 || bits > 4) return fail(nullptr, BK_ERR_INVALID, "bk_kvq_threshold_cells: bits must be 1..4");
+    float book[256];
+    host_codebook(kHd, bits, book);
+    static_assert(sizeof(uint2) == 2 * sizeof(uint32_t), "cell layout");
+    if (!build_threshold_cells(book, 1 << bits, reinterpret_cast<uint2 *>(out)))
+        return fail(nullptr, BK_ERR_UNSUPPORTED, "codebook thresholds do not fit the cell table");
+    return BK_OK;
+}
+
 bk_status bk_kvq_givens(int32_t hd, float *out) {
     if (!out || hd < 1) return fail(nullptr, BK_ERR_INVALID, "bk_kvq_givens: bad argument");
     host_givens(hd, out);

@@ -86,6 +86,48 @@ def test_setup_tables_equal_the_oracle(bk, oracle, bits):
     assert bk.packed_bytes(256, bits) == 32 * bits == bk._abi.load().bk_kvq_packed_len(256, bits)
 
 
+@pytest.mark.parametrize("bits", [1, 2, 3, 4])
+def test_threshold_cells_give_the_reference_scan(bk, oracle, bits):
+    """The bulk append finds the nearest centroid with one table read and one comparison.  The table is built
+    on the host; here it is checked against the reference's scan (src/kvquant.rs:357-370: ascending, strict
+    '<', f32 differences) on the values where the two could part: centroids, exact midpoints, the decision
+    thresholds themselves, cell edges, each with their neighbouring floats, and a dense random sample."""
+    lib = bk._abi.load()
+    cells = np.zeros((512, 2), np.uint32)
+    assert lib.bk_kvq_threshold_cells(bits, cells.ctypes.data) == 0
+    count, thr = cells[:, 0].astype(np.int64), cells[:, 1].copy().view(np.float32)
+    book = oracle.codebook(256, bits).astype(np.float32)
+    n = 1 << bits
+    assert count[0] == 0 and count[-1] + np.isfinite(thr[-1]) <= n - 1 and np.all(np.diff(count) >= 0)
+    assert int(np.isfinite(thr).sum()) == n - 1            # every threshold sits in a cell of its own
+
+    def neighbours(x, k=3):
+        out = [np.float32(x)]
+        lo = hi = np.float32(x)
+        for _ in range(k):
+            lo, hi = np.nextafter(lo, np.float32(-np.inf)), np.nextafter(hi, np.float32(np.inf))
+            out += [lo, hi]
+        return out
+    probes = []
+    for c in book:
+        probes += neighbours(c)
+    for a, b in zip(book[:-1], book[1:]):
+        probes += neighbours(np.float32(0.5) * (a + b)) + neighbours(np.float32((np.float64(a) + np.float64(b)) / 2))
+    for t in thr[np.isfinite(thr)]:
+        probes += neighbours(t, 5)
+    for k in range(0, 513):
+        probes += neighbours(np.float32(k) / np.float32(1024) - np.float32(0.25))
+    probes += [np.float32(x) for x in (-3.9, -1.0, -0.26, -0.25, 0.0, -0.0, 0.25, 0.26, 1.0, 3.9)]
+    rng = np.random.default_rng(bits)
+    v = np.concatenate([np.array(probes, np.float32), (rng.standard_normal(200000) / 16).astype(np.float32),
+                        rng.uniform(-0.3, 0.3, 200000).astype(np.float32)])
+    want = np.argmin(np.abs(v[:, None] - book[None, :]), axis=1)       # f32 differences; first minimum = lowest index
+    cell = np.clip(np.floor((v + np.float32(0.25)) * np.float32(1024)).astype(np.int64), 0, 511)
+    got = count[cell] + (v >= thr[cell])
+    bad = np.flatnonzero(got != want)
+    assert bad.size == 0, (v[bad[:5]], got[bad[:5]], want[bad[:5]])
+
+
 def test_default_config_is_qwen35(bk):
     cfg = bk._abi.CacheConfig()
     bk._abi.load().bk_default_config(C.byref(cfg))
