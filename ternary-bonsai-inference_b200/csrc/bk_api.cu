@@ -798,7 +798,7 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
     for (int i = 0; i < nb; i++) order[i] = i;
     std::stable_sort(order, order + nb, [&](int x, int y) { return list[x].np > list[y].np; });
     int64_t total = 0;
-    int max_np = 0;
+    int max_np = 0, min_np = INT32_MAX;
     for (int i = 0; i < nb; i++) {
         const DecodeEntry &e = list[order[i]];
         m.slot[i] = e.slot;
@@ -807,6 +807,7 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
         m.q_pos[i] = e.qp;
         total += e.np;
         max_np = std::max(max_np, e.np);
+        min_np = std::min(min_np, e.np);
     }
     const int64_t gran = use_mma ? 128 : 64;
     auto items_for = [&](int64_t len) {
@@ -857,19 +858,17 @@ bk_status launch_decode_group(bk_ctx *ctx, const DecodeArgs &a, const DecodeEntr
     // every CTA holds a whole SM, so a launch of at most n_sms items is resident all at once
     a2.dist = (ctx->dist_combine && items <= ctx->n_sms) ? 1 : 0;
     return decode_f16_mma_supported(a) ? launch_decode_f16_mma(ctx, a2, m, a.k_kind == ROW_PLANAR ? ctx->lut_alpha[a.bits] : 1.0f, ctx->qsplit)
-                               : launch_decode_p4_mma(ctx, a2, m, ctx->lut_alpha[a.bits], ctx->qsplit);
+                               : launch_decode_p4_mma(ctx, a2, m, ctx->lut_alpha[a.bits], ctx->qsplit, min_np < kMmaMinPos);
 }
 
 bool decode_entry_uses_mma(const bk_ctx *ctx, const DecodeArgs &a, int n_pos) {
-    // Long sequences of 4-, 3- and 2-bit planar caches go to the tensor-core kernel, short ones to the
-    // generic f32 kernel: below kMmaMinPos positions the f16 lookup table of that path (relative error ~1e-4 per
-    // centroid) is not averaged out over enough positions, so short contexts keep the exact f32 arithmetic.
-    // f16, f32 and K-only caches take the row kernel from kRowMinPos rows on: it carries about 22 bits at any
-    // length and (append fused in, one launch) is faster than the generic kernel even at 256 rows.
+    // Sequences of kRowMinPos rows and more take the tensor-core kernels (append fused in, one launch: faster than
+    // the generic kernel plus the append kernel even at 256 rows).  The row kernel (f16, f32, K-only) carries about
+    // 22 bits at any length; the 4-, 3- and 2-bit kernel's f16 table (relative error ~1e-4 per centroid) is only
+    // averaged out over long contexts, so a launch with a sequence below kMmaMinPos rows runs its precise form
+    // (launch_decode_group), which carries the table's rounding remainders.
     if (ctx->force_generic || !decode_mma_supported(a)) return false;
-    // the row kernel (f16, f32, K-only) computes with about 22 bits whatever the length; only speed decides there
-    if (decode_f16_mma_supported(a)) return n_pos >= (ctx->mma_min_rows > 0 ? ctx->mma_min_rows : kRowMinPos);
-    return n_pos >= kMmaMinPos;
+    return n_pos >= (ctx->mma_min_rows > 0 ? ctx->mma_min_rows : kRowMinPos);
 }
 
 }  // namespace bk

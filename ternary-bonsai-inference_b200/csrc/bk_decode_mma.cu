@@ -132,11 +132,20 @@ __device__ __forceinline__ uint32_t lut(uint32_t x, uint32_t lane_base) {
     return v;
 }
 
+// The same lookup with the entry's rounding remainder (the upper half of the table slot, see PRECISE).
+template <int K>
+__device__ __forceinline__ void lut2(uint32_t x, uint32_t lane_base, uint32_t &v, uint32_t &rem) {
+    uint32_t addr;
+    asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(addr) : "r"(x), "r"(lane_base), "n"(0x7604 | (K << 4)));
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    asm volatile("ld.shared.b32 %0, [%1+128];\n" : "=r"(rem) : "r"(addr));
+}
+
 __device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi) {
     return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
 }
 
-template <int BITS, int NREP, bool QSPLIT>
+template <int BITS, int NREP, bool QSPLIT, bool PRECISE = false>
 __global__ void __launch_bounds__(kMT, 1)
 decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t smem_bytes, int *err_flag,
                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -369,6 +378,20 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             }
         }
     }
+    if constexpr (PRECISE) {
+        // Short contexts: the table's f16 centroids (good to 1e-4) are not averaged out over enough positions, so
+        // what their rounding left over goes into the upper halves of the table slots (free again now that every
+        // warp has its q fragments) and every product gets a second term.
+        __syncthreads();
+        constexpr int kIdxMask = (1 << BITS) - 1;
+        const float c_lo = a.book[lane & kIdxMask] * lut_alpha;
+        for (int e = warp; e < 256; e += kMW) {
+            const float lo = __shfl_sync(0xffffffffu, c_lo, e & kIdxMask), hi = __shfl_sync(0xffffffffu, c_lo, (e >> 4) & kIdxMask);
+            const float2 hf = __half22float2(__floats2half2_rn(lo, hi));
+            *reinterpret_cast<__half2 *>(lut_ptr + e * 256 + 128 + lane * 4) = __floats2half2_rn(lo - hf.x, hi - hf.y);
+        }
+        __syncthreads();
+    }
     BK_STAMP(2);
     // ---- fused append: warps 0 and 1 of the CTA that scans the last chunk of this kv head store the
     // head's new K and V rows, exactly as the append kernel would (src/forward.rs:259-285; the rope
@@ -515,6 +538,23 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                 const int ks = c * 8 + w * 2;
 #pragma unroll
                 for (int m = 0; m < 2; m++) {
+                    if constexpr (PRECISE) {  // centroid = table value + remainder: a third term per fragment
+                        uint32_t a0, a1, a2, a3, r0, r1, r2, r3;
+                        lut2<0>(kg[m][w], lane_base, a0, r0);
+                        lut2<0>(kh[m][w], lane_base, a1, r1);
+                        lut2<1>(kg[m][w], lane_base, a2, r2);
+                        lut2<1>(kh[m][w], lane_base, a3, r3);
+                        mma16816(S[m][c], a0, a1, a2, a3, qh[ks][0], qh[ks][1]);
+                        mma16816(S[m][2 + c], r0, r1, r2, r3, qh[ks][0], qh[ks][1]);
+                        if constexpr (QSPLIT) mma16816(S[m][2 + c], a0, a1, a2, a3, ql[ks][0], ql[ks][1]);
+                        lut2<2>(kg[m][w], lane_base, a0, r0);
+                        lut2<2>(kh[m][w], lane_base, a1, r1);
+                        lut2<3>(kg[m][w], lane_base, a2, r2);
+                        lut2<3>(kh[m][w], lane_base, a3, r3);
+                        mma16816(S[m][2 + c], a0, a1, a2, a3, qh[ks + 1][0], qh[ks + 1][1]);
+                        mma16816(S[m][c], r0, r1, r2, r3, qh[ks + 1][0], qh[ks + 1][1]);
+                        if constexpr (QSPLIT) mma16816(S[m][c], a0, a1, a2, a3, ql[ks + 1][0], ql[ks + 1][1]);
+                    } else {
                     {
                         const uint32_t a0 = lut<0>(kg[m][w], lane_base), a1 = lut<0>(kh[m][w], lane_base);
                         const uint32_t a2 = lut<1>(kg[m][w], lane_base), a3 = lut<1>(kh[m][w], lane_base);
@@ -526,6 +566,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                         const uint32_t a2 = lut<3>(kg[m][w], lane_base), a3 = lut<3>(kh[m][w], lane_base);
                         mma16816(S[m][2 + c], a0, a1, a2, a3, qh[ks + 1][0], qh[ks + 1][1]);
                         if constexpr (QSPLIT) mma16816(S[m][c], a0, a1, a2, a3, ql[ks + 1][0], ql[ks + 1][1]);
+                    }
                     }
                 }
             }
@@ -570,6 +611,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             M1 = n1;
         }
         uint32_t b0[2], b1[2];
+        [[maybe_unused]] uint32_t b0l[2] = {0u, 0u}, b1l[2] = {0u, 0u};  // PRECISE: what the weights' rounding to f16 left over
 #pragma unroll
         for (int m = 0; m < 2; m++) {
             const float w00 = fast_exp2(tt[m][0] - M0) * kWScale, w01 = fast_exp2(tt[m][1] - M1) * kWScale;
@@ -579,6 +621,12 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             const __half2 pl = __floats2half2_rn(w00, w01), ph = __floats2half2_rn(w10, w11);
             b0[m] = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&pl));  // head g; pos 2t, 2t+1
             b1[m] = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ph));  // head g; pos 2t+8, 2t+9
+            if constexpr (PRECISE) {
+                const float2 fl = __half22float2(pl), fh = __half22float2(ph);
+                const __half2 ql2 = __floats2half2_rn(w00 - fl.x, w01 - fl.y), qh2 = __floats2half2_rn(w10 - fh.x, w11 - fh.y);
+                b0l[m] = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&ql2));
+                b1l[m] = movmatrix_trans(*reinterpret_cast<const uint32_t *>(&qh2));
+            }
         }
         // ---- out^T += Vc^T . W : MMA j covers coordinates 32g + 2j (rows g) and 32g + 2j + 1 (rows g+8)
         const uint32_t v_tile = st_addr + kTileBytes;
@@ -588,6 +636,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
             // coordinates 32 g .. 32 g + 31 of position rows 2t, 2t+1, 2t+8, 2t+9 of this row block, four words each
             const uint32_t v_blk = v_tile + (uint32_t)(16 * m * kRowBytes);
             const uint32_t bm0 = m ? b0[1] : b0[0], bm1 = m ? b1[1] : b1[0];
+            [[maybe_unused]] const uint32_t bm0l = m ? b0l[1] : b0l[0], bm1l = m ? b1l[1] : b1l[0];
             uint32_t x0[4], x1[4], x2[4], x3[4];
             if constexpr (BITS == 4) {  // chunk g of each row; rows r and r + 8 share the swizzle
                 const uint32_t vo0 = r0 * kRowBytes + (((uint32_t)g ^ (r0 & 7)) << 4), vo1 = r1 * kRowBytes + (((uint32_t)g ^ (r1 & 7)) << 4);
@@ -627,6 +676,22 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                 const uint32_t msk = 0x0f0f0f0fu;
                 const uint32_t lo01 = (x0[w] & msk) | ((x1[w] & msk) << 4), hi01 = ((x0[w] >> 4) & msk) | (x1[w] & ~msk);
                 const uint32_t lo23 = (x2[w] & msk) | ((x3[w] & msk) << 4), hi23 = ((x2[w] >> 4) & msk) | (x3[w] & ~msk);
+                if constexpr (PRECISE) {
+                    auto both = [&]<int B>(float (&dst)[4]) {
+                        uint32_t a0, a1, a2, a3, r0, r1, r2, r3;
+                        lut2<B>(lo01, lane_base, a0, r0);
+                        lut2<B>(hi01, lane_base, a1, r1);
+                        lut2<B>(lo23, lane_base, a2, r2);
+                        lut2<B>(hi23, lane_base, a3, r3);
+                        mma16816(dst, a0, a1, a2, a3, bm0, bm1);
+                        mma16816(dst, r0, r1, r2, r3, bm0, bm1);
+                        mma16816(dst, a0, a1, a2, a3, bm0l, bm1l);
+                    };
+                    both.template operator()<0>(acc[4 * w + 0]);
+                    both.template operator()<1>(acc[4 * w + 1]);
+                    both.template operator()<2>(acc[4 * w + 2]);
+                    both.template operator()<3>(acc[4 * w + 3]);
+                } else {
                 mma16816(acc[4 * w + 0], lut<0>(lo01, lane_base), lut<0>(hi01, lane_base), lut<0>(lo23, lane_base),
                          lut<0>(hi23, lane_base), bm0, bm1);
                 mma16816(acc[4 * w + 1], lut<1>(lo01, lane_base), lut<1>(hi01, lane_base), lut<1>(lo23, lane_base),
@@ -635,6 +700,7 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
                          lut<2>(hi23, lane_base), bm0, bm1);
                 mma16816(acc[4 * w + 3], lut<3>(lo01, lane_base), lut<3>(hi01, lane_base), lut<3>(lo23, lane_base),
                          lut<3>(hi23, lane_base), bm0, bm1);
+                }
             }
         }
     };
@@ -773,9 +839,9 @@ decode_p4_mma_kernel(DecodeArgs a, DecodeMeta meta, float lut_alpha, uint32_t sm
     BK_STAMP(9);
 }
 
-template <int BITS, int NREP, bool QSPLIT>
+template <int BITS, int NREP, bool QSPLIT, bool PRECISE = false>
 bk_status launch_one(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha) {
-    auto *kernel = decode_p4_mma_kernel<BITS, NREP, QSPLIT>;
+    auto *kernel = decode_p4_mma_kernel<BITS, NREP, QSPLIT, PRECISE>;
     // Dynamic shared memory: everything the SM allows beyond the kernel's static part.  The kernel
     // lays out table, bookkeeping and as many ring stages as fit.
     static std::atomic<size_t> smem_for[64] = {};  // per device; racing first calls compute the same value
@@ -869,14 +935,18 @@ bool decode_p4_mma_supported(const DecodeArgs &a) {
            a.n_kv <= 8 && rope_ok && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 6);
 }
 
-bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit) {
+bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit, bool precise) {
     if (m.n_items <= 0) return BK_OK;
     const int n_rep = a.n_head / a.n_kv;
-#define BK_MMA_CASE(R)                                                                                     \
-    case R:                                                                                                \
-        if (a.bits == 3) return qsplit ? launch_one<3, R, true>(ctx, a, m, alpha) : launch_one<3, R, false>(ctx, a, m, alpha); \
-        if (a.bits == 2) return qsplit ? launch_one<2, R, true>(ctx, a, m, alpha) : launch_one<2, R, false>(ctx, a, m, alpha); \
-        return qsplit ? launch_one<4, R, true>(ctx, a, m, alpha) : launch_one<4, R, false>(ctx, a, m, alpha);
+    // (the precise form always carries the q split as well: it exists for accuracy)
+#define BK_MMA_BITS(B, R)                                                        \
+    if (a.bits == B) {                                                           \
+        if (precise) return launch_one<B, R, true, true>(ctx, a, m, alpha);      \
+        return qsplit ? launch_one<B, R, true>(ctx, a, m, alpha) : launch_one<B, R, false>(ctx, a, m, alpha); \
+    }
+#define BK_MMA_CASE(R) \
+    case R:            \
+        BK_MMA_BITS(3, R) BK_MMA_BITS(2, R) BK_MMA_BITS(4, R) break;
     switch (n_rep) {
         BK_MMA_CASE(1)
         BK_MMA_CASE(2)
@@ -885,6 +955,8 @@ bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMet
         default: return fail(ctx, BK_ERR_UNSUPPORTED, "decode (mma): n_head/n_kv must be 1, 2, 4 or 6");
     }
 #undef BK_MMA_CASE
+#undef BK_MMA_BITS
+    return fail(ctx, BK_ERR_UNSUPPORTED, "decode (mma): index width must be 4, 3 or 2");
 }
 
 }  // namespace bk

@@ -20,8 +20,8 @@ constexpr int kMaxItems = 4096;        // split-K work items one decode launch m
 constexpr int kMaxRep = 8;             // q heads per kv head the scratch is sized for
 constexpr int kPartStride = kHd + 2;   // floats per partial result handed to callers: acc[hd], m, l
 constexpr int kScratchStride = kHd + 4; // floats per partial in the split-K scratch (16-byte aligned rows)
-constexpr int kMmaMinPos = 2048;       // 4-, 3- and 2-bit caches: shorter sequences take the generic f32 decode kernel
-constexpr int kRowMinPos = 128;        // f16, f32 and K-only caches: the same for the row kernel (speed only: it is exact to ~1e-5 at any length)
+constexpr int kMmaMinPos = 2048;       // 4-, 3- and 2-bit caches: launches with a shorter sequence carry the table's rounding remainders
+constexpr int kRowMinPos = 128;        // sequences shorter than this take the generic f32 decode kernel (speed only)
 constexpr int kMaxWorld = 8;            // ranks a context-split mailbox can connect
 // The arrival counters of the split-K scratch, one per (sequence in the launch, kv head) pair i (i < 512),
 // in three sets of kCtrSet: set 0 for the generic kernel, whose last arriver puts its counter back to zero;
@@ -267,7 +267,7 @@ bool decode_f16_mma_supported(const DecodeArgs &a);
 inline bool decode_mma_supported(const DecodeArgs &a) { return decode_p4_mma_supported(a) || decode_f16_mma_supported(a); }
 bk_status make_tile_tensor_maps(bk_ctx *ctx, const void *k_rows, const void *v_rows, size_t k_row_bytes, size_t v_row_bytes, int n_kv,
                                 size_t total_pos, int box_rows, void *out_k, void *out_v);
-bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit);
+bk_status launch_decode_p4_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float alpha, bool qsplit, bool precise);
 bk_status launch_decode_f16_mma(bk_ctx *ctx, const DecodeArgs &a, const DecodeMeta &m, float lut_alpha, bool qsplit);
 // RMSNorm over rows (bk_layer.cu): up to two row groups per launch, each with its own source
 // stride, weight and contiguous destination.

@@ -438,7 +438,7 @@ def test_partials_merge_equals_whole(bk, gpu_ctx, oracle):
     dout = gpu_ctx.alloc(NH * HD * 4)
     gpu_ctx.check(gpu_ctx.lib.bk_lse_merge(gpu_ctx.h, 2, NH, HD, dparts.ptr, dout.ptr))
     got = dout.download((NH, HD), np.float32)
-    assert np.max(np.abs(got - want)) < 2e-5
+    assert np.max(np.abs(got - want)) < 5e-5   # two tensor-core results over different splits
     ref = oracle.cache(MODE_PLANAR, 4, True)
     for p in range(n):
         ref.append(0, k[p], v[p], p)
@@ -450,9 +450,9 @@ def test_partials_merge_equals_whole(bk, gpu_ctx, oracle):
 @pytest.mark.parametrize("env", [{"BONSAI_KV_GENERIC": "1"}, {}])
 def test_planar4_kernel_variants(bk, oracle, monkeypatch, env):
     """The 4-bit cache has two decode kernels behind the same entry point: the tensor-core
-    path (default for 2048 positions and more) and the generic f32 path
-    (BONSAI_KV_GENERIC=1, read when the context is created).  All must meet the bar, on
-    lengths that hit ragged tiles, single chunks and many chunks."""
+    path (default for 128 positions and more; launches with a sequence below 2048 rows in its precise
+    form) and the generic f32 path (BONSAI_KV_GENERIC=1, read when the context is created).  All must
+    meet the bar, on lengths that hit ragged tiles, single chunks and many chunks."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     ctx = bk.Context(0)
@@ -511,7 +511,7 @@ def test_planar3_kernel_variants(bk, oracle, monkeypatch, env):
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     ctx = bk.Context(0)
-    for lens in ([17], [2047], [2048], [2049], [2063, 2064, 2065], [5000], [40000, 3, 2500]):
+    for lens in ([17], [143, 144, 145], [1000], [2047], [2048], [2049], [2063, 2064, 2065], [5000], [40000, 3, 2500]):
         got, want = run_both(bk, ctx, oracle, "planar3", MODE_PLANAR, 3, True, lens, seed=sum(lens) + 3)
         assert_close(got, want, f"{env} {lens}")
     ctx.close()
@@ -691,10 +691,8 @@ def test_f32_rows_past_the_end_do_not_leak_in(bk, gpu_ctx, oracle, tag, mode, bi
 @pytest.mark.parametrize("n0", [2600, 131])
 @pytest.mark.parametrize("tag,mode,bits,vq", ROW_KERNEL_MODES)
 def test_fused_step_on_long_f32_and_k_only_caches(bk, gpu_ctx, oracle, tag, mode, bits, vq, n0):
-    """On f32 and K-only caches (from 128 rows on; 2-bit ones from 2048) the attention step is one launch too;
-    stored rows stay bit-exact."""
-    if tag == "planar2" and n0 < 2048:
-        pytest.skip("2-bit caches take the tensor-core kernel from 2048 rows on")
+    """On f32, K-only and 2-bit caches (from 128 rows on) the attention step is one launch too; stored rows stay
+    bit-exact."""
     rng = np.random.default_rng(44 + bits)
     steps = 12
     k, v = synth_kv(rng, n0 + steps)
@@ -712,6 +710,31 @@ def test_fused_step_on_long_f32_and_k_only_caches(bk, gpu_ctx, oracle, tag, mode
         assert_close(got, want, f"{tag} step {t}")
     compare_dumps(cache.dump_kv(0, pos0=n0 - 3), {key: val[n0 - 3:] for key, val in ref.dump(0).items()})
     cache.close()
+
+
+@pytest.mark.parametrize("tag,bits", [("planar4", 4), ("planar3", 3), ("planar2", 2)])
+def test_short_context_planar_tensor_core_path_is_precise(bk, gpu_ctx, oracle, tag, bits):
+    """Below 2048 rows nothing averages the f16 table's rounding out, so the 4-, 3- and 2-bit kernel carries the
+    remainders there: with x20 outlier channels and a peaked softmax the result stays within 1e-4 of the f32 CPU
+    path (absolute and relative) at every length, ragged tiles included."""
+    worst = 0.0
+    for seed, n in enumerate((128, 129, 200, 517, 1000, 1531, 2047)):
+        rng = np.random.default_rng(300 + 17 * seed + bits)
+        k, v = synth_kv(rng, n)
+        q = (rng.standard_normal((NH, HD)) * 3).astype(np.float32)
+        cache = bk.AttnCache(gpu_ctx, bk.parse_mode(tag), n_layers=1, n_ctx=n)
+        cache.append(0, k, v)
+        ref = oracle.cache(MODE_PLANAR, bits, True)
+        for p in range(n):
+            ref.append(0, k[p], v[p], p)
+        want = ref.attend(0, q, n - 1, n, threads=8)
+        launches = gpu_ctx.launch_count
+        got = cache.attend(0, q)[0]
+        assert gpu_ctx.launch_count - launches == 1
+        err = float(np.max(np.abs(got - want)))
+        worst = max(worst, err, err / float(np.max(np.abs(want))))
+        cache.close()
+    assert worst <= 1e-4, worst
 
 
 def test_f32_tensor_core_path_precision(bk, gpu_ctx, oracle):
@@ -825,8 +848,8 @@ def test_layer_step_on_a_filled_cache(bk, gpu_ctx, oracle, tag, mode, bits, vq, 
     cache.append(0, k, v)
     for p in range(n0):
         ref.append(0, k[p], v[p], p)
-    # 4-, 3- and 2-bit caches take the tensor-core kernel (append fused in) from 2048 rows on, the others from 128
-    one_launch = (n0 >= 2048 and tag in ("planar4", "planar3", "planar2")) or (n0 >= 128 and tag in ("f16", "f32", "planar4k", "planar3k"))
+    # from 128 rows on these caches take a tensor-core kernel with the append fused in
+    one_launch = n0 >= 128 and tag in ("planar4", "planar3", "planar2", "f16", "f32", "planar4k", "planar3k")
     for t in range(steps):
         launches = gpu_ctx.launch_count
         got = bk.full_attention_layer_core(cache, 0, qfull[t], kraw[t], vraw[t], qw, kw, 1e-6, n0 + t)
