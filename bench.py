@@ -18,7 +18,10 @@ headline pass the same process group also runs the two configurations that shard
 the GPUs - 64 sequences split over the ranks, and one 262144-token sequence cut into context
 chunks whose partial results meet through peer memory - for a few steps each and reports them
 under `sharded` (with each one's own 1-GPU time measured on rank 0 in the same run, and a
-small split-context self-check against a whole cache).
+small split-context self-check against a whole cache).  The split-context step is timed in two
+forms: every layer's exchange completed before the next layer starts (what a model needs, the
+headline of that workload), and all 16 layers scanned first with one exchange per token
+(`layers_batched`, for callers whose layers do not depend on one another).
 
 Prints one JSON line.  `value` is device-resident throughput (CUDA events on the library's
 stream, max over ranks), `e2e` the same step through the host-buffer entry point
