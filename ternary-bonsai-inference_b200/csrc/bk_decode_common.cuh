@@ -65,6 +65,11 @@ struct FinishSmem {
 // finish a call), so a word is never overwritten before it was read.  vals: [n_rep][dn] in shared memory,
 // relative to s_M (exp2 domain), not normalised.  Every thread of the CTA must call; on a time-out the
 // affected outputs are zeros and the context's error word is raised.
+// One mailbox word: value and sequence number in a single 8-byte store (never two 4-byte ones).
+__device__ __forceinline__ void store_word(uint2 *p, float value, unsigned seqno) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};\n" ::"l"(p), "r"(__float_as_uint(value)), "r"(seqno) : "memory");
+}
+
 __device__ __forceinline__ void exchange_slice(const DecodeArgs &a, int n_rep, int slot, int kv, int d0, int dn,
                                                const float *vals, const float *s_M, const float *s_L, int *s_ok) {
     constexpr int kStride = kHd + 2;
@@ -78,11 +83,11 @@ __device__ __forceinline__ void exchange_slice(const DecodeArgs &a, int n_rep, i
         uint2 *dst = reinterpret_cast<uint2 *>(a.xch_peer[r]) + ((size_t)par * world + rank) * slot_w + (size_t)row0 * kStride;
         for (int i = tid; i < n_rep * dn; i += nt) {
             const int rr = i / dn, d = i - rr * dn;
-            dst[rr * kStride + d0 + d] = make_uint2(__float_as_uint(vals[i]), seqno);
+            store_word(dst + rr * kStride + d0 + d, vals[i], seqno);
         }
         if (d0 == 0 && tid < n_rep) {
-            dst[tid * kStride + kHd] = make_uint2(__float_as_uint(s_M[tid] * 0.6931471805599453f), seqno);  // log2 -> ln
-            dst[tid * kStride + kHd + 1] = make_uint2(__float_as_uint(s_L[tid]), seqno);
+            store_word(dst + tid * kStride + kHd, s_M[tid] * 0.6931471805599453f, seqno);  // log2 -> ln
+            store_word(dst + tid * kStride + kHd + 1, s_L[tid], seqno);
         }
     }
     const uint2 *mbox = reinterpret_cast<const uint2 *>(a.xch_peer[rank]) + (size_t)par * world * slot_w + (size_t)row0 * kStride;
