@@ -254,8 +254,10 @@ def workload_config(args, mode):
             "kv_mode": args.mode, "context": args.ctx, "layers": N_LAYERS, "batch_per_gpu": 1,
             "step": ("bk_attn_layer_step (q|gate split, q/k RMSNorm, append, attention, sigmoid gate)"
                      if getattr(args, "step", "attn") == "layer" else "bk_attn_step (append + attention)"),
-            "l2": "each step streams %.2f GB of cache, larger than the 126 MB L2 (no flush needed)"
-                  % (N_LAYERS * attn_bytes(mode, args.ctx) / 1e9)}
+            "l2": ("each step streams %.2f GB of cache, larger than the 126 MB L2 (no flush needed)"
+                   if N_LAYERS * attn_bytes(mode, args.ctx) > 2 * 126e6 else
+                   "each step streams only %.2f GB of cache: it may stay in the 126 MB L2 between steps, so this is "
+                   "not an HBM measurement") % (N_LAYERS * attn_bytes(mode, args.ctx) / 1e9)}
 
 
 # ---------------------------------------------------------------------------------------------
