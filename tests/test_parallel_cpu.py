@@ -92,3 +92,45 @@ def test_context_split_exchange_on_two_gloo_ranks():
         assert p.exitcode == 0
     results = dict(q.get(timeout=10) for _ in range(2))
     assert set(results) == {0, 1} and max(results.values()) < 1e-5
+
+
+def _rank_main_layers(rank, world, port, out_q):
+    """The layers-batched form of the context split: every rank scans all layers first and the partial rows of
+    all of them cross in ONE exchange per token (bk_exchange_merge); the merge is row-wise, so stacking the
+    layers' rows changes nothing but the row count."""
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(11)
+        n_layers, n = 3, 700
+        s = rng.standard_normal((n_layers, 24, n)) * 3
+        v = rng.standard_normal((n_layers, n, 256))
+        b, e = par.split_context(n, world, granularity=128)[rank]
+        mine = np.concatenate([_partials(s[il][:, b:e], v[il][b:e]) if e > b else np.zeros((24, 258), np.float32)
+                               for il in range(n_layers)])                      # [n_layers * 24][258]
+        gathered = par.all_gather_partials(dist, torch.from_numpy(mine), world).numpy()
+        got = par.merge_partials_host(gathered)                                 # ONE exchange, ONE merge
+        worst = 0.0
+        for il in range(n_layers):
+            whole = _partials(s[il], v[il])
+            worst = max(worst, float(np.max(np.abs(got[il * 24:(il + 1) * 24] - whole[:, :256] / whole[:, 257:258]))))
+        out_q.put((rank, worst))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_layers_batched_exchange_on_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main_layers, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    results = dict(q.get(timeout=10) for _ in range(2))
+    assert set(results) == {0, 1} and max(results.values()) < 1e-5
